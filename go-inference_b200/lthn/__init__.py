@@ -1,0 +1,317 @@
+"""ctypes binding of liblthn_cuda.so (the C ABI in include/lthn_cuda.h).
+
+This module is the Python face of the shared library that tests and bench.py use;
+it adds nothing to the compute path. Importing it never needs a GPU; calling a
+compute function without the library built, or without a device, raises."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "liblthn_cuda.so")
+
+OK = 0
+F32, BF16 = 0, 1
+
+
+class LthnError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"lthn error {code}: {msg}")
+        self.code = code
+        self.msg = msg
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 128), ("architecture", C.c_char * 16), ("memory_size", C.c_uint64),
+                ("max_buffer_length", C.c_uint64), ("max_recommended_working_set", C.c_uint64),
+                ("sm_count", C.c_int32), ("compute_major", C.c_int32), ("compute_minor", C.c_int32)]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads the shared library; fails loudly when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise LthnError(3, f"{LIB_PATH} is missing: run `python go-inference_b200/build.py`")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.lthn_last_error.restype = C.c_char_p
+        for name in dir(_Sig):
+            if name.startswith("lthn_"):
+                fn = getattr(_lib, name)
+                fn.restype, fn.argtypes = getattr(_Sig, name)
+    return _lib
+
+
+vp, i32, i64, u64, f32, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float, C.c_size_t
+pvp = C.POINTER(C.c_void_p)
+
+
+class _Sig:
+    lthn_cuda_available = (i32, [])
+    lthn_cuda_device_count = (i32, [])
+    lthn_cuda_set_device = (i32, [i32])
+    lthn_cuda_device_info = (i32, [i32, C.POINTER(DeviceInfo)])
+    lthn_cuda_mem_info = (i32, [C.POINTER(u64), C.POINTER(u64)])
+    lthn_malloc = (i32, [pvp, sz])
+    lthn_free = (i32, [vp])
+    lthn_host_alloc = (i32, [pvp, sz])
+    lthn_host_free = (i32, [vp])
+    lthn_memcpy_h2d = (i32, [vp, vp, sz, vp])
+    lthn_memcpy_d2h = (i32, [vp, vp, sz, vp])
+    lthn_memcpy_d2d = (i32, [vp, vp, sz, vp])
+    lthn_memset = (i32, [vp, i32, sz, vp])
+    lthn_stream_create = (i32, [pvp])
+    lthn_stream_destroy = (i32, [vp])
+    lthn_stream_sync = (i32, [vp])
+    lthn_device_sync = (i32, [])
+    lthn_event_create = (i32, [pvp])
+    lthn_event_destroy = (i32, [vp])
+    lthn_event_record = (i32, [vp, vp])
+    lthn_event_elapsed_ms = (i32, [vp, vp, C.POINTER(f32)])
+    lthn_graph_begin = (i32, [vp])
+    lthn_graph_end = (i32, [vp, pvp])
+    lthn_graph_launch = (i32, [vp, vp])
+    lthn_graph_destroy = (i32, [vp])
+    lthn_affine_quantize = (i32, [vp, vp, i64, i64, i32, i32, i32, vp, vp, vp])
+    lthn_affine_dequantize = (i32, [vp, vp, vp, vp, i64, i64, i32, i32, vp])
+    lthn_affine_dequantize_bf16 = (i32, [vp, vp, vp, vp, i64, i64, i32, i32, vp])
+    lthn_synth_normal_fill = (i32, [vp, u64, u64, i64, f32, vp])
+    lthn_synth_affine_weight = (i32, [vp, u64, f32, i64, i64, i32, i32, i32, vp, vp, vp])
+    lthn_affine_qmv = (i32, [vp, vp, i32, i32, vp, vp, vp, i64, i64, i32, i32, vp, i32])
+    lthn_affine_qmv_host = (i32, [vp, sz, vp, sz, vp, sz, vp, sz, i64, i64, i32, i32, vp, sz])
+    lthn_debug_qmv_force_config = (None, [i32, i32])
+
+
+def check(rc: int):
+    if rc != OK:
+        raise LthnError(rc, lib().lthn_last_error().decode(errors="replace"))
+
+
+def device_count() -> int:
+    try:
+        return int(lib().lthn_cuda_device_count())
+    except (OSError, LthnError):
+        return 0
+
+
+def available() -> bool:
+    try:
+        return bool(lib().lthn_cuda_available())
+    except (OSError, LthnError):
+        return False
+
+
+def set_device(i: int):
+    check(lib().lthn_cuda_set_device(i))
+
+
+def device_info(i: int = 0) -> DeviceInfo:
+    info = DeviceInfo()
+    check(lib().lthn_cuda_device_info(i, C.byref(info)))
+    return info
+
+
+def sync():
+    check(lib().lthn_device_sync())
+
+
+class Stream:
+    def __init__(self):
+        h = C.c_void_p()
+        check(lib().lthn_stream_create(C.byref(h)))
+        self.h = h
+
+    def sync(self):
+        check(lib().lthn_stream_sync(self.h))
+
+    def close(self):
+        if self.h:
+            lib().lthn_stream_destroy(self.h)
+            self.h = None
+
+
+class Event:
+    def __init__(self):
+        h = C.c_void_p()
+        check(lib().lthn_event_create(C.byref(h)))
+        self.h = h
+
+    def record(self, stream=None):
+        check(lib().lthn_event_record(self.h, stream.h if stream else None))
+
+    def elapsed_ms(self, stop: "Event") -> float:
+        ms = C.c_float()
+        check(lib().lthn_event_elapsed_ms(self.h, stop.h, C.byref(ms)))
+        return float(ms.value)
+
+
+class Graph:
+    """Captures the calls issued on `stream` inside the `with` block into a CUDA graph."""
+
+    def __init__(self, stream: Stream):
+        self.stream = stream
+        self.h = None
+
+    def __enter__(self):
+        check(lib().lthn_graph_begin(self.stream.h))
+        return self
+
+    def __exit__(self, et, ev, tb):
+        h = C.c_void_p()
+        rc = lib().lthn_graph_end(self.stream.h, C.byref(h))
+        if et is None:
+            check(rc)
+            self.h = h
+        return False
+
+    def launch(self, stream=None):
+        check(lib().lthn_graph_launch(self.h, (stream or self.stream).h))
+
+    def destroy(self):
+        if self.h:
+            lib().lthn_graph_destroy(self.h)
+            self.h = None
+
+
+class Buf:
+    """A device allocation with NumPy upload / download helpers."""
+
+    def __init__(self, nbytes: int):
+        self.nbytes = int(nbytes)
+        p = C.c_void_p()
+        check(lib().lthn_malloc(C.byref(p), max(self.nbytes, 1)))
+        self.ptr = p.value
+
+    @classmethod
+    def from_array(cls, a: np.ndarray, stream=None) -> "Buf":
+        a = np.ascontiguousarray(a)
+        b = cls(a.nbytes)
+        b.upload(a, stream)
+        return b
+
+    def upload(self, a: np.ndarray, stream=None):
+        a = np.ascontiguousarray(a)
+        assert a.nbytes <= self.nbytes
+        check(lib().lthn_memcpy_h2d(self.ptr, a.ctypes.data, a.nbytes, stream.h if stream else None))
+        check(lib().lthn_stream_sync(stream.h if stream else None))
+
+    def download(self, dtype, shape, stream=None) -> np.ndarray:
+        out = np.empty(shape, dtype=dtype)
+        assert out.nbytes <= self.nbytes
+        check(lib().lthn_memcpy_d2h(out.ctypes.data, self.ptr, out.nbytes, stream.h if stream else None))
+        return out
+
+    def zero(self, stream=None):
+        check(lib().lthn_memset(self.ptr, 0, self.nbytes, stream.h if stream else None))
+
+    def free(self):
+        if self.ptr:
+            lib().lthn_free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class PinnedArray:
+    """NumPy view over pinned host memory (for full-rate host<->device copies)."""
+
+    def __init__(self, shape, dtype):
+        self.dtype = np.dtype(dtype)
+        self.shape = tuple(shape) if not np.isscalar(shape) else (int(shape),)
+        n = int(np.prod(self.shape)) * self.dtype.itemsize
+        p = C.c_void_p()
+        check(lib().lthn_host_alloc(C.byref(p), max(n, 1)))
+        self.ptr = p.value
+        self.nbytes = n
+        self.array = np.frombuffer((C.c_char * max(n, 1)).from_address(self.ptr), dtype=self.dtype,
+                                   count=int(np.prod(self.shape))).reshape(self.shape)
+
+    def free(self):
+        if self.ptr:
+            self.array = None
+            lib().lthn_host_free(self.ptr)
+            self.ptr = None
+
+
+def _s(stream):
+    return stream.h if stream else None
+
+
+class QuantWeight:
+    """Device-resident MLX-affine weight: packed u32 [N,K*bits/32], bf16 scales/biases [N,K/gs]."""
+
+    def __init__(self, N, K, bits=4, gs=64):
+        self.N, self.K, self.bits, self.gs = int(N), int(K), int(bits), int(gs)
+        self.packed = Buf(self.N * self.K * bits // 8)
+        self.scales = Buf(self.N * (self.K // gs) * 2)
+        self.biases = Buf(self.N * (self.K // gs) * 2)
+
+    @classmethod
+    def from_host(cls, packed, scales, biases, bits=4, gs=64):
+        packed = np.ascontiguousarray(packed, dtype=np.uint32)
+        N, K = packed.shape[0], packed.shape[1] * 32 // bits
+        w = cls(N, K, bits, gs)
+        w.packed.upload(packed)
+        w.scales.upload(np.ascontiguousarray(scales, dtype=np.uint16))
+        w.biases.upload(np.ascontiguousarray(biases, dtype=np.uint16))
+        return w
+
+    @classmethod
+    def synth(cls, seed, sigma, N, K, bits=4, gs=64, variant=0, stream=None):
+        w = cls(N, K, bits, gs)
+        check(lib().lthn_synth_affine_weight(_s(stream), seed, sigma, N, K, bits, gs, variant, w.packed.ptr,
+                                             w.scales.ptr, w.biases.ptr))
+        return w
+
+    @property
+    def stream_bytes(self):
+        return self.packed.nbytes + self.scales.nbytes + self.biases.nbytes
+
+    def to_host(self):
+        return (self.packed.download(np.uint32, (self.N, self.K * self.bits // 32)),
+                self.scales.download(np.uint16, (self.N, self.K // self.gs)),
+                self.biases.download(np.uint16, (self.N, self.K // self.gs)))
+
+    def free(self):
+        for b in (self.packed, self.scales, self.biases):
+            b.free()
+
+
+def quantize(w_dev: Buf, N, K, bits=4, gs=64, variant=0, stream=None) -> QuantWeight:
+    q = QuantWeight(N, K, bits, gs)
+    check(lib().lthn_affine_quantize(_s(stream), w_dev.ptr, N, K, bits, gs, variant, q.packed.ptr, q.scales.ptr,
+                                     q.biases.ptr))
+    return q
+
+
+def dequantize(q: QuantWeight, out: Buf, bf16=False, stream=None):
+    fn = lib().lthn_affine_dequantize_bf16 if bf16 else lib().lthn_affine_dequantize
+    check(fn(_s(stream), q.packed.ptr, q.scales.ptr, q.biases.ptr, q.N, q.K, q.bits, q.gs, out.ptr))
+
+
+def qmv(x: Buf, x_dtype, M, q: QuantWeight, y: Buf, y_dtype, stream=None):
+    check(lib().lthn_affine_qmv(_s(stream), x.ptr, x_dtype, M, q.packed.ptr, q.scales.ptr, q.biases.ptr, q.N, q.K,
+                                q.gs, q.bits, y.ptr, y_dtype))
+
+
+def qmv_host(x_bf16: np.ndarray, packed: np.ndarray, scales: np.ndarray, biases: np.ndarray, out_dim, in_dim, gs,
+             bits) -> np.ndarray:
+    """model.QuantMatVec.MatVec over host byte buffers (bf16 in, bf16 out)."""
+    xb = np.ascontiguousarray(x_bf16).view(np.uint8).reshape(-1)
+    pb = np.ascontiguousarray(packed).view(np.uint8).reshape(-1)
+    sb = np.ascontiguousarray(scales).view(np.uint8).reshape(-1)
+    bb = np.ascontiguousarray(biases).view(np.uint8).reshape(-1)
+    y = np.zeros(max(int(out_dim), 0), dtype=np.uint16)
+    check(lib().lthn_affine_qmv_host(xb.ctypes.data, xb.size, pb.ctypes.data, pb.size, sb.ctypes.data, sb.size,
+                                     bb.ctypes.data, bb.size, out_dim, in_dim, gs, bits, y.ctypes.data, y.nbytes))
+    return y

@@ -1,0 +1,169 @@
+"""affine_qmv parity through the C ABI against the CPU oracle.
+
+Tolerances: the north-star bound is max relative error <= 1e-2 against an fp32
+reference on the dequantised weights; the reference's own tests use
+|got-want| <= 1e-2*(1+|want|) (engine/metal/quant_seam_backend_test.go:46-89) and
+0.05 absolute on the bf16 fixture (enginetest/quant_parity.go:23). The kernel is
+held to much tighter bounds here (f32 accumulation): 2e-5 of the output RMS."""
+import numpy as np
+import pytest
+
+from gpu_util import make_weight, make_x, rel_err, rms_err
+from test_oracle_kat import parity_fixture
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL_RMS = 2e-5   # f32 output vs f64 oracle, relative to output RMS
+REF_TOL = 1e-2       # the reference's tolerance form
+
+
+def run_qmv(lthn, x_arr, x_dtype, M, q, y_dtype):
+    xb = lthn.Buf.from_array(x_arr)
+    y = lthn.Buf(M * q.N * (2 if y_dtype == lthn.BF16 else 4))
+    lthn.qmv(xb, x_dtype, M, q, y, y_dtype)
+    lthn.sync()
+    return y.download(np.uint16 if y_dtype == lthn.BF16 else np.float32, (M, q.N))
+
+
+# --- enginetest.QuantParity (quant_parity.go:77-108) through MatVec ---
+def test_quant_parity_fixture_matvec(oracle):
+    import lthn
+    x, packed, scales, biases, out_dim, in_dim, gs, bits = parity_fixture(oracle)
+    got = lthn.qmv_host(x, packed, scales, biases, out_dim, in_dim, gs, bits)
+    want = oracle.ref_affine_matvec(x, packed, scales, biases, out_dim, in_dim, gs, bits)
+    if not np.array_equal(got, want):
+        assert np.max(np.abs(oracle.bf16_to_f32(got) - oracle.bf16_to_f32(want))) <= 0.05
+    # held tighter than the reference asks: at most one bf16 ulp
+    assert np.max(np.abs(got.astype(np.int32) - want.astype(np.int32))) <= 1
+
+
+# --- engine/metal/quant_seam_backend_test.go:46-89 shapes (qmv M=1 and M>1, ragged N, 2/8 bit) ---
+@pytest.mark.parametrize("M,K,N,bits,gs", [(1, 512, 40, 4, 64), (1, 256, 24, 2, 128), (3, 512, 64, 4, 64),
+                                           (5, 256, 40, 2, 128), (2, 128, 8, 8, 64)])
+def test_seam_fixture_shapes(oracle, M, K, N, bits, gs):
+    import lthn
+    w = (((np.arange(N * K) % 17) - 8) * np.float32(0.037)).astype(np.float32).reshape(N, K)
+    x = (((np.arange(M * K) % 9) - 4) * np.float32(0.05)).astype(np.float32).reshape(M, K)
+    p, s, b = oracle.quantize(w, bits, gs)
+    want = oracle.matnt(x, oracle.dequantize(p, s, b, bits, gs))
+    q = lthn.QuantWeight.from_host(p, s, b, bits, gs)
+    got = run_qmv(lthn, x, lthn.F32, M, q, lthn.F32)
+    assert rel_err(got, want) <= REF_TOL
+    assert rms_err(got, want) <= 1e-4
+    xb = oracle.f32_to_bf16(x)
+    want_b = oracle.matnt(oracle.bf16_to_f32(xb), oracle.dequantize(p, s, b, bits, gs))
+    got_b = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.F32)
+    assert rms_err(got_b, want_b) <= 1e-4
+
+
+@pytest.mark.parametrize("N,K", [(2304, 2304), (9216, 2304), (2304, 9216)])
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16, 32])
+def test_decode_sweep_shapes_bf16(oracle, N, K, M):
+    """BASELINE decode sweep shapes, bf16 activations ~ N(0,1), weights ~ N(0,0.02)."""
+    import lthn
+    p, s, b = make_weight(oracle, N, K, seed=N + K)
+    xf, xb = make_x(oracle, M, K, seed=M)
+    want = oracle.matnt_quant_host(xf, p, s, b, threads=8)
+    q = lthn.QuantWeight.from_host(p, s, b)
+    got = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.F32)
+    assert rel_err(got, want) <= REF_TOL
+    assert rms_err(got, want) <= F32_TOL_RMS
+    got16 = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.BF16)
+    want16 = oracle.f32_to_bf16(want)
+    assert np.max(np.abs(got16.astype(np.int32) - want16.astype(np.int32))) <= 1
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 7, 16, 32])
+def test_f32_activations_keep_f32_precision(oracle, M):
+    """f32 activations go through the bf16 split columns; the result must match the
+    f64 oracle on the unrounded f32 activations."""
+    import lthn
+    N, K = 1024, 2304
+    p, s, b = make_weight(oracle, N, K, seed=5)
+    x = np.random.default_rng(M).standard_normal((M, K)).astype(np.float32)
+    want = oracle.matnt_quant_host(x, p, s, b, threads=8)
+    q = lthn.QuantWeight.from_host(p, s, b)
+    got = run_qmv(lthn, x, lthn.F32, M, q, lthn.F32)
+    tol = F32_TOL_RMS if M <= 2 else 4e-5  # 3-term split up to M=2, 2-term (16 bits) above
+    assert rms_err(got, want) <= tol
+
+
+@pytest.mark.parametrize("N,K", [(1, 64), (7, 64), (17, 128), (1000, 2304), (33, 4096), (4095, 512)])
+def test_ragged_and_tiny_shapes(oracle, N, K):
+    import lthn
+    p, s, b = make_weight(oracle, N, K, seed=N * 7 + K)
+    for M in (1, 5):
+        xf, xb = make_x(oracle, M, K, seed=3)
+        want = oracle.matnt_quant_host(xf, p, s, b)
+        got = run_qmv(lthn, xb, lthn.BF16, M, lthn.QuantWeight.from_host(p, s, b), lthn.F32)
+        assert rms_err(got, want) <= F32_TOL_RMS
+
+
+def test_every_kernel_configuration_agrees(oracle):
+    """All (rows-per-CTA, warps) configurations compute the same function."""
+    import lthn
+    N, K = 2304, 2304
+    p, s, b = make_weight(oracle, N, K, seed=1)
+    q = lthn.QuantWeight.from_host(p, s, b)
+    try:
+        for M in (1, 8, 16):
+            xf, xb = make_x(oracle, M, K, seed=9)
+            want = oracle.matnt_quant_host(xf, p, s, b, threads=8)
+            for rt in (1, 2, 4):
+                for nw in (1, 2, 4, 8):
+                    if M > 8 and rt == 4 and M > 16:
+                        continue
+                    lthn.lib().lthn_debug_qmv_force_config(rt, nw)
+                    got = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.F32)
+                    assert rms_err(got, want) <= F32_TOL_RMS, (M, rt, nw)
+    finally:
+        lthn.lib().lthn_debug_qmv_force_config(0, 0)
+
+
+def test_negative_scales_and_literal_variant(oracle):
+    """The reference quantiser signs the scale (mlxaffine.go:150-154); the literal
+    min/max rule never does. The kernel must serve both."""
+    import lthn
+    N, K = 512, 1024
+    for variant in (0, 1):
+        p, s, b = make_weight(oracle, N, K, seed=2, variant=variant)
+        if variant == 0:
+            assert (oracle.bf16_to_f32(s) < 0).any()
+        xf, xb = make_x(oracle, 1, K, seed=4)
+        want = oracle.matnt_quant_host(xf, p, s, b)
+        got = run_qmv(lthn, xb, lthn.BF16, 1, lthn.QuantWeight.from_host(p, s, b), lthn.F32)
+        assert rms_err(got, want) <= F32_TOL_RMS
+
+
+def test_lm_head_full_size(oracle):
+    """Full BASELINE lm_head shape (262144 x 2304), weights generated on the device:
+    compared row-for-row with the oracle, plus linearity as a size-independent check."""
+    import lthn
+    N, K = 262144, 2304
+    q = lthn.QuantWeight.synth(3, 0.02, N, K)
+    p, s, b = q.to_host()
+    xf, xb = make_x(oracle, 2, K, seed=8)
+    want = oracle.matnt_quant_host(xf, p, s, b, threads=oracle.lib().lthn_o_num_threads())
+    got = run_qmv(lthn, xb, lthn.BF16, 2, q, lthn.F32)
+    assert rel_err(got, want) <= REF_TOL
+    assert rms_err(got, want) <= F32_TOL_RMS
+    # linearity: W(x0 + x1) = W x0 + W x1 (f32 activations so the sum is representable)
+    xs = (xf[0] + xf[1])[None, :].astype(np.float32)
+    got_sum = run_qmv(lthn, xs, lthn.F32, 1, q, lthn.F32)
+    assert rms_err(got_sum[0], got[0].astype(np.float64) + got[1]) <= 5e-5
+
+
+def test_zero_sized_and_rejected_arguments(oracle):
+    import lthn
+    q = lthn.QuantWeight.from_host(*make_weight(oracle, 16, 64, seed=0))
+    x = lthn.Buf(64 * 2)
+    y = lthn.Buf(16 * 4)
+    lthn.qmv(x, lthn.BF16, 0, q, y, lthn.F32)  # M == 0: no-op
+    with pytest.raises(lthn.LthnError):
+        lthn.qmv(x, lthn.BF16, 33, q, y, lthn.F32)
+    with pytest.raises(lthn.LthnError):
+        lthn.check(lthn.lib().lthn_affine_qmv(None, x.ptr, lthn.BF16, 1, q.packed.ptr, q.scales.ptr, q.biases.ptr,
+                                              16, 64, 48, 4, y.ptr, lthn.F32))
+    with pytest.raises(lthn.LthnError):
+        lthn.check(lthn.lib().lthn_affine_qmv(None, x.ptr, lthn.BF16, 1, q.packed.ptr, q.scales.ptr, q.biases.ptr,
+                                              16, 64, 64, 3, y.ptr, lthn.F32))
