@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""bench.py — headline benchmark of the MLX-affine 4-bit hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--full]
+
+Workload (BASELINE.json configs[1], the decode sweep): affine_qmv at batch 1 on
+the lm_head shape (N=262144, K=2304), uint4 weights, group 64, bf16 scales/biases,
+weights ~ N(0, 0.02) generated on the device by the seeded synthetic source that
+the CPU oracle shares, bf16 activations ~ N(0, 1). A "step" is one pass of the hot
+path over that matrix. `value` is algorithmic GB/s = (0.5625*N*K + 2*M*K + 4*M*N)
+bytes / step time with everything resident in HBM; three weight copies (1 GB, far
+larger than the 126 MB L2) are rotated between steps. `e2e` is the same metric
+through the reference-facing call (model.QuantMatVec.MatVec semantics: host byte
+buffers in, host bytes out) with the host<->device copies inside the timed region.
+The other shapes and batch sizes of the sweep are reported under `sweep`.
+
+With --gpus N (launched by torch.distributed.run) every rank runs the same
+per-GPU workload on its own device (row-sharded weights need no collective), so
+the scaling is weak and `value` is the sum over ranks / max time over ranks.
+
+--impl reference times the reference's own CPU algorithm for this path (the C
+restatement of attn.matNTQuantHost in oracle/, all host threads) on a bounded
+sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "go-inference_b200"))
+
+HEAD_N, HEAD_K, HEAD_M = 262144, 2304, 1
+SWEEP_SHAPES = [(2304, 2304), (9216, 2304), (2304, 9216), (262144, 2304)]
+SWEEP_M = [1, 2, 4, 8, 16, 32]
+
+
+def algo_bytes(N, K, M, out_bytes=4):
+    return N * K * 9 // 16 + 2 * M * K + out_bytes * M * N
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def bf16_bits(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    return ((u + (0x7FFF + ((u >> 16) & 1))) >> 16).astype(np.uint16)
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# ------------------------------------------------------------------ ours ----
+
+def time_graph(lthn, st, fn, iters):
+    """Average device time (us) of `iters` back-to-back calls captured in one CUDA graph."""
+    fn(0)
+    st.sync()
+    g = lthn.Graph(st)
+    with g:
+        for i in range(iters):
+            fn(i)
+    for _ in range(3):
+        g.launch()
+    st.sync()
+    e0, e1 = lthn.Event(), lthn.Event()
+    e0.record(st)
+    g.launch()
+    e1.record(st)
+    st.sync()
+    us = e0.elapsed_ms(e1) * 1e3 / iters
+    g.destroy()
+    return us
+
+
+def run_sweep(lthn, st, peak, full):
+    """Per-shape GB/s for the decode sweep; small shapes rotate >= 600 MB of weight copies."""
+    out = []
+    ms = SWEEP_M if full else [1, 8, 32]
+    for (N, K) in SWEEP_SHAPES:
+        wbytes = N * K * 9 // 16
+        copies = max(3, min(64, int(np.ceil(600e6 / wbytes))))
+        ws = [lthn.QuantWeight.synth(1000 + i, 0.02, N, K, stream=st) for i in range(copies)]
+        for M in ms:
+            x = lthn.Buf.from_array(bf16_bits(np.random.default_rng(M).standard_normal((M, K))))
+            y = lthn.Buf(M * N * 4)
+            iters = 30 if N > 100000 else 200
+            us = time_graph(lthn, st, lambda i: lthn.qmv(x, lthn.BF16, M, ws[i % copies], y, lthn.F32, st), iters)
+            gbs = algo_bytes(N, K, M) / us / 1e3
+            out.append({"N": N, "K": K, "M": M, "us": round(us, 3), "GBps": round(gbs, 1),
+                        "frac_of_measured_hbm": round(gbs / peak, 4)})
+            x.free()
+            y.free()
+        for w in ws:
+            w.free()
+    return out
+
+
+def run_ours(args):
+    rank, local_rank, world = dist_env()
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    import lthn
+    if not lthn.available():
+        raise SystemExit("bench.py: no sm_100 device / liblthn_cuda.so unavailable (there is no CPU fallback)")
+    lthn.set_device(local_rank)
+    peak, peak_kind = measured_peak()
+    st = lthn.Stream()
+    N, K, M = HEAD_N, HEAD_K, HEAD_M
+    copies = 3
+    ws = [lthn.QuantWeight.synth(7 + i + 100 * rank, 0.02, N, K, stream=st) for i in range(copies)]
+    xh = bf16_bits(np.random.default_rng(0).standard_normal((M, K)))
+    x = lthn.Buf.from_array(xh)
+    y = lthn.Buf(M * N * 4)
+    st.sync()
+
+    def step(i):
+        lthn.qmv(x, lthn.BF16, M, ws[i % copies], y, lthn.F32, st)
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    st.sync()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    barrier()
+    lthn.sync()
+    e0, e1 = lthn.Event(), lthn.Event()
+    with ClockSampler(local_rank) as clk:
+        # keep the GPU busy long enough for clock samples, then the timed K steps
+        e0.record(st)
+        for i in range(args.steps):
+            step(i)
+        e1.record(st)
+        st.sync()
+        ms = e0.elapsed_ms(e1)
+        t_end = time.time() + 0.6
+        j = 0
+        while time.time() < t_end:   # untimed: same kernel, only so that nvidia-smi sees load
+            step(j)
+            j += 1
+            if j % 64 == 0:
+                st.sync()
+        st.sync()
+    barrier()
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    bytes_step = algo_bytes(N, K, M)
+    value = world * bytes_step / (ms_per_step * 1e-3) / 1e9
+
+    # kernel duration of the dominant kernel, live, on the launching stream
+    us_kernel = time_graph(lthn, st, step, 30)
+    achieved = bytes_step / us_kernel / 1e3
+
+    # end to end through the host-buffer call (QuantMatVec.MatVec semantics), pinned buffers
+    p, s, b = ws[0].to_host()
+    hp = lthn.PinnedArray(p.shape, np.uint32); hp.array[...] = p
+    hs = lthn.PinnedArray(s.shape, np.uint16); hs.array[...] = s
+    hb = lthn.PinnedArray(b.shape, np.uint16); hb.array[...] = b
+    hx = lthn.PinnedArray(xh.shape, np.uint16); hx.array[...] = xh
+    e2e_steps = max(2, min(args.steps, 5))
+    lthn.qmv_host(hx.array, hp.array, hs.array, hb.array, N, K, 64, 4)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        yh = lthn.qmv_host(hx.array, hp.array, hs.array, hb.array, N, K, 64, 4)
+    t1 = time.perf_counter()
+    e2e_s = (t1 - t0) / e2e_steps
+    if dist is not None:
+        import torch
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    h2d = p.nbytes + s.nbytes + b.nbytes + xh.nbytes
+    e2e = {"value": round(world * algo_bytes(N, K, M, 2) / e2e_s / 1e9, 2), "unit": "GB/s",
+           "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(yh.nbytes)}
+
+    line = {
+        "metric": "affine_qmv_4bit_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u4*bf16->f32",
+        "data": "synthetic",
+        "config": {"workload": "affine_qmv decode sweep (BASELINE configs[1]): lm_head N=262144 K=2304 M=1, "
+                               "uint4 g64 bf16 scale/bias, weights N(0,0.02), x bf16 N(0,1)",
+                   "l2": "3 rotated weight copies of 340 MB each (inputs larger than the 126 MB L2)",
+                   "sharding": "independent row shards per GPU, no collective"},
+        "clocks": clk.summary(), "e2e": e2e, "gpu_launches": args.steps,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                     "peak_kind": f"of {peak_kind}", "algorithmic_bytes": bytes_step,
+                     "kernel_us": round(us_kernel, 3), "frac_of_nominal_8TBps": round(achieved / 8000.0, 4)},
+    }
+    if rank == 0:
+        line["cpu_baseline"] = cpu_baseline(sample_rows=65536, threads=1)
+        if not args.no_sweep:
+            line["sweep"] = run_sweep(lthn, st, peak, args.full)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one lm_head launch (ncu capture
+# summarised in profiles/affine_qmv_lm_head_M1.md)
+TRAFFIC_BYTES_PER_LAUNCH = 344687616
+
+
+# ------------------------------------------------------------- reference ----
+
+def cpu_baseline(sample_rows, threads):
+    """Times the CPU restatement of attn.matNTQuantHost on the first `sample_rows`
+    rows of the headline matrix (same generator, same x)."""
+    from oracle import oracle as o
+    o.build()
+    N, K, M = sample_rows, HEAD_K, HEAD_M
+    w = o.synth_normal(7, 0, N * K, 0.02).reshape(N, K)
+    p, s, b = o.quantize(w)
+    x = o.bf16_to_f32(bf16_bits(np.random.default_rng(0).standard_normal((M, K))))
+    o.matnt_quant_host(x[:, :], p[:256], s[:256], b[:256], threads=threads)
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        o.matnt_quant_host(x, p, s, b, threads=threads)
+        reps += 1
+        if time.perf_counter() - t0 > 4.0 or reps >= 50:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": round(algo_bytes(N, K, M) / dt / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"first {N} of {HEAD_N} rows of the lm_head matrix, M=1, f64 accumulate, {reps} repetitions",
+            "ms_per_sample": round(dt * 1e3, 3)}
+
+
+def run_reference(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    from oracle import oracle as o
+    o.build()
+    threads = o.lib().lthn_o_num_threads()
+    steps = max(args.steps, 1)
+    N, K, M = 65536, HEAD_K, HEAD_M
+    w = o.synth_normal(7, 0, N * K, 0.02).reshape(N, K)
+    p, s, b = o.quantize(w)
+    x = o.bf16_to_f32(bf16_bits(np.random.default_rng(0).standard_normal((M, K))))
+    for _ in range(max(args.warmup, 1)):
+        o.matnt_quant_host(x, p, s, b, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        o.matnt_quant_host(x, p, s, b, threads=threads)
+    dt = (time.perf_counter() - t0) / steps
+    v = round(algo_bytes(N, K, M) / dt / 1e9, 3)
+    sample = f"first {N} of {HEAD_N} lm_head rows per step, M=1, all {threads} host threads"
+    print(json.dumps({
+        "impl": "reference", "metric": "affine_qmv_4bit_GBps", "value": v, "unit": "GB/s", "n_gpus": world,
+        "steps": steps, "warmup": max(args.warmup, 1), "ms_per_step": round(dt * 1e3, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u4*f32->f64", "data": "synthetic",
+        "config": {"workload": "affine_qmv decode sweep (BASELINE configs[1]): lm_head N=262144 K=2304 M=1 "
+                               "(bounded sample of rows), CPU restatement of attn.matNTQuantHost"},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--full", action="store_true", help="report every batch size of the sweep")
+    ap.add_argument("--no-sweep", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -557,7 +557,12 @@ int32_t lthn_affine_qmv_host(const void* x, size_t x_len, const void* packed, si
     const size_t o_x = 0, o_p = o_x + up(x_len), o_s = o_p + up(packed_len), o_b = o_s + up(scales_len),
                  o_y = o_b + up(biases_len), total = o_y + up(y_len);
     unsigned char* d = nullptr;
-    LTHN_CUDA_TRY(cudaMalloc((void**)&d, total));
+    {
+        void* arena = nullptr;
+        int32_t arc = scratch_get(total, &arena, 1);  // cached staging arena: no cudaMalloc per call
+        if (arc) return arc;
+        d = (unsigned char*)arena;
+    }
     cudaStream_t s = nullptr;
     int32_t rc = LTHN_OK;
     cudaError_t e;
@@ -574,9 +579,6 @@ int32_t lthn_affine_qmv_host(const void* x, size_t x_len, const void* packed, si
         rc = cuda_fail(e, "MatVec: device to host copy");
     if (rc == LTHN_OK && (e = cudaStreamSynchronize(s)) != cudaSuccess) rc = cuda_fail(e, "MatVec: synchronize");
     if (rc == LTHN_OK) rc = check_device_status(s);
-    const std::string keep = lthn_last_error();
-    cudaFree(d);
-    if (rc != LTHN_OK) return fail(rc, keep);
     return rc;
 }
 

@@ -21,8 +21,9 @@ void clear_error() { g_err.clear(); }
 static const int kMaxDev = 16;
 static std::mutex g_mu;
 static uint32_t* g_status[kMaxDev];
-static void* g_scratch[kMaxDev];
-static size_t g_scratch_bytes[kMaxDev];
+static const int kSlots = 4;
+static void* g_scratch[kMaxDev][kSlots];
+static size_t g_scratch_bytes[kMaxDev][kSlots];
 
 uint32_t* device_status_word() {
     int dev = 0;
@@ -48,23 +49,23 @@ int32_t check_device_status(cudaStream_t s) {
     return LTHN_OK;
 }
 
-int32_t scratch_get(size_t bytes, void** out) {
+int32_t scratch_get(size_t bytes, void** out, int slot) {
     int dev = 0;
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= kMaxDev) return fail(LTHN_ERR_INVALID, "device index out of range");
+    if (dev < 0 || dev >= kMaxDev || slot < 0 || slot >= kSlots) return fail(LTHN_ERR_INVALID, "scratch: bad device or slot");
     std::lock_guard<std::mutex> lk(g_mu);
-    if (g_scratch_bytes[dev] < bytes) {
-        if (g_scratch[dev]) {
+    if (g_scratch_bytes[dev][slot] < bytes) {
+        if (g_scratch[dev][slot]) {
             LTHN_CUDA_TRY(cudaDeviceSynchronize());
-            LTHN_CUDA_TRY(cudaFree(g_scratch[dev]));
-            g_scratch[dev] = nullptr;
-            g_scratch_bytes[dev] = 0;
+            LTHN_CUDA_TRY(cudaFree(g_scratch[dev][slot]));
+            g_scratch[dev][slot] = nullptr;
+            g_scratch_bytes[dev][slot] = 0;
         }
         size_t want = bytes < (size_t)(8u << 20) ? (size_t)(8u << 20) : bytes;
-        LTHN_CUDA_TRY(cudaMalloc(&g_scratch[dev], want));
-        g_scratch_bytes[dev] = want;
+        LTHN_CUDA_TRY(cudaMalloc(&g_scratch[dev][slot], want));
+        g_scratch_bytes[dev][slot] = want;
     }
-    *out = g_scratch[dev];
+    *out = g_scratch[dev][slot];
     return LTHN_OK;
 }
 

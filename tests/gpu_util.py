@@ -27,3 +27,13 @@ def rms_err(got, want):
     got = np.asarray(got, dtype=np.float64)
     want = np.asarray(want, dtype=np.float64)
     return float(np.max(np.abs(got - want)) / (np.sqrt(np.mean(want * want)) + 1e-30))
+
+
+def bf16_close(oracle, got_bits, want_f32):
+    """bf16 outputs agree with the rounded oracle value to one bf16 ulp of the value
+    plus the f32 accumulation noise (3e-5 of the output RMS) that can move a value
+    across a rounding boundary."""
+    g = oracle.bf16_to_f32(np.asarray(got_bits, dtype=np.uint16)).astype(np.float64)
+    w = np.asarray(want_f32, dtype=np.float64)
+    rms = np.sqrt(np.mean(w * w)) + 1e-30
+    return bool(np.all(np.abs(g - w) <= np.abs(w) * 2.0 ** -7 + 3e-5 * rms))

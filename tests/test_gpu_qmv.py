@@ -8,7 +8,7 @@ held to much tighter bounds here (f32 accumulation): 2e-5 of the output RMS."""
 import numpy as np
 import pytest
 
-from gpu_util import make_weight, make_x, rel_err, rms_err
+from gpu_util import bf16_close, make_weight, make_x, rel_err, rms_err
 from test_oracle_kat import parity_fixture
 
 pytestmark = pytest.mark.gpu
@@ -69,8 +69,7 @@ def test_decode_sweep_shapes_bf16(oracle, N, K, M):
     assert rel_err(got, want) <= REF_TOL
     assert rms_err(got, want) <= F32_TOL_RMS
     got16 = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.BF16)
-    want16 = oracle.f32_to_bf16(want)
-    assert np.max(np.abs(got16.astype(np.int32) - want16.astype(np.int32))) <= 1
+    assert bf16_close(oracle, got16, want)
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 7, 16, 32])
