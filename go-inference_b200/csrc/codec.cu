@@ -90,11 +90,17 @@ struct MemSource {
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     }
 };
+// Element (r,c) of the local [N,Klocal] tensor is element (r+row0, c+col0) of a full
+// tensor with Kfull columns, so a tensor-parallel shard draws the same values as the
+// unsharded tensor.
 struct SynthSource {
     uint64_t seed; float k;
+    int64_t Klocal, Kfull, row0, col0;
     __device__ __forceinline__ void load8(int64_t idx, float (&v)[8]) const {
+        const int64_t r = idx / Klocal, c = idx - r * Klocal;
+        const int64_t g = (r + row0) * Kfull + c + col0;
 #pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = synth_value(seed, (uint64_t)(idx + i), k);
+        for (int i = 0; i < 8; i++) v[i] = synth_value(seed, (uint64_t)(g + i), k);
     }
 };
 
@@ -225,8 +231,20 @@ int32_t lthn_synth_affine_weight(void* stream, uint64_t seed, float sigma, int64
     int32_t rc = validate_codec(N, K, bits, gs, "lthn_synth_affine_weight");
     if (rc) return rc;
     LTHN_REQUIRE(packed && scales && biases, "lthn_synth_affine_weight: NULL pointer");
-    return launch_quantize((cudaStream_t)stream, SynthSource{seed, synth_scale(sigma)}, N, K, bits, gs, variant, packed,
-                           scales, biases);
+    return launch_quantize((cudaStream_t)stream, SynthSource{seed, synth_scale(sigma), K, K, 0, 0}, N, K, bits, gs, variant,
+                           packed, scales, biases);
+}
+
+// Rows [row0,row0+N) x columns [col0,col0+K) of the synthetic [*,Kfull] tensor, 4 bit, group 64.
+int32_t lthn_synth_affine_weight_shard(void* stream, uint64_t seed, float sigma, int64_t N, int64_t K, int64_t row0,
+                                       int64_t col0, int64_t Kfull, uint32_t* packed, uint16_t* scales,
+                                       uint16_t* biases) {
+    clear_error();
+    int32_t rc = validate_codec(N, K, 4, 64, "lthn_synth_affine_weight_shard");
+    if (rc) return rc;
+    LTHN_REQUIRE(packed && scales && biases && col0 % 64 == 0 && col0 + K <= Kfull, "lthn_synth_affine_weight_shard: bad shard");
+    return launch_quantize((cudaStream_t)stream, SynthSource{seed, synth_scale(sigma), K, Kfull, row0, col0}, N, K, 4, 64, 0,
+                           packed, scales, biases);
 }
 
 static int32_t dequant_any(void* stream, const uint32_t* packed, const uint16_t* scales, const uint16_t* biases,

@@ -1,0 +1,496 @@
+// decoder_kernels.cu — the small fused kernels around the quantized linears of a
+// Gemma-style decoder step: embedding row dequantise, RMSNorm (+residual, +next
+// norm), per-head RMSNorm + NeoX RoPE + KV append, split-KV decode attention over
+// the seq-major bf16 cache, and greedy argmax.
+//
+// They are all latency-sized (a few KB to a few MB per launch); the design goal is
+// few launches and exact, reproducible arithmetic:
+//  * sums of squares are accumulated in f64 so the reciprocal RMS is the same
+//    value the CPU reference computes (hipReferenceRMSNorm, engine/hip/
+//    hip_transformer_reference.go:171-194), and x / rms * w is issued as separately
+//    rounded f32 operations;
+//  * RoPE uses a cos/sin table computed on the host in f64 exactly as the reference
+//    does (hip_transformer_reference.go:242-289), so the rotation is bit-identical;
+//  * reductions have a fixed order (no atomics in the value path).
+#include "common.cuh"
+#include "decoder_kernels.hpp"
+
+namespace lthn {
+
+// ---- block reductions ---------------------------------------------------------------
+__device__ __forceinline__ double block_sum_f64(double v, double* sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    double t = 0.0;
+    for (int w = 0; w < nw; w++) t += sh[w];
+    return t;
+}
+
+// ---- embedding ----------------------------------------------------------------------
+// h[row, :] = (float(code)*scale + bias) * embed_scale for token ids[row]
+// (hipReferenceMLXAffineEmbeddingLookup, hip_transformer_reference.go:60-92, and the
+// output scale of engine/hip/kernels/embedding/lookup.hipinc:3-31).
+__global__ void embed_kernel(const int32_t* __restrict__ ids, const uint32_t* __restrict__ packed,
+                             const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases, int hidden,
+                             int vocab, float embed_scale, float* __restrict__ out) {
+    const int row = blockIdx.x;
+    int id = ids[row];
+    if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; stay in bounds regardless
+    const int wpr = hidden >> 3, gpr = hidden >> 6;
+    for (int w = threadIdx.x; w < wpr; w += blockDim.x) {
+        const uint32_t word = __ldg(packed + (int64_t)id * wpr + w);
+        const int g = w >> 3;
+        const float s = bf16_bits_to_f32(__ldg(scales + (int64_t)id * gpr + g));
+        const float b = bf16_bits_to_f32(__ldg(biases + (int64_t)id * gpr + g));
+        float* o = out + (int64_t)row * hidden + w * 8;
+#pragma unroll
+        for (int p = 0; p < 8; p++) {
+            const float q = (float)((word >> (4 * p)) & 15u);
+            o[p] = __fmul_rn(__fadd_rn(__fmul_rn(q, s), b), embed_scale);
+        }
+    }
+}
+
+// ---- RMSNorm family -------------------------------------------------------------------
+// mode 0: out = norm(x, w)
+// mode 1: h = h + norm(a, w_post); out = norm(h, w_next)      (post-norm, residual, next pre-norm)
+// One CTA per row. (hipOracleReferenceLayer, hip_gemma4_q4_oracle_test.go:925-951.)
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ a, float* __restrict__ h,
+                                                      const float* __restrict__ w_post,
+                                                      const float* __restrict__ w_next, float* __restrict__ out,
+                                                      int width, float eps, int mode) {
+    __shared__ double sh[32];
+    const int row = blockIdx.x;
+    const float* ar = a + (int64_t)row * width;
+    float* hr = h ? h + (int64_t)row * width : nullptr;
+    float* orow = out + (int64_t)row * width;
+    double ss = 0.0;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = ar[i];
+        ss += (double)__fmul_rn(v, v);
+    }
+    ss = block_sum_f64(ss, sh);
+    const float rms = (float)sqrt(ss / (double)width + (double)eps);
+    if (mode == 0) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x)
+            orow[i] = __fmul_rn(__fdiv_rn(ar[i], rms), w_post[i]);
+        return;
+    }
+    double ss2 = 0.0;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float n = __fmul_rn(__fdiv_rn(ar[i], rms), w_post[i]);
+        const float v = __fadd_rn(hr[i], n);
+        hr[i] = v;
+        ss2 += (double)__fmul_rn(v, v);
+    }
+    ss2 = block_sum_f64(ss2, sh);
+    const float rms2 = (float)sqrt(ss2 / (double)width + (double)eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        orow[i] = __fmul_rn(__fdiv_rn(hr[i], rms2), w_next[i]);
+}
+
+// ---- per-head RMSNorm + NeoX RoPE + KV append -----------------------------------------
+// qkv: [rows, (Hq + 2*Hkv) * D] f32 (q heads, then k heads, then v heads).
+// q heads -> q_out [rows, Hq*D] f32 (normed, rotated); k heads -> bf16 cache row at the
+// token's position; v heads -> bf16 cache row (no norm for this architecture).
+// One CTA per (row, head); D/2 threads, thread i owns the rotation pair (i, i + D/2).
+// (rocm_rms_norm_rope_heads, engine/hip/kernels/norms/rms_norm.hipinc:306-377;
+// lthn_qknorm_rope_bf16, engine/metal/kernels/norms/lthn_qknorm_rope_bf16.metal.)
+__global__ void qknorm_rope_append_kernel(const float* __restrict__ qkv, const float* __restrict__ q_norm,
+                                          const float* __restrict__ k_norm, const float2* __restrict__ rope_table,
+                                          const int32_t* __restrict__ row_pos, const int32_t* __restrict__ row_lane,
+                                          float* __restrict__ q_out, uint16_t* __restrict__ kcache,
+                                          uint16_t* __restrict__ vcache, int Hq, int Hkv, int D, float eps,
+                                          int64_t lane_stride, int max_len) {
+    __shared__ double sh[32];
+    const int row = blockIdx.x, head = blockIdx.y, i = threadIdx.x, half = D >> 1;
+    const int QKV = (Hq + 2 * Hkv) * D;
+    const float* src = qkv + (int64_t)row * QKV + (int64_t)head * D;
+    const int pos = row_pos[row];
+    const int KR = Hkv * D;
+    if (head >= Hq + Hkv) {  // value head: round to bf16 and store
+        const int vh = head - Hq - Hkv;
+        uint16_t* dst = vcache + (int64_t)row_lane[row] * lane_stride + (int64_t)pos * KR + vh * D;
+        dst[i] = f32_to_bf16_bits(src[i]);
+        dst[i + half] = f32_to_bf16_bits(src[i + half]);
+        return;
+    }
+    const float x0 = src[i], x1 = src[i + half];
+    double ss = (double)__fmul_rn(x0, x0) + (double)__fmul_rn(x1, x1);
+    ss = block_sum_f64(ss, sh);
+    const float rms = (float)sqrt(ss / (double)D + (double)eps);
+    const float* w = head < Hq ? q_norm : k_norm;
+    const float n0 = __fmul_rn(__fdiv_rn(x0, rms), w[i]);
+    const float n1 = __fmul_rn(__fdiv_rn(x1, rms), w[i + half]);
+    const float2 cs = rope_table[(int64_t)min(pos, max_len - 1) * half + i];
+    const float r0 = __fsub_rn(__fmul_rn(n0, cs.x), __fmul_rn(n1, cs.y));
+    const float r1 = __fadd_rn(__fmul_rn(n0, cs.y), __fmul_rn(n1, cs.x));
+    if (head < Hq) {
+        float* dst = q_out + (int64_t)row * Hq * D + (int64_t)head * D;
+        dst[i] = r0;
+        dst[i + half] = r1;
+    } else {
+        const int kh = head - Hq;
+        uint16_t* dst = kcache + (int64_t)row_lane[row] * lane_stride + (int64_t)pos * KR + kh * D;
+        dst[i] = f32_to_bf16_bits(r0);
+        dst[i + half] = f32_to_bf16_bits(r1);
+    }
+}
+
+// Standalone fused per-head RMSNorm + RoPE on f32 rows (no cache append), for the
+// C entry point and its parity test: x [rows, heads*D] -> out, positions per row.
+__global__ void rmsnorm_rope_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                    const int32_t* __restrict__ positions, float* __restrict__ out, int heads, int D,
+                                    int rotary, float eps, float rope_base, int out_bf16_double_round) {
+    __shared__ double sh[32];
+    const int row = blockIdx.x, head = blockIdx.y, i = threadIdx.x, half = D >> 1;
+    const float* src = x + ((int64_t)row * heads + head) * D;
+    const float x0 = src[i], x1 = src[i + half];
+    double ss = (double)__fmul_rn(x0, x0) + (double)__fmul_rn(x1, x1);
+    ss = block_sum_f64(ss, sh);
+    const float rms = (float)sqrt(ss / (double)D + (double)eps);
+    float n0, n1;
+    if (out_bf16_double_round) {
+        // Metal rounding seams: bf16(w * bf16(x * inv)) (lthn_qknorm_rope_bf16.metal:75-78)
+        const float inv = 1.0f / sqrtf((float)(ss / (double)D) + eps);
+        n0 = bf16_bits_to_f32(f32_to_bf16_bits(w[i] * bf16_bits_to_f32(f32_to_bf16_bits(x0 * inv))));
+        n1 = bf16_bits_to_f32(f32_to_bf16_bits(w[i + half] * bf16_bits_to_f32(f32_to_bf16_bits(x1 * inv))));
+    } else {
+        n0 = __fmul_rn(__fdiv_rn(x0, rms), w[i]);
+        n1 = __fmul_rn(__fdiv_rn(x1, rms), w[i + half]);
+    }
+    float* dst = out + ((int64_t)row * heads + head) * D;
+    const int active = rotary >> 1;
+    // NeoX pairing is (i, i + D/2); the first rotary/2 pairs rotate
+    if (i >= active) { dst[i] = n0; dst[i + half] = n1; return; }
+    const double freq = 1.0 / pow((double)rope_base, (double)(2 * i) / (double)D);
+    const double angle = (double)positions[row] * freq;
+    const float c = (float)cos(angle), s = (float)sin(angle);
+    float r0 = __fsub_rn(__fmul_rn(n0, c), __fmul_rn(n1, s));
+    float r1 = __fadd_rn(__fmul_rn(n0, s), __fmul_rn(n1, c));
+    if (out_bf16_double_round) { r0 = bf16_bits_to_f32(f32_to_bf16_bits(r0)); r1 = bf16_bits_to_f32(f32_to_bf16_bits(r1)); }
+    dst[i] = r0;
+    dst[i + half] = r1;
+}
+
+// ---- decode attention over the seq-major bf16 cache -----------------------------------
+// cache layout per lane: [max_len][Hkv*D] bf16 (k_seq_stride = Hkv*D, k_head_stride = D;
+// engine/metal/decode_step.go:20-26). One CTA handles one (row, kv head, key chunk) and
+// all GQ query heads of that kv head, so K and V are streamed once per group
+// (rocm_attention_heads_chunked_stage1 _gqa variants, engine/hip/kernels/attention/
+// chunked.hipinc). Eight lanes share a key position, each holding D/8 of the head
+// dimension; 16 positions are in flight per 128-thread CTA. Pass 1 writes scaled scores to
+// shared memory and finds the chunk maximum, pass 2 accumulates exp(s-max)*V. The chunk
+// result (max, sum, unnormalised accumulator) goes to scratch and is merged by
+// sdpa_merge_kernel (stage 2); with a single chunk the normalised output is written
+// directly.
+template <int D, int GQ>
+__global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
+    constexpr int E = D / 8;       // elements per lane
+    constexpr int V8 = E / 8;      // 16-byte loads per lane per row
+    constexpr int MAXC = 512;      // positions per chunk (scores kept in shared memory)
+    __shared__ float sc[GQ][MAXC];
+    __shared__ float red[4][GQ][D + 2];
+    __shared__ float smax[GQ][4], ssum[GQ][4];
+
+    // blockIdx.x indexes a bundle of GQ consecutive query heads that share one kv head
+    const int row = blockIdx.z, chunk = blockIdx.y;
+    const int qh0 = blockIdx.x * GQ, kvh = qh0 / (a.Hq / a.Hkv);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int l8 = lane & 7, pg = warp * 4 + (lane >> 3);  // position group 0..15
+    const int ctx = a.row_pos[row] + 1;                    // keys 0..pos inclusive
+    const int p0 = chunk * a.chunk_len;
+    if (p0 >= ctx) return;
+    const int p1 = min(ctx, p0 + a.chunk_len), len = p1 - p0;
+    const int KR = a.Hkv * D;
+    const uint16_t* kbase = a.kcache + (int64_t)a.row_lane[row] * a.lane_stride + (int64_t)kvh * D;
+    const uint16_t* vbase = a.vcache + (int64_t)a.row_lane[row] * a.lane_stride + (int64_t)kvh * D;
+
+    // query slices of this lane for the GQ heads, pre-multiplied by the softmax scale
+    float q[GQ][E];
+#pragma unroll
+    for (int h = 0; h < GQ; h++) {
+        const float* qh = a.q + ((int64_t)row * a.Hq + qh0 + h) * D;
+#pragma unroll
+        for (int v = 0; v < V8; v++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) q[h][v * 8 + e] = qh[(v * 8 + l8) * 8 + e] * a.scale;
+    }
+    // ---- pass 1: scores -----------------------------------------------------------
+    float mx[GQ];
+#pragma unroll
+    for (int h = 0; h < GQ; h++) mx[h] = -INFINITY;
+    for (int p = pg; p < len; p += 16) {
+        const uint16_t* kr = kbase + (int64_t)(p0 + p) * KR;
+        float dot[GQ];
+#pragma unroll
+        for (int h = 0; h < GQ; h++) dot[h] = 0.f;
+#pragma unroll
+        for (int v = 0; v < V8; v++) {
+            const uint4 kk = __ldg((const uint4*)(kr + (v * 8 + l8) * 8));
+            const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float k0 = __uint_as_float(kw[e] << 16), k1 = __uint_as_float(kw[e] & 0xffff0000u);
+#pragma unroll
+                for (int h = 0; h < GQ; h++) dot[h] = fmaf(q[h][v * 8 + 2 * e + 1], k1, fmaf(q[h][v * 8 + 2 * e], k0, dot[h]));
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < GQ; h++) {
+            float d = dot[h];
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            if (l8 == 0) sc[h][p] = d;
+            mx[h] = fmaxf(mx[h], d);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < GQ; h++) {
+        float m = warp_max(mx[h]);
+        if (lane == 0) smax[h][warp] = m;
+    }
+    __syncthreads();
+    float cmax[GQ];
+#pragma unroll
+    for (int h = 0; h < GQ; h++) cmax[h] = fmaxf(fmaxf(smax[h][0], smax[h][1]), fmaxf(smax[h][2], smax[h][3]));
+    // ---- pass 2: weights and weighted values -----------------------------------------
+    float acc[GQ][E], lsum[GQ];
+#pragma unroll
+    for (int h = 0; h < GQ; h++) {
+        lsum[h] = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; e++) acc[h][e] = 0.f;
+    }
+    for (int p = pg; p < len; p += 16) {
+        const uint16_t* vr = vbase + (int64_t)(p0 + p) * KR;
+        float w[GQ];
+#pragma unroll
+        for (int h = 0; h < GQ; h++) { w[h] = __expf(sc[h][p] - cmax[h]); lsum[h] += w[h]; }
+#pragma unroll
+        for (int v = 0; v < V8; v++) {
+            const uint4 vv = __ldg((const uint4*)(vr + (v * 8 + l8) * 8));
+            const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float v0 = __uint_as_float(vw[e] << 16), v1 = __uint_as_float(vw[e] & 0xffff0000u);
+#pragma unroll
+                for (int h = 0; h < GQ; h++) {
+                    acc[h][v * 8 + 2 * e] = fmaf(w[h], v0, acc[h][v * 8 + 2 * e]);
+                    acc[h][v * 8 + 2 * e + 1] = fmaf(w[h], v1, acc[h][v * 8 + 2 * e + 1]);
+                }
+            }
+        }
+    }
+    // combine the 4 position groups of a warp, then the 4 warps
+#pragma unroll
+    for (int h = 0; h < GQ; h++) {
+#pragma unroll
+        for (int e = 0; e < E; e++) {
+            float v = acc[h][e];
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            acc[h][e] = v;
+        }
+        float l = lsum[h];  // every lane of a position group holds the same weight: count one lane per group
+        l = (l8 == 0) ? l : 0.f;
+        l = warp_sum(l);
+        if (lane == 0) ssum[h][warp] = l;
+        if (lane < 8) {
+#pragma unroll
+            for (int v = 0; v < V8; v++)
+#pragma unroll
+                for (int e = 0; e < 8; e++) red[warp][h][(v * 8 + l8) * 8 + e] = acc[h][v * 8 + e];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < GQ * D; idx += 128) {
+        const int h = idx / D, d = idx - h * D;
+        const float v = red[0][h][d] + red[1][h][d] + red[2][h][d] + red[3][h][d];
+        const float l = ssum[h][0] + ssum[h][1] + ssum[h][2] + ssum[h][3];
+        const int qh = qh0 + h;
+        if (a.nchunks == 1) {
+            a.out[((int64_t)row * a.Hq + qh) * D + d] = v / l;
+        } else {
+            float* pa = a.part + (((int64_t)row * a.Hq + qh) * a.nchunks + chunk) * (D + 2);
+            pa[d] = v;
+            if (d == 0) { pa[D] = cmax[h]; pa[D + 1] = l; }
+        }
+    }
+}
+
+// stage 2: merge chunk partials with their log-sum-exp weights.
+__global__ void sdpa_merge_kernel(const float* __restrict__ part, const int32_t* __restrict__ row_pos, int Hq, int D,
+                                  int nchunks, int chunk_len, float* __restrict__ out) {
+    const int row = blockIdx.y, qh = blockIdx.x;
+    const int ctx = row_pos[row] + 1;
+    const int used = min(nchunks, (ctx + chunk_len - 1) / chunk_len);
+    const float* pa = part + ((int64_t)row * Hq + qh) * nchunks * (D + 2);
+    float m = -INFINITY;
+    for (int c = 0; c < used; c++) m = fmaxf(m, pa[(int64_t)c * (D + 2) + D]);
+    float denom = 0.f;
+    for (int c = 0; c < used; c++) denom += pa[(int64_t)c * (D + 2) + D + 1] * __expf(pa[(int64_t)c * (D + 2) + D] - m);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = 0.f;
+        for (int c = 0; c < used; c++) v += pa[(int64_t)c * (D + 2) + d] * __expf(pa[(int64_t)c * (D + 2) + D] - m);
+        out[((int64_t)row * Hq + qh) * D + d] = v / denom;
+    }
+}
+
+// ---- greedy argmax --------------------------------------------------------------------
+// Strict '>' with the lowest index winning ties (model.Greedy, model/sample.go:33-50;
+// hipReferenceGreedySample). Two stages: per-block best, then one block per row.
+__device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+__global__ void argmax_stage1_kernel(const float* __restrict__ logits, int V, int blocks_per_row,
+                                     float* __restrict__ pv, int* __restrict__ pi) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int row = blockIdx.y;
+    const float* lr = logits + (int64_t)row * V;
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < V; i += gridDim.x * blockDim.x) argmax_merge(v, idx, lr[i], i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) argmax_merge(v, idx, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = v; si[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (blockDim.x >> 5); w++) argmax_merge(v, idx, sv[w], si[w]);
+        pv[row * blocks_per_row + blockIdx.x] = v;
+        pi[row * blocks_per_row + blockIdx.x] = idx;
+    }
+}
+__global__ void argmax_stage2_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int blocks_per_row,
+                                     int32_t* __restrict__ out_idx, float* __restrict__ out_val, int index_offset) {
+    const int row = blockIdx.x;
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < blocks_per_row; i += 32) argmax_merge(v, idx, pv[row * blocks_per_row + i], pi[row * blocks_per_row + i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) argmax_merge(v, idx, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    if (threadIdx.x == 0) {
+        out_idx[row] = idx + index_offset;
+        if (out_val) out_val[row] = v;
+    }
+}
+
+// advance per-row positions and feed the chosen token back (one decode step bookkeeping)
+__global__ void advance_kernel(int32_t* row_pos, int32_t* ids, const int32_t* next, int rows) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < rows) { row_pos[r] += 1; ids[r] = next[r]; }
+}
+
+// ---- launch wrappers ----------------------------------------------------------------------
+int32_t launch_embed(cudaStream_t s, const int32_t* ids, int rows, const uint32_t* packed, const uint16_t* scales,
+                     const uint16_t* biases, int hidden, int vocab, float embed_scale, float* out) {
+    embed_kernel<<<rows, 256, 0, s>>>(ids, packed, scales, biases, hidden, vocab, embed_scale, out);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    return LTHN_OK;
+}
+
+int32_t launch_rmsnorm(cudaStream_t s, const float* a, float* h, const float* w_post, const float* w_next, float* out,
+                       int rows, int width, float eps, int mode) {
+    rmsnorm_kernel<<<rows, 256, 0, s>>>(a, h, w_post, w_next, out, width, eps, mode);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    return LTHN_OK;
+}
+
+int32_t launch_qknorm_rope_append(cudaStream_t s, const float* qkv, const float* q_norm, const float* k_norm,
+                                  const float2* rope_table, const int32_t* row_pos, const int32_t* row_lane,
+                                  float* q_out, uint16_t* kcache, uint16_t* vcache, int rows, int Hq, int Hkv, int D,
+                                  float eps, int64_t lane_stride, int max_len) {
+    dim3 grid(rows, Hq + 2 * Hkv);
+    qknorm_rope_append_kernel<<<grid, D / 2, 0, s>>>(qkv, q_norm, k_norm, rope_table, row_pos, row_lane, q_out, kcache,
+                                                     vcache, Hq, Hkv, D, eps, lane_stride, max_len);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    return LTHN_OK;
+}
+
+int32_t launch_rmsnorm_rope(cudaStream_t s, const float* x, const float* w, const int32_t* positions, float* out,
+                            int rows, int heads, int D, int rotary, float eps, float rope_base, int bf16_seams) {
+    dim3 grid(rows, heads);
+    rmsnorm_rope_kernel<<<grid, D / 2, 0, s>>>(x, w, positions, out, heads, D, rotary, eps, rope_base, bf16_seams);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    return LTHN_OK;
+}
+
+int sdpa_chunking(int max_ctx, int rows, int Hkv, int* chunk_len) {
+    // enough CTAs to cover the SMs a few times over, chunks of 64..512 keys
+    int want = (148 * 2 + rows * Hkv - 1) / (rows * Hkv);
+    if (want < 1) want = 1;
+    int len = (max_ctx + want - 1) / want;
+    len = (len + 63) / 64 * 64;
+    if (len < 64) len = 64;
+    if (len > 512) len = 512;
+    *chunk_len = len;
+    return (max_ctx + len - 1) / len;
+}
+
+size_t sdpa_scratch_bytes(int rows, int Hq, int D, int nchunks) {
+    return (size_t)rows * Hq * nchunks * (D + 2) * sizeof(float);
+}
+
+// bundle = query heads handled per CTA (they share K/V loads); must divide the GQA group
+template <int D>
+static int32_t launch_sdpa_d(cudaStream_t s, const SdpaArgs& a, int rows, int bundle) {
+    dim3 grid(a.Hq / bundle, a.nchunks, rows);
+    switch (bundle) {
+        case 1: sdpa_decode_kernel<D, 1><<<grid, 128, 0, s>>>(a); break;
+        case 2: if (D <= 256) { sdpa_decode_kernel<(D <= 256 ? D : 64), 2><<<grid, 128, 0, s>>>(a); break; }
+        case 4: if (D <= 128) { sdpa_decode_kernel<(D <= 128 ? D : 64), 4><<<grid, 128, 0, s>>>(a); break; }
+        default: return fail(LTHN_ERR_INVALID, "sdpa_decode: unsupported head bundle");
+    }
+    LTHN_CUDA_TRY(cudaGetLastError());
+    return LTHN_OK;
+}
+
+int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D) {
+    if (a.Hq % a.Hkv != 0) return fail(LTHN_ERR_INVALID, "sdpa_decode: Hq must be a multiple of Hkv");
+    const int GQ = a.Hq / a.Hkv;
+    if (a.nchunks > 1 && !a.part) return fail(LTHN_ERR_INVALID, "sdpa_decode: split-KV needs a scratch buffer");
+    if (a.chunk_len > 512) return fail(LTHN_ERR_INVALID, "sdpa_decode: chunk length above 512");
+    // register budget: bundle * D/8 accumulators and as many query values per lane
+    const int max_bundle = D <= 128 ? 4 : (D <= 256 ? 2 : 1);
+    int bundle = 1;
+    for (int c = max_bundle; c >= 1; c >>= 1)
+        if (GQ % c == 0) { bundle = c; break; }
+    int32_t rc;
+    if (D == 128) rc = launch_sdpa_d<128>(s, a, rows, bundle);
+    else if (D == 256) rc = launch_sdpa_d<256>(s, a, rows, bundle);
+    else if (D == 64) rc = launch_sdpa_d<64>(s, a, rows, bundle);
+    else if (D == 512) rc = launch_sdpa_d<512>(s, a, rows, bundle);
+    else return fail(LTHN_ERR_INVALID, "sdpa_decode: head_dim must be 64, 128, 256 or 512");
+    if (rc) return rc;
+    if (a.nchunks > 1) {
+        dim3 grid(a.Hq, rows);
+        sdpa_merge_kernel<<<grid, 128, 0, s>>>(a.part, a.row_pos, a.Hq, D, a.nchunks, a.chunk_len, a.out);
+        LTHN_CUDA_TRY(cudaGetLastError());
+    }
+    return LTHN_OK;
+}
+
+int32_t launch_argmax(cudaStream_t s, const float* logits, int rows, int V, float* pv, int* pi, int32_t* out_idx,
+                      float* out_val, int index_offset) {
+    const int bpr = ARGMAX_BLOCKS;
+    dim3 grid(bpr, rows);
+    argmax_stage1_kernel<<<grid, 256, 0, s>>>(logits, V, bpr, pv, pi);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    argmax_stage2_kernel<<<rows, 32, 0, s>>>(pv, pi, bpr, out_idx, out_val, index_offset);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    return LTHN_OK;
+}
+
+int32_t launch_advance(cudaStream_t s, int32_t* row_pos, int32_t* ids, const int32_t* next, int rows) {
+    advance_kernel<<<(rows + 63) / 64, 64, 0, s>>>(row_pos, ids, next, rows);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    return LTHN_OK;
+}
+
+}  // namespace lthn

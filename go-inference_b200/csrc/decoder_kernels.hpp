@@ -1,0 +1,42 @@
+// decoder_kernels.hpp — launch wrappers of the fused decoder-step kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+namespace lthn {
+
+constexpr int ARGMAX_BLOCKS = 64;
+
+struct SdpaArgs {
+    const float* q;            // [rows, Hq, D] f32, already normed and rotated
+    const uint16_t* kcache;    // bf16, lane-major: [lanes][max_len][Hkv*D]
+    const uint16_t* vcache;
+    const int32_t* row_pos;    // [rows] position of the row's newest key
+    const int32_t* row_lane;   // [rows] cache lane of each row
+    float* out;                // [rows, Hq, D]
+    float* part;               // [rows, Hq, nchunks, D+2] split-KV partials (scratch)
+    int64_t lane_stride;       // elements between cache lanes
+    int Hq, Hkv;
+    int nchunks, chunk_len;
+    float scale;
+};
+
+int32_t launch_embed(cudaStream_t s, const int32_t* ids, int rows, const uint32_t* packed, const uint16_t* scales,
+                     const uint16_t* biases, int hidden, int vocab, float embed_scale, float* out);
+int32_t launch_rmsnorm(cudaStream_t s, const float* a, float* h, const float* w_post, const float* w_next, float* out,
+                       int rows, int width, float eps, int mode);
+int32_t launch_qknorm_rope_append(cudaStream_t s, const float* qkv, const float* q_norm, const float* k_norm,
+                                  const float2* rope_table, const int32_t* row_pos, const int32_t* row_lane,
+                                  float* q_out, uint16_t* kcache, uint16_t* vcache, int rows, int Hq, int Hkv, int D,
+                                  float eps, int64_t lane_stride, int max_len);
+int32_t launch_rmsnorm_rope(cudaStream_t s, const float* x, const float* w, const int32_t* positions, float* out,
+                            int rows, int heads, int D, int rotary, float eps, float rope_base, int bf16_seams);
+int sdpa_chunking(int max_ctx, int rows, int Hkv, int* chunk_len);
+size_t sdpa_scratch_bytes(int rows, int Hq, int D, int nchunks);
+int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D);
+int32_t launch_argmax(cudaStream_t s, const float* logits, int rows, int V, float* pv, int* pi, int32_t* out_idx,
+                      float* out_val, int index_offset);
+int32_t launch_advance(cudaStream_t s, int32_t* row_pos, int32_t* ids, const int32_t* next, int rows);
+
+}  // namespace lthn

@@ -1,0 +1,892 @@
+// engine.cu — the decoder engine behind the C ABI: resident 4-bit weights, the
+// seq-major bf16 KV cache, retained sessions and multi-lane batched decode.
+//
+// It mirrors what a go-inference engine package supplies to the shared adapters:
+//   Model    -> engine.TokenModel (engine/model.go:25-31): weights stay resident,
+//               OpenEngineSession hands out a Session over a free KV lane.
+//   Session  -> engine.Session (engine/session.go:40-61): PrefillTokens / AppendTokens /
+//               Pos / GenerateFromCacheEach (greedy) plus logits read-out for host-side
+//               sampling.
+//   LaneSet  -> inference.LaneSet (batch_step.go:97-119): K lanes with their own KV and
+//               position advanced by ONE batched forward per Step.
+// The forward follows the reference's layer order (engine/hip/hip_gemma4_q4_layer.go:
+// 1441-2067; CPU oracle hip_gemma4_q4_oracle_test.go:873-961) for the gemma3 block:
+//   norm -> q|k|v projection -> per-head norm + RoPE + KV append -> attention -> o proj
+//   -> post-norm + residual + pre-FF norm -> gate|up + GeGLU -> down -> post-norm +
+//   residual (+ the next layer's input norm), final norm, tied lm_head, greedy argmax.
+// Activations are f32 between kernels; K and V are rounded to bf16 when appended.
+//
+// Tensor parallelism (no counterpart in the reference, which is single-device):
+// q/k/v/gate/up are sharded by output rows (heads), o/down by input columns in whole
+// 64-wide groups, the KV cache by kv head; each rank's partial o/down output is summed
+// with one all-reduce (NCCL, loaded at run time) per projection.
+#include "common.cuh"
+#include "decoder_kernels.hpp"
+#include "qmv.hpp"
+
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace lthn {
+
+// ---- NCCL, bound at run time so the library loads without it --------------------------
+struct UniqueId { char internal[128]; };
+struct NcclApi {
+    void* lib = nullptr;
+    int (*GetUniqueId)(void*) = nullptr;
+    int (*CommInitRank)(void**, int, UniqueId /* ncclUniqueId, passed by value */, int) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+};
+static NcclApi g_nccl;
+static std::mutex g_nccl_mu;
+
+static int32_t nccl_load() {
+    std::lock_guard<std::mutex> lk(g_nccl_mu);
+    if (g_nccl.lib) return LTHN_OK;
+    const char* names[] = {getenv("LTHN_CUDA_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+    void* h = nullptr;
+    for (const char* n : names) {
+        if (!n || !*n) continue;
+        h = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (h) break;
+    }
+    if (!h) return fail(LTHN_ERR_UNAVAILABLE, "NCCL not found (set LTHN_CUDA_NCCL_LIB to libnccl.so.2)");
+    g_nccl.GetUniqueId = (decltype(g_nccl.GetUniqueId))dlsym(h, "ncclGetUniqueId");
+    g_nccl.CommInitRank = (decltype(g_nccl.CommInitRank))dlsym(h, "ncclCommInitRank");
+    g_nccl.CommDestroy = (decltype(g_nccl.CommDestroy))dlsym(h, "ncclCommDestroy");
+    g_nccl.AllReduce = (decltype(g_nccl.AllReduce))dlsym(h, "ncclAllReduce");
+    g_nccl.AllGather = (decltype(g_nccl.AllGather))dlsym(h, "ncclAllGather");
+    g_nccl.GetErrorString = (decltype(g_nccl.GetErrorString))dlsym(h, "ncclGetErrorString");
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.AllGather || !g_nccl.CommDestroy) {
+        dlclose(h);
+        return fail(LTHN_ERR_UNAVAILABLE, "NCCL library lacks a required symbol");
+    }
+    g_nccl.lib = h;
+    return LTHN_OK;
+}
+static int32_t nccl_check(int rc, const char* what) {
+    if (rc == 0) return LTHN_OK;
+    return fail(LTHN_ERR_CUDA, std::string(what) + ": NCCL error " + (g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?"));
+}
+enum { kNcclFloat32 = 7, kNcclSum = 0 };
+
+// ---- model --------------------------------------------------------------------------
+struct Linear {
+    uint32_t* wq = nullptr; uint16_t* s = nullptr; uint16_t* b = nullptr;
+    int64_t N = 0, K = 0;  // local (sharded) shape
+};
+enum { ROLE_Q = 0, ROLE_K, ROLE_V, ROLE_O, ROLE_GATE, ROLE_UP, ROLE_DOWN, ROLE_COUNT };
+enum { NORM_INPUT = 0, NORM_POST_ATTN, NORM_PRE_FF, NORM_POST_FF, NORM_Q, NORM_K, NORM_COUNT };
+
+struct Layer {
+    Linear qkv, o, gate, up, down;
+    float* norm[NORM_COUNT] = {};
+    bool have[ROLE_COUNT] = {};
+};
+
+constexpr int kMaxRows = 32;  // rows per forward (the batched matvec serves up to 32)
+
+struct Model {
+    lthn_model_config c{};
+    int Hq_l = 0, Hkv_l = 0, QR_l = 0, KR_l = 0, F_l = 0, V_l = 0, v0 = 0;
+    std::vector<Layer> layers;
+    Linear embed;       // full table (embedding lookup)
+    Linear head;        // lm_head shard: rows [v0, v0+V_l) of the tied table (aliases embed)
+    bool have_embed = false;
+    float* final_norm = nullptr;
+    float2* rope = nullptr;
+    uint16_t *kcache = nullptr, *vcache = nullptr;
+    int64_t lane_stride = 0, layer_stride = 0;
+    std::vector<char> lane_used;
+    bool finalized = false;
+    void* comm = nullptr;
+    cudaStream_t stream = nullptr;
+    // workspace for up to kMaxRows rows
+    int32_t *d_ids = nullptr, *d_pos = nullptr, *d_lane = nullptr, *d_next = nullptr;
+    float *h = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *att = nullptr, *a = nullptr, *act = nullptr;
+    float *logits = nullptr, *amax_v = nullptr, *sdpa_part = nullptr, *best_v = nullptr, *gather = nullptr;
+    int* amax_i = nullptr;
+    size_t sdpa_part_bytes = 0;
+    int32_t* h_pinned = nullptr;  // pinned staging for ids / positions / tokens
+    uint64_t weight_bytes = 0;
+    std::mutex mu;
+    std::vector<void*> allocs;
+};
+
+template <typename T>
+static int32_t dalloc(Model* m, T** p, size_t n) {
+    void* q = nullptr;
+    LTHN_CUDA_TRY(cudaMalloc(&q, std::max<size_t>(n * sizeof(T), 256)));
+    m->allocs.push_back(q);
+    *p = (T*)q;
+    return LTHN_OK;
+}
+
+static int32_t linear_alloc(Model* m, Linear* l, int64_t N, int64_t K) {
+    l->N = N; l->K = K;
+    int32_t rc;
+    if ((rc = dalloc(m, &l->wq, (size_t)N * K / 8))) return rc;
+    if ((rc = dalloc(m, &l->s, (size_t)N * K / 64))) return rc;
+    if ((rc = dalloc(m, &l->b, (size_t)N * K / 64))) return rc;
+    m->weight_bytes += (uint64_t)N * K * 9 / 16;
+    return LTHN_OK;
+}
+
+static int32_t model_validate(const lthn_model_config& c) {
+    LTHN_REQUIRE(c.layers > 0 && c.hidden > 0 && c.q_heads > 0 && c.kv_heads > 0 && c.head_dim > 0 && c.ffn > 0 && c.vocab > 0,
+                 "model: dimensions must be positive");
+    LTHN_REQUIRE(c.group_size == 64 && c.bits == 4, "model: the decoder serves 4-bit, group-64 affine weights");
+    LTHN_REQUIRE(c.q_heads % c.kv_heads == 0, "model: q_heads must be a multiple of kv_heads");
+    LTHN_REQUIRE(c.head_dim == 64 || c.head_dim == 128 || c.head_dim == 256 || c.head_dim == 512, "model: head_dim must be 64, 128, 256 or 512");
+    LTHN_REQUIRE(c.hidden % 64 == 0 && c.ffn % 64 == 0, "model: hidden and ffn must be multiples of the group size");
+    LTHN_REQUIRE(c.max_len > 0 && c.max_lanes > 0, "model: max_len and max_lanes must be positive");
+    const int t = c.tp_size > 0 ? c.tp_size : 1;
+    LTHN_REQUIRE(c.tp_rank >= 0 && c.tp_rank < t, "model: tp_rank out of range");
+    LTHN_REQUIRE(c.q_heads % t == 0 && c.kv_heads % t == 0, "model: heads must divide by the tensor-parallel degree");
+    LTHN_REQUIRE((c.q_heads / t * c.head_dim) % 64 == 0 && (c.ffn / t) % 64 == 0, "model: a tensor-parallel shard must hold whole groups");
+    LTHN_REQUIRE(c.vocab % t == 0, "model: vocab must divide by the tensor-parallel degree");
+    return LTHN_OK;
+}
+
+static uint64_t tensor_seed(uint64_t seed, int layer, int role) {
+    return seed * 1000003ull + (uint64_t)(layer + 1) * 16ull + (uint64_t)role;
+}
+
+}  // namespace lthn
+
+// declared in codec.cu
+extern "C" int32_t lthn_synth_affine_weight_shard(void* stream, uint64_t seed, float sigma, int64_t N, int64_t K,
+                                                  int64_t row0, int64_t col0, int64_t Kfull, uint32_t* packed,
+                                                  uint16_t* scales, uint16_t* biases);
+
+namespace lthn {
+
+// rows [r0, r0+n) x cols [c0, c0+k) of a host-resident packed tensor [N,K] -> device linear
+static int32_t upload_shard(Model* m, Linear* dst, int64_t dst_row0, const uint8_t* packed, const uint8_t* scales,
+                            const uint8_t* biases, int64_t K, int64_t r0, int64_t n, int64_t c0, int64_t k) {
+    // packed: K/2 bytes per row; scales/biases: K/64*2 bytes per row
+    const size_t src_pitch_p = (size_t)K / 2, src_pitch_s = (size_t)K / 64 * 2;
+    const size_t dst_pitch_p = (size_t)dst->K / 2, dst_pitch_s = (size_t)dst->K / 64 * 2;
+    LTHN_CUDA_TRY(cudaMemcpy2DAsync((uint8_t*)dst->wq + dst_row0 * dst_pitch_p, dst_pitch_p,
+                                    packed + r0 * src_pitch_p + c0 / 2, src_pitch_p, (size_t)k / 2, (size_t)n,
+                                    cudaMemcpyHostToDevice, m->stream));
+    LTHN_CUDA_TRY(cudaMemcpy2DAsync((uint8_t*)dst->s + dst_row0 * dst_pitch_s, dst_pitch_s,
+                                    scales + r0 * src_pitch_s + c0 / 64 * 2, src_pitch_s, (size_t)k / 64 * 2, (size_t)n,
+                                    cudaMemcpyHostToDevice, m->stream));
+    LTHN_CUDA_TRY(cudaMemcpy2DAsync((uint8_t*)dst->b + dst_row0 * dst_pitch_s, dst_pitch_s,
+                                    biases + r0 * src_pitch_s + c0 / 64 * 2, src_pitch_s, (size_t)k / 64 * 2, (size_t)n,
+                                    cudaMemcpyHostToDevice, m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));  // the caller's buffers may be unmapped after return
+    return LTHN_OK;
+}
+
+struct ShardPlan { Linear* dst; int64_t dst_row0, r0, n, c0, k, Nfull, Kfull; };
+
+// Where (layer, role) lands on this rank.
+static int32_t shard_plan(Model* m, int layer, int role, ShardPlan* p) {
+    const auto& c = m->c;
+    const int t = std::max(1, c.tp_size), r = c.tp_rank;
+    const int64_t D = c.head_dim, H = c.hidden, F = c.ffn;
+    Layer& L = m->layers[layer];
+    switch (role) {
+        case ROLE_Q: *p = {&L.qkv, 0, (int64_t)r * m->QR_l, m->QR_l, 0, H, (int64_t)c.q_heads * D, H}; break;
+        case ROLE_K: *p = {&L.qkv, m->QR_l, (int64_t)r * m->KR_l, m->KR_l, 0, H, (int64_t)c.kv_heads * D, H}; break;
+        case ROLE_V: *p = {&L.qkv, (int64_t)m->QR_l + m->KR_l, (int64_t)r * m->KR_l, m->KR_l, 0, H, (int64_t)c.kv_heads * D, H}; break;
+        case ROLE_O: *p = {&L.o, 0, 0, H, (int64_t)r * m->QR_l, m->QR_l, H, (int64_t)c.q_heads * D}; break;
+        case ROLE_GATE: *p = {&L.gate, 0, (int64_t)r * m->F_l, m->F_l, 0, H, F, H}; break;
+        case ROLE_UP: *p = {&L.up, 0, (int64_t)r * m->F_l, m->F_l, 0, H, F, H}; break;
+        case ROLE_DOWN: *p = {&L.down, 0, 0, H, (int64_t)r * m->F_l, m->F_l, H, F}; break;
+        default: return fail(LTHN_ERR_INVALID, "model: unknown linear role");
+    }
+    (void)t;
+    return LTHN_OK;
+}
+
+static int32_t all_reduce(Model* m, float* buf, size_t n) {
+    if (m->c.tp_size <= 1) return LTHN_OK;
+    if (!m->comm) return fail(LTHN_ERR_STATE, "model: tensor-parallel model has no communicator (call lthn_model_set_comm)");
+    return nccl_check(g_nccl.AllReduce(buf, buf, n, kNcclFloat32, kNcclSum, m->comm, m->stream), "ncclAllReduce");
+}
+
+// gathers (value, index) pairs of every rank and keeps the best (ties -> lowest index)
+__global__ void tp_pack_kernel(const float* v, const int32_t* idx, float* out, int rows) {
+    const int r = threadIdx.x;
+    if (r < rows) { out[2 * r] = v[r]; out[2 * r + 1] = __int_as_float(idx[r]); }
+}
+__global__ void tp_pick_kernel(const float* gathered, int ranks, int rows, int32_t* out_idx) {
+    const int r = threadIdx.x;
+    if (r >= rows) return;
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int k = 0; k < ranks; k++) {
+        const float v = gathered[(k * rows + r) * 2];
+        const int i = __float_as_int(gathered[(k * rows + r) * 2 + 1]);
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+    out_idx[r] = bi;
+}
+
+// One forward over `rows` (<= kMaxRows) tokens whose ids / positions / lanes are already in
+// d_ids / d_pos / d_lane. max_ctx bounds pos+1 over the rows (host knowledge, sizes the
+// split-KV grid). Leaves the final-normed hidden rows in xn; computes logits + greedy
+// token for rows [logit_row0, rows) when want_logits.
+static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int logit_row0) {
+    const auto& c = m->c;
+    cudaStream_t s = m->stream;
+    const int H = c.hidden, D = c.head_dim;
+    int32_t rc;
+    if ((rc = launch_embed(s, m->d_ids, rows, m->embed.wq, m->embed.s, m->embed.b, H, c.vocab, c.embed_scale, m->h))) return rc;
+    if ((rc = launch_rmsnorm(s, m->h, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, m->xn, rows, H, c.eps, 0))) return rc;
+    int chunk_len = 0;
+    const int nchunks = sdpa_chunking(max_ctx, rows, m->Hkv_l, &chunk_len);
+    const size_t need = sdpa_scratch_bytes(rows, m->Hq_l, D, nchunks);
+    if (nchunks > 1 && need > m->sdpa_part_bytes) return fail(LTHN_ERR_STATE, "forward: attention scratch too small");
+    for (int li = 0; li < c.layers; li++) {
+        Layer& L = m->layers[li];
+        QmvCall qc{L.qkv.wq, L.qkv.s, L.qkv.b, nullptr, nullptr, nullptr, m->xn, LTHN_DTYPE_F32, m->qkv, LTHN_DTYPE_F32, L.qkv.N, L.qkv.K, rows};
+        if ((rc = qmv_dispatch(s, qc))) return rc;
+        uint16_t* kc = m->kcache + (int64_t)li * m->layer_stride;
+        uint16_t* vc = m->vcache + (int64_t)li * m->layer_stride;
+        if ((rc = launch_qknorm_rope_append(s, m->qkv, L.norm[NORM_Q], L.norm[NORM_K], m->rope, m->d_pos, m->d_lane, m->q, kc, vc,
+                                            rows, m->Hq_l, m->Hkv_l, D, c.eps, m->lane_stride, c.max_len))) return rc;
+        SdpaArgs sa{m->q, kc, vc, m->d_pos, m->d_lane, m->att, m->sdpa_part, m->lane_stride, m->Hq_l, m->Hkv_l, nchunks, chunk_len, c.attn_scale};
+        if ((rc = launch_sdpa_decode(s, sa, rows, D))) return rc;
+        QmvCall oc{L.o.wq, L.o.s, L.o.b, nullptr, nullptr, nullptr, m->att, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.o.N, L.o.K, rows};
+        if ((rc = qmv_dispatch(s, oc))) return rc;
+        if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
+        if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, 1))) return rc;
+        QmvCall gc{L.gate.wq, L.gate.s, L.gate.b, L.up.wq, L.up.s, L.up.b, m->xn, LTHN_DTYPE_F32, m->act, LTHN_DTYPE_F32, L.gate.N, L.gate.K, rows};
+        if ((rc = qmv_dispatch(s, gc))) return rc;
+        QmvCall dc{L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, m->act, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.down.N, L.down.K, rows};
+        if ((rc = qmv_dispatch(s, dc))) return rc;
+        if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
+        const float* next_norm = li + 1 < c.layers ? m->layers[li + 1].norm[NORM_INPUT] : m->final_norm;
+        if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, 1))) return rc;
+    }
+    if (!want_logits) return LTHN_OK;
+    const int lr = rows - logit_row0;
+    QmvCall hc{m->head.wq, m->head.s, m->head.b, nullptr, nullptr, nullptr, m->xn + (int64_t)logit_row0 * H, LTHN_DTYPE_F32,
+               m->logits, LTHN_DTYPE_F32, m->head.N, m->head.K, lr};
+    if ((rc = qmv_dispatch(s, hc))) return rc;
+    if (c.tp_size <= 1)
+        return launch_argmax(s, m->logits, lr, m->V_l, m->amax_v, m->amax_i, m->d_next + logit_row0, nullptr, 0);
+    // vocab-sharded head: local best (value, global index) per row, gathered from all ranks
+    if ((rc = launch_argmax(s, m->logits, lr, m->V_l, m->amax_v, m->amax_i, m->d_next + logit_row0, m->best_v, m->v0))) return rc;
+    tp_pack_kernel<<<1, 32, 0, s>>>(m->best_v, m->d_next + logit_row0, m->gather, lr);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    float* all = m->gather + 2 * kMaxRows;
+    if ((rc = nccl_check(g_nccl.AllGather(m->gather, all, (size_t)2 * lr, kNcclFloat32, m->comm, s), "ncclAllGather"))) return rc;
+    tp_pick_kernel<<<1, 32, 0, s>>>(all, c.tp_size, lr, m->d_next + logit_row0);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    return LTHN_OK;
+}
+
+static int32_t forward_full(Model* m, int rows, int max_ctx, bool want_logits, int logit_row0) {
+    return forward(m, rows, max_ctx, want_logits, logit_row0);
+}
+
+// ---- lanes / sessions ------------------------------------------------------------------
+struct Lane {
+    int id = -1;       // KV lane index in the model
+    int pos = 0;       // tokens in the cache
+    int pending = -1;  // generated token not yet fed
+    bool have_next = false;  // d_next of the last forward holds this lane's next token
+    int next_tok = -1;
+    // lane-set bookkeeping
+    int handle = 0, produced = 0, max_new = 0;
+    bool terminal = false;
+    std::vector<int32_t> stop;
+};
+
+static int lane_acquire(Model* m) {
+    std::lock_guard<std::mutex> lk(m->mu);
+    for (size_t i = 0; i < m->lane_used.size(); i++)
+        if (!m->lane_used[i]) { m->lane_used[i] = 1; return (int)i; }
+    return -1;
+}
+static void lane_release(Model* m, int id) {
+    std::lock_guard<std::mutex> lk(m->mu);
+    if (id >= 0 && id < (int)m->lane_used.size()) m->lane_used[id] = 0;
+}
+
+// Feeds `n` tokens of one lane (prefill / append), kMaxRows at a time. The greedy token
+// after the last one lands in lane->next_tok.
+static int32_t feed_lane(Model* m, Lane* ln, const int32_t* ids, int n) {
+    LTHN_REQUIRE(n > 0, "session: no tokens to feed");
+    LTHN_REQUIRE(ln->pos + n <= m->c.max_len, "session: context length exceeded");
+    for (int i = 0; i < n; i++) LTHN_REQUIRE(ids[i] >= 0 && ids[i] < m->c.vocab, "session: token id outside the vocabulary");
+    std::lock_guard<std::mutex> lk(m->mu);
+    int32_t rc;
+    for (int off = 0; off < n; off += kMaxRows) {
+        const int rows = std::min(kMaxRows, n - off);
+        int32_t* hp = m->h_pinned;
+        for (int r = 0; r < rows; r++) { hp[r] = ids[off + r]; hp[kMaxRows + r] = ln->pos + r; hp[2 * kMaxRows + r] = ln->id; }
+        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_ids, hp, rows * 4, cudaMemcpyHostToDevice, m->stream));
+        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_pos, hp + kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
+        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_lane, hp + 2 * kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
+        const bool last = off + rows >= n;
+        if ((rc = forward_full(m, rows, ln->pos + rows, last, rows - 1))) return rc;
+        ln->pos += rows;
+        if (last) {
+            LTHN_CUDA_TRY(cudaMemcpyAsync(hp + 3 * kMaxRows, m->d_next + rows - 1, 4, cudaMemcpyDeviceToHost, m->stream));
+        }
+        LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));  // the pinned staging is reused by the next chunk
+    }
+    ln->next_tok = m->h_pinned[3 * kMaxRows];
+    ln->have_next = true;
+    ln->pending = -1;
+    return check_device_status(m->stream);
+}
+
+struct Session { Model* m; Lane lane; };
+struct LaneSet {
+    Model* m;
+    int max_lanes;
+    std::vector<Lane> lanes;
+    int next_handle = 1;
+    uint64_t forwards = 0;
+};
+
+}  // namespace lthn
+
+using namespace lthn;
+
+extern "C" {
+
+// ---- tensor-parallel communicator ---------------------------------------------------------
+int32_t lthn_tp_unique_id(void* out128) {
+    clear_error();
+    LTHN_REQUIRE(out128 != nullptr, "lthn_tp_unique_id: out is NULL");
+    int32_t rc = nccl_load();
+    if (rc) return rc;
+    return nccl_check(g_nccl.GetUniqueId(out128), "ncclGetUniqueId");
+}
+int32_t lthn_tp_init(int32_t rank, int32_t world, const void* id128, void** comm) {
+    clear_error();
+    LTHN_REQUIRE(comm && id128 && world > 0 && rank >= 0 && rank < world, "lthn_tp_init: bad arguments");
+    int32_t rc = nccl_load();
+    if (rc) return rc;
+    UniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    return nccl_check(g_nccl.CommInitRank(comm, world, id, rank), "ncclCommInitRank");
+}
+int32_t lthn_tp_destroy(void* comm) {
+    clear_error();
+    if (!comm) return LTHN_OK;
+    return nccl_check(g_nccl.CommDestroy(comm), "ncclCommDestroy");
+}
+
+// ---- model ----------------------------------------------------------------------------------
+int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
+    clear_error();
+    LTHN_REQUIRE(cfg && model, "lthn_model_create: NULL argument");
+    lthn_model_config c = *cfg;
+    if (c.tp_size <= 0) c.tp_size = 1;
+    if (c.eps <= 0) c.eps = 1e-6f;
+    if (c.rope_base <= 0) c.rope_base = 10000.0f;
+    if (c.attn_scale <= 0) c.attn_scale = (float)(1.0 / std::sqrt((double)c.head_dim));  // gemma3.go:150
+    if (c.embed_scale <= 0)  // bf16(sqrt(hidden)), hip_gemma4_q4_layer.go:2757-2763
+        c.embed_scale = bf16_bits_to_f32(f32_to_bf16_bits((float)std::sqrt((double)c.hidden)));
+    int32_t rc = model_validate(c);
+    if (rc) return rc;
+    Model* m = new Model();
+    m->c = c;
+    const int t = c.tp_size;
+    m->Hq_l = c.q_heads / t; m->Hkv_l = c.kv_heads / t;
+    m->QR_l = m->Hq_l * c.head_dim; m->KR_l = m->Hkv_l * c.head_dim;
+    m->F_l = c.ffn / t; m->V_l = c.vocab / t; m->v0 = c.tp_rank * m->V_l;
+    m->layers.resize(c.layers);
+    cudaError_t e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { delete m; return cuda_fail(e, "cudaStreamCreate"); }
+    auto bail = [&](int32_t code) {
+        const std::string keep = lthn_last_error();
+        for (void* p : m->allocs) cudaFree(p);
+        if (m->h_pinned) cudaFreeHost(m->h_pinned);
+        cudaStreamDestroy(m->stream);
+        delete m;
+        return fail(code, keep);
+    };
+    const int64_t H = c.hidden;
+    for (auto& L : m->layers) {
+        if ((rc = linear_alloc(m, &L.qkv, (int64_t)m->QR_l + 2 * m->KR_l, H))) return bail(rc);
+        if ((rc = linear_alloc(m, &L.o, H, m->QR_l))) return bail(rc);
+        if ((rc = linear_alloc(m, &L.gate, m->F_l, H))) return bail(rc);
+        if ((rc = linear_alloc(m, &L.up, m->F_l, H))) return bail(rc);
+        if ((rc = linear_alloc(m, &L.down, H, m->F_l))) return bail(rc);
+        for (int i = 0; i < NORM_COUNT; i++)
+            if ((rc = dalloc(m, &L.norm[i], (size_t)(i >= NORM_Q ? c.head_dim : H)))) return bail(rc);
+    }
+    if ((rc = linear_alloc(m, &m->embed, c.vocab, H))) return bail(rc);
+    m->head = m->embed;
+    m->head.N = m->V_l;
+    m->head.wq = m->embed.wq + (int64_t)m->v0 * (H / 8);
+    m->head.s = m->embed.s + (int64_t)m->v0 * (H / 64);
+    m->head.b = m->embed.b + (int64_t)m->v0 * (H / 64);
+    if ((rc = dalloc(m, &m->final_norm, (size_t)H))) return bail(rc);
+    // RoPE table, f64 on the host exactly as hipReferenceRoPENeoXWithFrequencyDimScale
+    {
+        const int half = c.head_dim / 2;
+        std::vector<float2> tab((size_t)c.max_len * half);
+        for (int p = 0; p < c.max_len; p++)
+            for (int i = 0; i < half; i++) {
+                const double freq = 1.0 / std::pow((double)c.rope_base, (double)(2 * i) / (double)c.head_dim);
+                const double angle = (double)p * freq * 1.0;
+                tab[(size_t)p * half + i] = make_float2((float)std::cos(angle), (float)std::sin(angle));
+            }
+        if ((rc = dalloc(m, &m->rope, tab.size()))) return bail(rc);
+        e = cudaMemcpy(m->rope, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { cuda_fail(e, "rope table upload"); return bail(LTHN_ERR_CUDA); }
+    }
+    m->layer_stride = (int64_t)c.max_len * m->KR_l;
+    m->lane_stride = (int64_t)c.layers * m->layer_stride;
+    const size_t kv_elems = (size_t)c.max_lanes * m->lane_stride;
+    if ((rc = dalloc(m, &m->kcache, kv_elems))) return bail(rc);
+    if ((rc = dalloc(m, &m->vcache, kv_elems))) return bail(rc);
+    m->lane_used.assign(c.max_lanes, 0);
+    const size_t R = kMaxRows;
+    if ((rc = dalloc(m, &m->d_ids, R)) || (rc = dalloc(m, &m->d_pos, R)) || (rc = dalloc(m, &m->d_lane, R)) ||
+        (rc = dalloc(m, &m->d_next, R)) || (rc = dalloc(m, &m->h, R * H)) || (rc = dalloc(m, &m->xn, R * H)) ||
+        (rc = dalloc(m, &m->qkv, R * (m->QR_l + 2 * m->KR_l))) || (rc = dalloc(m, &m->q, R * m->QR_l)) ||
+        (rc = dalloc(m, &m->att, R * m->QR_l)) || (rc = dalloc(m, &m->a, R * H)) || (rc = dalloc(m, &m->act, R * m->F_l)) ||
+        (rc = dalloc(m, &m->logits, R * m->V_l)) || (rc = dalloc(m, &m->amax_v, R * ARGMAX_BLOCKS)) ||
+        (rc = dalloc(m, &m->amax_i, R * ARGMAX_BLOCKS)) || (rc = dalloc(m, &m->best_v, R)) ||
+        (rc = dalloc(m, &m->gather, 2 * R * (1 + (size_t)c.tp_size))))
+        return bail(rc);
+    {
+        int chunk_len = 0;
+        const int nch = sdpa_chunking(c.max_len, 1, m->Hkv_l, &chunk_len);  // fewest rows -> most chunks
+        m->sdpa_part_bytes = sdpa_scratch_bytes(kMaxRows, m->Hq_l, c.head_dim, nch);
+        if ((rc = dalloc(m, &m->sdpa_part, m->sdpa_part_bytes / sizeof(float) + 64))) return bail(rc);
+    }
+    e = cudaHostAlloc((void**)&m->h_pinned, 4 * kMaxRows * sizeof(int32_t) + 256, cudaHostAllocDefault);
+    if (e != cudaSuccess) { cuda_fail(e, "cudaHostAlloc"); return bail(LTHN_ERR_CUDA); }
+    *model = m;
+    return LTHN_OK;
+}
+
+int32_t lthn_model_set_comm(void* model, void* comm) {
+    clear_error();
+    LTHN_REQUIRE(model != nullptr, "lthn_model_set_comm: model is NULL");
+    ((Model*)model)->comm = comm;
+    return LTHN_OK;
+}
+
+int32_t lthn_model_upload_linear(void* model, int32_t layer, int32_t role, const void* packed, const void* scales,
+                                 const void* biases, int64_t N, int64_t K) {
+    clear_error();
+    Model* m = (Model*)model;
+    LTHN_REQUIRE(m && packed && scales && biases, "lthn_model_upload_linear: NULL argument");
+    if (layer < 0) {  // token embedding / tied lm_head, replicated
+        LTHN_REQUIRE(N == m->c.vocab && K == m->c.hidden, "lthn_model_upload_linear: embedding must be [vocab, hidden]");
+        int32_t rc = upload_shard(m, &m->embed, 0, (const uint8_t*)packed, (const uint8_t*)scales, (const uint8_t*)biases, K, 0, N, 0, K);
+        if (rc == LTHN_OK) m->have_embed = true;
+        return rc;
+    }
+    LTHN_REQUIRE(layer < m->c.layers, "lthn_model_upload_linear: layer out of range");
+    ShardPlan p;
+    int32_t rc = shard_plan(m, layer, role, &p);
+    if (rc) return rc;
+    LTHN_REQUIRE(N == p.Nfull && K == p.Kfull, "lthn_model_upload_linear: tensor shape does not match the model configuration");
+    rc = upload_shard(m, p.dst, p.dst_row0, (const uint8_t*)packed, (const uint8_t*)scales, (const uint8_t*)biases, K, p.r0, p.n, p.c0, p.k);
+    if (rc == LTHN_OK) m->layers[layer].have[role] = true;
+    return rc;
+}
+
+int32_t lthn_model_upload_norm(void* model, int32_t layer, int32_t role, const float* w, int64_t n) {
+    clear_error();
+    Model* m = (Model*)model;
+    LTHN_REQUIRE(m && w, "lthn_model_upload_norm: NULL argument");
+    float* dst;
+    int64_t want;
+    if (layer < 0) { dst = m->final_norm; want = m->c.hidden; }
+    else {
+        LTHN_REQUIRE(layer < m->c.layers && role >= 0 && role < NORM_COUNT, "lthn_model_upload_norm: layer/role out of range");
+        dst = m->layers[layer].norm[role];
+        want = role >= NORM_Q ? m->c.head_dim : m->c.hidden;
+    }
+    LTHN_REQUIRE(n == want, "lthn_model_upload_norm: wrong length");
+    LTHN_CUDA_TRY(cudaMemcpy(dst, w, (size_t)n * 4, cudaMemcpyHostToDevice));
+    return LTHN_OK;
+}
+
+// Fills every tensor with the seeded synthetic source: linear (layer, role) is the
+// [N,K] tensor of stream seed*1000003 + (layer+1)*16 + role (embedding: layer = -1,
+// role 0) quantised with the reference rule; norm weights are 1 (zero stored weight
+// under the gemma (1+w) fold, model/norm_bias.go).
+int32_t lthn_model_synthesize(void* model, uint64_t seed, float sigma) {
+    clear_error();
+    Model* m = (Model*)model;
+    LTHN_REQUIRE(m != nullptr, "lthn_model_synthesize: model is NULL");
+    int32_t rc;
+    const auto& c = m->c;
+    for (int li = 0; li < c.layers; li++) {
+        for (int role = 0; role < ROLE_COUNT; role++) {
+            ShardPlan p;
+            if ((rc = shard_plan(m, li, role, &p))) return rc;
+            Linear* d = p.dst;
+            rc = lthn_synth_affine_weight_shard(m->stream, tensor_seed(seed, li, role), sigma, p.n, p.k, p.r0, p.c0, p.Kfull,
+                                                d->wq + p.dst_row0 * (d->K / 8), d->s + p.dst_row0 * (d->K / 64),
+                                                d->b + p.dst_row0 * (d->K / 64));
+            if (rc) return rc;
+            m->layers[li].have[role] = true;
+        }
+    }
+    if ((rc = lthn_synth_affine_weight_shard(m->stream, tensor_seed(seed, -1, 0), sigma, c.vocab, c.hidden, 0, 0, c.hidden,
+                                             m->embed.wq, m->embed.s, m->embed.b))) return rc;
+    m->have_embed = true;
+    std::vector<float> ones((size_t)std::max(c.hidden, c.head_dim), 1.0f);
+    for (int li = 0; li < c.layers; li++)
+        for (int i = 0; i < NORM_COUNT; i++)
+            LTHN_CUDA_TRY(cudaMemcpyAsync(m->layers[li].norm[i], ones.data(), (size_t)(i >= NORM_Q ? c.head_dim : c.hidden) * 4,
+                                          cudaMemcpyHostToDevice, m->stream));
+    LTHN_CUDA_TRY(cudaMemcpyAsync(m->final_norm, ones.data(), (size_t)c.hidden * 4, cudaMemcpyHostToDevice, m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LTHN_OK;
+}
+
+int32_t lthn_model_finalize(void* model) {
+    clear_error();
+    Model* m = (Model*)model;
+    LTHN_REQUIRE(m != nullptr, "lthn_model_finalize: model is NULL");
+    LTHN_REQUIRE(m->have_embed, "lthn_model_finalize: the embedding table was not uploaded");
+    for (int li = 0; li < m->c.layers; li++)
+        for (int r = 0; r < ROLE_COUNT; r++)
+            LTHN_REQUIRE(m->layers[li].have[r], "lthn_model_finalize: a layer is missing a linear");
+    if (m->c.tp_size > 1) LTHN_REQUIRE(m->comm != nullptr, "lthn_model_finalize: tensor-parallel model needs a communicator");
+    m->finalized = true;
+    return LTHN_OK;
+}
+
+int32_t lthn_model_weight_bytes(void* model, uint64_t* bytes) {
+    clear_error();
+    LTHN_REQUIRE(model && bytes, "lthn_model_weight_bytes: NULL argument");
+    *bytes = ((Model*)model)->weight_bytes;
+    return LTHN_OK;
+}
+
+int32_t lthn_model_destroy(void* model) {
+    clear_error();
+    Model* m = (Model*)model;
+    if (!m) return LTHN_OK;
+    cudaStreamSynchronize(m->stream);
+    for (void* p : m->allocs) cudaFree(p);
+    if (m->h_pinned) cudaFreeHost(m->h_pinned);
+    cudaStreamDestroy(m->stream);
+    delete m;
+    return LTHN_OK;
+}
+
+// ---- session ------------------------------------------------------------------------------------
+int32_t lthn_session_open(void* model, void** session) {
+    clear_error();
+    Model* m = (Model*)model;
+    LTHN_REQUIRE(m && session, "lthn_session_open: NULL argument");
+    LTHN_REQUIRE(m->finalized, "lthn_session_open: model is not finalized");
+    const int id = lane_acquire(m);
+    if (id < 0) return fail(LTHN_ERR_STATE, "lthn_session_open: every KV lane is in use");
+    Session* s = new Session{m, Lane{}};
+    s->lane.id = id;
+    *session = s;
+    return LTHN_OK;
+}
+
+int32_t lthn_session_close(void* session) {
+    clear_error();
+    Session* s = (Session*)session;
+    if (!s) return LTHN_OK;
+    lane_release(s->m, s->lane.id);
+    delete s;
+    return LTHN_OK;
+}
+
+int32_t lthn_session_prefill(void* session, const int32_t* ids, int32_t n) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && ids, "lthn_session_prefill: NULL argument");
+    s->lane.pos = 0;
+    s->lane.pending = -1;
+    s->lane.have_next = false;
+    return feed_lane(s->m, &s->lane, ids, n);
+}
+
+int32_t lthn_session_append(void* session, const int32_t* ids, int32_t n) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && ids, "lthn_session_append: NULL argument");
+    if (s->lane.pending >= 0) {  // a generated token that was yielded but not yet fed comes first
+        const int32_t t = s->lane.pending;
+        int32_t rc = feed_lane(s->m, &s->lane, &t, 1);
+        if (rc) return rc;
+    }
+    return feed_lane(s->m, &s->lane, ids, n);
+}
+
+int32_t lthn_session_pos(void* session) {
+    Session* s = (Session*)session;
+    return s ? s->lane.pos : -1;
+}
+
+// GenerateFromCacheEach (engine/session.go:49): up to max_new greedy tokens; eos_id < 0
+// leaves the stop decision to the caller. The last produced token is not fed.
+int32_t lthn_session_decode_greedy(void* session, int32_t max_new, int32_t eos_id, int32_t* out_ids, int32_t* n_out) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && out_ids && n_out, "lthn_session_decode_greedy: NULL argument");
+    *n_out = 0;
+    LTHN_REQUIRE(s->lane.pos > 0, "lthn_session_decode_greedy: the session has no prefilled state");
+    for (int i = 0; i < max_new; i++) {
+        if (!s->lane.have_next) {
+            LTHN_REQUIRE(s->lane.pending >= 0, "lthn_session_decode_greedy: no pending token");
+            if (s->lane.pos + 1 > s->m->c.max_len) return fail(LTHN_ERR_STATE, "lthn_session_decode_greedy: context length exceeded");
+            const int32_t t = s->lane.pending;
+            int32_t rc = feed_lane(s->m, &s->lane, &t, 1);
+            if (rc) return rc;
+        }
+        const int32_t tok = s->lane.next_tok;
+        out_ids[(*n_out)++] = tok;
+        s->lane.pending = tok;
+        s->lane.have_next = false;
+        if (eos_id >= 0 && tok == eos_id) break;
+    }
+    return LTHN_OK;
+}
+
+// Logits of the last fed token (vocab floats; local shard under tensor parallelism) for
+// host-side sampling (engine/session.go:51 GenerateSampledFromCacheEach).
+int32_t lthn_session_logits(void* session, float* logits_host, int64_t n) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && logits_host, "lthn_session_logits: NULL argument");
+    LTHN_REQUIRE(s->lane.have_next, "lthn_session_logits: no forward has been run since the last token was taken");
+    LTHN_REQUIRE(n == s->m->V_l, "lthn_session_logits: buffer must hold the (local) vocabulary");
+    std::lock_guard<std::mutex> lk(s->m->mu);
+    LTHN_CUDA_TRY(cudaMemcpyAsync(logits_host, s->m->logits, (size_t)n * 4, cudaMemcpyDeviceToHost, s->m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(s->m->stream));
+    return LTHN_OK;
+}
+
+// KV read-out of one layer (bf16 [pos, kv_heads_local*head_dim]) - the payload of a
+// kv.Snapshot layer (kv/snapshot.go:98-143); which: 0 keys, 1 values.
+int32_t lthn_session_kv_export(void* session, int32_t layer, int32_t which, void* out_host, size_t out_bytes) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && out_host, "lthn_session_kv_export: NULL argument");
+    Model* m = s->m;
+    LTHN_REQUIRE(layer >= 0 && layer < m->c.layers, "lthn_session_kv_export: layer out of range");
+    const size_t bytes = (size_t)s->lane.pos * m->KR_l * 2;
+    LTHN_REQUIRE(out_bytes == bytes, "lthn_session_kv_export: buffer must hold pos*kv_heads*head_dim bf16 values");
+    const uint16_t* src = (which ? m->vcache : m->kcache) + (int64_t)s->lane.id * m->lane_stride + (int64_t)layer * m->layer_stride;
+    std::lock_guard<std::mutex> lk(m->mu);
+    LTHN_CUDA_TRY(cudaMemcpyAsync(out_host, src, bytes, cudaMemcpyDeviceToHost, m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LTHN_OK;
+}
+
+int32_t lthn_session_kv_import(void* session, int32_t layer, int32_t which, const void* in_host, int32_t tokens) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && in_host, "lthn_session_kv_import: NULL argument");
+    Model* m = s->m;
+    LTHN_REQUIRE(layer >= 0 && layer < m->c.layers && tokens >= 0 && tokens <= m->c.max_len, "lthn_session_kv_import: out of range");
+    uint16_t* dst = (which ? m->vcache : m->kcache) + (int64_t)s->lane.id * m->lane_stride + (int64_t)layer * m->layer_stride;
+    std::lock_guard<std::mutex> lk(m->mu);
+    LTHN_CUDA_TRY(cudaMemcpyAsync(dst, in_host, (size_t)tokens * m->KR_l * 2, cudaMemcpyHostToDevice, m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LTHN_OK;
+}
+
+// After importing every layer: declares the restored length and the token to continue from.
+int32_t lthn_session_set_state(void* session, int32_t pos, int32_t pending_token) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s != nullptr, "lthn_session_set_state: NULL argument");
+    LTHN_REQUIRE(pos >= 0 && pos <= s->m->c.max_len, "lthn_session_set_state: pos out of range");
+    s->lane.pos = pos;
+    s->lane.pending = pending_token;
+    s->lane.have_next = false;
+    return LTHN_OK;
+}
+
+// ---- lane set -------------------------------------------------------------------------------------
+int32_t lthn_laneset_open(void* model, int32_t max_lanes, void** set) {
+    clear_error();
+    Model* m = (Model*)model;
+    LTHN_REQUIRE(m && set, "lthn_laneset_open: NULL argument");
+    LTHN_REQUIRE(m->finalized, "lthn_laneset_open: model is not finalized");
+    if (max_lanes <= 0) max_lanes = std::min(8, m->c.max_lanes);  // cf. hip_lane_set.go:14-16 default of 8
+    LTHN_REQUIRE(max_lanes <= kMaxRows, "lthn_laneset_open: at most 32 lanes per set");
+    LaneSet* ls = new LaneSet{m, max_lanes, {}, 1, 0};
+    *set = ls;
+    return LTHN_OK;
+}
+
+int32_t lthn_laneset_prepare(void* set, const int32_t* ids, int32_t n, int32_t max_new, const int32_t* stop,
+                             int32_t n_stop, int32_t* lane_handle) {
+    clear_error();
+    LaneSet* ls = (LaneSet*)set;
+    LTHN_REQUIRE(ls && ids && lane_handle, "lthn_laneset_prepare: NULL argument");
+    LTHN_REQUIRE((int)ls->lanes.size() < ls->max_lanes, "lthn_laneset_prepare: the lane set is at MaxLanes");
+    const int id = lane_acquire(ls->m);
+    if (id < 0) return fail(LTHN_ERR_STATE, "lthn_laneset_prepare: every KV lane of the model is in use");
+    Lane ln;
+    ln.id = id;
+    ln.max_new = max_new;
+    if (stop && n_stop > 0) ln.stop.assign(stop, stop + n_stop);
+    int32_t rc = feed_lane(ls->m, &ln, ids, n);
+    if (rc) { lane_release(ls->m, id); return rc; }
+    ln.handle = ls->next_handle++;
+    ls->lanes.push_back(ln);
+    *lane_handle = ln.handle;
+    return LTHN_OK;
+}
+
+// One batched forward for every active, non-terminal lane (inference.LaneSet.Step).
+// flags: bit0 HasToken, bit1 Terminal. The first Step after Prepare yields the token the
+// prefill already determined; every Step runs exactly one forward when any lane has a
+// pending token to feed.
+int32_t lthn_laneset_step(void* set, int32_t* lane_handles, int32_t* tokens, int32_t* flags, int32_t* n) {
+    clear_error();
+    LaneSet* ls = (LaneSet*)set;
+    LTHN_REQUIRE(ls && lane_handles && tokens && flags && n, "lthn_laneset_step: NULL argument");
+    Model* m = ls->m;
+    *n = 0;
+    std::vector<Lane*> feed;
+    for (auto& ln : ls->lanes)
+        if (!ln.terminal && !ln.have_next && ln.pending >= 0) feed.push_back(&ln);
+    if (!feed.empty()) {
+        std::lock_guard<std::mutex> lk(m->mu);
+        const int rows = (int)feed.size();
+        int32_t* hp = m->h_pinned;
+        int max_ctx = 1;
+        for (int r = 0; r < rows; r++) {
+            if (feed[r]->pos + 1 > m->c.max_len) return fail(LTHN_ERR_STATE, "lthn_laneset_step: context length exceeded");
+            hp[r] = feed[r]->pending; hp[kMaxRows + r] = feed[r]->pos; hp[2 * kMaxRows + r] = feed[r]->id;
+            max_ctx = std::max(max_ctx, feed[r]->pos + 1);
+        }
+        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_ids, hp, rows * 4, cudaMemcpyHostToDevice, m->stream));
+        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_pos, hp + kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
+        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_lane, hp + 2 * kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
+        int32_t rc = forward_full(m, rows, max_ctx, true, 0);
+        if (rc) return rc;
+        LTHN_CUDA_TRY(cudaMemcpyAsync(hp + 3 * kMaxRows, m->d_next, rows * 4, cudaMemcpyDeviceToHost, m->stream));
+        LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+        for (int r = 0; r < rows; r++) {
+            feed[r]->pos += 1;
+            feed[r]->next_tok = hp[3 * kMaxRows + r];
+            feed[r]->have_next = true;
+            feed[r]->pending = -1;
+        }
+        ls->forwards++;
+        if ((rc = check_device_status(m->stream))) return rc;
+    }
+    for (auto& ln : ls->lanes) {
+        if (ln.terminal || !ln.have_next) continue;
+        const int32_t tok = ln.next_tok;
+        ln.have_next = false;
+        ln.pending = tok;
+        ln.produced++;
+        bool stop = ln.max_new > 0 && ln.produced >= ln.max_new;
+        for (int32_t st : ln.stop) stop = stop || st == tok;
+        ln.terminal = stop;
+        lane_handles[*n] = ln.handle;
+        tokens[*n] = tok;
+        flags[*n] = 1 | (stop ? 2 : 0);
+        (*n)++;
+    }
+    return LTHN_OK;
+}
+
+int32_t lthn_laneset_retire(void* set, int32_t lane_handle) {
+    clear_error();
+    LaneSet* ls = (LaneSet*)set;
+    LTHN_REQUIRE(ls != nullptr, "lthn_laneset_retire: NULL argument");
+    for (size_t i = 0; i < ls->lanes.size(); i++)
+        if (ls->lanes[i].handle == lane_handle) {
+            lane_release(ls->m, ls->lanes[i].id);
+            ls->lanes.erase(ls->lanes.begin() + i);
+            return LTHN_OK;
+        }
+    return fail(LTHN_ERR_INVALID, "lthn_laneset_retire: unknown lane");
+}
+
+int32_t lthn_laneset_active(void* set) { return set ? (int32_t)((LaneSet*)set)->lanes.size() : 0; }
+uint64_t lthn_laneset_batch_forward_count(void* set) { return set ? ((LaneSet*)set)->forwards : 0; }
+
+int32_t lthn_laneset_close(void* set) {
+    clear_error();
+    LaneSet* ls = (LaneSet*)set;
+    if (!ls) return LTHN_OK;
+    for (auto& ln : ls->lanes) lane_release(ls->m, ln.id);
+    delete ls;
+    return LTHN_OK;
+}
+
+// ---- standalone fused kernels (for callers that drive the layer loop themselves) -----------------
+int32_t lthn_rmsnorm(void* stream, const float* x, const float* w, float* out, int32_t rows, int32_t width, float eps) {
+    clear_error();
+    if (rows == 0) return LTHN_OK;
+    LTHN_REQUIRE(x && w && out && rows > 0 && width > 0 && eps >= 0, "lthn_rmsnorm: bad arguments");
+    return launch_rmsnorm((cudaStream_t)stream, x, nullptr, w, nullptr, out, rows, width, eps, 0);
+}
+
+int32_t lthn_rmsnorm_residual(void* stream, const float* a, float* h, const float* w_post, const float* w_next,
+                              float* out, int32_t rows, int32_t width, float eps) {
+    clear_error();
+    if (rows == 0) return LTHN_OK;
+    LTHN_REQUIRE(a && h && w_post && w_next && out && rows > 0 && width > 0 && eps >= 0, "lthn_rmsnorm_residual: bad arguments");
+    return launch_rmsnorm((cudaStream_t)stream, a, h, w_post, w_next, out, rows, width, eps, 1);
+}
+
+int32_t lthn_rmsnorm_rope(void* stream, const float* x, const float* w, const int32_t* positions, float* out,
+                          int32_t rows, int32_t heads, int32_t head_dim, int32_t rotary_dim, float eps, float rope_base,
+                          int32_t bf16_seams) {
+    clear_error();
+    if (rows == 0 || heads == 0) return LTHN_OK;
+    LTHN_REQUIRE(x && w && positions && out && rows > 0 && heads > 0, "lthn_rmsnorm_rope: bad arguments");
+    LTHN_REQUIRE(head_dim > 0 && head_dim <= 512 && head_dim % 64 == 0, "lthn_rmsnorm_rope: head_dim must be a multiple of 64 up to 512");
+    if (rotary_dim == 0) rotary_dim = head_dim;
+    LTHN_REQUIRE(rotary_dim > 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0, "lthn_rmsnorm_rope: rotary_dim must be even and at most head_dim");
+    LTHN_REQUIRE(rope_base > 0 && eps >= 0, "lthn_rmsnorm_rope: base must be positive and eps non-negative");
+    return launch_rmsnorm_rope((cudaStream_t)stream, x, w, positions, out, rows, heads, head_dim, rotary_dim, eps, rope_base, bf16_seams);
+}
+
+int32_t lthn_sdpa_decode(void* stream, const float* q, const uint16_t* kcache, const uint16_t* vcache,
+                         const int32_t* row_pos, const int32_t* row_lane, float* out, int32_t rows, int32_t q_heads,
+                         int32_t kv_heads, int32_t head_dim, int64_t lane_stride, float scale, int32_t max_ctx) {
+    clear_error();
+    if (rows == 0) return LTHN_OK;
+    LTHN_REQUIRE(q && kcache && vcache && row_pos && row_lane && out, "lthn_sdpa_decode: NULL pointer");
+    LTHN_REQUIRE(rows > 0 && q_heads > 0 && kv_heads > 0 && max_ctx > 0, "lthn_sdpa_decode: dimensions must be positive");
+    if (scale <= 0) scale = (float)(1.0 / std::sqrt((double)head_dim));
+    int chunk_len = 0;
+    const int nchunks = sdpa_chunking(max_ctx, rows, kv_heads, &chunk_len);
+    void* part = nullptr;
+    if (nchunks > 1) {
+        int32_t rc = scratch_get(sdpa_scratch_bytes(rows, q_heads, head_dim, nchunks), &part, 2);
+        if (rc) return rc;
+    }
+    SdpaArgs a{q, kcache, vcache, row_pos, row_lane, out, (float*)part, lane_stride, q_heads, kv_heads, nchunks, chunk_len, scale};
+    return launch_sdpa_decode((cudaStream_t)stream, a, rows, head_dim);
+}
+
+int32_t lthn_argmax(void* stream, const float* logits, int32_t rows, int32_t vocab, int32_t* out_idx) {
+    clear_error();
+    if (rows == 0) return LTHN_OK;
+    LTHN_REQUIRE(logits && out_idx && rows > 0 && vocab > 0, "lthn_argmax: bad arguments");
+    void* scratch = nullptr;
+    int32_t rc = scratch_get((size_t)rows * ARGMAX_BLOCKS * 8, &scratch, 3);
+    if (rc) return rc;
+    float* pv = (float*)scratch;
+    int* pi = (int*)(pv + (size_t)rows * ARGMAX_BLOCKS);
+    return launch_argmax((cudaStream_t)stream, logits, rows, vocab, pv, pi, out_idx, nullptr, 0);
+}
+
+}  // extern "C"

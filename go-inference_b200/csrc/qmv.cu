@@ -32,6 +32,7 @@
 // A second, general kernel (one warp per row, SIMT) serves the other widths of
 // the format (2/8 bit, group 32/128) that the reference's fixtures exercise.
 #include "common.cuh"
+#include "qmv.hpp"
 
 #include <algorithm>
 
@@ -466,7 +467,39 @@ int32_t qmv_split_for(int M, int x_dtype) {
 }
 
 // test / tuning hooks (not part of the public header)
-static int g_force_rt = 0, g_force_warps = 0;
+static int g_force_rt = 0, g_force_warps = 0, g_force_kernel = 0;
+
+// Routes one call: 1-2 activation rows go to the dp4a kernel, 3..32 rows to the
+// tensor-core kernel (f32 activations are first split into bf16 columns).
+int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
+    const int fuse = c.wq2 ? 1 : 0;
+    // Measured on B200: the dp4a kernel wins for long rows and few of them (K >= 8192,
+    // N <= 4096); elsewhere the tensor-core kernel is currently faster.
+    const bool prefer_dp4a = g_force_kernel == 1 || (g_force_kernel == 0 && c.K >= 8192 && c.N <= 4096);
+    if (prefer_dp4a && c.M <= 2) {
+        Dp4aPlan plan;
+        const bool aligned = (((uintptr_t)c.wq | (uintptr_t)c.x | (uintptr_t)(c.wq2 ? c.wq2 : c.wq)) & 15) == 0;
+        if (aligned && !(fuse && c.M == 2) && dp4a_plan(c.N, c.K, c.M, fuse, g_force_rt, &plan))
+            return dp4a_launch(s, c, plan);
+    }
+    QmvArgs a{};
+    a.wq = c.wq; a.scales = c.scales; a.biases = c.biases;
+    a.wq2 = c.wq2; a.scales2 = c.scales2; a.biases2 = c.biases2;
+    a.y = c.y; a.N = c.N; a.K = c.K; a.M = c.M; a.y_dtype = c.y_dtype; a.y_split = 0;
+    a.split = qmv_split_for(c.M, c.x_dtype);
+    a.C = c.M * a.split;
+    if (c.x_dtype == LTHN_DTYPE_BF16) {
+        a.x = (const uint16_t*)c.x;
+    } else {
+        void* scratch = nullptr;
+        int32_t rc = scratch_get((size_t)a.C * c.K * 2, &scratch);
+        if (rc) return rc;
+        rc = split_f32_launch(s, (const float*)c.x, c.M, c.K, a.split, (uint16_t*)scratch);
+        if (rc) return rc;
+        a.x = (const uint16_t*)scratch;
+    }
+    return qmv_launch(s, a, fuse, g_force_kernel == 1 ? 0 : g_force_rt, g_force_warps);
+}
 
 }  // namespace lthn
 
@@ -474,24 +507,26 @@ using namespace lthn;
 
 extern "C" {
 
-// Tuning hook used by the benchmark sweep: 0 restores the built-in heuristic.
+// Tuning hooks used by the benchmark sweep and the tests: 0 restores the defaults.
+// rt: rows per thread (dp4a) / 16-row tiles per CTA (tensor-core kernel); kernel: 1 dp4a, 2 tensor-core.
 void lthn_debug_qmv_force_config(int32_t rt, int32_t nwarps) {
     g_force_rt = rt;
     g_force_warps = nwarps;
 }
+void lthn_debug_qmv_force_kernel(int32_t kernel) { g_force_kernel = kernel; }
 
-int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M, const uint32_t* packed,
-                        const uint16_t* scales, const uint16_t* biases, int64_t N, int64_t K, int32_t gs,
-                        int32_t bits, void* y, int32_t y_dtype) {
-    clear_error();
-    cudaStream_t s = (cudaStream_t)stream;
+static int32_t qmv_validate(const void* x, int32_t x_dtype, int32_t M, const void* packed, const void* scales,
+                            const void* biases, int64_t N, int64_t K, int32_t gs, int32_t bits, void* y,
+                            int32_t y_dtype, cudaStream_t s, bool* done) {
+    *done = false;
     LTHN_REQUIRE(M >= 0 && N >= 0 && K >= 0, "affine_qmv: negative dimension");
-    if (M == 0 || N == 0) return LTHN_OK;
+    if (M == 0 || N == 0) { *done = true; return LTHN_OK; }
     LTHN_REQUIRE(y != nullptr, "affine_qmv: y is NULL");
     LTHN_REQUIRE(x_dtype == LTHN_DTYPE_F32 || x_dtype == LTHN_DTYPE_BF16, "affine_qmv: bad x dtype");
     LTHN_REQUIRE(y_dtype == LTHN_DTYPE_F32 || y_dtype == LTHN_DTYPE_BF16, "affine_qmv: bad y dtype");
     if (K == 0) {
         LTHN_CUDA_TRY(cudaMemsetAsync(y, 0, (size_t)M * N * (y_dtype == LTHN_DTYPE_BF16 ? 2 : 4), s));
+        *done = true;
         return LTHN_OK;
     }
     LTHN_REQUIRE(M <= 32, "affine_qmv: M must be at most 32 (use affine_qmm for prefill)");
@@ -499,7 +534,17 @@ int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M,
     LTHN_REQUIRE(gs == 32 || gs == 64 || gs == 128, "affine_qmv: group size must be 32, 64 or 128");
     LTHN_REQUIRE(K % gs == 0, "affine_qmv: group size must divide K");
     LTHN_REQUIRE(x && packed && scales && biases, "affine_qmv: NULL pointer");
+    return LTHN_OK;
+}
 
+int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M, const uint32_t* packed,
+                        const uint16_t* scales, const uint16_t* biases, int64_t N, int64_t K, int32_t gs,
+                        int32_t bits, void* y, int32_t y_dtype) {
+    clear_error();
+    cudaStream_t s = (cudaStream_t)stream;
+    bool done = false;
+    int32_t rc = qmv_validate(x, x_dtype, M, packed, scales, biases, N, K, gs, bits, y, y_dtype, s, &done);
+    if (rc || done) return rc;
     const bool fast = bits == 4 && gs == 64 && ((uintptr_t)packed & 7) == 0 && ((uintptr_t)x & 15) == 0;
     if (!fast) {
         const int wpb = 8;
@@ -511,23 +556,25 @@ int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M,
         LTHN_CUDA_TRY(cudaGetLastError());
         return LTHN_OK;
     }
+    QmvCall c{packed, scales, biases, nullptr, nullptr, nullptr, x, x_dtype, y, y_dtype, N, K, M};
+    return qmv_dispatch(s, c);
+}
 
-    QmvArgs a{};
-    a.wq = packed; a.scales = scales; a.biases = biases; a.y = y;
-    a.N = N; a.K = K; a.M = M; a.y_dtype = y_dtype; a.y_split = 0;
-    a.split = qmv_split_for(M, x_dtype);
-    a.C = M * a.split;
-    if (x_dtype == LTHN_DTYPE_BF16) {
-        a.x = (const uint16_t*)x;
-    } else {
-        void* scratch = nullptr;
-        int32_t rc = scratch_get((size_t)a.C * K * 2, &scratch);
-        if (rc) return rc;
-        rc = split_f32_launch(s, (const float*)x, M, K, a.split, (uint16_t*)scratch);
-        if (rc) return rc;
-        a.x = (const uint16_t*)scratch;
-    }
-    return qmv_launch(s, a, 0, g_force_rt, g_force_warps);
+int32_t lthn_affine_qmv_geglu(void* stream, const void* x, int32_t x_dtype, int32_t M, const uint32_t* gate_packed,
+                              const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
+                              const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, void* y,
+                              int32_t y_dtype) {
+    clear_error();
+    cudaStream_t s = (cudaStream_t)stream;
+    bool done = false;
+    int32_t rc = qmv_validate(x, x_dtype, M, gate_packed, gate_scales, gate_biases, N, K, 64, 4, y, y_dtype, s, &done);
+    if (rc || done) return rc;
+    LTHN_REQUIRE(up_packed && up_scales && up_biases, "affine_qmv_geglu: NULL pointer");
+    LTHN_REQUIRE(K > 0 && K % 64 == 0, "affine_qmv_geglu: K must be a positive multiple of 64");
+    LTHN_REQUIRE((((uintptr_t)gate_packed | (uintptr_t)up_packed) & 7) == 0 && ((uintptr_t)x & 15) == 0,
+                 "affine_qmv_geglu: packed weights must be 8-byte and x 16-byte aligned");
+    QmvCall c{gate_packed, gate_scales, gate_biases, up_packed, up_scales, up_biases, x, x_dtype, y, y_dtype, N, K, M};
+    return qmv_dispatch(s, c);
 }
 
 int32_t lthn_affine_qmv_host(const void* x, size_t x_len, const void* packed, size_t packed_len,

@@ -1,0 +1,28 @@
+// qmv.hpp — internal interface between the affine_qmv entry points and its kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lthn {
+
+// One decode matvec: y[M,N] = x[M,K] * dequant(W)^T, optionally fused with a second
+// weight set as gelu_tanh(W x) * (W2 x). 4-bit codes, group 64.
+struct QmvCall {
+    const uint32_t* wq; const uint16_t* scales; const uint16_t* biases;
+    const uint32_t* wq2; const uint16_t* scales2; const uint16_t* biases2;  // NULL unless fused GeGLU
+    const void* x; int x_dtype;
+    void* y; int y_dtype;
+    int64_t N, K;
+    int M;
+};
+
+struct Dp4aPlan { int J, R, T_row, S, threads, nblocks; size_t smem; };
+
+// dp4a kernel (1-2 activation rows). dp4a_plan returns false when the shape is not served.
+bool dp4a_plan(int64_t N, int64_t K, int M, int fuse, int force_r, Dp4aPlan* p);
+int32_t dp4a_launch(cudaStream_t st, const QmvCall& c, const Dp4aPlan& p);
+
+// Dispatcher used by the C entry points and by the decoder engine.
+int32_t qmv_dispatch(cudaStream_t st, const QmvCall& c);
+
+}  // namespace lthn

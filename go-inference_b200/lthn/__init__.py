@@ -30,6 +30,13 @@ class DeviceInfo(C.Structure):
                 ("sm_count", C.c_int32), ("compute_major", C.c_int32), ("compute_minor", C.c_int32)]
 
 
+class ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab",
+                                         "group_size", "bits", "max_len", "max_lanes")] + \
+               [(n, C.c_float) for n in ("eps", "rope_base", "attn_scale", "embed_scale")] + \
+               [("tp_rank", C.c_int32), ("tp_size", C.c_int32)]
+
+
 _lib = None
 
 
@@ -85,7 +92,42 @@ class _Sig:
     lthn_synth_affine_weight = (i32, [vp, u64, f32, i64, i64, i32, i32, i32, vp, vp, vp])
     lthn_affine_qmv = (i32, [vp, vp, i32, i32, vp, vp, vp, i64, i64, i32, i32, vp, i32])
     lthn_affine_qmv_host = (i32, [vp, sz, vp, sz, vp, sz, vp, sz, i64, i64, i32, i32, vp, sz])
+    lthn_affine_qmv_geglu = (i32, [vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, i64, i64, vp, i32])
+    lthn_rmsnorm = (i32, [vp, vp, vp, vp, i32, i32, f32])
+    lthn_rmsnorm_residual = (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32])
+    lthn_rmsnorm_rope = (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, f32, i32])
+    lthn_sdpa_decode = (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, f32, i32])
+    lthn_argmax = (i32, [vp, vp, i32, i32, vp])
+    lthn_model_create = (i32, [C.POINTER(ModelConfig), pvp])
+    lthn_model_upload_linear = (i32, [vp, i32, i32, vp, vp, vp, i64, i64])
+    lthn_model_upload_norm = (i32, [vp, i32, i32, vp, i64])
+    lthn_model_synthesize = (i32, [vp, u64, f32])
+    lthn_model_finalize = (i32, [vp])
+    lthn_model_weight_bytes = (i32, [vp, C.POINTER(u64)])
+    lthn_model_destroy = (i32, [vp])
+    lthn_tp_unique_id = (i32, [vp])
+    lthn_tp_init = (i32, [i32, i32, vp, pvp])
+    lthn_tp_destroy = (i32, [vp])
+    lthn_model_set_comm = (i32, [vp, vp])
+    lthn_session_open = (i32, [vp, pvp])
+    lthn_session_prefill = (i32, [vp, vp, i32])
+    lthn_session_append = (i32, [vp, vp, i32])
+    lthn_session_pos = (i32, [vp])
+    lthn_session_decode_greedy = (i32, [vp, i32, i32, vp, C.POINTER(i32)])
+    lthn_session_logits = (i32, [vp, vp, i64])
+    lthn_session_kv_export = (i32, [vp, i32, i32, vp, sz])
+    lthn_session_kv_import = (i32, [vp, i32, i32, vp, i32])
+    lthn_session_set_state = (i32, [vp, i32, i32])
+    lthn_session_close = (i32, [vp])
+    lthn_laneset_open = (i32, [vp, i32, pvp])
+    lthn_laneset_prepare = (i32, [vp, vp, i32, i32, vp, i32, C.POINTER(i32)])
+    lthn_laneset_step = (i32, [vp, vp, vp, vp, C.POINTER(i32)])
+    lthn_laneset_retire = (i32, [vp, i32])
+    lthn_laneset_active = (i32, [vp])
+    lthn_laneset_batch_forward_count = (u64, [vp])
+    lthn_laneset_close = (i32, [vp])
     lthn_debug_qmv_force_config = (None, [i32, i32])
+    lthn_debug_qmv_force_kernel = (None, [i32])
 
 
 def check(rc: int):
@@ -304,6 +346,11 @@ def qmv(x: Buf, x_dtype, M, q: QuantWeight, y: Buf, y_dtype, stream=None):
                                 q.gs, q.bits, y.ptr, y_dtype))
 
 
+def qmv_geglu(x: Buf, x_dtype, M, gate: QuantWeight, up: QuantWeight, y: Buf, y_dtype, stream=None):
+    check(lib().lthn_affine_qmv_geglu(_s(stream), x.ptr, x_dtype, M, gate.packed.ptr, gate.scales.ptr, gate.biases.ptr,
+                                      up.packed.ptr, up.scales.ptr, up.biases.ptr, gate.N, gate.K, y.ptr, y_dtype))
+
+
 def qmv_host(x_bf16: np.ndarray, packed: np.ndarray, scales: np.ndarray, biases: np.ndarray, out_dim, in_dim, gs,
              bits) -> np.ndarray:
     """model.QuantMatVec.MatVec over host byte buffers (bf16 in, bf16 out)."""
@@ -315,3 +362,164 @@ def qmv_host(x_bf16: np.ndarray, packed: np.ndarray, scales: np.ndarray, biases:
     check(lib().lthn_affine_qmv_host(xb.ctypes.data, xb.size, pb.ctypes.data, pb.size, sb.ctypes.data, sb.size,
                                      bb.ctypes.data, bb.size, out_dim, in_dim, gs, bits, y.ctypes.data, y.nbytes))
     return y
+
+
+# ------------------------------------------------------------------ engine ----
+
+ROLE = dict(q=0, k=1, v=2, o=3, gate=4, up=5, down=6)
+NORM = dict(input=0, post_attn=1, pre_ff=2, post_ff=3, q_norm=4, k_norm=5)
+
+
+def make_config(layers, hidden, q_heads, kv_heads, head_dim, ffn, vocab, max_len, max_lanes=1, eps=1e-6,
+                rope_base=10000.0, tp_rank=0, tp_size=1) -> ModelConfig:
+    return ModelConfig(layers=layers, hidden=hidden, q_heads=q_heads, kv_heads=kv_heads, head_dim=head_dim, ffn=ffn,
+                       vocab=vocab, group_size=64, bits=4, max_len=max_len, max_lanes=max_lanes, eps=eps,
+                       rope_base=rope_base, attn_scale=0.0, embed_scale=0.0, tp_rank=tp_rank, tp_size=tp_size)
+
+
+class Model:
+    """engine.TokenModel: resident weights + KV lanes (lthn_model_*)."""
+
+    def __init__(self, cfg: ModelConfig):
+        self.cfg = cfg
+        h = C.c_void_p()
+        check(lib().lthn_model_create(C.byref(cfg), C.byref(h)))
+        self.h = h
+
+    def upload_linear(self, layer, role, packed, scales, biases):
+        pk = np.ascontiguousarray(packed, dtype=np.uint32)
+        sc = np.ascontiguousarray(scales, dtype=np.uint16)
+        bi = np.ascontiguousarray(biases, dtype=np.uint16)
+        r = ROLE[role] if isinstance(role, str) else role
+        check(lib().lthn_model_upload_linear(self.h, layer, r, pk.ctypes.data, sc.ctypes.data, bi.ctypes.data,
+                                             pk.shape[0], pk.shape[1] * 8))
+
+    def upload_norm(self, layer, role, w):
+        a = np.ascontiguousarray(w, dtype=np.float32)
+        r = NORM[role] if isinstance(role, str) else role
+        check(lib().lthn_model_upload_norm(self.h, layer, r, a.ctypes.data, a.size))
+
+    def synthesize(self, seed, sigma=0.02):
+        check(lib().lthn_model_synthesize(self.h, seed, sigma))
+
+    def set_comm(self, comm):
+        check(lib().lthn_model_set_comm(self.h, comm))
+
+    def finalize(self):
+        check(lib().lthn_model_finalize(self.h))
+
+    @property
+    def weight_bytes(self):
+        v = C.c_uint64()
+        check(lib().lthn_model_weight_bytes(self.h, C.byref(v)))
+        return int(v.value)
+
+    def open_session(self) -> "Session":
+        return Session(self)
+
+    def open_lane_set(self, max_lanes=0) -> "LaneSet":
+        return LaneSet(self, max_lanes)
+
+    def close(self):
+        if self.h:
+            lib().lthn_model_destroy(self.h)
+            self.h = None
+
+
+class Session:
+    """engine.Session over one KV lane."""
+
+    def __init__(self, model: Model):
+        self.model = model
+        h = C.c_void_p()
+        check(lib().lthn_session_open(model.h, C.byref(h)))
+        self.h = h
+
+    def prefill(self, ids):
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        check(lib().lthn_session_prefill(self.h, a.ctypes.data, a.size))
+
+    def append(self, ids):
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        check(lib().lthn_session_append(self.h, a.ctypes.data, a.size))
+
+    @property
+    def pos(self):
+        return int(lib().lthn_session_pos(self.h))
+
+    def decode_greedy(self, max_new, eos_id=-1):
+        out = np.empty(max(max_new, 1), dtype=np.int32)
+        n = C.c_int32()
+        check(lib().lthn_session_decode_greedy(self.h, max_new, eos_id, out.ctypes.data, C.byref(n)))
+        return out[:n.value].copy()
+
+    def logits(self):
+        n = self.model.cfg.vocab // max(1, self.model.cfg.tp_size)
+        out = np.empty(n, dtype=np.float32)
+        check(lib().lthn_session_logits(self.h, out.ctypes.data, n))
+        return out
+
+    def kv_export(self, layer, which):
+        kr = self.model.cfg.kv_heads // max(1, self.model.cfg.tp_size) * self.model.cfg.head_dim
+        out = np.empty((self.pos, kr), dtype=np.uint16)
+        check(lib().lthn_session_kv_export(self.h, layer, which, out.ctypes.data, out.nbytes))
+        return out
+
+    def kv_import(self, layer, which, data):
+        a = np.ascontiguousarray(data, dtype=np.uint16)
+        check(lib().lthn_session_kv_import(self.h, layer, which, a.ctypes.data, a.shape[0]))
+
+    def set_state(self, pos, pending):
+        check(lib().lthn_session_set_state(self.h, pos, pending))
+
+    def close(self):
+        if self.h:
+            lib().lthn_session_close(self.h)
+            self.h = None
+
+
+class LaneSet:
+    """inference.LaneSet: K lanes advanced by one batched forward per step."""
+
+    def __init__(self, model: Model, max_lanes=0):
+        self.model = model
+        h = C.c_void_p()
+        check(lib().lthn_laneset_open(model.h, max_lanes, C.byref(h)))
+        self.h = h
+
+    def prepare(self, ids, max_new=0, stop=()):
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        st = np.ascontiguousarray(stop, dtype=np.int32)
+        lane = C.c_int32()
+        check(lib().lthn_laneset_prepare(self.h, a.ctypes.data, a.size, max_new, st.ctypes.data if st.size else None,
+                                         st.size, C.byref(lane)))
+        return int(lane.value)
+
+    def step(self):
+        lanes = np.empty(32, dtype=np.int32)
+        toks = np.empty(32, dtype=np.int32)
+        flags = np.empty(32, dtype=np.int32)
+        n = C.c_int32()
+        check(lib().lthn_laneset_step(self.h, lanes.ctypes.data, toks.ctypes.data, flags.ctypes.data, C.byref(n)))
+        return [(int(lanes[i]), int(toks[i]), bool(flags[i] & 1), bool(flags[i] & 2)) for i in range(n.value)]
+
+    def retire(self, lane):
+        check(lib().lthn_laneset_retire(self.h, lane))
+
+    @property
+    def active(self):
+        return int(lib().lthn_laneset_active(self.h))
+
+    @property
+    def batch_forward_count(self):
+        return int(lib().lthn_laneset_batch_forward_count(self.h))
+
+    def close(self):
+        if self.h:
+            lib().lthn_laneset_close(self.h)
+            self.h = None
+
+
+def tensor_seed(seed, layer, role):
+    """Seed of the synthetic tensor lthn_model_synthesize draws for (layer, role); layer -1 = embedding."""
+    return (seed * 1000003 + (layer + 1) * 16 + role) & 0xFFFFFFFFFFFFFFFF

@@ -123,6 +123,17 @@ int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M,
                         const uint16_t* scales, const uint16_t* biases, int64_t N, int64_t K, int32_t gs,
                         int32_t bits, void* y, int32_t y_dtype);
 
+/* Fused GeGLU pair: y[M,N] = gelu_tanh(x * dequant(Wgate)^T) * (x * dequant(Wup)^T),
+ * both weights [N,K], 4 bit, group 64; gate and up rows are streamed together so
+ * the activation is read once and the intermediate never reaches memory.
+ * Replaces rocm_mlx_q4_gelu_tanh_multiply (engine/hip/kernels/quant/
+ * affine_gelu_tanh.hipinc:3-180); gelu as hipGemma4Q4HostGELU
+ * (engine/hip/hip_gemma4_q4_layer.go:3582-3597). */
+int32_t lthn_affine_qmv_geglu(void* stream, const void* x, int32_t x_dtype, int32_t M, const uint32_t* gate_packed,
+                              const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
+                              const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, void* y,
+                              int32_t y_dtype);
+
 /* model.QuantMatVec.MatVec (model/quant.go:35-38): bf16 LE bytes in HOST memory
  * in, bf16 LE bytes out; lengths are validated like the reference
  * (enginetest/quant_reference.go:79-104). Copies in, launches, copies out,
@@ -130,6 +141,119 @@ int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M,
 int32_t lthn_affine_qmv_host(const void* x, size_t x_len, const void* packed, size_t packed_len,
                              const void* scales, size_t scales_len, const void* biases, size_t biases_len,
                              int64_t out_dim, int64_t in_dim, int32_t gs, int32_t bits, void* y, size_t y_len);
+
+/* ---- fused decoder-step kernels ----------------------------------------------
+ * For callers that drive the layer loop themselves; the engine below uses the same
+ * kernels. All pointers are device pointers, activations f32.
+ *
+ * lthn_rmsnorm: hipReferenceRMSNorm (engine/hip/hip_transformer_reference.go:171-194),
+ * rocm_rms_norm (engine/hip/kernels/norms/rms_norm.hipinc:28). out[r,:] = x/rms*w. */
+int32_t lthn_rmsnorm(void* stream, const float* x, const float* w, float* out, int32_t rows, int32_t width, float eps);
+/* h += norm(a, w_post); out = norm(h, w_next): the fused post-norm + residual + next
+ * pre-norm of rocm_rms_norm_residual_add_norm (rms_norm.hipinc) / lthn_rmsnorm_residual_bf16. */
+int32_t lthn_rmsnorm_residual(void* stream, const float* a, float* h, const float* w_post, const float* w_next,
+                              float* out, int32_t rows, int32_t width, float eps);
+/* lthn_rmsnorm_rope: per-head RMSNorm then NeoX RoPE over the first rotary_dim dims
+ * (pairs (i, i+head_dim/2)), one position per row; head_dim <= 512.
+ * Replaces lthn_qknorm_rope_bf16(_rows) (engine/metal/kernels/norms/
+ * lthn_qknorm_rope_bf16.metal:28-206) and rocm_rms_norm_rope_heads (rms_norm.hipinc:
+ * 306-377); CPU refs hip_transformer_reference.go:171-194,242-289. x/out [rows,
+ * heads*head_dim] f32. bf16_seams=1 reproduces the Metal kernel's bf16 rounding points
+ * (bf16(w*bf16(x*inv)), bf16 output values). */
+int32_t lthn_rmsnorm_rope(void* stream, const float* x, const float* w, const int32_t* positions, float* out,
+                          int32_t rows, int32_t heads, int32_t head_dim, int32_t rotary_dim, float eps, float rope_base,
+                          int32_t bf16_seams);
+/* lthn_sdpa_decode: softmax(q K^T scale) V for `rows` single-token queries over the
+ * seq-major bf16 KV cache (cache row p of lane l at l*lane_stride + p*kv_heads*head_dim;
+ * engine/metal/decode_step.go:20-26), keys 0..row_pos[r] inclusive, GQA head map
+ * kv = q_head / (q_heads/kv_heads). Split-KV with a log-sum-exp merge; partials live in a
+ * library-owned scratch arena. Replaces sdpa_vector(_2pass) routing (engine/metal/sdpa.go:
+ * 520-545) and rocm_attention_heads(_chunked) (engine/hip/kernels/attention/); CPU ref
+ * hipReferenceSingleHeadAttentionWithScale (hip_transformer_reference.go:295-330).
+ * q/out [rows, q_heads*head_dim] f32; scale<=0 means 1/sqrt(head_dim); max_ctx bounds
+ * row_pos+1 and sizes the grid. head_dim in {64,128,256,512}. */
+int32_t lthn_sdpa_decode(void* stream, const float* q, const uint16_t* kcache, const uint16_t* vcache,
+                         const int32_t* row_pos, const int32_t* row_lane, float* out, int32_t rows, int32_t q_heads,
+                         int32_t kv_heads, int32_t head_dim, int64_t lane_stride, float scale, int32_t max_ctx);
+/* Greedy pick per row: strict '>', lowest index wins ties (model.Greedy, model/sample.go:
+ * 29-50; hipReferenceGreedySample). logits [rows, vocab] f32. */
+int32_t lthn_argmax(void* stream, const float* logits, int32_t rows, int32_t vocab, int32_t* out_idx);
+
+/* ---- the engine: engine.TokenModel / engine.Session / inference.LaneSet ----------
+ * A Gemma-style decoder (gemma3 block: four norms, per-head Q/K norm, full NeoX
+ * rotary, GeGLU, tied embedding/lm_head; model/arch/google/gemma3/gemma3.go:141-161)
+ * over resident MLX-affine 4-bit weights and a seq-major bf16 KV cache. */
+typedef struct {
+    int32_t layers, hidden, q_heads, kv_heads, head_dim, ffn, vocab;
+    int32_t group_size, bits;   /* 64, 4 */
+    int32_t max_len;            /* KV positions per lane (LoadConfig.ContextLen, options.go:281-288) */
+    int32_t max_lanes;          /* resident KV lanes: sessions + lane-set lanes (LoadConfig.ParallelSlots) */
+    float eps;                  /* 0 -> 1e-6 */
+    float rope_base;            /* 0 -> 10000 */
+    float attn_scale;           /* 0 -> 1/sqrt(head_dim) (model.Arch.AttnScale) */
+    float embed_scale;          /* 0 -> bf16(sqrt(hidden)) (model.Arch.EmbedScale) */
+    int32_t tp_rank, tp_size;   /* tensor-parallel rank / degree (tp_size 0 or 1: single GPU) */
+} lthn_model_config;
+
+enum { LTHN_ROLE_Q = 0, LTHN_ROLE_K, LTHN_ROLE_V, LTHN_ROLE_O, LTHN_ROLE_GATE, LTHN_ROLE_UP, LTHN_ROLE_DOWN };
+enum { LTHN_NORM_INPUT = 0, LTHN_NORM_POST_ATTN, LTHN_NORM_PRE_FF, LTHN_NORM_POST_FF, LTHN_NORM_Q, LTHN_NORM_K };
+
+/* Backend.LoadModel's device half (inference.go:394; engine/hip/inference_model.go:402):
+ * create, upload every tensor of model.LoadedModel (model/loaded.go:157-175), finalize.
+ * Uploads take HOST pointers to the full (unsharded) MLX-affine tensors - exactly the
+ * byte slices of model.Linear (model/linear.go:21-29) - and copy what this rank owns;
+ * nothing is retained, so the safetensors mmap may be closed afterwards. layer < 0 names
+ * the token embedding (tied lm_head) / the final norm. Norm weights are the effective
+ * weights (the gemma "(1+w)" fold of model/norm_bias.go:22-49 applied by the loader). */
+int32_t lthn_model_create(const lthn_model_config* cfg, void** model);
+int32_t lthn_model_upload_linear(void* model, int32_t layer, int32_t role, const void* packed, const void* scales,
+                                 const void* biases, int64_t N, int64_t K);
+int32_t lthn_model_upload_norm(void* model, int32_t layer, int32_t role, const float* w, int64_t n);
+/* Synthetic weights (benchmarks, tests): tensor (layer, role) is the seeded synthetic
+ * [N,K] tensor of stream seed*1000003 + (layer+1)*16 + role quantised with the
+ * reference rule; norms are 1. No counterpart in the reference. */
+int32_t lthn_model_synthesize(void* model, uint64_t seed, float sigma);
+int32_t lthn_model_finalize(void* model);
+int32_t lthn_model_weight_bytes(void* model, uint64_t* bytes);
+int32_t lthn_model_destroy(void* model);   /* TokenModel.Close (engine/model.go:30) */
+
+/* Tensor parallelism over NCCL (the reference is single-device; new functionality).
+ * Rank 0 makes the id, the host distributes its 128 bytes, every rank joins. */
+int32_t lthn_tp_unique_id(void* out128);
+int32_t lthn_tp_init(int32_t rank, int32_t world, const void* id128, void** comm);
+int32_t lthn_tp_destroy(void* comm);
+int32_t lthn_model_set_comm(void* model, void* comm);
+
+/* engine.Session (engine/session.go:40-61). One session is driven by one host thread at
+ * a time (SessionHandle.mu, engine/session.go:105-117); sessions of one model serialise
+ * on the model's stream. */
+int32_t lthn_session_open(void* model, void** session);                      /* TokenModel.OpenEngineSession */
+int32_t lthn_session_prefill(void* session, const int32_t* ids, int32_t n); /* PrefillTokens: replaces state */
+int32_t lthn_session_append(void* session, const int32_t* ids, int32_t n);  /* AppendTokens */
+int32_t lthn_session_pos(void* session);                                     /* Pos */
+/* GenerateFromCacheEach: up to max_new greedy tokens into out_ids; eos_id < 0 leaves the
+ * stop decision to the caller (the Go side calls this in small chunks so `yield` can
+ * stop it). The last produced token stays pending and is fed by the next call. */
+int32_t lthn_session_decode_greedy(void* session, int32_t max_new, int32_t eos_id, int32_t* out_ids, int32_t* n_out);
+/* Logits after the last fed token, for GenerateSampledFromCacheEach's host-side sampler. */
+int32_t lthn_session_logits(void* session, float* logits_host, int64_t n);
+/* CaptureKVWithOptions / RestoreFromKV payloads (kv/snapshot.go:98-143): one layer's keys
+ * (which=0) or values (which=1) as bf16 [pos, kv_heads_local*head_dim]. */
+int32_t lthn_session_kv_export(void* session, int32_t layer, int32_t which, void* out_host, size_t out_bytes);
+int32_t lthn_session_kv_import(void* session, int32_t layer, int32_t which, const void* in_host, int32_t tokens);
+int32_t lthn_session_set_state(void* session, int32_t pos, int32_t pending_token);
+int32_t lthn_session_close(void* session);
+
+/* inference.LaneSet (batch_step.go:97-119) behind engine.LaneSetOpener
+ * (engine/batch_step.go:21-23). Single host thread per set. */
+int32_t lthn_laneset_open(void* model, int32_t max_lanes, void** set);
+int32_t lthn_laneset_prepare(void* set, const int32_t* ids, int32_t n, int32_t max_new, const int32_t* stop,
+                             int32_t n_stop, int32_t* lane_handle);           /* lane ids start at 1 */
+int32_t lthn_laneset_step(void* set, int32_t* lane_handles, int32_t* tokens, int32_t* flags, int32_t* n);
+int32_t lthn_laneset_retire(void* set, int32_t lane_handle);
+int32_t lthn_laneset_active(void* set);
+uint64_t lthn_laneset_batch_forward_count(void* set);
+int32_t lthn_laneset_close(void* set);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,209 @@
+"""Whole-decoder parity: the device engine (Session / LaneSet through the C ABI)
+against the CPU reference decoder on identical weights and token ids."""
+import numpy as np
+import pytest
+
+from decoder_util import GEMMA_2B, MID, SMALL, build_device, build_oracle, synth_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def logits_close(got, want, tol=2e-4):
+    rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    return float(np.max(np.abs(got - want))) <= tol * rms
+
+
+@pytest.mark.parametrize("cfg", [SMALL, MID], ids=["small", "mid"])
+def test_prefill_and_decode_match_oracle(oracle, cfg):
+    import lthn
+    w, norms = synth_weights(oracle, lthn, cfg, seed=3, random_norms=True)
+    max_len = 160
+    od = build_oracle(oracle, cfg, w, norms, max_len)
+    m = build_device(lthn, cfg, w, norms, max_len)
+    ids = np.random.default_rng(0).integers(0, cfg["vocab"], 70).astype(np.int32)
+    want_logits = od.forward(ids)
+    s = m.open_session()
+    s.prefill(ids)
+    assert s.pos == 70
+    assert logits_close(s.logits(), want_logits)
+    # the KV cache holds the same bf16 values the oracle stored (RoPE and norms are exact)
+    for layer in range(cfg["layers"]):
+        for which in (0, 1):
+            dev_kv = oracle.bf16_to_f32(s.kv_export(layer, which))
+            ref_kv = od.read_kv(layer, which)
+            mism = np.mean(dev_kv != ref_kv)
+            assert mism < 2e-3, (layer, which, mism)           # rare 1-ulp flips from f32 summation order
+            assert np.max(np.abs(dev_kv - ref_kv)) <= 2.0 ** -7 * np.max(np.abs(ref_kv))
+    want_tokens, margin = od.generate(want_logits, 48)
+    got_tokens = s.decode_greedy(48)
+    first_bad = next((i for i in range(48) if got_tokens[i] != want_tokens[i]), None)
+    assert first_bad is None, (first_bad, float(margin[first_bad]))
+    assert s.pos == 70 + 47  # the last token is yielded, not fed (engine/session.go:49 semantics)
+    s.close()
+    m.close()
+
+
+def test_append_equals_prefill_and_chunked_decode(oracle):
+    """AppendTokens extends the cache without replaying the prefix; decoding in small
+    chunks (how a yield callback is served) gives the same tokens as one call."""
+    import lthn
+    cfg = SMALL
+    w, norms = synth_weights(oracle, lthn, cfg, seed=5, random_norms=True)
+    m = build_device(lthn, cfg, w, norms, 128, max_lanes=2)
+    ids = np.random.default_rng(1).integers(0, cfg["vocab"], 50).astype(np.int32)
+    a, b = m.open_session(), m.open_session()
+    a.prefill(ids)
+    b.prefill(ids[:33])
+    b.append(ids[33:])
+    assert np.array_equal(a.logits(), b.logits())
+    one = a.decode_greedy(24)
+    chunks = np.concatenate([b.decode_greedy(5), b.decode_greedy(1), b.decode_greedy(18)])
+    assert np.array_equal(one, chunks)
+    # eos stops the loop at the token that matches
+    c = one[3]
+    a.prefill(ids)
+    stopped = a.decode_greedy(24, eos_id=int(c))
+    assert stopped[-1] == c and len(stopped) == list(one).index(c) + 1
+    a.close(); b.close(); m.close()
+
+
+def test_kv_export_import_round_trip(oracle):
+    """CaptureKV / RestoreFromKV payloads: a session restored from another's exported
+    cache continues with the same tokens (enginetest/session.go:54-155 restore subtest)."""
+    import lthn
+    cfg = SMALL
+    w, norms = synth_weights(oracle, lthn, cfg, seed=6)
+    m = build_device(lthn, cfg, w, norms, 96, max_lanes=2)
+    ids = np.random.default_rng(2).integers(0, cfg["vocab"], 40).astype(np.int32)
+    a = m.open_session()
+    a.prefill(ids)
+    first = a.decode_greedy(1)
+    b = m.open_session()
+    for layer in range(cfg["layers"]):
+        for which in (0, 1):
+            b.kv_import(layer, which, a.kv_export(layer, which))
+    b.set_state(a.pos, int(first[0]))
+    assert np.array_equal(a.decode_greedy(12), b.decode_greedy(12))
+    a.close(); b.close(); m.close()
+
+
+def test_lane_set_matches_single_sessions(oracle):
+    """inference.LaneSet: K lanes with ragged prompts advanced by ONE batched forward per
+    Step produce the tokens each prompt gets alone; BatchForwardCount advances by one per
+    Step (batch_step.go:112-116)."""
+    import lthn
+    cfg = MID
+    w, norms = synth_weights(oracle, lthn, cfg, seed=7, random_norms=True)
+    K = 5
+    m = build_device(lthn, cfg, w, norms, 128, max_lanes=K + 1)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg["vocab"], n).astype(np.int32) for n in (9, 33, 64, 1, 40)]
+    solo = []
+    s = m.open_session()
+    for p in prompts:
+        s.prefill(p)
+        solo.append(s.decode_greedy(10))
+    s.close()
+    ls = m.open_lane_set(K)
+    handles = [ls.prepare(p, max_new=10) for p in prompts]
+    assert handles == [1, 2, 3, 4, 5] and ls.active == K
+    got = {h: [] for h in handles}
+    steps = 0
+    while True:
+        before = ls.batch_forward_count
+        res = ls.step()
+        if not res:
+            break
+        steps += 1
+        if steps > 1:
+            assert ls.batch_forward_count == before + 1
+        for h, tok, has, term in res:
+            assert has
+            got[h].append(tok)
+            assert term == (len(got[h]) == 10)
+    assert steps == 10
+    for h, want in zip(handles, solo):
+        assert got[h] == want.tolist(), h
+    # ragged admission between steps and retirement
+    ls.retire(handles[0])
+    assert ls.active == K - 1
+    h6 = ls.prepare(prompts[0], max_new=3)
+    assert h6 == 6
+    out = []
+    for _ in range(3):
+        out += [t for (h, t, _, _) in ls.step() if h == h6]
+    assert out == solo[0][:3].tolist()
+    with pytest.raises(lthn.LthnError):
+        ls.retire(99)
+    ls.close(); m.close()
+
+
+def test_synthesize_equals_uploaded_synthetic_weights(oracle):
+    """lthn_model_synthesize draws the same tensors the oracle's generator does."""
+    import lthn
+    cfg = SMALL
+    w, norms = synth_weights(oracle, lthn, cfg, seed=11)
+    up = build_device(lthn, cfg, w, norms, 64)
+    mc = lthn.make_config(cfg["layers"], cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"],
+                          cfg["vocab"], 64, 1)
+    sy = lthn.Model(mc)
+    sy.synthesize(11, 0.02)
+    sy.finalize()
+    ids = np.arange(20, dtype=np.int32) * 7 % cfg["vocab"]
+    a, b = up.open_session(), sy.open_session()
+    a.prefill(ids); b.prefill(ids)
+    assert np.array_equal(a.logits(), b.logits())
+    a.close(); b.close(); up.close(); sy.close()
+
+
+def test_rejected_arguments(oracle):
+    import lthn
+    with pytest.raises(lthn.LthnError):
+        lthn.Model(lthn.make_config(1, 100, 2, 2, 64, 128, 64, 16))       # hidden not a multiple of 64
+    with pytest.raises(lthn.LthnError):
+        lthn.Model(lthn.make_config(1, 128, 3, 2, 64, 128, 64, 16))       # q_heads % kv_heads
+    m = lthn.Model(lthn.make_config(1, 128, 2, 2, 64, 128, 64, 16))
+    with pytest.raises(lthn.LthnError):
+        m.open_session()                                                  # not finalized
+    with pytest.raises(lthn.LthnError):
+        m.finalize()                                                      # nothing uploaded
+    m.synthesize(1)
+    m.finalize()
+    s = m.open_session()
+    with pytest.raises(lthn.LthnError):
+        m.open_session()                                                  # only one KV lane
+    with pytest.raises(lthn.LthnError):
+        s.prefill(np.array([64], dtype=np.int32))                         # id outside the vocabulary
+    with pytest.raises(lthn.LthnError):
+        s.prefill(np.zeros(17, dtype=np.int32))                           # longer than max_len
+    with pytest.raises(lthn.LthnError):
+        s.decode_greedy(4)                                                # nothing prefilled
+    s.close(); m.close()
+
+
+def test_gemma_2b_shape_greedy_256_tokens(oracle):
+    """BASELINE configs[3]: the 26-layer decoder (hidden 2304, 8/4 heads x 256, GeGLU 9216,
+    vocab 262144), synthetic N(0,0.02) 4-bit weights, a 1024-token random prompt, then 256
+    greedy tokens: the device must reproduce the CPU reference's token sequence. Where the
+    sequences part, the reference's top-1/top-2 logit margin at that step is reported."""
+    import lthn
+    cfg = GEMMA_2B
+    seed, prompt_len, new = 0, 1024, 256
+    mc = lthn.make_config(cfg["layers"], cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"],
+                          cfg["vocab"], prompt_len + new, 1)
+    m = lthn.Model(mc)
+    m.synthesize(seed, 0.02)
+    m.finalize()
+    ids = np.random.default_rng(0).integers(0, cfg["vocab"], prompt_len).astype(np.int32)
+    s = m.open_session()
+    s.prefill(ids)
+    got = s.decode_greedy(new)
+    got_logits_first = None
+    w, norms = synth_weights(oracle, lthn, cfg, seed)
+    od = build_oracle(oracle, cfg, w, norms, prompt_len + new)
+    want_logits = od.forward(ids)
+    want, margin = od.generate(want_logits, new)
+    first_bad = next((i for i in range(new) if got[i] != want[i]), None)
+    assert first_bad is None, f"diverged at step {first_bad}: reference margin {float(margin[first_bad]):.3e}, " \
+                              f"min margin so far {float(margin[:first_bad + 1].min()):.3e}"
+    s.close(); m.close()

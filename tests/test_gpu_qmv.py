@@ -99,24 +99,77 @@ def test_ragged_and_tiny_shapes(oracle, N, K):
 
 
 def test_every_kernel_configuration_agrees(oracle):
-    """All (rows-per-CTA, warps) configurations compute the same function."""
+    """Both kernels and all their launch configurations compute the same function."""
     import lthn
     N, K = 2304, 2304
     p, s, b = make_weight(oracle, N, K, seed=1)
     q = lthn.QuantWeight.from_host(p, s, b)
+    L = lthn.lib()
     try:
-        for M in (1, 8, 16):
+        for M in (1, 2, 8, 16):
             xf, xb = make_x(oracle, M, K, seed=9)
             want = oracle.matnt_quant_host(xf, p, s, b, threads=8)
+            L.lthn_debug_qmv_force_kernel(2)  # tensor-core kernel: tiles per CTA x warps
             for rt in (1, 2, 4):
                 for nw in (1, 2, 4, 8):
-                    if M > 8 and rt == 4 and M > 16:
-                        continue
-                    lthn.lib().lthn_debug_qmv_force_config(rt, nw)
+                    L.lthn_debug_qmv_force_config(rt, nw)
                     got = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.F32)
-                    assert rms_err(got, want) <= F32_TOL_RMS, (M, rt, nw)
+                    assert rms_err(got, want) <= F32_TOL_RMS, ("mma", M, rt, nw)
+            if M <= 2:
+                L.lthn_debug_qmv_force_kernel(1)  # dp4a kernel: rows per thread
+                for r in (1, 2, 4):
+                    L.lthn_debug_qmv_force_config(r, 0)
+                    got = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.F32)
+                    assert rms_err(got, want) <= F32_TOL_RMS, ("dp4a", M, r)
     finally:
-        lthn.lib().lthn_debug_qmv_force_config(0, 0)
+        L.lthn_debug_qmv_force_config(0, 0)
+        L.lthn_debug_qmv_force_kernel(0)
+
+
+@pytest.mark.parametrize("K,N", [(2304, 512), (9216, 300), (5376, 256), (21504, 64), (4096, 128), (2048, 1000),
+                                 (128, 40), (64, 5), (1536, 77)])
+@pytest.mark.parametrize("M", [1, 2])
+def test_dp4a_kernel_shapes(oracle, K, N, M):
+    """The batch-1/2 kernel over every K of the BASELINE models (2304, 9216, 5376, 21504,
+    4096, 2048) and awkward small ones, f32 and bf16 activations."""
+    import lthn
+    p, s, b = make_weight(oracle, N, K, seed=K + N)
+    q = lthn.QuantWeight.from_host(p, s, b)
+    xf, xb = make_x(oracle, M, K, seed=M + K)
+    want = oracle.matnt_quant_host(xf, p, s, b, threads=8)
+    lthn.lib().lthn_debug_qmv_force_kernel(1)
+    try:
+        got = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.F32)
+        assert rms_err(got, want) <= F32_TOL_RMS
+        x32 = np.random.default_rng(K).standard_normal((M, K)).astype(np.float32)
+        x32[0, :64] *= 1e-4   # a group of tiny activations next to ordinary ones
+        if K >= 128:
+            x32[0, 64:128] = 0.0  # an all-zero group
+        want32 = oracle.matnt_quant_host(x32, p, s, b, threads=8)
+        got32 = run_qmv(lthn, x32, lthn.F32, M, q, lthn.F32)
+        assert rms_err(got32, want32) <= F32_TOL_RMS
+    finally:
+        lthn.lib().lthn_debug_qmv_force_kernel(0)
+
+
+@pytest.mark.parametrize("M", [1, 2, 5])
+@pytest.mark.parametrize("N,K", [(9216, 2304), (1000, 2304), (21504 // 8, 5376)])
+def test_fused_geglu(oracle, M, N, K):
+    """gate/up pair with the GeGLU epilogue against gelu_tanh(gate)*up from the oracle
+    (hip_gemma4_q4_layer.go:3582-3597 GELU, oracle_test.go:939-948 multiply)."""
+    import lthn
+    gp = make_weight(oracle, N, K, seed=1)
+    up = make_weight(oracle, N, K, seed=2)
+    x = np.random.default_rng(3).standard_normal((M, K)).astype(np.float32)
+    g = oracle.matnt_quant_host(x, *gp, threads=8)
+    u = oracle.matnt_quant_host(x, *up, threads=8)
+    want = oracle.gelu_tanh(g) * u
+    gq, uq = lthn.QuantWeight.from_host(*gp), lthn.QuantWeight.from_host(*up)
+    y = lthn.Buf(M * N * 4)
+    lthn.qmv_geglu(lthn.Buf.from_array(x), lthn.F32, M, gq, uq, y, lthn.F32)
+    lthn.sync()
+    got = y.download(np.float32, (M, N))
+    assert rms_err(got, want) <= 1e-4
 
 
 def test_negative_scales_and_literal_variant(oracle):
