@@ -224,8 +224,11 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
     float mx[GQ];
 #pragma unroll
     for (int h = 0; h < GQ; h++) mx[h] = -INFINITY;
-    for (int p = pg; p < len; p += 16) {
-        const uint16_t* kr = kbase + (int64_t)(p0 + p) * KR;
+    // every lane runs the same number of iterations: the shuffles below name the whole warp
+    for (int pb = 0; pb < len; pb += 16) {
+        const int p = pb + pg;
+        const bool valid = p < len;
+        const uint16_t* kr = kbase + (int64_t)(p0 + (valid ? p : 0)) * KR;
         float dot[GQ];
 #pragma unroll
         for (int h = 0; h < GQ; h++) dot[h] = 0.f;
@@ -246,8 +249,10 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
             d += __shfl_xor_sync(0xffffffffu, d, 1);
             d += __shfl_xor_sync(0xffffffffu, d, 2);
             d += __shfl_xor_sync(0xffffffffu, d, 4);
-            if (l8 == 0) sc[h][p] = d;
-            mx[h] = fmaxf(mx[h], d);
+            if (valid) {
+                if (l8 == 0) sc[h][p] = d;
+                mx[h] = fmaxf(mx[h], d);
+            }
         }
     }
 #pragma unroll
@@ -288,6 +293,7 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
         }
     }
     // combine the 4 position groups of a warp, then the 4 warps
+    __syncwarp();
 #pragma unroll
     for (int h = 0; h < GQ; h++) {
 #pragma unroll

@@ -126,6 +126,8 @@ class _Sig:
     lthn_laneset_active = (i32, [vp])
     lthn_laneset_batch_forward_count = (u64, [vp])
     lthn_laneset_close = (i32, [vp])
+    lthn_affine_qmm = (i32, [vp, vp, i32, vp, vp, vp, i64, i64, i32, i32, vp])
+    lthn_debug_qmm_force_tile = (None, [i32])
     lthn_debug_qmv_force_config = (None, [i32, i32])
     lthn_debug_qmv_force_kernel = (None, [i32])
 
@@ -344,6 +346,11 @@ def dequantize(q: QuantWeight, out: Buf, bf16=False, stream=None):
 def qmv(x: Buf, x_dtype, M, q: QuantWeight, y: Buf, y_dtype, stream=None):
     check(lib().lthn_affine_qmv(_s(stream), x.ptr, x_dtype, M, q.packed.ptr, q.scales.ptr, q.biases.ptr, q.N, q.K,
                                 q.gs, q.bits, y.ptr, y_dtype))
+
+
+def qmm(x: Buf, M, q: QuantWeight, y: Buf, stream=None):
+    check(lib().lthn_affine_qmm(_s(stream), x.ptr, M, q.packed.ptr, q.scales.ptr, q.biases.ptr, q.N, q.K, q.gs, q.bits,
+                                y.ptr))
 
 
 def qmv_geglu(x: Buf, x_dtype, M, gate: QuantWeight, up: QuantWeight, y: Buf, y_dtype, stream=None):

@@ -134,6 +134,18 @@ int32_t lthn_affine_qmv_geglu(void* stream, const void* x, int32_t x_dtype, int3
                               const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, void* y,
                               int32_t y_dtype);
 
+/* ---- affine_qmm: prefill-time quantized matmul on the tensor cores --------------
+ * y[M,N] (bf16) = x[M,K] (bf16) * dequant(W[N,K])^T, fp32 accumulation in TMEM.
+ * Replaces the Metal engine's affine_qmm_t dispatch (engine/metal/
+ * quant_seam_backend.go:84-110, attention.go:731-749) and HIP's
+ * rocm_mlx_q4_projection_batch* (engine/hip/kernels/quant/
+ * affine_projection_tuned.hipinc:166-559). Weights are dequantised to bf16
+ * (one rounding of scale*q+bias) tile by tile in shared memory and multiplied with
+ * tcgen05.mma. bits=4, gs=64, M>32 take the tensor-core kernel; other widths and
+ * small M are served by the decode kernels. x, y device pointers, 16-byte aligned. */
+int32_t lthn_affine_qmm(void* stream, const uint16_t* x, int32_t M, const uint32_t* packed, const uint16_t* scales,
+                        const uint16_t* biases, int64_t N, int64_t K, int32_t gs, int32_t bits, uint16_t* y);
+
 /* model.QuantMatVec.MatVec (model/quant.go:35-38): bf16 LE bytes in HOST memory
  * in, bf16 LE bytes out; lengths are validated like the reference
  * (enginetest/quant_reference.go:79-104). Copies in, launches, copies out,

@@ -6,8 +6,18 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
+_KEEP = []
+
+
 def dev(lthn, a):
-    return lthn.Buf.from_array(np.ascontiguousarray(a))
+    """Uploads an array; the buffer is kept alive for the rest of the test session
+    (a temporary would be freed before the asynchronous kernel reads it)."""
+    b = lthn.Buf.from_array(np.ascontiguousarray(a))
+    _KEEP.append(b)
+    if len(_KEEP) > 64:
+        lthn.sync()
+        del _KEEP[:32]
+    return b
 
 
 @pytest.mark.parametrize("rows,width", [(1, 2304), (5, 5376), (32, 256), (3, 64)])

@@ -1,0 +1,84 @@
+"""affine_qmm (tcgen05 tensor-core prefill matmul) parity through the C ABI.
+
+Oracle: lthn_o_qmm_bf16, the prefill contract of the reference's Metal engine (bf16
+activations, weights dequantised to bf16, f32-or-better accumulation, bf16 output), and
+the f32 reference on the unrounded dequantised weights with the north-star bound of 1e-2."""
+import numpy as np
+import pytest
+
+from gpu_util import bf16_close, make_weight, make_x, rms_err
+
+pytestmark = pytest.mark.gpu
+
+
+def run_qmm(lthn, xb, M, q):
+    x = lthn.Buf.from_array(xb)
+    y = lthn.Buf(M * q.N * 2)
+    lthn.qmm(x, M, q, y)
+    lthn.sync()
+    return y.download(np.uint16, (M, q.N))
+
+
+@pytest.mark.parametrize("tile", [128, 256])
+@pytest.mark.parametrize("M,N,K", [(64, 256, 128), (256, 256, 64), (100, 300, 192), (512, 1024, 2304), (33, 40, 512),
+                                   (700, 2304, 1024)])
+def test_qmm_matches_oracle(oracle, tile, M, N, K):
+    import lthn
+    p, s, b = make_weight(oracle, N, K, seed=N + K)
+    xf, xb = make_x(oracle, M, K, seed=M)
+    want16 = oracle.qmm_bf16(xb, p, s, b)
+    q = lthn.QuantWeight.from_host(p, s, b)
+    lthn.lib().lthn_debug_qmm_force_tile(tile)
+    try:
+        got16 = run_qmm(lthn, xb, M, q)
+    finally:
+        lthn.lib().lthn_debug_qmm_force_tile(0)
+    assert bf16_close(oracle, got16, oracle.bf16_to_f32(want16))
+    # north-star bound against the f32 reference on the dequantised (unrounded) weights
+    ref = oracle.matnt_quant_host(xf, p, s, b, threads=8)
+    assert rms_err(oracle.bf16_to_f32(got16), ref) <= 1e-2
+
+
+def test_qmm_baseline_shape_m512(oracle):
+    """BASELINE configs[2] smallest case at full size: M=512, (N,K)=(9216,2304)."""
+    import lthn
+    M, N, K = 512, 9216, 2304
+    p, s, b = make_weight(oracle, N, K, seed=1)
+    xf, xb = make_x(oracle, M, K, seed=2)
+    want16 = oracle.qmm_bf16(xb, p, s, b)
+    got16 = run_qmm(lthn, xb, M, lthn.QuantWeight.from_host(p, s, b))
+    assert bf16_close(oracle, got16, oracle.bf16_to_f32(want16))
+
+
+def test_qmm_large_shape_agrees_with_decode_kernel(oracle):
+    """BASELINE configs[2] large case (M=2048, N=21504, K=5376): too big for the CPU
+    oracle in seconds, so sampled token rows are checked against affine_qmv (itself
+    oracle-checked), which multiplies the unrounded weights: agreement within 1e-2."""
+    import lthn
+    M, N, K = 2048, 21504, 5376
+    q = lthn.QuantWeight.synth(9, 0.02, N, K)
+    xb = oracle.f32_to_bf16(np.random.default_rng(3).standard_normal((M, K)).astype(np.float32))
+    got = oracle.bf16_to_f32(run_qmm(lthn, xb, M, q))
+    rows = np.array([0, 1, 127, 128, 255, 256, 1000, 2047])
+    xs = lthn.Buf.from_array(xb[rows])
+    y = lthn.Buf(len(rows) * N * 4)
+    lthn.qmv(xs, lthn.BF16, len(rows), q, y, lthn.F32)
+    lthn.sync()
+    ref = y.download(np.float32, (len(rows), N))
+    assert rms_err(got[rows], ref) <= 1e-2
+    assert np.isfinite(got).all()
+
+
+def test_qmm_small_m_and_other_widths_route_to_decode_kernels(oracle):
+    import lthn
+    for (M, N, K, bits, gs) in [(5, 128, 256, 4, 64), (40, 64, 256, 8, 64), (3, 24, 256, 2, 128)]:
+        p, s, b = make_weight(oracle, N, K, seed=7, bits=bits, gs=gs)
+        xf, xb = make_x(oracle, M, K, seed=1)
+        want = oracle.matnt_quant_host(xf, p, s, b, gs=gs, bits=bits)
+        got16 = run_qmm(lthn, xb, M, lthn.QuantWeight.from_host(p, s, b, bits, gs))
+        assert bf16_close(oracle, got16, want)
+    q = lthn.QuantWeight.from_host(*make_weight(oracle, 64, 128, seed=1))
+    x, y = lthn.Buf(128 * 2), lthn.Buf(64 * 2)
+    lthn.qmm(x, 0, q, y)  # M == 0 is a no-op
+    with pytest.raises(lthn.LthnError):
+        lthn.check(lthn.lib().lthn_affine_qmm(None, x.ptr, 1, q.packed.ptr, q.scales.ptr, q.biases.ptr, 64, 128, 48, 4, y.ptr))

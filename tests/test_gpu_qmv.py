@@ -166,7 +166,8 @@ def test_fused_geglu(oracle, M, N, K):
     want = oracle.gelu_tanh(g) * u
     gq, uq = lthn.QuantWeight.from_host(*gp), lthn.QuantWeight.from_host(*up)
     y = lthn.Buf(M * N * 4)
-    lthn.qmv_geglu(lthn.Buf.from_array(x), lthn.F32, M, gq, uq, y, lthn.F32)
+    xd = lthn.Buf.from_array(x)
+    lthn.qmv_geglu(xd, lthn.F32, M, gq, uq, y, lthn.F32)
     lthn.sync()
     got = y.download(np.float32, (M, N))
     assert rms_err(got, want) <= 1e-4
