@@ -162,6 +162,60 @@ def run_sweep(lthn, st, peak, full):
     return out
 
 
+GEMMA_2B = dict(layers=26, hidden=2304, q_heads=8, kv_heads=4, head_dim=256, ffn=9216, vocab=262144)
+GEMMA_27B = dict(layers=62, hidden=5376, q_heads=32, kv_heads=16, head_dim=128, ffn=21504, vocab=262144)
+
+
+def decode_weight_bytes(cfg, tp=1):
+    D, H, F = cfg["head_dim"], cfg["hidden"], cfg["ffn"]
+    per_layer = (cfg["q_heads"] * D * H + 2 * cfg["kv_heads"] * D * H + H * cfg["q_heads"] * D + 3 * F * H) * 9 // 16
+    return (cfg["layers"] * per_layer + cfg["vocab"] * H * 9 // 16) // tp
+
+
+def run_decode(lthn, cfg, name, prompt_len, new_tokens, batch, peak, comm=None, rank=0, world=1):
+    """Greedy decode tokens/s of a synthetic Gemma-style 4-bit decoder (BASELINE configs[3]/[4]):
+    random prompt, then `new_tokens` greedy tokens at batch 1 (Session) and at `batch` lanes (LaneSet)."""
+    mc = lthn.make_config(cfg["layers"], cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"],
+                          cfg["vocab"], prompt_len + new_tokens, batch + 1, tp_rank=rank, tp_size=world)
+    m = lthn.Model(mc)
+    m.synthesize(0, 0.02)
+    if comm is not None:
+        m.set_comm(comm)
+    m.finalize()
+    rng = np.random.default_rng(0)
+    out = {"model": name, "prompt": prompt_len, "new_tokens": new_tokens, "tp": world,
+           "weight_bytes_per_token_per_gpu": decode_weight_bytes(cfg, world)}
+    s = m.open_session()
+    ids = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
+    s.prefill(ids[:64])          # warm-up (first use allocates scratch)
+    s.decode_greedy(4)
+    t0 = time.perf_counter()
+    s.prefill(ids)
+    t1 = time.perf_counter()
+    toks = s.decode_greedy(new_tokens)
+    t2 = time.perf_counter()
+    s.close()
+    tps1 = (len(toks) - 1) / (t2 - t1)   # new_tokens-1 forwards: the first token comes from the prefill
+    out["batch1"] = {"prefill_tok_s": round(prompt_len / (t1 - t0), 1), "decode_tok_s": round(tps1, 1),
+                     "ms_per_token": round(1e3 / tps1, 4),
+                     "frac_of_measured_hbm": round(tps1 * out["weight_bytes_per_token_per_gpu"] / 1e9 / peak, 4)}
+    if batch > 1:
+        ls = m.open_lane_set(batch)
+        for b in range(batch):
+            ls.prepare(np.random.default_rng(b).integers(0, cfg["vocab"], prompt_len).astype(np.int32), max_new=new_tokens)
+        ls.step()
+        t0 = time.perf_counter()
+        n = 0
+        for _ in range(new_tokens - 1):
+            n += len(ls.step())
+        t1 = time.perf_counter()
+        out[f"batch{batch}"] = {"decode_tok_s": round(n / (t1 - t0), 1), "ms_per_step": round(1e3 * (t1 - t0) / (new_tokens - 1), 4),
+                                "batch_forwards": ls.batch_forward_count}
+        ls.close()
+    m.close()
+    return out
+
+
 def run_ours(args):
     rank, local_rank, world = dist_env()
     dist = None
@@ -270,6 +324,12 @@ def run_ours(args):
         line["cpu_baseline"] = cpu_baseline(sample_rows=65536, threads=1)
         if not args.no_sweep:
             line["sweep"] = run_sweep(lthn, st, peak, args.full)
+        if not args.no_decode and world == 1:
+            for w in ws:
+                w.free()
+            line["decode"] = [run_decode(lthn, GEMMA_2B, "gemma-style 26L/2304 (BASELINE configs[3])", 1024, 256, 16, peak)]
+            if args.full:
+                line["decode"].append(run_decode(lthn, GEMMA_27B, "gemma-style 62L/5376 (BASELINE configs[4])", 4096, 512, 32, peak))
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -345,6 +405,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--full", action="store_true", help="report every batch size of the sweep")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-decode", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
