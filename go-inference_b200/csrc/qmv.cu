@@ -35,6 +35,7 @@
 #include "qmv.hpp"
 
 #include <algorithm>
+#include <mutex>
 
 namespace lthn {
 
@@ -575,6 +576,71 @@ int32_t lthn_affine_qmv_geglu(void* stream, const void* x, int32_t x_dtype, int3
                  "affine_qmv_geglu: packed weights must be 8-byte and x 16-byte aligned");
     QmvCall c{gate_packed, gate_scales, gate_biases, up_packed, up_scales, up_biases, x, x_dtype, y, y_dtype, N, K, M};
     return qmv_dispatch(s, c);
+}
+
+// ---- allocation-free variant ----------------------------------------------------------
+// Some hosts must not allocate device memory on the request path: a serving process
+// whose memory budget was fixed at start-up (every byte of HBM already handed to the KV
+// pool), a caller inside a region where the CUDA allocator may not be entered (a stream
+// being captured, a real-time thread), or a sandboxed plugin that is only allowed kernel
+// launches. lthn_affine_qmv splits f32 activations into bf16 columns in a scratch buffer
+// that it obtains from a growing arena (cudaMalloc on first use or growth); this variant
+// keeps that scratch in a fixed array that is part of the loaded module instead.
+// The array costs kQmvNoAllocBytes of device memory on every GPU that loads the library,
+// for the life of the process.
+constexpr size_t kQmvNoAllocBytes = 512u << 10;
+constexpr size_t kQmvNoAllocHeader = 256;  // status word, then the bf16 activation columns
+static __device__ __align__(256) unsigned char g_qmv_noalloc[kQmvNoAllocBytes];
+// g_qmv_noalloc is only a host-side handle here; kernels need the device address, which
+// cudaGetSymbolAddress resolves once per device with that device current.
+static void* g_qmv_noalloc_addr[16];
+static std::mutex g_qmv_noalloc_mu;
+
+int32_t lthn_affine_qmv_noalloc(void* stream, const float* x, int32_t M, const uint32_t* packed,
+                                const uint16_t* scales, const uint16_t* biases, int64_t N, int64_t K, float* y) {
+    clear_error();
+    cudaStream_t s = (cudaStream_t)stream;
+    LTHN_REQUIRE(M >= 0 && N >= 0 && K >= 0, "affine_qmv_noalloc: negative dimension");
+    if (M == 0 || N == 0) return LTHN_OK;
+    LTHN_REQUIRE(x && packed && scales && biases && y, "affine_qmv_noalloc: NULL pointer");
+    LTHN_REQUIRE(M <= 32, "affine_qmv_noalloc: M must be at most 32");
+    LTHN_REQUIRE(K > 0 && K % 64 == 0, "affine_qmv_noalloc: K must be a positive multiple of 64 (4-bit, group 64 only)");
+    LTHN_REQUIRE(((uintptr_t)packed & 7) == 0 && ((uintptr_t)x & 3) == 0, "affine_qmv_noalloc: misaligned pointer");
+    const int split = qmv_split_for(M, LTHN_DTYPE_F32);
+    const size_t need = kQmvNoAllocHeader + (size_t)M * split * (size_t)K * 2;
+    if (need > kQmvNoAllocBytes)
+        return fail(LTHN_ERR_INVALID, "affine_qmv_noalloc: M*" + std::to_string(split) + "*K*2 bytes of activation columns (" +
+                                          std::to_string(need - kQmvNoAllocHeader) + ") exceed the fixed scratch of " +
+                                          std::to_string(kQmvNoAllocBytes - kQmvNoAllocHeader) +
+                                          " bytes; use lthn_affine_qmv for this size");
+    int dev = 0;
+    LTHN_CUDA_TRY(cudaGetDevice(&dev));
+    LTHN_REQUIRE(dev >= 0 && dev < 16, "affine_qmv_noalloc: device index out of range");
+    unsigned char* base;
+    {
+        std::lock_guard<std::mutex> lk(g_qmv_noalloc_mu);
+        if (!g_qmv_noalloc_addr[dev]) {  // first call on this device: resolve the array's device address
+            void* p = nullptr;
+            LTHN_CUDA_TRY(cudaGetSymbolAddress(&p, g_qmv_noalloc));
+            g_qmv_noalloc_addr[dev] = p;
+        }
+        base = (unsigned char*)g_qmv_noalloc_addr[dev];
+    }
+    // the array keeps the previous call's bytes: the status word must start at zero, the
+    // activation columns are fully rewritten below
+    LTHN_CUDA_TRY(cudaMemsetAsync(base, 0, 4, s));
+    uint16_t* cols = (uint16_t*)(base + kQmvNoAllocHeader);
+    int32_t rc = split_f32_launch(s, x, M, K, split, cols);
+    if (rc) return rc;
+    QmvArgs a{};
+    a.wq = packed; a.scales = scales; a.biases = biases; a.x = cols; a.y = y;
+    a.N = N; a.K = K; a.M = M; a.C = M * split; a.split = split; a.y_dtype = LTHN_DTYPE_F32; a.y_split = 0;
+    a.status = (uint32_t*)base;
+    int rt, nwarps;
+    qmv_pick_config(N, K, a.C, 1, &rt, &nwarps);
+    const int G = (int)(K / 64);
+    a.tma_ok = (((uintptr_t)scales | (uintptr_t)biases) & 15) == 0 && ((16 * rt * G * 2) % 16) == 0;
+    return launch_qmv<0>(s, a, rt, nwarps);
 }
 
 int32_t lthn_affine_qmv_host(const void* x, size_t x_len, const void* packed, size_t packed_len,

@@ -92,6 +92,7 @@ class _Sig:
     lthn_synth_affine_weight = (i32, [vp, u64, f32, i64, i64, i32, i32, i32, vp, vp, vp])
     lthn_affine_qmv = (i32, [vp, vp, i32, i32, vp, vp, vp, i64, i64, i32, i32, vp, i32])
     lthn_affine_qmv_host = (i32, [vp, sz, vp, sz, vp, sz, vp, sz, i64, i64, i32, i32, vp, sz])
+    lthn_affine_qmv_noalloc = (i32, [vp, vp, i32, vp, vp, vp, i64, i64, vp])
     lthn_affine_qmv_geglu = (i32, [vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, i64, i64, vp, i32])
     lthn_rmsnorm = (i32, [vp, vp, vp, vp, i32, i32, f32])
     lthn_rmsnorm_residual = (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32])
@@ -346,6 +347,12 @@ def dequantize(q: QuantWeight, out: Buf, bf16=False, stream=None):
 def qmv(x: Buf, x_dtype, M, q: QuantWeight, y: Buf, y_dtype, stream=None):
     check(lib().lthn_affine_qmv(_s(stream), x.ptr, x_dtype, M, q.packed.ptr, q.scales.ptr, q.biases.ptr, q.N, q.K,
                                 q.gs, q.bits, y.ptr, y_dtype))
+
+
+def qmv_noalloc(x_f32: Buf, M, q: QuantWeight, y_f32: Buf, stream=None):
+    """Allocation-free affine_qmv (f32 in, f32 out, 4 bit / group 64; see the header for its size limit)."""
+    check(lib().lthn_affine_qmv_noalloc(_s(stream), x_f32.ptr, M, q.packed.ptr, q.scales.ptr, q.biases.ptr, q.N, q.K,
+                                        y_f32.ptr))
 
 
 def qmm(x: Buf, M, q: QuantWeight, y: Buf, stream=None):

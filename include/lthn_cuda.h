@@ -123,6 +123,21 @@ int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M,
                         const uint16_t* scales, const uint16_t* biases, int64_t N, int64_t K, int32_t gs,
                         int32_t bits, void* y, int32_t y_dtype);
 
+/* Allocation-free form of lthn_affine_qmv for f32 activations (4 bit, group 64, f32 out).
+ * It has no counterpart in the reference. For hosts that may not allocate device memory
+ * while serving (a fixed start-up memory budget, code running where the CUDA allocator
+ * must not be entered, launch-only sandboxes): the bf16 activation columns that
+ * lthn_affine_qmv stages in a growing arena live here in a fixed 512 KiB array inside the
+ * library image (held by every GPU that loads it until exit), so the call performs no
+ * cudaMalloc / cudaFree. Limit: 256 + M*s*K*2 <= 524288 bytes with s = 3 for M <= 2 and
+ * s = 2 above (e.g. M=1: K <= 87296; M=8: K <= 16320; M=32: K <= 4032); larger sizes are
+ * rejected with LTHN_ERR_INVALID. The first call on a device resolves the array's device
+ * address (cudaGetSymbolAddress) and should therefore come before any stream capture.
+ * All calls on a device share the one array: calls whose kernels can overlap on the GPU
+ * (different streams without ordering) race; order them. */
+int32_t lthn_affine_qmv_noalloc(void* stream, const float* x, int32_t M, const uint32_t* packed,
+                                const uint16_t* scales, const uint16_t* biases, int64_t N, int64_t K, float* y);
+
 /* Fused GeGLU pair: y[M,N] = gelu_tanh(x * dequant(Wgate)^T) * (x * dequant(Wup)^T),
  * both weights [N,K], 4 bit, group 64; gate and up rows are streamed together so
  * the activation is read once and the intermediate never reaches memory.
