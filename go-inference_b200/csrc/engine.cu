@@ -118,6 +118,11 @@ struct Model {
     size_t sdpa_part_bytes = 0;
     int32_t* h_pinned = nullptr;  // pinned staging for ids / positions / tokens
     uint64_t weight_bytes = 0;
+    // one captured decode step per row count (all rows produce a token); positions, ids and
+    // lanes are read from device buffers, so the same graph serves every step
+    cudaGraphExec_t step_graph[kMaxRows + 1] = {};
+    bool step_warm[kMaxRows + 1] = {};
+    bool graphs_off = false;
     std::mutex mu;
     std::vector<void*> allocs;
 };
@@ -293,6 +298,39 @@ static int32_t forward_full(Model* m, int rows, int max_ctx, bool want_logits, i
     return forward(m, rows, max_ctx, want_logits, logit_row0);
 }
 
+// One decode step for `rows` lanes (ids / positions / lanes already in the device buffers),
+// every row producing a token. The first call per row count runs eagerly (first use of a
+// kernel may allocate scratch), the second captures the step into a CUDA graph, later calls
+// replay it: ~210 launches per token become one graph launch. The split-KV grid is sized for
+// max_len so the graph does not depend on the current context length. LTHN_CUDA_NO_GRAPH=1
+// keeps the eager path.
+static int32_t decode_step(Model* m, int rows) {
+    if (m->step_graph[rows]) {
+        LTHN_CUDA_TRY(cudaGraphLaunch(m->step_graph[rows], m->stream));
+        return LTHN_OK;
+    }
+    if (m->graphs_off || !m->step_warm[rows]) {
+        m->step_warm[rows] = true;
+        return forward(m, rows, m->c.max_len, true, 0);
+    }
+    LTHN_CUDA_TRY(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+    const int32_t rc = forward(m, rows, m->c.max_len, true, 0);
+    cudaGraph_t g = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+    cudaGraphExec_t ex = nullptr;
+    if (rc == LTHN_OK && e == cudaSuccess && g && cudaGraphInstantiate(&ex, g, 0) == cudaSuccess) {
+        cudaGraphDestroy(g);
+        m->step_graph[rows] = ex;
+        LTHN_CUDA_TRY(cudaGraphLaunch(ex, m->stream));
+        return LTHN_OK;
+    }
+    if (g) cudaGraphDestroy(g);
+    cudaGetLastError();
+    clear_error();
+    m->graphs_off = true;  // capture is not possible here: stay eager
+    return forward(m, rows, m->c.max_len, true, 0);
+}
+
 // ---- lanes / sessions ------------------------------------------------------------------
 struct Lane {
     int id = -1;       // KV lane index in the model
@@ -333,7 +371,9 @@ static int32_t feed_lane(Model* m, Lane* ln, const int32_t* ids, int n) {
         LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_pos, hp + kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
         LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_lane, hp + 2 * kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
         const bool last = off + rows >= n;
-        if ((rc = forward_full(m, rows, ln->pos + rows, last, rows - 1))) return rc;
+        if (n == 1) rc = decode_step(m, 1);
+        else rc = forward_full(m, rows, ln->pos + rows, last, rows - 1);
+        if (rc) return rc;
         ln->pos += rows;
         if (last) {
             LTHN_CUDA_TRY(cudaMemcpyAsync(hp + 3 * kMaxRows, m->d_next + rows - 1, 4, cudaMemcpyDeviceToHost, m->stream));
@@ -399,6 +439,7 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
     if (rc) return rc;
     Model* m = new Model();
     m->c = c;
+    m->graphs_off = getenv("LTHN_CUDA_NO_GRAPH") != nullptr;
     const int t = c.tp_size;
     m->Hq_l = c.q_heads / t; m->Hkv_l = c.kv_heads / t;
     m->QR_l = m->Hq_l * c.head_dim; m->KR_l = m->Hkv_l * c.head_dim;
@@ -577,6 +618,8 @@ int32_t lthn_model_destroy(void* model) {
     Model* m = (Model*)model;
     if (!m) return LTHN_OK;
     cudaStreamSynchronize(m->stream);
+    for (auto& g : m->step_graph)
+        if (g) cudaGraphExecDestroy(g);
     for (void* p : m->allocs) cudaFree(p);
     if (m->h_pinned) cudaFreeHost(m->h_pinned);
     cudaStreamDestroy(m->stream);
@@ -774,7 +817,7 @@ int32_t lthn_laneset_step(void* set, int32_t* lane_handles, int32_t* tokens, int
         LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_ids, hp, rows * 4, cudaMemcpyHostToDevice, m->stream));
         LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_pos, hp + kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
         LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_lane, hp + 2 * kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
-        int32_t rc = forward_full(m, rows, max_ctx, true, 0);
+        int32_t rc = decode_step(m, rows);
         if (rc) return rc;
         LTHN_CUDA_TRY(cudaMemcpyAsync(hp + 3 * kMaxRows, m->d_next, rows * 4, cudaMemcpyDeviceToHost, m->stream));
         LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));

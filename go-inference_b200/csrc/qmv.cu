@@ -474,13 +474,16 @@ static int g_force_rt = 0, g_force_warps = 0, g_force_kernel = 0;
 // tensor-core kernel (f32 activations are first split into bf16 columns).
 int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
     const int fuse = c.wq2 ? 1 : 0;
-    // Measured on B200: the dp4a kernel wins for long rows and few of them (K >= 8192,
-    // N <= 4096); elsewhere the tensor-core kernel is currently faster.
-    const bool prefer_dp4a = g_force_kernel == 1 || (g_force_kernel == 0 && c.K >= 8192 && c.N <= 4096);
+    // Measured on B200: the dp4a kernel wins on large matrices (it streams at ~4.5 TB/s where
+    // the tensor-core kernel is capped near 3 TB/s by the mma.sync issue rate) and on long
+    // rows; small matrices are launch/latency sized and the tensor-core kernel starts faster.
+    const bool big = (double)c.N * (double)c.K >= 64.0 * 1024 * 1024;
+    const bool prefer_dp4a = g_force_kernel == 1 || (g_force_kernel == 0 && (big || (c.K >= 8192 && c.N <= 4096)));
     if (prefer_dp4a && c.M <= 2) {
         Dp4aPlan plan;
-        const bool aligned = (((uintptr_t)c.wq | (uintptr_t)c.x | (uintptr_t)(c.wq2 ? c.wq2 : c.wq)) & 15) == 0;
-        if (aligned && !(fuse && c.M == 2) && dp4a_plan(c.N, c.K, c.M, fuse, g_force_rt, &plan))
+        bool aligned = (((uintptr_t)c.wq | (uintptr_t)c.x | (uintptr_t)c.scales | (uintptr_t)c.biases) & 15) == 0;
+        if (c.wq2) aligned = aligned && (((uintptr_t)c.wq2 | (uintptr_t)c.scales2 | (uintptr_t)c.biases2) & 15) == 0;
+        if (aligned && !(fuse && c.M == 2) && dp4a_plan(c.N, c.K, c.M, fuse, g_force_rt, g_force_warps, &plan))
             return dp4a_launch(s, c, plan);
     }
     QmvArgs a{};

@@ -16,10 +16,10 @@ struct QmvCall {
     int M;
 };
 
-struct Dp4aPlan { int J, R, T_row, S, threads, nblocks; size_t smem; };
+struct Dp4aPlan { int J, R, T_row, S, threads, cons_threads, nblocks, part_bytes; size_t smem; };
 
 // dp4a kernel (1-2 activation rows). dp4a_plan returns false when the shape is not served.
-bool dp4a_plan(int64_t N, int64_t K, int M, int fuse, int force_r, Dp4aPlan* p);
+bool dp4a_plan(int64_t N, int64_t K, int M, int fuse, int force_r, int force_s, Dp4aPlan* p);
 int32_t dp4a_launch(cudaStream_t st, const QmvCall& c, const Dp4aPlan& p);
 
 // Dispatcher used by the C entry points and by the decoder engine.

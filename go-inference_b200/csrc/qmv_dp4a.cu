@@ -19,15 +19,15 @@
 // in f32. The activation error bound (2^-22 of the group maximum) is below the
 // f32 rounding of the group maximum itself; all accumulation across groups is f32.
 //
-// Mapping. A row of K codes is K/32 "half groups" of 16 bytes. T_row = K/(32*J)
-// threads cooperate on a row, thread u owning half groups u, u+T_row, ... (J of
-// them), so a row is read as consecutive 16-byte loads. A CTA has S row slots
-// (S*T_row threads) and is persistent: it converts its activations once into
-// registers (24 registers per half group) and then streams row blocks of S*R
-// rows, R rows per thread in flight plus the next block prefetched. Partial sums
-// of the T_row threads of a row meet in shared memory (double buffered, one
-// __syncthreads per row block) and are reduced in a fixed order by one warp per
-// output, so results are deterministic.
+// Mapping. A row of K codes is K/64 groups of 32 bytes. T_row = K/(64*J) threads
+// cooperate on a row, thread u owning groups u, u+T_row, ... (J of them), so a row
+// is read as consecutive 32-byte pieces. A CTA has S row slots (S*T_row threads) and
+// is persistent: it converts its activations once into registers (48 registers per
+// group) and then streams row blocks of S*R rows, R rows per thread in flight plus
+// the next block prefetched into a second register set. The partial sums of a row's
+// threads are folded inside each quad with shuffles, meet in shared memory (double
+// buffered, one __syncthreads per row block) and are added in a fixed order by one
+// thread per output, so results are deterministic.
 #include "common.cuh"
 #include "qmv.hpp"
 
@@ -46,6 +46,9 @@ struct Dp4aArgs {
     int64_t N, K;
     int x_dtype, y_dtype;
     int T_row, S, nblocks;
+    int part_bytes;    // bytes of the reduction area at the start of dynamic shared memory (16-byte multiple)
+    int cons_threads;  // consumer threads (multiple of 32); one more warp is the producer
+    uint32_t* status;
 };
 
 __device__ __forceinline__ int dp4a_ss(int a, int b, int c) { return __dp4a(a, b, c); }
@@ -55,31 +58,138 @@ __device__ __forceinline__ float gelu_tanh_dev(float x) {
     return 0.5f * x * (1.0f + tanhf(k0 * (x + k1 * x * x * x)));
 }
 
-// J half groups per thread, R rows per thread per block, MT activation rows,
+// J groups per thread, R rows per thread per block, MT activation rows,
 // FUSE=1: two weight sets, output gelu_tanh(W1 x) * (W2 x).
+// A thread owns whole quantisation groups (64 codes = two 16-byte loads), so scale, bias
+// and the integer-to-float step are paid once per 32 weight bytes. T_row = K/(64*J) threads
+// share a row; T_row is a multiple of 4 so the four lanes of a quad always belong to one row
+// and V = SETS*R*MT partial sums per lane are folded with a V-value butterfly (2 shuffles per
+// level) before one lane per quad stores to shared memory.
+template <int V>
+__device__ __forceinline__ float quad_fold(float (&v)[V], int lane) {
+    if (V == 4) {
+        const bool hi = lane & 2;
+        const float sa = hi ? v[0] : v[2], sb = hi ? v[1] : v[3];
+        float ka = hi ? v[2] : v[0], kb = hi ? v[3] : v[1];
+        ka += __shfl_xor_sync(0xffffffffu, sa, 2);
+        kb += __shfl_xor_sync(0xffffffffu, sb, 2);
+        const bool odd = lane & 1;
+        const float send = odd ? ka : kb;
+        float keep = odd ? kb : ka;
+        keep += __shfl_xor_sync(0xffffffffu, send, 1);
+        return keep;  // lane (b1,b0) of the quad holds value index 2*b1+b0
+    } else if (V == 2) {
+        const bool odd = lane & 1;
+        const float send = odd ? v[0] : v[1];
+        float keep = odd ? v[1] : v[0];
+        keep += __shfl_xor_sync(0xffffffffu, send, 1);
+        keep += __shfl_xor_sync(0xffffffffu, keep, 2);
+        return keep;  // lanes with b0 = i hold value index i
+    } else {
+        float keep = v[0];
+        keep += __shfl_xor_sync(0xffffffffu, keep, 1);
+        keep += __shfl_xor_sync(0xffffffffu, keep, 2);
+        return keep;
+    }
+}
+
 template <int J, int R, int MT, int FUSE>
 __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
     constexpr int SETS = FUSE ? 2 : 1;
-    extern __shared__ float part[];  // [2][SETS*S*R*MT][T_row]
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    const int T_row = a.T_row;
+    constexpr int V = SETS * R * MT;
+    static_assert(V == 1 || V == 2 || V == 4, "1, 2 or 4 partial sums per lane");
+    extern __shared__ __align__(16) unsigned char dsm[];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int T_row = a.T_row, T4 = T_row >> 2;
     const int slot = tid / T_row, u = tid - slot * T_row;
     const bool active = slot < a.S;
     const int64_t K = a.K;
 
-    // ---- activations -> three int8 digit planes per owned half group ---------------
-    int X[MT][J][3][8];
+    // ---- persistent loop over row blocks, tiles staged by bulk (TMA) copies ------------------
+    // A row block (RB consecutive rows) is contiguous in each of the three tensors, so one
+    // elected lane of a dedicated producer warp fetches it with three 1-D bulk copies per
+    // weight set into a ring of STG shared-memory stages, STG-1 blocks ahead of the
+    // consumers; full/empty mbarriers hand the stages over. Consumer threads then read their
+    // own 32-byte pieces and bf16 scale/bias with plain shared loads: no per-thread global
+    // addressing, no registers spent on prefetch.
+    constexpr int STG = 4;
+    const int RB = a.S * R;
+    const int G = (int)(K >> 6);
+    const int rowbytes = (int)(K >> 1), sbrow = G * 2;
+    const int codes_bytes = RB * rowbytes;              // multiple of 16
+    const int sb_bytes = (RB * sbrow + 15) & ~15;       // section size, 16-byte aligned
+    const int set_bytes = codes_bytes + 2 * sb_bytes;
+    const int stage_bytes = SETS * set_bytes;
+    float* part = (float*)dsm;                                               // [2][V*S][T4]
+    uint64_t* full = (uint64_t*)(dsm + a.part_bytes);
+    uint64_t* empty = full + STG;
+    unsigned char* stages = dsm + a.part_bytes + 128;
+    const int ncons = a.cons_threads;                    // consumer threads (multiple of 32)
+    const bool producer_warp = tid >= ncons;
+    const int stride = gridDim.x;
+
+    if (tid == 0) {
+        for (int i = 0; i < STG; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], ncons >> 5); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (producer_warp) {
+        int it = 0;
+        for (int b = blockIdx.x; b < a.nblocks; b += stride, it++) {
+            const int st = it % STG;
+            if (!mbar_wait(&empty[st], ((it / STG) & 1) ^ 1)) { if (lane == 0) atomicOr(a.status, 32u); break; }
+            unsigned char* sbase = stages + (size_t)st * stage_bytes;
+            const int64_t row0 = (int64_t)b * RB;
+            const int rows = (int)min((int64_t)RB, a.N - row0);
+            const bool bulk_ok = rows == RB;
+            if (bulk_ok) {
+                if (lane == 0) {
+                    mbar_expect_tx(&full[st], (uint32_t)(SETS * (codes_bytes + 2 * RB * sbrow)));
+#pragma unroll
+                    for (int s = 0; s < SETS; s++) {
+                        unsigned char* d = sbase + (size_t)s * set_bytes;
+                        bulk_g2s(d, (const unsigned char*)a.wq[s] + row0 * rowbytes, (uint32_t)codes_bytes, &full[st]);
+                        bulk_g2s(d + codes_bytes, (const unsigned char*)a.scales[s] + row0 * sbrow, (uint32_t)(RB * sbrow), &full[st]);
+                        bulk_g2s(d + codes_bytes + sb_bytes, (const unsigned char*)a.biases[s] + row0 * sbrow, (uint32_t)(RB * sbrow), &full[st]);
+                    }
+                }
+            } else {
+                // last, partial block: plain copies by the producer warp (sizes are multiples of 8 bytes)
+#pragma unroll
+                for (int s = 0; s < SETS; s++) {
+                    unsigned char* d = sbase + (size_t)s * set_bytes;
+                    const uint2* src = (const uint2*)((const unsigned char*)a.wq[s] + row0 * rowbytes);
+                    for (int i = lane; i < rows * rowbytes / 8; i += 32) ((uint2*)d)[i] = __ldg(src + i);
+                    const uint2* ss = (const uint2*)((const unsigned char*)a.scales[s] + row0 * sbrow);
+                    const uint2* bs = (const uint2*)((const unsigned char*)a.biases[s] + row0 * sbrow);
+                    for (int i = lane; i < rows * sbrow / 8; i += 32) {
+                        ((uint2*)(d + codes_bytes))[i] = __ldg(ss + i);
+                        ((uint2*)(d + codes_bytes + sb_bytes))[i] = __ldg(bs + i);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[st])) : "memory");
+            }
+        }
+        return;
+    }
+
+    // ---- consumers ----------------------------------------------------------------------------
+    // (the producer is already fetching the first row blocks while this conversion runs)
+    // ---- activations -> three int8 digit planes per owned group -------------------------
+    int X[MT][J][3][16];
     float sxp[MT][J], xq[MT][J];
 #pragma unroll
     for (int m = 0; m < MT; m++)
 #pragma unroll
         for (int j = 0; j < J; j++) {
-            const int hg = (active ? u : 0) + j * T_row;
-            float xv[32];
+            const int g = (active ? u : 0) + j * T_row;
+            float xv[64];
             if (a.x_dtype == LTHN_DTYPE_BF16) {
-                const uint4* p = (const uint4*)((const uint16_t*)a.x + (int64_t)m * K + (int64_t)hg * 32);
+                const uint4* p = (const uint4*)((const uint16_t*)a.x + (int64_t)m * K + (int64_t)g * 64);
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
+                for (int q = 0; q < 8; q++) {
                     const uint4 v = __ldg(p + q);
                     const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -89,18 +199,16 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
                     }
                 }
             } else {
-                const float4* p = (const float4*)((const float*)a.x + (int64_t)m * K + (int64_t)hg * 32);
+                const float4* p = (const float4*)((const float*)a.x + (int64_t)m * K + (int64_t)g * 64);
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
+                for (int q = 0; q < 16; q++) {
                     const float4 v = __ldg(p + q);
                     xv[q * 4] = v.x; xv[q * 4 + 1] = v.y; xv[q * 4 + 2] = v.z; xv[q * 4 + 3] = v.w;
                 }
             }
             float amax = 0.f;
 #pragma unroll
-            for (int e = 0; e < 32; e++) amax = fmaxf(amax, fabsf(xv[e]));
-            // the other half of this quantisation group lives in the neighbouring thread
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            for (int e = 0; e < 64; e++) amax = fmaxf(amax, fabsf(xv[e]));
             const float sx = amax * (1.0f / 127.0f);
             const float inv = amax > 0.f ? 127.0f / amax : 0.f;
             const float sx1 = sx * (1.0f / 128.0f);
@@ -108,9 +216,9 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
 #pragma unroll
             for (int p = 0; p < 3; p++)
 #pragma unroll
-                for (int w8 = 0; w8 < 8; w8++) X[m][j][p][w8] = 0;
+                for (int w8 = 0; w8 < 16; w8++) X[m][j][p][w8] = 0;
 #pragma unroll
-            for (int e = 0; e < 32; e++) {
+            for (int e = 0; e < 64; e++) {
                 const float x0 = xv[e];
                 const float d0 = rintf(x0 * inv);
                 const float r1 = fmaf(-d0, sx, x0);
@@ -119,7 +227,7 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
                 const float d2 = rintf(r2 * inv * 16384.0f);
                 const int i0 = (int)d0, i1 = (int)d1, i2 = (int)d2;
                 isum += i0 * 16384 + i1 * 128 + i2;
-                // byte position inside the word pair: even k -> bytes of "even" reg, odd k -> "odd" reg
+                // even k -> bytes of the word's "even" register, odd k -> its "odd" register
                 const int word = e >> 3, pos = e & 7;
                 const int reg = word * 2 + (pos & 1), sh = (pos >> 1) * 8;
                 X[m][j][0][reg] |= (i0 & 0xff) << sh;
@@ -130,62 +238,42 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
             xq[m][j] = (float)isum * sxp[m][j];
         }
 
-    // ---- persistent loop over row blocks ----------------------------------------
-    const int RB = a.S * R;
-    const int64_t wpr = K >> 3;
-    const int gpr = (int)(K >> 6);
-    uint4 wcur[SETS][R][J], wnxt[SETS][R][J];
-    uint32_t sbcur[SETS][R][J], sbnxt[SETS][R][J];
-
-    auto load_block = [&](int b, uint4 (&w)[SETS][R][J], uint32_t (&sb)[SETS][R][J]) {
+    int buf = 0, it = 0;
+    for (int b = blockIdx.x; b < a.nblocks; b += stride, it++) {
+        const int st = it % STG;
+        if (!mbar_wait(&full[st], (it / STG) & 1)) { if (lane == 0) atomicOr(a.status, 64u); break; }
+        const unsigned char* sbase = stages + (size_t)st * stage_bytes;
+        float acc[V];
 #pragma unroll
-        for (int s = 0; s < SETS; s++)
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                int64_t row = (int64_t)b * RB + slot * R + r;
-                if (row >= a.N) row = a.N - 1;
-#pragma unroll
-                for (int j = 0; j < J; j++) {
-                    const int hg = u + j * T_row;
-                    w[s][r][j] = __ldg((const uint4*)(a.wq[s] + row * wpr + (int64_t)hg * 4));
-                    const int64_t gi = row * gpr + (hg >> 1);
-                    sb[s][r][j] = (uint32_t)__ldg(a.scales[s] + gi) | ((uint32_t)__ldg(a.biases[s] + gi) << 16);
-                }
-            }
-    };
-
-    int b = blockIdx.x;
-    if (active && b < a.nblocks) load_block(b, wcur, sbcur);
-    const int nout = a.S * R * MT;  // outputs per block per set
-    int buf = 0;
-    for (; b < a.nblocks; b += gridDim.x) {
-        const int bn = b + gridDim.x;
-        if (active && bn < a.nblocks) load_block(bn, wnxt, sbnxt);
+        for (int i = 0; i < V; i++) acc[i] = 0.f;
         if (active) {
 #pragma unroll
             for (int s = 0; s < SETS; s++)
 #pragma unroll
                 for (int r = 0; r < R; r++) {
-                    float acc[MT];
-#pragma unroll
-                    for (int m = 0; m < MT; m++) acc[m] = 0.f;
+                    const int lr = slot * R + r;  // row within the block
+                    const unsigned char* cb = sbase + (size_t)s * set_bytes + (size_t)lr * rowbytes;
+                    const uint16_t* sp = (const uint16_t*)(sbase + (size_t)s * set_bytes + codes_bytes) + lr * G;
+                    const uint16_t* bp = (const uint16_t*)(sbase + (size_t)s * set_bytes + codes_bytes + sb_bytes) + lr * G;
 #pragma unroll
                     for (int j = 0; j < J; j++) {
-                        const uint4 w = wcur[s][r][j];
-                        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-                        int ev[4], od[4];
+                        const int g = u + j * T_row;
+                        const uint4 w0 = *(const uint4*)(cb + g * 32);
+                        const uint4 w1 = *(const uint4*)(cb + g * 32 + 16);
+                        const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                        int ev[8], od[8];
 #pragma unroll
-                        for (int i = 0; i < 4; i++) {
+                        for (int i = 0; i < 8; i++) {
                             ev[i] = (int)(ww[i] & 0x0F0F0F0Fu);
                             od[i] = (int)((ww[i] >> 4) & 0x0F0F0F0Fu);
                         }
-                        const float sc = __uint_as_float(sbcur[s][r][j] << 16);
-                        const float bi = __uint_as_float(sbcur[s][r][j] & 0xffff0000u);
+                        const float sc = __uint_as_float((uint32_t)sp[g] << 16);
+                        const float bi = __uint_as_float((uint32_t)bp[g] << 16);
 #pragma unroll
                         for (int m = 0; m < MT; m++) {
                             int i0 = 0, i1 = 0, i2 = 0;
 #pragma unroll
-                            for (int i = 0; i < 4; i++) {
+                            for (int i = 0; i < 8; i++) {
                                 i0 = dp4a_ss(ev[i], X[m][j][0][2 * i], i0);
                                 i0 = dp4a_ss(od[i], X[m][j][0][2 * i + 1], i0);
                                 i1 = dp4a_ss(ev[i], X[m][j][1][2 * i], i1);
@@ -195,78 +283,88 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
                             }
                             const int itot = i0 * 16384 + i1 * 128 + i2;
                             const float f = (float)itot * sxp[m][j];
-                            acc[m] = fmaf(sc, f, acc[m]);
-                            acc[m] = fmaf(bi, xq[m][j], acc[m]);
+                            float& ac = acc[(s * R + r) * MT + m];
+                            ac = fmaf(sc, f, ac);
+                            ac = fmaf(bi, xq[m][j], ac);
                         }
                     }
-#pragma unroll
-                    for (int m = 0; m < MT; m++)
-                        part[((size_t)buf * SETS * nout + (size_t)s * nout + (slot * R + r) * MT + m) * T_row + u] = acc[m];
                 }
         }
-        __syncthreads();
-        // one warp per output: fixed-order sum over the T_row partials
-        for (int o = warp; o < nout; o += nwarps) {
-            float v[SETS];
-#pragma unroll
-            for (int s = 0; s < SETS; s++) {
-                const float* src = part + ((size_t)buf * SETS * nout + (size_t)s * nout + o) * T_row;
-                float t = 0.f;
-                for (int uu = lane; uu < T_row; uu += 32) t += src[uu];
-                v[s] = warp_sum(t);
+        // this warp is done reading the stage: hand it back to the producer
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[st])) : "memory");
+        // fold the quad's partial sums; lane (b1,b0) ends up owning value index vi
+        const float folded = quad_fold<V>(acc, lane);
+        const int vi = V == 4 ? (lane & 3) : (V == 2 ? (lane & 1) : 0);
+        const bool writer = V == 4 ? true : (V == 2 ? (lane & 2) == 0 : (lane & 3) == 0);
+        if (active && writer) part[((size_t)buf * V * a.S + (size_t)vi * a.S + slot) * T4 + (u >> 2)] = folded;
+        asm volatile("bar.sync 1, %0;" ::"r"(ncons) : "memory");  // consumers only
+        // final sums: one thread per (slot, r, m) output, fixed order over the T_row/4 partials
+        for (int o = tid; o < a.S * R * MT; o += ncons) {
+            const int sl = o / (R * MT), rm = o - sl * (R * MT);  // rm = r*MT + m
+            float v0 = 0.f, v1 = 0.f;
+            const float* p0 = part + ((size_t)buf * V * a.S + (size_t)rm * a.S + sl) * T4;
+            for (int i = 0; i < T4; i++) v0 += p0[i];
+            if (FUSE) {
+                const float* p1 = part + ((size_t)buf * V * a.S + (size_t)(R * MT + rm) * a.S + sl) * T4;
+                for (int i = 0; i < T4; i++) v1 += p1[i];
+                v0 = gelu_tanh_dev(v0) * v1;
             }
-            if (lane == 0) {
-                const int m = o % MT, sr = o / MT;  // sr = slot*R + r
-                const int64_t row = (int64_t)b * RB + sr;
-                if (row < a.N) {
-                    float out = v[0];
-                    if (FUSE) out = gelu_tanh_dev(v[0]) * v[SETS - 1];
-                    if (a.y_dtype == LTHN_DTYPE_BF16) ((uint16_t*)a.y)[(int64_t)m * a.N + row] = f32_to_bf16_bits(out);
-                    else ((float*)a.y)[(int64_t)m * a.N + row] = out;
-                }
+            const int r = rm / MT, m = rm - r * MT;
+            const int64_t row = (int64_t)b * RB + sl * R + r;
+            if (row < a.N) {
+                if (a.y_dtype == LTHN_DTYPE_BF16) ((uint16_t*)a.y)[(int64_t)m * a.N + row] = f32_to_bf16_bits(v0);
+                else ((float*)a.y)[(int64_t)m * a.N + row] = v0;
             }
         }
         buf ^= 1;
-        if (bn < a.nblocks) {
-#pragma unroll
-            for (int s = 0; s < SETS; s++)
-#pragma unroll
-                for (int r = 0; r < R; r++)
-#pragma unroll
-                    for (int j = 0; j < J; j++) { wcur[s][r][j] = wnxt[s][r][j]; sbcur[s][r][j] = sbnxt[s][r][j]; }
-        }
     }
 }
 
 // ---- host side --------------------------------------------------------------------
 
-bool dp4a_plan(int64_t N, int64_t K, int M, int fuse, int force_r, Dp4aPlan* p) {
+bool dp4a_plan(int64_t N, int64_t K, int M, int fuse, int force_r, int force_s, Dp4aPlan* p) {
     if (M < 1 || M > 2 || K % 64 != 0 || N < 1) return false;
-    const int hg = (int)(K / 32);
+    if (fuse && M == 2) return false;
+    const int G = (int)(K / 64);
     int J = 0;
-    for (int cand : {1, 2, 3, 4}) {
-        if (hg % cand) continue;
-        const int t = hg / cand;
-        if (t % 2 == 0 && t <= 352) { J = cand; break; }
+    for (int cand : {1, 2}) {
+        if (G % cand) continue;
+        const int t = G / cand;
+        if (t % 4 == 0 && t <= 352) { J = cand; break; }
     }
     if (!J) return false;
-    const int T_row = hg / J;
+    const int T_row = G / J;
+    const int sets = fuse ? 2 : 1;
+    // V = sets * R * M partial sums per lane must be 1, 2 or 4
+    int maxr = 4 / (sets * M);
+    if (J == 2) maxr = std::min(maxr, M == 2 ? 1 : 2);
+    // two rows per thread on large matrices (more CTAs per SM), four where few row blocks exist
+    int R = std::min(maxr, 2);
+    {
+        const int s0 = std::min(32, std::max(1, 288 / T_row));
+        if (maxr >= 4 && (N + (int64_t)s0 * 4 - 1) / ((int64_t)s0 * 4) <= 4 * 148) R = 4;
+    }
     int S = std::max(1, 288 / T_row);
-    S = std::min(S, 64);
-    // rows per thread: large matrices amortise the reduction, small ones want every SM busy
-    int R = 4;
-    if (M == 2 || fuse) R = 2;
-    while (R > 1 && (N + (int64_t)S * R - 1) / ((int64_t)S * R) < 2 * 148) R >>= 1;
-    if (force_r > 0) R = force_r;
-    if ((M == 2 || fuse) && R > 2) R = 2;
-    if (J >= 3 && R > 2) R = 2;
-    if (J >= 3 && (M == 2 || fuse)) R = 1;
+    S = std::min(S, 32);
+    if (force_s > 0 && force_s * T_row <= 352) S = force_s;
+    if (force_r == 1 || force_r == 2 || force_r == 4) R = std::min(force_r, maxr);
+    // small matrices: shrink the row block until every SM has work
+    if (force_r <= 0) while (R > 1 && (N + (int64_t)S * R - 1) / ((int64_t)S * R) < 148) R >>= 1;
+    if (force_s <= 0) while (S > 1 && (N + (int64_t)S * R - 1) / ((int64_t)S * R) < 148) S >>= 1;
+    if ((S * R) % 2) {  // bulk copies of the scale tile need an even number of rows per block
+        if (R < maxr) R *= 2; else if (S * T_row * 2 <= 352) S *= 2; else return false;
+    }
     p->J = J; p->R = R; p->T_row = T_row; p->S = S;
-    p->threads = (S * T_row + 31) / 32 * 32;
+    p->cons_threads = (S * T_row + 31) / 32 * 32;
+    p->threads = p->cons_threads + 32;
     if (p->threads > 384) return false;
     p->nblocks = (int)((N + (int64_t)S * R - 1) / ((int64_t)S * R));
-    p->smem = (size_t)2 * (fuse ? 2 : 1) * S * R * M * T_row * sizeof(float);
-    return p->smem <= 160 * 1024;
+    p->part_bytes = (int)(((size_t)2 * sets * R * M * S * (T_row / 4) * sizeof(float) + 15) / 16 * 16);
+    const size_t RB = (size_t)S * R;
+    const size_t stage = sets * (RB * (K / 2) + 2 * ((RB * G * 2 + 15) / 16 * 16));
+    p->smem = (size_t)p->part_bytes + 128 + 4 * stage;
+    return p->smem <= 200 * 1024;
 }
 
 template <int J, int R, int MT, int FUSE>
@@ -277,9 +375,9 @@ static int32_t launch_dp4a_t(cudaStream_t st, const Dp4aArgs& a, const Dp4aPlan&
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
     auto kern = qmv_dp4a_kernel<J, R, MT, FUSE>;
     if (cached_dev != dev || cached_smem < p.smem) {
-        LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         cached_dev = dev;
-        cached_smem = 160 * 1024;
+        cached_smem = 200 * 1024;
         cached_occ = 0;
     }
     // occupancy depends on the block size and shared memory of this launch
@@ -308,17 +406,17 @@ int32_t dp4a_launch(cudaStream_t st, const QmvCall& c, const Dp4aPlan& p) {
     a.wq[0] = c.wq; a.scales[0] = c.scales; a.biases[0] = c.biases;
     a.wq[1] = c.wq2; a.scales[1] = c.scales2; a.biases[1] = c.biases2;
     a.x = c.x; a.y = c.y; a.N = c.N; a.K = c.K; a.x_dtype = c.x_dtype; a.y_dtype = c.y_dtype;
-    a.T_row = p.T_row; a.S = p.S; a.nblocks = p.nblocks;
+    a.T_row = p.T_row; a.S = p.S; a.nblocks = p.nblocks; a.part_bytes = p.part_bytes;
+    a.cons_threads = p.cons_threads;
+    a.status = device_status_word();
+    if (!a.status) return fail(LTHN_ERR_CUDA, "affine_qmv: no device status word");
     const int fuse = c.wq2 ? 1 : 0;
 #define LTHN_DP4A(JJ, RR, MM, FF) \
     if (p.J == JJ && p.R == RR && c.M == MM && fuse == FF) return launch_dp4a_t<JJ, RR, MM, FF>(st, a, p);
     LTHN_DP4A(1, 4, 1, 0) LTHN_DP4A(1, 2, 1, 0) LTHN_DP4A(1, 1, 1, 0)
-    LTHN_DP4A(2, 4, 1, 0) LTHN_DP4A(2, 2, 1, 0) LTHN_DP4A(2, 1, 1, 0)
-    LTHN_DP4A(3, 2, 1, 0) LTHN_DP4A(3, 1, 1, 0) LTHN_DP4A(4, 2, 1, 0) LTHN_DP4A(4, 1, 1, 0)
-    LTHN_DP4A(1, 2, 2, 0) LTHN_DP4A(1, 1, 2, 0) LTHN_DP4A(2, 2, 2, 0) LTHN_DP4A(2, 1, 2, 0)
-    LTHN_DP4A(3, 1, 2, 0) LTHN_DP4A(4, 1, 2, 0)
-    LTHN_DP4A(1, 2, 1, 1) LTHN_DP4A(1, 1, 1, 1) LTHN_DP4A(2, 2, 1, 1) LTHN_DP4A(2, 1, 1, 1)
-    LTHN_DP4A(3, 1, 1, 1) LTHN_DP4A(4, 1, 1, 1)
+    LTHN_DP4A(2, 2, 1, 0) LTHN_DP4A(2, 1, 1, 0)
+    LTHN_DP4A(1, 2, 2, 0) LTHN_DP4A(1, 1, 2, 0) LTHN_DP4A(2, 1, 2, 0)
+    LTHN_DP4A(1, 2, 1, 1) LTHN_DP4A(1, 1, 1, 1) LTHN_DP4A(2, 1, 1, 1)
 #undef LTHN_DP4A
     return fail(LTHN_ERR_INVALID, "affine_qmv: no dp4a instantiation for this plan");
 }
