@@ -59,10 +59,22 @@ __global__ void embed_kernel(const int32_t* __restrict__ ids, const uint32_t* __
 // mode 0: out = norm(x, w)
 // mode 1: h = h + norm(a, w_post); out = norm(h, w_next)      (post-norm, residual, next pre-norm)
 // One CTA per row. (hipOracleReferenceLayer, hip_gemma4_q4_oracle_test.go:925-951.)
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ a, float* __restrict__ h,
+// cols/split (optional): the output additionally as bf16 hi/mid/lo columns
+// [rows*split, width] (column row*split+j), the form the tensor-core matvec consumes.
+__device__ __forceinline__ void store_split(uint16_t* cols, int split, int row, int width, int i, float v) {
+    float r = v;
+    for (int j = 0; j < split; j++) {
+        const uint16_t hbits = f32_to_bf16_bits(r);
+        cols[((int64_t)row * split + j) * width + i] = hbits;
+        r -= bf16_bits_to_f32(hbits);
+    }
+}
+
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__ a, float* __restrict__ h,
                                                       const float* __restrict__ w_post,
                                                       const float* __restrict__ w_next, float* __restrict__ out,
-                                                      int width, float eps, int mode) {
+                                                      int width, float eps, int mode, uint16_t* __restrict__ cols,
+                                                      int split) {
     __shared__ double sh[32];
     const int row = blockIdx.x;
     const float* ar = a + (int64_t)row * width;
@@ -76,8 +88,11 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
     ss = block_sum_f64(ss, sh);
     const float rms = (float)sqrt(ss / (double)width + (double)eps);
     if (mode == 0) {
-        for (int i = threadIdx.x; i < width; i += blockDim.x)
-            orow[i] = __fmul_rn(__fdiv_rn(ar[i], rms), w_post[i]);
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = __fmul_rn(__fdiv_rn(ar[i], rms), w_post[i]);
+            orow[i] = v;
+            if (cols) store_split(cols, split, row, width, i, v);
+        }
         return;
     }
     double ss2 = 0.0;
@@ -89,8 +104,11 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
     }
     ss2 = block_sum_f64(ss2, sh);
     const float rms2 = (float)sqrt(ss2 / (double)width + (double)eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x)
-        orow[i] = __fmul_rn(__fdiv_rn(hr[i], rms2), w_next[i]);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = __fmul_rn(__fdiv_rn(hr[i], rms2), w_next[i]);
+        orow[i] = v;
+        if (cols) store_split(cols, split, row, width, i, v);
+    }
 }
 
 // ---- per-head RMSNorm + NeoX RoPE + KV append -----------------------------------------
@@ -179,21 +197,20 @@ __global__ void rmsnorm_rope_kernel(const float* __restrict__ x, const float* __
 
 // ---- decode attention over the seq-major bf16 cache -----------------------------------
 // cache layout per lane: [max_len][Hkv*D] bf16 (k_seq_stride = Hkv*D, k_head_stride = D;
-// engine/metal/decode_step.go:20-26). One CTA handles one (row, kv head, key chunk) and
-// all GQ query heads of that kv head, so K and V are streamed once per group
+// engine/metal/decode_step.go:20-26). One CTA handles one (row, bundle of GQ query heads that
+// share a kv head, key chunk), so K and V are streamed once per bundle
 // (rocm_attention_heads_chunked_stage1 _gqa variants, engine/hip/kernels/attention/
-// chunked.hipinc). Eight lanes share a key position, each holding D/8 of the head
-// dimension; 16 positions are in flight per 128-thread CTA. Pass 1 writes scaled scores to
-// shared memory and finds the chunk maximum, pass 2 accumulates exp(s-max)*V. The chunk
-// result (max, sum, unnormalised accumulator) goes to scratch and is merged by
-// sdpa_merge_kernel (stage 2); with a single chunk the normalised output is written
-// directly.
+// chunked.hipinc). Eight lanes share a key position, each holding D/8 of the head dimension;
+// a 128-thread CTA covers 16*NIT positions and issues every K and V load of its chunk before
+// any arithmetic (the chunk is sized so they fit in registers: 8192/D positions), so a chunk
+// costs one memory round trip. Scores stay in registers; the chunk result (max, sum,
+// unnormalised accumulator) goes to scratch and is merged by sdpa_merge_kernel (stage 2).
+// With a single chunk the normalised output is written directly.
 template <int D, int GQ>
 __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
-    constexpr int E = D / 8;       // elements per lane
-    constexpr int V8 = E / 8;      // 16-byte loads per lane per row
-    constexpr int MAXC = 512;      // positions per chunk (scores kept in shared memory)
-    __shared__ float sc[GQ][MAXC];
+    constexpr int E = D / 8;          // elements per lane
+    constexpr int V8 = E / 8;         // 16-byte loads per lane per row
+    constexpr int NIT = 512 / D > 0 ? 512 / D : 1;  // positions per lane group: 16*NIT per CTA
     __shared__ float red[4][GQ][D + 2];
     __shared__ float smax[GQ][4], ssum[GQ][4];
 
@@ -203,39 +220,53 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int l8 = lane & 7, pg = warp * 4 + (lane >> 3);  // position group 0..15
     const int ctx = a.row_pos[row] + 1;                    // keys 0..pos inclusive
-    const int p0 = chunk * a.chunk_len;
+    const int p0 = chunk * (16 * NIT);
     if (p0 >= ctx) return;
-    const int p1 = min(ctx, p0 + a.chunk_len), len = p1 - p0;
     const int KR = a.Hkv * D;
     const uint16_t* kbase = a.kcache + (int64_t)a.row_lane[row] * a.lane_stride + (int64_t)kvh * D;
     const uint16_t* vbase = a.vcache + (int64_t)a.row_lane[row] * a.lane_stride + (int64_t)kvh * D;
 
+    // ---- every load of the chunk goes out first ---------------------------------------------
+    uint4 kreg[NIT][V8], vreg[NIT][V8];
+    bool valid[NIT];
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
+        const int p = p0 + pg + 16 * i;
+        valid[i] = p < ctx;
+        const int64_t off = (int64_t)(valid[i] ? p : p0) * KR;
+#pragma unroll
+        for (int v = 0; v < V8; v++) {
+            kreg[i][v] = __ldg((const uint4*)(kbase + off + (v * 8 + l8) * 8));
+            vreg[i][v] = __ldg((const uint4*)(vbase + off + (v * 8 + l8) * 8));
+        }
+    }
     // query slices of this lane for the GQ heads, pre-multiplied by the softmax scale
     float q[GQ][E];
 #pragma unroll
     for (int h = 0; h < GQ; h++) {
         const float* qh = a.q + ((int64_t)row * a.Hq + qh0 + h) * D;
 #pragma unroll
-        for (int v = 0; v < V8; v++)
-#pragma unroll
-            for (int e = 0; e < 8; e++) q[h][v * 8 + e] = qh[(v * 8 + l8) * 8 + e] * a.scale;
+        for (int v = 0; v < V8; v++) {
+            const float4 qa = *(const float4*)(qh + (v * 8 + l8) * 8);
+            const float4 qb = *(const float4*)(qh + (v * 8 + l8) * 8 + 4);
+            q[h][v * 8 + 0] = qa.x * a.scale; q[h][v * 8 + 1] = qa.y * a.scale;
+            q[h][v * 8 + 2] = qa.z * a.scale; q[h][v * 8 + 3] = qa.w * a.scale;
+            q[h][v * 8 + 4] = qb.x * a.scale; q[h][v * 8 + 5] = qb.y * a.scale;
+            q[h][v * 8 + 6] = qb.z * a.scale; q[h][v * 8 + 7] = qb.w * a.scale;
+        }
     }
-    // ---- pass 1: scores -----------------------------------------------------------
-    float mx[GQ];
+    // ---- scores ---------------------------------------------------------------------------------
+    float sc[NIT][GQ], mx[GQ];
 #pragma unroll
     for (int h = 0; h < GQ; h++) mx[h] = -INFINITY;
-    // every lane runs the same number of iterations: the shuffles below name the whole warp
-    for (int pb = 0; pb < len; pb += 16) {
-        const int p = pb + pg;
-        const bool valid = p < len;
-        const uint16_t* kr = kbase + (int64_t)(p0 + (valid ? p : 0)) * KR;
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
         float dot[GQ];
 #pragma unroll
         for (int h = 0; h < GQ; h++) dot[h] = 0.f;
 #pragma unroll
         for (int v = 0; v < V8; v++) {
-            const uint4 kk = __ldg((const uint4*)(kr + (v * 8 + l8) * 8));
-            const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w};
+            const uint32_t kw[4] = {kreg[i][v].x, kreg[i][v].y, kreg[i][v].z, kreg[i][v].w};
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const float k0 = __uint_as_float(kw[e] << 16), k1 = __uint_as_float(kw[e] & 0xffff0000u);
@@ -249,22 +280,20 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
             d += __shfl_xor_sync(0xffffffffu, d, 1);
             d += __shfl_xor_sync(0xffffffffu, d, 2);
             d += __shfl_xor_sync(0xffffffffu, d, 4);
-            if (valid) {
-                if (l8 == 0) sc[h][p] = d;
-                mx[h] = fmaxf(mx[h], d);
-            }
+            sc[i][h] = valid[i] ? d : -INFINITY;
+            mx[h] = fmaxf(mx[h], sc[i][h]);
         }
     }
 #pragma unroll
     for (int h = 0; h < GQ; h++) {
-        float m = warp_max(mx[h]);
+        const float m = warp_max(mx[h]);
         if (lane == 0) smax[h][warp] = m;
     }
     __syncthreads();
     float cmax[GQ];
 #pragma unroll
     for (int h = 0; h < GQ; h++) cmax[h] = fmaxf(fmaxf(smax[h][0], smax[h][1]), fmaxf(smax[h][2], smax[h][3]));
-    // ---- pass 2: weights and weighted values -----------------------------------------
+    // ---- weights and weighted values ---------------------------------------------------------------
     float acc[GQ][E], lsum[GQ];
 #pragma unroll
     for (int h = 0; h < GQ; h++) {
@@ -272,15 +301,14 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
 #pragma unroll
         for (int e = 0; e < E; e++) acc[h][e] = 0.f;
     }
-    for (int p = pg; p < len; p += 16) {
-        const uint16_t* vr = vbase + (int64_t)(p0 + p) * KR;
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
         float w[GQ];
 #pragma unroll
-        for (int h = 0; h < GQ; h++) { w[h] = __expf(sc[h][p] - cmax[h]); lsum[h] += w[h]; }
+        for (int h = 0; h < GQ; h++) { w[h] = valid[i] ? __expf(sc[i][h] - cmax[h]) : 0.f; lsum[h] += w[h]; }
 #pragma unroll
         for (int v = 0; v < V8; v++) {
-            const uint4 vv = __ldg((const uint4*)(vr + (v * 8 + l8) * 8));
-            const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
+            const uint32_t vw[4] = {vreg[i][v].x, vreg[i][v].y, vreg[i][v].z, vreg[i][v].w};
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const float v0 = __uint_as_float(vw[e] << 16), v1 = __uint_as_float(vw[e] & 0xffff0000u);
@@ -293,7 +321,6 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
         }
     }
     // combine the 4 position groups of a warp, then the 4 warps
-    __syncwarp();
 #pragma unroll
     for (int h = 0; h < GQ; h++) {
 #pragma unroll
@@ -303,8 +330,7 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
             v += __shfl_xor_sync(0xffffffffu, v, 16);
             acc[h][e] = v;
         }
-        float l = lsum[h];  // every lane of a position group holds the same weight: count one lane per group
-        l = (l8 == 0) ? l : 0.f;
+        float l = (l8 == 0) ? lsum[h] : 0.f;  // the 8 lanes of a group hold the same weight: count it once
         l = warp_sum(l);
         if (lane == 0) ssum[h][warp] = l;
         if (lane < 8) {
@@ -330,21 +356,37 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
     }
 }
 
-// stage 2: merge chunk partials with their log-sum-exp weights.
-__global__ void sdpa_merge_kernel(const float* __restrict__ part, const int32_t* __restrict__ row_pos, int Hq, int D,
-                                  int nchunks, int chunk_len, float* __restrict__ out) {
-    const int row = blockIdx.y, qh = blockIdx.x;
+// stage 2: merge chunk partials with their log-sum-exp weights. One CTA per (head, row).
+__global__ void __launch_bounds__(128) sdpa_merge_kernel(const float* __restrict__ part,
+                                                         const int32_t* __restrict__ row_pos, int Hq, int D,
+                                                         int nchunks, int chunk_len, float* __restrict__ out,
+                                                         uint16_t* __restrict__ cols, int split) {
+    __shared__ float wgt[1024];
+    __shared__ float sden[4];
+    const int row = blockIdx.y, qh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int ctx = row_pos[row] + 1;
     const int used = min(nchunks, (ctx + chunk_len - 1) / chunk_len);
     const float* pa = part + ((int64_t)row * Hq + qh) * nchunks * (D + 2);
-    float m = -INFINITY;
-    for (int c = 0; c < used; c++) m = fmaxf(m, pa[(int64_t)c * (D + 2) + D]);
-    float denom = 0.f;
-    for (int c = 0; c < used; c++) denom += pa[(int64_t)c * (D + 2) + D + 1] * __expf(pa[(int64_t)c * (D + 2) + D] - m);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float m = -INFINITY;  // every warp finds the global maximum itself (cheap, no extra barrier)
+    for (int c = lane; c < used; c += 32) m = fmaxf(m, pa[(int64_t)c * (D + 2) + D]);
+    m = warp_max(m);
+    float den = 0.f;
+    for (int c = tid; c < used; c += 128) {
+        const float e = __expf(pa[(int64_t)c * (D + 2) + D] - m);
+        wgt[c] = e;
+        den += pa[(int64_t)c * (D + 2) + D + 1] * e;
+    }
+    den = warp_sum(den);
+    if (lane == 0) sden[warp] = den;
+    __syncthreads();
+    const float denom = sden[0] + sden[1] + sden[2] + sden[3];
+    for (int d = tid; d < D; d += 128) {
         float v = 0.f;
-        for (int c = 0; c < used; c++) v += pa[(int64_t)c * (D + 2) + d] * __expf(pa[(int64_t)c * (D + 2) + D] - m);
-        out[((int64_t)row * Hq + qh) * D + d] = v / denom;
+#pragma unroll 4
+        for (int c = 0; c < used; c++) v = fmaf(pa[(int64_t)c * (D + 2) + d], wgt[c], v);
+        const float o = v / denom;
+        out[((int64_t)row * Hq + qh) * D + d] = o;
+        if (cols) store_split(cols, split, row, Hq * D, qh * D + d, o);
     }
 }
 
@@ -402,8 +444,11 @@ int32_t launch_embed(cudaStream_t s, const int32_t* ids, int rows, const uint32_
 }
 
 int32_t launch_rmsnorm(cudaStream_t s, const float* a, float* h, const float* w_post, const float* w_next, float* out,
-                       int rows, int width, float eps, int mode) {
-    rmsnorm_kernel<<<rows, 256, 0, s>>>(a, h, w_post, w_next, out, width, eps, mode);
+                       int rows, int width, float eps, int mode, uint16_t* cols, int split) {
+    // one CTA per row; enough threads that each handles two or three elements (the f64 sum of
+    // squares and the IEEE divisions are latency, not throughput, so parallelism is what helps)
+    const int threads = width >= 2048 ? 1024 : (width >= 512 ? 512 : 256);
+    rmsnorm_kernel<<<rows, threads, 0, s>>>(a, h, w_post, w_next, out, width, eps, mode, cols, split);
     LTHN_CUDA_TRY(cudaGetLastError());
     return LTHN_OK;
 }
@@ -427,16 +472,11 @@ int32_t launch_rmsnorm_rope(cudaStream_t s, const float* x, const float* w, cons
     return LTHN_OK;
 }
 
-int sdpa_chunking(int max_ctx, int rows, int Hkv, int* chunk_len) {
-    // enough CTAs to cover the SMs a few times over, chunks of 64..512 keys
-    int want = (148 * 2 + rows * Hkv - 1) / (rows * Hkv);
-    if (want < 1) want = 1;
-    int len = (max_ctx + want - 1) / want;
-    len = (len + 63) / 64 * 64;
-    if (len < 64) len = 64;
-    if (len > 512) len = 512;
-    *chunk_len = len;
-    return (max_ctx + len - 1) / len;
+int sdpa_chunking(int max_ctx, int D, int* chunk_len) {
+    // a CTA covers as many keys as fit in registers with all loads in flight: 8192/D
+    const int nit = 512 / D > 0 ? 512 / D : 1;
+    *chunk_len = 16 * nit;
+    return (max_ctx + *chunk_len - 1) / *chunk_len;
 }
 
 size_t sdpa_scratch_bytes(int rows, int Hq, int D, int nchunks) {
@@ -461,7 +501,7 @@ int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D) {
     if (a.Hq % a.Hkv != 0) return fail(LTHN_ERR_INVALID, "sdpa_decode: Hq must be a multiple of Hkv");
     const int GQ = a.Hq / a.Hkv;
     if (a.nchunks > 1 && !a.part) return fail(LTHN_ERR_INVALID, "sdpa_decode: split-KV needs a scratch buffer");
-    if (a.chunk_len > 512) return fail(LTHN_ERR_INVALID, "sdpa_decode: chunk length above 512");
+    if (a.nchunks > 1024) return fail(LTHN_ERR_INVALID, "sdpa_decode: context too long for the merge stage (more than 1024 chunks)");
     // register budget: bundle * D/8 accumulators and as many query values per lane
     const int max_bundle = D <= 128 ? 4 : (D <= 256 ? 2 : 1);
     int bundle = 1;
@@ -476,7 +516,7 @@ int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D) {
     if (rc) return rc;
     if (a.nchunks > 1) {
         dim3 grid(a.Hq, rows);
-        sdpa_merge_kernel<<<grid, 128, 0, s>>>(a.part, a.row_pos, a.Hq, D, a.nchunks, a.chunk_len, a.out);
+        sdpa_merge_kernel<<<grid, 128, 0, s>>>(a.part, a.row_pos, a.Hq, D, a.nchunks, a.chunk_len, a.out, a.cols, a.split);
         LTHN_CUDA_TRY(cudaGetLastError());
     }
     return LTHN_OK;

@@ -20,19 +20,21 @@ struct SdpaArgs {
     int Hq, Hkv;
     int nchunks, chunk_len;
     float scale;
+    uint16_t* cols = nullptr;  // optional bf16 split columns of the output (written by the merge stage)
+    int split = 0;
 };
 
 int32_t launch_embed(cudaStream_t s, const int32_t* ids, int rows, const uint32_t* packed, const uint16_t* scales,
                      const uint16_t* biases, int hidden, int vocab, float embed_scale, float* out);
 int32_t launch_rmsnorm(cudaStream_t s, const float* a, float* h, const float* w_post, const float* w_next, float* out,
-                       int rows, int width, float eps, int mode);
+                       int rows, int width, float eps, int mode, uint16_t* cols = nullptr, int split = 0);
 int32_t launch_qknorm_rope_append(cudaStream_t s, const float* qkv, const float* q_norm, const float* k_norm,
                                   const float2* rope_table, const int32_t* row_pos, const int32_t* row_lane,
                                   float* q_out, uint16_t* kcache, uint16_t* vcache, int rows, int Hq, int Hkv, int D,
                                   float eps, int64_t lane_stride, int max_len);
 int32_t launch_rmsnorm_rope(cudaStream_t s, const float* x, const float* w, const int32_t* positions, float* out,
                             int rows, int heads, int D, int rotary, float eps, float rope_base, int bf16_seams);
-int sdpa_chunking(int max_ctx, int rows, int Hkv, int* chunk_len);
+int sdpa_chunking(int max_ctx, int D, int* chunk_len);
 size_t sdpa_scratch_bytes(int rows, int Hq, int D, int nchunks);
 int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D);
 int32_t launch_argmax(cudaStream_t s, const float* logits, int rows, int V, float* pv, int* pi, int32_t* out_idx,

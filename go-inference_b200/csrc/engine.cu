@@ -113,6 +113,7 @@ struct Model {
     // workspace for up to kMaxRows rows
     int32_t *d_ids = nullptr, *d_pos = nullptr, *d_lane = nullptr, *d_next = nullptr;
     float *h = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *att = nullptr, *a = nullptr, *act = nullptr;
+    uint16_t *xn_cols = nullptr, *att_cols = nullptr;  // bf16 split columns of xn / att for the tensor-core matvec
     float *logits = nullptr, *amax_v = nullptr, *sdpa_part = nullptr, *best_v = nullptr, *gather = nullptr;
     int* amax_i = nullptr;
     size_t sdpa_part_bytes = 0;
@@ -249,37 +250,43 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
     const int H = c.hidden, D = c.head_dim;
     int32_t rc;
     if ((rc = launch_embed(s, m->d_ids, rows, m->embed.wq, m->embed.s, m->embed.b, H, c.vocab, c.embed_scale, m->h))) return rc;
-    if ((rc = launch_rmsnorm(s, m->h, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, m->xn, rows, H, c.eps, 0))) return rc;
+    const int split = qmv_split_for(rows, LTHN_DTYPE_F32);
+    if ((rc = launch_rmsnorm(s, m->h, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, m->xn, rows, H, c.eps, 0, m->xn_cols, split))) return rc;
     int chunk_len = 0;
-    const int nchunks = sdpa_chunking(max_ctx, rows, m->Hkv_l, &chunk_len);
+    const int nchunks = sdpa_chunking(max_ctx, D, &chunk_len);
     const size_t need = sdpa_scratch_bytes(rows, m->Hq_l, D, nchunks);
     if (nchunks > 1 && need > m->sdpa_part_bytes) return fail(LTHN_ERR_STATE, "forward: attention scratch too small");
     for (int li = 0; li < c.layers; li++) {
         Layer& L = m->layers[li];
         QmvCall qc{L.qkv.wq, L.qkv.s, L.qkv.b, nullptr, nullptr, nullptr, m->xn, LTHN_DTYPE_F32, m->qkv, LTHN_DTYPE_F32, L.qkv.N, L.qkv.K, rows};
+        qc.x_cols = m->xn_cols; qc.x_split = split;
         if ((rc = qmv_dispatch(s, qc))) return rc;
         uint16_t* kc = m->kcache + (int64_t)li * m->layer_stride;
         uint16_t* vc = m->vcache + (int64_t)li * m->layer_stride;
         if ((rc = launch_qknorm_rope_append(s, m->qkv, L.norm[NORM_Q], L.norm[NORM_K], m->rope, m->d_pos, m->d_lane, m->q, kc, vc,
                                             rows, m->Hq_l, m->Hkv_l, D, c.eps, m->lane_stride, c.max_len))) return rc;
         SdpaArgs sa{m->q, kc, vc, m->d_pos, m->d_lane, m->att, m->sdpa_part, m->lane_stride, m->Hq_l, m->Hkv_l, nchunks, chunk_len, c.attn_scale};
+        sa.cols = m->att_cols; sa.split = split;
         if ((rc = launch_sdpa_decode(s, sa, rows, D))) return rc;
         QmvCall oc{L.o.wq, L.o.s, L.o.b, nullptr, nullptr, nullptr, m->att, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.o.N, L.o.K, rows};
+        if (nchunks > 1) { oc.x_cols = m->att_cols; oc.x_split = split; }  // the merge stage wrote them
         if ((rc = qmv_dispatch(s, oc))) return rc;
         if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
-        if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, 1))) return rc;
+        if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
         QmvCall gc{L.gate.wq, L.gate.s, L.gate.b, L.up.wq, L.up.s, L.up.b, m->xn, LTHN_DTYPE_F32, m->act, LTHN_DTYPE_F32, L.gate.N, L.gate.K, rows};
+        gc.x_cols = m->xn_cols; gc.x_split = split;
         if ((rc = qmv_dispatch(s, gc))) return rc;
         QmvCall dc{L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, m->act, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.down.N, L.down.K, rows};
         if ((rc = qmv_dispatch(s, dc))) return rc;
         if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
         const float* next_norm = li + 1 < c.layers ? m->layers[li + 1].norm[NORM_INPUT] : m->final_norm;
-        if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, 1))) return rc;
+        if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
     }
     if (!want_logits) return LTHN_OK;
     const int lr = rows - logit_row0;
     QmvCall hc{m->head.wq, m->head.s, m->head.b, nullptr, nullptr, nullptr, m->xn + (int64_t)logit_row0 * H, LTHN_DTYPE_F32,
                m->logits, LTHN_DTYPE_F32, m->head.N, m->head.K, lr};
+    if (qmv_split_for(lr, LTHN_DTYPE_F32) == split) { hc.x_cols = m->xn_cols + (int64_t)logit_row0 * split * H; hc.x_split = split; }
     if ((rc = qmv_dispatch(s, hc))) return rc;
     if (c.tp_size <= 1)
         return launch_argmax(s, m->logits, lr, m->V_l, m->amax_v, m->amax_i, m->d_next + logit_row0, nullptr, 0);
@@ -497,13 +504,14 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
         (rc = dalloc(m, &m->d_next, R)) || (rc = dalloc(m, &m->h, R * H)) || (rc = dalloc(m, &m->xn, R * H)) ||
         (rc = dalloc(m, &m->qkv, R * (m->QR_l + 2 * m->KR_l))) || (rc = dalloc(m, &m->q, R * m->QR_l)) ||
         (rc = dalloc(m, &m->att, R * m->QR_l)) || (rc = dalloc(m, &m->a, R * H)) || (rc = dalloc(m, &m->act, R * m->F_l)) ||
+        (rc = dalloc(m, &m->xn_cols, R * 3 * H)) || (rc = dalloc(m, &m->att_cols, R * 3 * m->QR_l)) ||
         (rc = dalloc(m, &m->logits, R * m->V_l)) || (rc = dalloc(m, &m->amax_v, R * ARGMAX_BLOCKS)) ||
         (rc = dalloc(m, &m->amax_i, R * ARGMAX_BLOCKS)) || (rc = dalloc(m, &m->best_v, R)) ||
         (rc = dalloc(m, &m->gather, 2 * R * (1 + (size_t)c.tp_size))))
         return bail(rc);
     {
         int chunk_len = 0;
-        const int nch = sdpa_chunking(c.max_len, 1, m->Hkv_l, &chunk_len);  // fewest rows -> most chunks
+        const int nch = sdpa_chunking(c.max_len, c.head_dim, &chunk_len);
         m->sdpa_part_bytes = sdpa_scratch_bytes(kMaxRows, m->Hq_l, c.head_dim, nch);
         if ((rc = dalloc(m, &m->sdpa_part, m->sdpa_part_bytes / sizeof(float) + 64))) return bail(rc);
     }
@@ -910,7 +918,7 @@ int32_t lthn_sdpa_decode(void* stream, const float* q, const uint16_t* kcache, c
     LTHN_REQUIRE(rows > 0 && q_heads > 0 && kv_heads > 0 && max_ctx > 0, "lthn_sdpa_decode: dimensions must be positive");
     if (scale <= 0) scale = (float)(1.0 / std::sqrt((double)head_dim));
     int chunk_len = 0;
-    const int nchunks = sdpa_chunking(max_ctx, rows, kv_heads, &chunk_len);
+    const int nchunks = sdpa_chunking(max_ctx, head_dim, &chunk_len);
     void* part = nullptr;
     if (nchunks > 1) {
         int32_t rc = scratch_get(sdpa_scratch_bytes(rows, q_heads, head_dim, nchunks), &part, 2);

@@ -92,8 +92,10 @@ __device__ __forceinline__ void load_x16(const uint16_t* __restrict__ p, uint32_
 
 // RT: 16-row tiles per CTA (per weight set). NT: 8-column activation tiles.
 // FUSE: 0 plain, 1 GeGLU over two weight sets (tile rt of set 1 and of set 2).
+// Single-tile, single-column-tile CTAs may be launched with up to 32 (16 when fused) warps so
+// that a small matrix has all of its groups in flight at once.
 template <int RT, int NT, int FUSE>
-__global__ void __launch_bounds__(256) qmv_mma_kernel(const QmvArgs a) {
+__global__ void __launch_bounds__((RT == 1 && NT == 1) ? (FUSE ? 512 : 1024) : 256) qmv_mma_kernel(const QmvArgs a) {
     constexpr int SETS = FUSE == 1 ? 2 : 1;
     constexpr int TR = 16 * RT;  // rows per set per CTA
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -434,6 +436,14 @@ void qmv_pick_config(int64_t N, int64_t K, int C, int sets, int* rt, int* nwarps
     if (sets == 2 && r > 2) r = 2;
     int w = 8;
     if (r >= 2 && C <= 8) w = 4;
+    if (r == 1 && C <= 8) {
+        // as many K-splitting warps as still let every 16-row tile be resident in one wave
+        const int maxw = sets == 2 ? 16 : 32;
+        for (int cand = maxw; cand >= 8; cand >>= 1) {
+            const int per_sm = std::max(1, std::min(2048 / (32 * cand), 65536 / (80 * 32 * cand)));
+            if (tiles16 <= (int64_t)148 * per_sm || cand == 8) { w = cand; break; }
+        }
+    }
     while (w > 1 && w > G) w >>= 1;
     *rt = r;
     *nwarps = w;
@@ -494,6 +504,8 @@ int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
     a.C = c.M * a.split;
     if (c.x_dtype == LTHN_DTYPE_BF16) {
         a.x = (const uint16_t*)c.x;
+    } else if (c.x_cols && c.x_split == a.split) {
+        a.x = c.x_cols;  // the producer already wrote the bf16 columns
     } else {
         void* scratch = nullptr;
         int32_t rc = scratch_get((size_t)a.C * c.K * 2, &scratch);

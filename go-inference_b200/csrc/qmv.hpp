@@ -14,7 +14,14 @@ struct QmvCall {
     void* y; int y_dtype;
     int64_t N, K;
     int M;
+    // optional: the same activations already split into bf16 columns ([M*x_split, K], column
+    // m*x_split+j) by the kernel that produced x; used when the tensor-core kernel is chosen
+    const uint16_t* x_cols = nullptr;
+    int x_split = 0;
 };
+
+// bf16 columns a tensor-core matvec over f32 activations wants per activation row
+int32_t qmv_split_for(int M, int x_dtype);
 
 struct Dp4aPlan { int J, R, T_row, S, threads, cons_threads, nblocks, part_bytes; size_t smem; };
 
