@@ -320,13 +320,25 @@ def run_ours(args):
                      "peak_kind": f"of {peak_kind}", "algorithmic_bytes": bytes_step,
                      "kernel_us": round(us_kernel, 3), "frac_of_nominal_8TBps": round(achieved / 8000.0, 4)},
     }
+    if world > 1 and not args.no_decode:
+        # tensor-parallel decoder (BASELINE configs[4]): every rank holds its shard, NCCL all-reduce per block
+        from lthn import tp
+        for w in ws:
+            w.free()
+        comm = tp.init_comm(rank, world)
+        dec = run_decode(lthn, GEMMA_27B, f"gemma-style 62L/5376 (BASELINE configs[4]), TP{world}", 4096, 512,
+                         32 if args.full else 1, peak, comm=comm, rank=rank, world=world)
+        if rank == 0:
+            line["decode_tp"] = dec
+        ws = []
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline(sample_rows=65536, threads=1)
-        if not args.no_sweep:
+        if not args.no_sweep and world == 1:
             line["sweep"] = run_sweep(lthn, st, peak, args.full)
         if not args.no_decode and world == 1:
             for w in ws:
                 w.free()
+            ws = []
             line["decode"] = [run_decode(lthn, GEMMA_2B, "gemma-style 26L/2304 (BASELINE configs[3])", 1024, 256, 16, peak)]
             if args.full:
                 line["decode"].append(run_decode(lthn, GEMMA_27B, "gemma-style 62L/5376 (BASELINE configs[4])", 4096, 512, 32, peak))
@@ -337,8 +349,8 @@ def run_ours(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one lm_head launch (ncu capture
-# summarised in profiles/affine_qmv_lm_head_M1.md)
-TRAFFIC_BYTES_PER_LAUNCH = 344687616
+# summarised in profiles/affine_qmv_dp4a_lm_head_M1.md)
+TRAFFIC_BYTES_PER_LAUNCH = 346665728
 
 
 # ------------------------------------------------------------- reference ----

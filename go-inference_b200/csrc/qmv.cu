@@ -484,11 +484,13 @@ static int g_force_rt = 0, g_force_warps = 0, g_force_kernel = 0;
 // tensor-core kernel (f32 activations are first split into bf16 columns).
 int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
     const int fuse = c.wq2 ? 1 : 0;
-    // Measured on B200: the dp4a kernel wins on large matrices (it streams at ~4.5 TB/s where
-    // the tensor-core kernel is capped near 3 TB/s by the mma.sync issue rate) and on long
-    // rows; small matrices are launch/latency sized and the tensor-core kernel starts faster.
-    const bool big = (double)c.N * (double)c.K >= 64.0 * 1024 * 1024;
-    const bool prefer_dp4a = g_force_kernel == 1 || (g_force_kernel == 0 && (big || (c.K >= 8192 && c.N <= 4096)));
+    // Measured on B200: the dp4a kernel wins once a matrix is large enough to amortise its
+    // activation conversion (it streams at ~4.5 TB/s where the tensor-core kernel is capped near
+    // 3 TB/s by the mma.sync issue rate); small matrices are launch/latency sized and the
+    // tensor-core kernel, with every group in flight at once, starts and finishes sooner.
+    const double wbytes = (double)c.N * (double)c.K * 0.5625 * (fuse ? 2 : 1);
+    const bool big = wbytes >= 28e6 || (wbytes >= 12e6 && c.K >= 4096);
+    const bool prefer_dp4a = g_force_kernel == 1 || (g_force_kernel == 0 && big);
     if (prefer_dp4a && c.M <= 2) {
         Dp4aPlan plan;
         bool aligned = (((uintptr_t)c.wq | (uintptr_t)c.x | (uintptr_t)c.scales | (uintptr_t)c.biases) & 15) == 0;
