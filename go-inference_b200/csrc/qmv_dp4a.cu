@@ -26,8 +26,8 @@
 // group) and then streams row blocks of S*R rows, R rows per thread in flight plus
 // the next block prefetched into a second register set. The partial sums of a row's
 // threads are folded inside each quad with shuffles, meet in shared memory (double
-// buffered, one __syncthreads per row block) and are added in a fixed order by one
-// thread per output, so results are deterministic.
+// in a ring published through mbarriers, no block-wide barrier) and are added in a fixed
+// order by one thread per output, so results are deterministic.
 #include "common.cuh"
 #include "qmv.hpp"
 
@@ -120,9 +120,11 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
     const int sb_bytes = (RB * sbrow + 15) & ~15;       // section size, 16-byte aligned
     const int set_bytes = codes_bytes + 2 * sb_bytes;
     const int stage_bytes = SETS * set_bytes;
-    float* part = (float*)dsm;                                               // [2][V*S][T4]
+    constexpr int PR = 8;  // ring of partial-sum buffers; must be at least 2*STG (see below)
+    float* part = (float*)dsm;                                               // [PR][V*S][T4]
     uint64_t* full = (uint64_t*)(dsm + a.part_bytes);
     uint64_t* empty = full + STG;
+    uint64_t* pfull = empty + STG;                                           // [PR]
     unsigned char* stages = dsm + a.part_bytes + 128;
     const int ncons = a.cons_threads;                    // consumer threads (multiple of 32)
     const bool producer_warp = tid >= ncons;
@@ -130,6 +132,7 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
 
     if (tid == 0) {
         for (int i = 0; i < STG; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], ncons >> 5); }
+        for (int i = 0; i < PR; i++) mbar_init(&pfull[i], ncons >> 5);
         mbar_fence_init();
     }
     __syncthreads();
@@ -238,7 +241,7 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
             xq[m][j] = (float)isum * sxp[m][j];
         }
 
-    int buf = 0, it = 0;
+    int it = 0;
     for (int b = blockIdx.x; b < a.nblocks; b += stride, it++) {
         const int st = it % STG;
         if (!mbar_wait(&full[st], (it / STG) & 1)) { if (lane == 0) atomicOr(a.status, 64u); break; }
@@ -297,27 +300,35 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
         const float folded = quad_fold<V>(acc, lane);
         const int vi = V == 4 ? (lane & 3) : (V == 2 ? (lane & 1) : 0);
         const bool writer = V == 4 ? true : (V == 2 ? (lane & 2) == 0 : (lane & 3) == 0);
-        if (active && writer) part[((size_t)buf * V * a.S + (size_t)vi * a.S + slot) * T4 + (u >> 2)] = folded;
-        asm volatile("bar.sync 1, %0;" ::"r"(ncons) : "memory");  // consumers only
-        // final sums: one thread per (slot, r, m) output, fixed order over the T_row/4 partials
-        for (int o = tid; o < a.S * R * MT; o += ncons) {
-            const int sl = o / (R * MT), rm = o - sl * (R * MT);  // rm = r*MT + m
-            float v0 = 0.f, v1 = 0.f;
-            const float* p0 = part + ((size_t)buf * V * a.S + (size_t)rm * a.S + sl) * T4;
-            for (int i = 0; i < T4; i++) v0 += p0[i];
-            if (FUSE) {
-                const float* p1 = part + ((size_t)buf * V * a.S + (size_t)(R * MT + rm) * a.S + sl) * T4;
-                for (int i = 0; i < T4; i++) v1 += p1[i];
-                v0 = gelu_tanh_dev(v0) * v1;
-            }
-            const int r = rm / MT, m = rm - r * MT;
-            const int64_t row = (int64_t)b * RB + sl * R + r;
-            if (row < a.N) {
-                if (a.y_dtype == LTHN_DTYPE_BF16) ((uint16_t*)a.y)[(int64_t)m * a.N + row] = f32_to_bf16_bits(v0);
-                else ((float*)a.y)[(int64_t)m * a.N + row] = v0;
+        const int pb = it % PR;
+        if (active && writer) part[((size_t)pb * V * a.S + (size_t)vi * a.S + slot) * T4 + (u >> 2)] = folded;
+        // No block-wide barrier: each warp publishes its partials on the buffer's mbarrier and
+        // moves on; one warp (rotating with the block number) waits for all of them and adds the
+        // T_row/4 partials of every output in a fixed order. A warp can run at most STG blocks
+        // ahead of the slowest one (the weight ring throttles it), so PR >= 2*STG buffers are
+        // never overwritten while they are being summed.
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&pfull[pb])) : "memory");
+        if ((tid >> 5) == it % (ncons >> 5)) {
+            if (!mbar_wait(&pfull[pb], (it / PR) & 1)) { if (lane == 0) atomicOr(a.status, 128u); break; }
+            for (int o = lane; o < a.S * R * MT; o += 32) {
+                const int sl = o / (R * MT), rm = o - sl * (R * MT);  // rm = r*MT + m
+                float v0 = 0.f, v1 = 0.f;
+                const float* p0 = part + ((size_t)pb * V * a.S + (size_t)rm * a.S + sl) * T4;
+                for (int i = 0; i < T4; i++) v0 += p0[i];
+                if (FUSE) {
+                    const float* p1 = part + ((size_t)pb * V * a.S + (size_t)(R * MT + rm) * a.S + sl) * T4;
+                    for (int i = 0; i < T4; i++) v1 += p1[i];
+                    v0 = gelu_tanh_dev(v0) * v1;
+                }
+                const int r = rm / MT, m = rm - r * MT;
+                const int64_t row = (int64_t)b * RB + sl * R + r;
+                if (row < a.N) {
+                    if (a.y_dtype == LTHN_DTYPE_BF16) ((uint16_t*)a.y)[(int64_t)m * a.N + row] = f32_to_bf16_bits(v0);
+                    else ((float*)a.y)[(int64_t)m * a.N + row] = v0;
+                }
             }
         }
-        buf ^= 1;
     }
 }
 
@@ -339,12 +350,8 @@ bool dp4a_plan(int64_t N, int64_t K, int M, int fuse, int force_r, int force_s, 
     // V = sets * R * M partial sums per lane must be 1, 2 or 4
     int maxr = 4 / (sets * M);
     if (J == 2) maxr = std::min(maxr, M == 2 ? 1 : 2);
-    // two rows per thread on large matrices (more CTAs per SM), four where few row blocks exist
-    int R = std::min(maxr, 2);
-    {
-        const int s0 = std::min(32, std::max(1, 288 / T_row));
-        if (maxr >= 4 && (N + (int64_t)s0 * 4 - 1) / ((int64_t)s0 * 4) <= 4 * 148) R = 4;
-    }
+    // four rows per thread where the format allows it (fewer hand-offs per byte)
+    int R = std::min(maxr, 4);
     int S = std::max(1, 288 / T_row);
     S = std::min(S, 32);
     if (force_s > 0 && force_s * T_row <= 352) S = force_s;
@@ -355,16 +362,20 @@ bool dp4a_plan(int64_t N, int64_t K, int M, int fuse, int force_r, int force_s, 
     if ((S * R) % 2) {  // bulk copies of the scale tile need an even number of rows per block
         if (R < maxr) R *= 2; else if (S * T_row * 2 <= 352) S *= 2; else return false;
     }
-    p->J = J; p->R = R; p->T_row = T_row; p->S = S;
-    p->cons_threads = (S * T_row + 31) / 32 * 32;
-    p->threads = p->cons_threads + 32;
-    if (p->threads > 384) return false;
-    p->nblocks = (int)((N + (int64_t)S * R - 1) / ((int64_t)S * R));
-    p->part_bytes = (int)(((size_t)2 * sets * R * M * S * (T_row / 4) * sizeof(float) + 15) / 16 * 16);
-    const size_t RB = (size_t)S * R;
-    const size_t stage = sets * (RB * (K / 2) + 2 * ((RB * G * 2 + 15) / 16 * 16));
-    p->smem = (size_t)p->part_bytes + 128 + 4 * stage;
-    return p->smem <= 200 * 1024;
+    for (;;) {
+        p->J = J; p->R = R; p->T_row = T_row; p->S = S;
+        p->cons_threads = (S * T_row + 31) / 32 * 32;
+        p->threads = p->cons_threads + 32;
+        if (p->threads > 384) return false;
+        p->nblocks = (int)((N + (int64_t)S * R - 1) / ((int64_t)S * R));
+        p->part_bytes = (int)(((size_t)8 * sets * R * M * S * (T_row / 4) * sizeof(float) + 15) / 16 * 16);
+        const size_t RB = (size_t)S * R;
+        const size_t stage = sets * (RB * (K / 2) + 2 * ((RB * G * 2 + 15) / 16 * 16));
+        p->smem = (size_t)p->part_bytes + 128 + 4 * stage;
+        if (p->smem <= 200 * 1024) return true;
+        if (R > 1 && ((S * (R / 2)) % 2 == 0)) { R /= 2; continue; }  // smaller row block, still an even row count
+        return false;
+    }
 }
 
 template <int J, int R, int MT, int FUSE>
