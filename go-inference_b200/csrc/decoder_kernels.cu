@@ -37,6 +37,8 @@ __device__ __forceinline__ double block_sum_f64(double v, double* sh) {
 __global__ void embed_kernel(const int32_t* __restrict__ ids, const uint32_t* __restrict__ packed,
                              const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases, int hidden,
                              int vocab, float embed_scale, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     int id = ids[row];
     if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; stay in bounds regardless
@@ -75,6 +77,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
                                                       const float* __restrict__ w_next, float* __restrict__ out,
                                                       int width, float eps, int mode, uint16_t* __restrict__ cols,
                                                       int split) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ double sh[32];
     const int row = blockIdx.x;
     const float* ar = a + (int64_t)row * width;
@@ -124,6 +128,8 @@ __global__ void qknorm_rope_append_kernel(const float* __restrict__ qkv, const f
                                           float* __restrict__ q_out, uint16_t* __restrict__ kcache,
                                           uint16_t* __restrict__ vcache, int Hq, int Hkv, int D, float eps,
                                           int64_t lane_stride, int max_len) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ double sh[32];
     const int row = blockIdx.x, head = blockIdx.y, i = threadIdx.x, half = D >> 1;
     const int QKV = (Hq + 2 * Hkv) * D;
@@ -208,6 +214,8 @@ __global__ void rmsnorm_rope_kernel(const float* __restrict__ x, const float* __
 // With a single chunk the normalised output is written directly.
 template <int D, int GQ>
 __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int E = D / 8;          // elements per lane
     constexpr int V8 = E / 8;         // 16-byte loads per lane per row
     constexpr int NIT = 512 / D > 0 ? 512 / D : 1;  // positions per lane group: 16*NIT per CTA
@@ -361,6 +369,8 @@ __global__ void __launch_bounds__(128) sdpa_merge_kernel(const float* __restrict
                                                          const int32_t* __restrict__ row_pos, int Hq, int D,
                                                          int nchunks, int chunk_len, float* __restrict__ out,
                                                          uint16_t* __restrict__ cols, int split) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float wgt[1024];
     __shared__ float sden[4];
     const int row = blockIdx.y, qh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -398,6 +408,8 @@ __device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi)
 }
 __global__ void argmax_stage1_kernel(const float* __restrict__ logits, int V, int blocks_per_row,
                                      float* __restrict__ pv, int* __restrict__ pi) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ int si[32];
     const int row = blockIdx.y;
@@ -417,6 +429,8 @@ __global__ void argmax_stage1_kernel(const float* __restrict__ logits, int V, in
 }
 __global__ void argmax_stage2_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int blocks_per_row,
                                      int32_t* __restrict__ out_idx, float* __restrict__ out_val, int index_offset) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     float v = -INFINITY;
     int idx = 0x7fffffff;
@@ -438,8 +452,7 @@ __global__ void advance_kernel(int32_t* row_pos, int32_t* ids, const int32_t* ne
 // ---- launch wrappers ----------------------------------------------------------------------
 int32_t launch_embed(cudaStream_t s, const int32_t* ids, int rows, const uint32_t* packed, const uint16_t* scales,
                      const uint16_t* biases, int hidden, int vocab, float embed_scale, float* out) {
-    embed_kernel<<<rows, 256, 0, s>>>(ids, packed, scales, biases, hidden, vocab, embed_scale, out);
-    LTHN_CUDA_TRY(cudaGetLastError());
+    LTHN_CUDA_TRY(launch_k(embed_kernel, dim3(rows), dim3(256), 0, s, ids, packed, scales, biases, hidden, vocab, embed_scale, out));
     return LTHN_OK;
 }
 
@@ -448,8 +461,7 @@ int32_t launch_rmsnorm(cudaStream_t s, const float* a, float* h, const float* w_
     // one CTA per row; enough threads that each handles two or three elements (the f64 sum of
     // squares and the IEEE divisions are latency, not throughput, so parallelism is what helps)
     const int threads = width >= 2048 ? 1024 : (width >= 512 ? 512 : 256);
-    rmsnorm_kernel<<<rows, threads, 0, s>>>(a, h, w_post, w_next, out, width, eps, mode, cols, split);
-    LTHN_CUDA_TRY(cudaGetLastError());
+    LTHN_CUDA_TRY(launch_k(rmsnorm_kernel, dim3(rows), dim3(threads), 0, s, a, h, w_post, w_next, out, width, eps, mode, cols, split));
     return LTHN_OK;
 }
 
@@ -458,9 +470,8 @@ int32_t launch_qknorm_rope_append(cudaStream_t s, const float* qkv, const float*
                                   float* q_out, uint16_t* kcache, uint16_t* vcache, int rows, int Hq, int Hkv, int D,
                                   float eps, int64_t lane_stride, int max_len) {
     dim3 grid(rows, Hq + 2 * Hkv);
-    qknorm_rope_append_kernel<<<grid, D / 2, 0, s>>>(qkv, q_norm, k_norm, rope_table, row_pos, row_lane, q_out, kcache,
-                                                     vcache, Hq, Hkv, D, eps, lane_stride, max_len);
-    LTHN_CUDA_TRY(cudaGetLastError());
+    LTHN_CUDA_TRY(launch_k(qknorm_rope_append_kernel, grid, dim3(D / 2), 0, s, qkv, q_norm, k_norm, rope_table, row_pos, row_lane,
+                           q_out, kcache, vcache, Hq, Hkv, D, eps, lane_stride, max_len));
     return LTHN_OK;
 }
 
@@ -488,12 +499,11 @@ template <int D>
 static int32_t launch_sdpa_d(cudaStream_t s, const SdpaArgs& a, int rows, int bundle) {
     dim3 grid(a.Hq / bundle, a.nchunks, rows);
     switch (bundle) {
-        case 1: sdpa_decode_kernel<D, 1><<<grid, 128, 0, s>>>(a); break;
-        case 2: if (D <= 256) { sdpa_decode_kernel<(D <= 256 ? D : 64), 2><<<grid, 128, 0, s>>>(a); break; }
-        case 4: if (D <= 128) { sdpa_decode_kernel<(D <= 128 ? D : 64), 4><<<grid, 128, 0, s>>>(a); break; }
+        case 1: LTHN_CUDA_TRY(launch_k(sdpa_decode_kernel<D, 1>, grid, dim3(128), 0, s, a)); break;
+        case 2: if (D <= 256) { LTHN_CUDA_TRY(launch_k(sdpa_decode_kernel<(D <= 256 ? D : 64), 2>, grid, dim3(128), 0, s, a)); break; }
+        case 4: if (D <= 128) { LTHN_CUDA_TRY(launch_k(sdpa_decode_kernel<(D <= 128 ? D : 64), 4>, grid, dim3(128), 0, s, a)); break; }
         default: return fail(LTHN_ERR_INVALID, "sdpa_decode: unsupported head bundle");
     }
-    LTHN_CUDA_TRY(cudaGetLastError());
     return LTHN_OK;
 }
 
@@ -516,8 +526,7 @@ int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D) {
     if (rc) return rc;
     if (a.nchunks > 1) {
         dim3 grid(a.Hq, rows);
-        sdpa_merge_kernel<<<grid, 128, 0, s>>>(a.part, a.row_pos, a.Hq, D, a.nchunks, a.chunk_len, a.out, a.cols, a.split);
-        LTHN_CUDA_TRY(cudaGetLastError());
+        LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel, grid, dim3(128), 0, s, (const float*)a.part, a.row_pos, a.Hq, D, a.nchunks, a.chunk_len, a.out, a.cols, a.split));
     }
     return LTHN_OK;
 }
@@ -526,10 +535,8 @@ int32_t launch_argmax(cudaStream_t s, const float* logits, int rows, int V, floa
                       float* out_val, int index_offset) {
     const int bpr = ARGMAX_BLOCKS;
     dim3 grid(bpr, rows);
-    argmax_stage1_kernel<<<grid, 256, 0, s>>>(logits, V, bpr, pv, pi);
-    LTHN_CUDA_TRY(cudaGetLastError());
-    argmax_stage2_kernel<<<rows, 32, 0, s>>>(pv, pi, bpr, out_idx, out_val, index_offset);
-    LTHN_CUDA_TRY(cudaGetLastError());
+    LTHN_CUDA_TRY(launch_k(argmax_stage1_kernel, grid, dim3(256), 0, s, logits, V, bpr, pv, pi));
+    LTHN_CUDA_TRY(launch_k(argmax_stage2_kernel, dim3(rows), dim3(32), 0, s, (const float*)pv, (const int*)pi, bpr, out_idx, out_val, index_offset));
     return LTHN_OK;
 }
 

@@ -302,7 +302,13 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
 }
 
 static int32_t forward_full(Model* m, int rows, int max_ctx, bool want_logits, int logit_row0) {
-    return forward(m, rows, max_ctx, want_logits, logit_row0);
+    // kernels of a forward are chained with programmatic dependent launch: each one may start
+    // (and prefetch its weights) while its predecessor drains. LTHN_CUDA_NO_PDL=1 turns it off.
+    static const bool pdl = getenv("LTHN_CUDA_NO_PDL") == nullptr;
+    pdl_set(pdl);
+    const int32_t rc = forward(m, rows, max_ctx, want_logits, logit_row0);
+    pdl_set(false);
+    return rc;
 }
 
 // One decode step for `rows` lanes (ids / positions / lanes already in the device buffers),
@@ -318,10 +324,10 @@ static int32_t decode_step(Model* m, int rows) {
     }
     if (m->graphs_off || !m->step_warm[rows]) {
         m->step_warm[rows] = true;
-        return forward(m, rows, m->c.max_len, true, 0);
+        return forward_full(m, rows, m->c.max_len, true, 0);
     }
     LTHN_CUDA_TRY(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
-    const int32_t rc = forward(m, rows, m->c.max_len, true, 0);
+    const int32_t rc = forward_full(m, rows, m->c.max_len, true, 0);
     cudaGraph_t g = nullptr;
     const cudaError_t e = cudaStreamEndCapture(m->stream, &g);
     cudaGraphExec_t ex = nullptr;
@@ -335,7 +341,7 @@ static int32_t decode_step(Model* m, int rows) {
     cudaGetLastError();
     clear_error();
     m->graphs_off = true;  // capture is not possible here: stay eager
-    return forward(m, rows, m->c.max_len, true, 0);
+    return forward_full(m, rows, m->c.max_len, true, 0);
 }
 
 // ---- lanes / sessions ------------------------------------------------------------------

@@ -20,8 +20,9 @@
 //    product does not care about; that is what lets the code pairs come out of
 //    the packed word without any shuffling.
 //  * Per group the f32 accumulator D_g = sum (128+q) x is folded as
-//    acc += scale*D_g + (bias - 128*scale)*X_g with X_g = sum x, which a second
-//    MMA against an all-ones A operand yields in exactly the lanes that need it.
+//    acc += scale*D_g + (bias - 128*scale)*X_g with X_g = sum x, which a second MMA
+//    against an all-ones A operand yields in exactly the lanes that need it (the fused
+//    GeGLU form, whose MMA count is highest, forms X_g with f32 adds and shuffles instead).
 //  * f32 activations are supplied as 2 or 3 bf16 columns (hi/mid/lo split, exact
 //    to 16/24 mantissa bits) whose results are added in the epilogue, so the
 //    tensor-core path keeps f32-grade activations.
@@ -101,6 +102,7 @@ __global__ void __launch_bounds__((RT == 1 && NT == 1) ? (FUSE ? 512 : 1024) : 2
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar;
 
+    pdl_trigger();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int qr = lane >> 2, t = lane & 3;
     const int G = (int)(a.K >> 6);
@@ -179,13 +181,15 @@ __global__ void __launch_bounds__((RT == 1 && NT == 1) ? (FUSE ? 512 : 1024) : 2
     // ---- stream the groups this warp owns, one group prefetched ahead -----------
     uint2 wcur[SETS][RT][2], wnxt[SETS][RT][2];
     uint32_t xcur[NT][8], xnxt[NT][8];
-    auto load_group = [&](int g, uint2 (&w)[SETS][RT][2], uint32_t (&xf)[NT][8]) {
+    auto load_w = [&](int g, uint2 (&w)[SETS][RT][2]) {
 #pragma unroll
         for (int s = 0; s < SETS; s++)
 #pragma unroll
             for (int rt = 0; rt < RT; rt++)
 #pragma unroll
                 for (int h = 0; h < 2; h++) w[s][rt][h] = __ldg((const uint2*)(wrow[s][rt][h] + g * 8));
+    };
+    auto load_x = [&](int g, uint32_t (&xf)[NT][8]) {
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             if (xlive[nt]) {
@@ -197,8 +201,13 @@ __global__ void __launch_bounds__((RT == 1 && NT == 1) ? (FUSE ? 512 : 1024) : 2
         }
     };
 
+    auto load_group = [&](int g, uint2 (&w)[SETS][RT][2], uint32_t (&xf)[NT][8]) { load_w(g, w); load_x(g, xf); };
+
+    // weights do not depend on the previous kernel: fetch the first group before waiting for it
     int g = warp;
-    if (g < G) load_group(g, wcur, xcur);
+    if (g < G) load_w(g, wcur);
+    pdl_wait();
+    if (g < G) load_x(g, xcur);
 
     if (use_tma) {
         if (!mbar_wait(&bar, 0)) {
@@ -212,16 +221,34 @@ __global__ void __launch_bounds__((RT == 1 && NT == 1) ? (FUSE ? 512 : 1024) : 2
         const int gn = g + nwarps;
         if (gn < G) load_group(gn, wnxt, xnxt);
 
-        // X_g for this lane's two accumulator columns via an all-ones A operand
+        // X_g = sum of the group's activations for this lane's two accumulator columns. The
+        // tensor pipe is the scarce resource of this kernel (mma.sync retires one m16n8k16 per
+        // ~8 SM cycles on B200), so the sums are formed with f32 adds and shuffles instead of an
+        // all-ones MMA in the fused two-weight-set kernel, where the MMA count is highest: each lane
+        // adds its 16 values of column qr, the quad completes the group, and the columns 2t and
+        // 2t+1 are fetched from the quads that own them. Elsewhere the all-ones MMA is cheaper.
         float xs[NT][2];
+        constexpr bool FP_SUMS = FUSE == 1 && NT == 1;  // measured: pays only where the MMA count is highest
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-            float d[4] = {0.f, 0.f, 0.f, 0.f};
+            if (FP_SUMS) {
+                float part = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; j++)
-                mma_bf16_16816(d, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u, xcur[nt][2 * j], xcur[nt][2 * j + 1]);
-            xs[nt][0] = d[0];
-            xs[nt][1] = d[1];
+                for (int i = 0; i < 8; i++)
+                    part += __uint_as_float(xcur[nt][i] << 16) + __uint_as_float(xcur[nt][i] & 0xffff0000u);
+                part += __shfl_xor_sync(0xffffffffu, part, 1);
+                part += __shfl_xor_sync(0xffffffffu, part, 2);
+                xs[nt][0] = __shfl_sync(0xffffffffu, part, (2 * t) * 4);
+                xs[nt][1] = __shfl_sync(0xffffffffu, part, (2 * t + 1) * 4);
+            } else {
+                // an all-ones A operand yields the sums in exactly the lanes that need them
+                float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    mma_bf16_16816(d, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u, xcur[nt][2 * j], xcur[nt][2 * j + 1]);
+                xs[nt][0] = d[0];
+                xs[nt][1] = d[1];
+            }
         }
 #pragma unroll
         for (int s = 0; s < SETS; s++)
@@ -327,6 +354,8 @@ __global__ void __launch_bounds__((RT == 1 && NT == 1) ? (FUSE ? 512 : 1024) : 2
 // (x = hi + mid + lo exactly to 8*split mantissa bits).
 __global__ void split_f32_kernel(const float* __restrict__ x, int64_t total, int64_t K, int split,
                                  uint16_t* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
@@ -400,8 +429,7 @@ static int32_t launch_one(cudaStream_t s, const QmvArgs& a, int nwarps) {
     }
     const int64_t tr = 16 * RT;
     const unsigned grid = (unsigned)((a.N + tr - 1) / tr);
-    qmv_mma_kernel<RT, NT, FUSE><<<grid, nwarps * 32, smem, s>>>(a);
-    LTHN_CUDA_TRY(cudaGetLastError());
+    LTHN_CUDA_TRY(launch_k(qmv_mma_kernel<RT, NT, FUSE>, dim3(grid), dim3(nwarps * 32), smem, s, a));
     return LTHN_OK;
 }
 
@@ -467,8 +495,7 @@ int32_t qmv_launch(cudaStream_t s, QmvArgs a, int fuse, int force_rt, int force_
 int32_t split_f32_launch(cudaStream_t s, const float* x, int64_t M, int64_t K, int split, uint16_t* out) {
     const int64_t total = M * K;
     int grid = (int)std::min<int64_t>((total + 255) / 256, 148 * 8);
-    split_f32_kernel<<<grid, 256, 0, s>>>(x, total, K, split, out);
-    LTHN_CUDA_TRY(cudaGetLastError());
+    LTHN_CUDA_TRY(launch_k(split_f32_kernel, dim3(grid), dim3(256), 0, s, x, total, K, split, out));
     return LTHN_OK;
 }
 

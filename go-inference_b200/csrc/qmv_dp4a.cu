@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
     constexpr int V = SETS * R * MT;
     static_assert(V == 1 || V == 2 || V == 4, "1, 2 or 4 partial sums per lane");
     extern __shared__ __align__(16) unsigned char dsm[];
+    pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31;
     const int T_row = a.T_row, T4 = T_row >> 2;
     const int slot = tid / T_row, u = tid - slot * T_row;
@@ -179,7 +180,9 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
     }
 
     // ---- consumers ----------------------------------------------------------------------------
-    // (the producer is already fetching the first row blocks while this conversion runs)
+    // (the producer is already fetching the first row blocks - weights do not depend on the
+    // previous kernel - while the consumers wait for it and convert the activations)
+    pdl_wait();
     // ---- activations -> three int8 digit planes per owned group -------------------------
     int X[MT][J][3][16];
     float sxp[MT][J], xq[MT][J];
@@ -407,8 +410,7 @@ static int32_t launch_dp4a_t(cudaStream_t st, const Dp4aArgs& a, const Dp4aPlan&
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = std::min(p.nblocks, sms * occ);
-    kern<<<grid, p.threads, p.smem, st>>>(a);
-    LTHN_CUDA_TRY(cudaGetLastError());
+    LTHN_CUDA_TRY(launch_k(kern, dim3(grid), dim3(p.threads), p.smem, st, a));
     return LTHN_OK;
 }
 

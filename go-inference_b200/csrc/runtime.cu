@@ -10,6 +10,9 @@
 namespace lthn {
 
 static thread_local std::string g_err;
+static thread_local bool g_pdl = false;
+bool pdl_enabled() { return g_pdl; }
+void pdl_set(bool on) { g_pdl = on; }
 
 int32_t fail(int32_t code, const std::string& msg) { g_err = msg; return code; }
 int32_t cuda_fail(cudaError_t e, const char* what) {
