@@ -115,6 +115,66 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
     }
 }
 
+// Same arithmetic with the row held in registers (up to 8 elements per thread): every
+// global load (activation, residual, both weight vectors) is issued before the first
+// reduction, so the kernel costs one memory round trip instead of three.
+__global__ void __launch_bounds__(1024) rmsnorm_reg_kernel(const float* __restrict__ a, float* __restrict__ h,
+                                                          const float* __restrict__ w_post,
+                                                          const float* __restrict__ w_next, float* __restrict__ out,
+                                                          int width, float eps, int mode, uint16_t* __restrict__ cols,
+                                                          int split) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int MAXE = 8;
+    __shared__ double sh[32];
+    const int row = blockIdx.x;
+    const float* ar = a + (int64_t)row * width;
+    float* hr = h ? h + (int64_t)row * width : nullptr;
+    float* orow = out + (int64_t)row * width;
+    float av[MAXE], hv[MAXE], wp[MAXE], wn[MAXE];
+#pragma unroll
+    for (int k = 0; k < MAXE; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        av[k] = 0.f; hv[k] = 0.f; wp[k] = 0.f; wn[k] = 0.f;
+        if (i < width) {
+            av[k] = ar[i];
+            wp[k] = w_post[i];
+            if (mode) { hv[k] = hr[i]; wn[k] = w_next[i]; }
+        }
+    }
+    double ss = 0.0;
+#pragma unroll
+    for (int k = 0; k < MAXE; k++) ss += (double)__fmul_rn(av[k], av[k]);
+    ss = block_sum_f64(ss, sh);
+    const float rms = (float)sqrt(ss / (double)width + (double)eps);
+    double ss2 = 0.0;
+#pragma unroll
+    for (int k = 0; k < MAXE; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i >= width) continue;
+        const float n = __fmul_rn(__fdiv_rn(av[k], rms), wp[k]);
+        if (mode == 0) {
+            orow[i] = n;
+            if (cols) store_split(cols, split, row, width, i, n);
+        } else {
+            hv[k] = __fadd_rn(hv[k], n);
+            hr[i] = hv[k];
+            ss2 += (double)__fmul_rn(hv[k], hv[k]);
+        }
+    }
+    if (mode == 0) return;
+    ss2 = block_sum_f64(ss2, sh);
+    const float rms2 = (float)sqrt(ss2 / (double)width + (double)eps);
+#pragma unroll
+    for (int k = 0; k < MAXE; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i >= width) continue;
+        const float v = __fmul_rn(__fdiv_rn(hv[k], rms2), wn[k]);
+        orow[i] = v;
+        if (cols) store_split(cols, split, row, width, i, v);
+    }
+}
+
 // ---- per-head RMSNorm + NeoX RoPE + KV append -----------------------------------------
 // qkv: [rows, (Hq + 2*Hkv) * D] f32 (q heads, then k heads, then v heads).
 // q heads -> q_out [rows, Hq*D] f32 (normed, rotated); k heads -> bf16 cache row at the
@@ -364,15 +424,21 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
     }
 }
 
-// stage 2: merge chunk partials with their log-sum-exp weights. One CTA per (head, row).
+// stage 2: merge chunk partials with their log-sum-exp weights. One CTA per (head, row), four
+// warps; warp w takes chunks w, w+4, ... and each lane D/32 consecutive dimensions, so the
+// partial accumulators are read with independent 16-byte loads (several chunks in flight per
+// lane); the four warps' sums meet in shared memory.
+template <int D>
 __global__ void __launch_bounds__(128) sdpa_merge_kernel(const float* __restrict__ part,
-                                                         const int32_t* __restrict__ row_pos, int Hq, int D,
-                                                         int nchunks, int chunk_len, float* __restrict__ out,
+                                                         const int32_t* __restrict__ row_pos, int Hq, int nchunks,
+                                                         int chunk_len, float* __restrict__ out,
                                                          uint16_t* __restrict__ cols, int split) {
     pdl_trigger();
     pdl_wait();
+    constexpr int DL = D / 32;  // dimensions per lane (2, 4, 8 or 16)
     __shared__ float wgt[1024];
     __shared__ float sden[4];
+    __shared__ float acc_s[4][D];
     const int row = blockIdx.y, qh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int ctx = row_pos[row] + 1;
     const int used = min(nchunks, (ctx + chunk_len - 1) / chunk_len);
@@ -389,12 +455,26 @@ __global__ void __launch_bounds__(128) sdpa_merge_kernel(const float* __restrict
     den = warp_sum(den);
     if (lane == 0) sden[warp] = den;
     __syncthreads();
+    float acc[DL];
+#pragma unroll
+    for (int i = 0; i < DL; i++) acc[i] = 0.f;
+#pragma unroll 4
+    for (int c = warp; c < used; c += 4) {
+        const float w = wgt[c];
+        const float2* src = (const float2*)(pa + (int64_t)c * (D + 2) + lane * DL);  // rows are 8-byte aligned
+#pragma unroll
+        for (int i = 0; i < DL / 2; i++) {
+            const float2 v = src[i];
+            acc[2 * i] = fmaf(v.x, w, acc[2 * i]);
+            acc[2 * i + 1] = fmaf(v.y, w, acc[2 * i + 1]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DL; i++) acc_s[warp][lane * DL + i] = acc[i];
+    __syncthreads();
     const float denom = sden[0] + sden[1] + sden[2] + sden[3];
     for (int d = tid; d < D; d += 128) {
-        float v = 0.f;
-#pragma unroll 4
-        for (int c = 0; c < used; c++) v = fmaf(pa[(int64_t)c * (D + 2) + d], wgt[c], v);
-        const float o = v / denom;
+        const float o = (acc_s[0][d] + acc_s[1][d] + acc_s[2][d] + acc_s[3][d]) / denom;
         out[((int64_t)row * Hq + qh) * D + d] = o;
         if (cols) store_split(cols, split, row, Hq * D, qh * D + d, o);
     }
@@ -461,7 +541,10 @@ int32_t launch_rmsnorm(cudaStream_t s, const float* a, float* h, const float* w_
     // one CTA per row; enough threads that each handles two or three elements (the f64 sum of
     // squares and the IEEE divisions are latency, not throughput, so parallelism is what helps)
     const int threads = width >= 2048 ? 1024 : (width >= 512 ? 512 : 256);
-    LTHN_CUDA_TRY(launch_k(rmsnorm_kernel, dim3(rows), dim3(threads), 0, s, a, h, w_post, w_next, out, width, eps, mode, cols, split));
+    if (width <= 8 * threads)
+        LTHN_CUDA_TRY(launch_k(rmsnorm_reg_kernel, dim3(rows), dim3(threads), 0, s, a, h, w_post, w_next, out, width, eps, mode, cols, split));
+    else
+        LTHN_CUDA_TRY(launch_k(rmsnorm_kernel, dim3(rows), dim3(threads), 0, s, a, h, w_post, w_next, out, width, eps, mode, cols, split));
     return LTHN_OK;
 }
 
@@ -526,7 +609,11 @@ int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D) {
     if (rc) return rc;
     if (a.nchunks > 1) {
         dim3 grid(a.Hq, rows);
-        LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel, grid, dim3(128), 0, s, (const float*)a.part, a.row_pos, a.Hq, D, a.nchunks, a.chunk_len, a.out, a.cols, a.split));
+        const float* cpart = a.part;
+        if (D == 64) LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<64>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split));
+        else if (D == 128) LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<128>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split));
+        else if (D == 256) LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<256>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split));
+        else LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<512>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split));
     }
     return LTHN_OK;
 }
