@@ -349,8 +349,8 @@ def run_ours(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one lm_head launch (ncu capture
-# summarised in profiles/affine_qmv_dp4a_lm_head_M1.md)
-TRAFFIC_BYTES_PER_LAUNCH = 346665728
+# summarised in profiles/affine_qmv_i8mma_lm_head_M1.md)
+TRAFFIC_BYTES_PER_LAUNCH = 344690944
 
 
 # ------------------------------------------------------------- reference ----

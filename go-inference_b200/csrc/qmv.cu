@@ -517,6 +517,17 @@ int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
     // tensor-core kernel, with every group in flight at once, starts and finishes sooner.
     const double wbytes = (double)c.N * (double)c.K * 0.5625 * (fuse ? 2 : 1);
     const bool big = wbytes >= 28e6 || (wbytes >= 12e6 && c.K >= 4096);
+    // Batch 1-2: the integer tensor-core kernel serves every shape it can plan (measured faster than
+    // both other kernels from 2 MB matrices to the 340 MB lm_head).
+    if ((g_force_kernel == 3 || g_force_kernel == 0) && c.M <= 2) {
+        I8Plan plan;
+        bool aligned = (((uintptr_t)c.wq | (uintptr_t)c.x | (uintptr_t)c.scales | (uintptr_t)c.biases) & 15) == 0;
+        if (c.wq2) aligned = aligned && (((uintptr_t)c.wq2 | (uintptr_t)c.scales2 | (uintptr_t)c.biases2) & 15) == 0;
+        const bool forced = g_force_kernel == 3;
+        if (aligned && i8_plan(c.N, c.K, c.M, fuse, forced ? g_force_rt : 0, forced ? g_force_warps : 0, &plan))
+            return i8_launch(s, c, plan);
+        if (forced && g_force_warps) return fail(LTHN_ERR_INVALID, "affine_qmv: forced integer tensor-core configuration is not available");
+    }
     const bool prefer_dp4a = g_force_kernel == 1 || (g_force_kernel == 0 && big);
     if (prefer_dp4a && c.M <= 2) {
         Dp4aPlan plan;
@@ -543,7 +554,8 @@ int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
         if (rc) return rc;
         a.x = (const uint16_t*)scratch;
     }
-    return qmv_launch(s, a, fuse, g_force_kernel == 1 ? 0 : g_force_rt, g_force_warps);
+    const bool cfg = g_force_kernel == 2 || g_force_kernel == 0;
+    return qmv_launch(s, a, fuse, cfg ? g_force_rt : 0, cfg ? g_force_warps : 0);
 }
 
 }  // namespace lthn
@@ -558,7 +570,11 @@ void lthn_debug_qmv_force_config(int32_t rt, int32_t nwarps) {
     g_force_rt = rt;
     g_force_warps = nwarps;
 }
-void lthn_debug_qmv_force_kernel(int32_t kernel) { g_force_kernel = kernel; }
+void lthn_debug_qmv_force_kernel(int32_t kernel) {
+    g_force_kernel = kernel & 15;
+    g_i8_probe = (kernel >> 4) & 1;
+    g_i8_stg = (kernel >> 8) & 7;
+}
 
 static int32_t qmv_validate(const void* x, int32_t x_dtype, int32_t M, const void* packed, const void* scales,
                             const void* biases, int64_t N, int64_t K, int32_t gs, int32_t bits, void* y,

@@ -29,6 +29,12 @@ struct Dp4aPlan { int J, R, T_row, S, threads, cons_threads, nblocks, part_bytes
 bool dp4a_plan(int64_t N, int64_t K, int M, int fuse, int force_r, int force_s, Dp4aPlan* p);
 int32_t dp4a_launch(cudaStream_t st, const QmvCall& c, const Dp4aPlan& p);
 
+// Integer tensor-core kernel (1-2 activation rows, N a multiple of 16).
+struct I8Plan { int J, W, RT, stg, RS, nblocks, threads, bs_off, stage_off; size_t smem; };
+extern int g_i8_stg, g_i8_probe;
+bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_rt, int force_w, I8Plan* p);
+int32_t i8_launch(cudaStream_t st, const QmvCall& c, const I8Plan& p);
+
 // Dispatcher used by the C entry points and by the decoder engine.
 int32_t qmv_dispatch(cudaStream_t st, const QmvCall& c);
 

@@ -152,6 +152,39 @@ def test_dp4a_kernel_shapes(oracle, K, N, M):
         lthn.lib().lthn_debug_qmv_force_kernel(0)
 
 
+@pytest.mark.parametrize("K,N", [(2304, 512), (2304, 4112), (9216, 304), (5376, 256), (4096, 128), (2048, 1008),
+                                 (8192, 64), (3072, 96), (128, 48), (64, 16), (1536, 80), (576, 9488)])
+@pytest.mark.parametrize("M", [1, 2])
+def test_i8_tensor_core_kernel_shapes(oracle, K, N, M):
+    """The integer tensor-core batch-1/2 kernel (forced) over the K of the BASELINE models and
+    awkward small ones, f32 and bf16 activations, both tile heights, ragged last row block."""
+    import lthn
+    p, s, b = make_weight(oracle, N, K, seed=K + N)
+    q = lthn.QuantWeight.from_host(p, s, b)
+    xf, xb = make_x(oracle, M, K, seed=M + K)
+    want = oracle.matnt_quant_host(xf, p, s, b, threads=8)
+    L = lthn.lib()
+    L.lthn_debug_qmv_force_kernel(3)
+    try:
+        for rt in (0, 1, 2):
+            L.lthn_debug_qmv_force_config(rt, 0)
+            got = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.F32)
+            assert rms_err(got, want) <= F32_TOL_RMS, rt
+        L.lthn_debug_qmv_force_config(0, 0)
+        x32 = np.random.default_rng(K).standard_normal((M, K)).astype(np.float32)
+        x32[0, :64] *= 1e-4   # a group of tiny activations next to ordinary ones
+        if K >= 128:
+            x32[0, 64:128] = 0.0  # an all-zero group
+        want32 = oracle.matnt_quant_host(x32, p, s, b, threads=8)
+        got32 = run_qmv(lthn, x32, lthn.F32, M, q, lthn.F32)
+        assert rms_err(got32, want32) <= F32_TOL_RMS
+        gotb = run_qmv(lthn, x32, lthn.F32, M, q, lthn.BF16)
+        assert bf16_close(oracle, gotb, want32)
+    finally:
+        L.lthn_debug_qmv_force_config(0, 0)
+        L.lthn_debug_qmv_force_kernel(0)
+
+
 @pytest.mark.parametrize("M", [1, 2, 5])
 @pytest.mark.parametrize("N,K", [(9216, 2304), (1000, 2304), (21504 // 8, 5376)])
 def test_fused_geglu(oracle, M, N, K):
