@@ -184,6 +184,7 @@ def run_decode(lthn, cfg, name, prompt_len, new_tokens, batch, peak, comm=None, 
     m.finalize()
     rng = np.random.default_rng(0)
     out = {"model": name, "prompt": prompt_len, "new_tokens": new_tokens, "tp": world,
+           "tp_exchange": {0: "none", 1: "nccl all-reduce", 2: "peer memory, fused into the residual norm"}[m.tp_exchange],
            "weight_bytes_per_token_per_gpu": decode_weight_bytes(cfg, world)}
     s = m.open_session()
     ids = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)

@@ -175,6 +175,114 @@ __global__ void __launch_bounds__(1024) rmsnorm_reg_kernel(const float* __restri
     }
 }
 
+// ---- tensor-parallel residual RMSNorm over peer memory ---------------------------------
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Exchange protocol. Every rank runs the same sequence of these kernels; exchange number seq
+// (kept in local memory, advanced by the last CTA of each launch) names the current one.
+//  1. the projection kernel before this one (same stream) wrote this rank's partial sums into
+//     its buffer for this call site; the kernel boundary makes them visible;
+//  2. CTA 0 stores seq into element [rank] of every peer's flag array (release, system scope);
+//  3. every CTA waits until all t elements of the local flag array are >= seq (acquire), with a
+//     bounded number of polls: if a peer never arrives the kernel records status bit 256 and goes
+//     on, so that the context stays usable and the host reports the failure;
+//  4. partials are read from the peers' buffers and added in rank order, so every rank computes
+//     bit-identical sums.
+// Buffers are not overwritten early: a rank reuses a call site's buffer only two exchanges later,
+// after it has passed the next exchange, which every peer signals only after finishing this one.
+__global__ void __launch_bounds__(1024) rmsnorm_gather_kernel(const PeerGather pg, float* __restrict__ h,
+                                                             const float* __restrict__ w_post,
+                                                             const float* __restrict__ w_next, float* __restrict__ out,
+                                                             int width, float eps, uint16_t* __restrict__ cols, int split) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int MAXE = 8;
+    __shared__ double sh[32];
+    __shared__ uint32_t seq_s;
+    const int row = blockIdx.x;
+    if (threadIdx.x == 0) seq_s = *(volatile uint32_t*)&pg.ctr[0] + 1u;
+    __syncthreads();
+    const uint32_t seq = seq_s;
+    if (threadIdx.x < pg.t) {
+        if (blockIdx.x == 0) {
+            __threadfence_system();
+            st_release_sys(pg.flag_out[threadIdx.x] + pg.rank, seq);
+        }
+        bool ok = false;
+        for (uint32_t it = 0; it < (1u << 21); ++it) {
+            if ((int32_t)(ld_acquire_sys(pg.flag_in + threadIdx.x) - seq) >= 0) { ok = true; break; }
+            __nanosleep(it < 64 ? 20 : 500);
+        }
+        if (!ok) atomicOr(pg.status, 256u);
+    }
+    __syncthreads();
+    float* hr = h + (int64_t)row * width;
+    float* orow = out + (int64_t)row * width;
+    float av[MAXE], hv[MAXE], wp[MAXE], wn[MAXE];
+#pragma unroll
+    for (int k = 0; k < MAXE; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        av[k] = 0.f; hv[k] = 0.f; wp[k] = 0.f; wn[k] = 0.f;
+        if (i < width) {
+            float pv[8];
+#pragma unroll
+            for (int r = 0; r < 8; r++) pv[r] = r < pg.t ? ld_relaxed_sys_f32(pg.part[r] + (int64_t)row * width + i) : 0.f;
+            float sum = pv[0];
+#pragma unroll
+            for (int r = 1; r < 8; r++) if (r < pg.t) sum = __fadd_rn(sum, pv[r]);
+            av[k] = sum;
+            wp[k] = w_post[i]; hv[k] = hr[i]; wn[k] = w_next[i];
+        }
+    }
+    double ss = 0.0;
+#pragma unroll
+    for (int k = 0; k < MAXE; k++) ss += (double)__fmul_rn(av[k], av[k]);
+    ss = block_sum_f64(ss, sh);
+    const float rms = (float)sqrt(ss / (double)width + (double)eps);
+    double ss2 = 0.0;
+#pragma unroll
+    for (int k = 0; k < MAXE; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i >= width) continue;
+        const float n = __fmul_rn(__fdiv_rn(av[k], rms), wp[k]);
+        hv[k] = __fadd_rn(hv[k], n);
+        hr[i] = hv[k];
+        ss2 += (double)__fmul_rn(hv[k], hv[k]);
+    }
+    ss2 = block_sum_f64(ss2, sh);
+    const float rms2 = (float)sqrt(ss2 / (double)width + (double)eps);
+#pragma unroll
+    for (int k = 0; k < MAXE; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i >= width) continue;
+        const float v = __fmul_rn(__fdiv_rn(hv[k], rms2), wn[k]);
+        orow[i] = v;
+        if (cols) store_split(cols, split, row, width, i, v);
+    }
+    // the last CTA to finish advances the sequence number (every CTA read it before arriving)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&pg.ctr[1], 1u) == gridDim.x - 1) {
+            pg.ctr[1] = 0u;
+            __threadfence();
+            *(volatile uint32_t*)&pg.ctr[0] = seq;
+        }
+    }
+}
+
 // ---- per-head RMSNorm + NeoX RoPE + KV append -----------------------------------------
 // qkv: [rows, (Hq + 2*Hkv) * D] f32 (q heads, then k heads, then v heads).
 // q heads -> q_out [rows, Hq*D] f32 (normed, rotated); k heads -> bf16 cache row at the
@@ -545,6 +653,15 @@ int32_t launch_rmsnorm(cudaStream_t s, const float* a, float* h, const float* w_
         LTHN_CUDA_TRY(launch_k(rmsnorm_reg_kernel, dim3(rows), dim3(threads), 0, s, a, h, w_post, w_next, out, width, eps, mode, cols, split));
     else
         LTHN_CUDA_TRY(launch_k(rmsnorm_kernel, dim3(rows), dim3(threads), 0, s, a, h, w_post, w_next, out, width, eps, mode, cols, split));
+    return LTHN_OK;
+}
+
+int32_t launch_rmsnorm_gather(cudaStream_t s, const PeerGather& pg, float* h, const float* w_post, const float* w_next,
+                              float* out, int rows, int width, float eps, uint16_t* cols, int split) {
+    if (width > 8192) return fail(LTHN_ERR_INVALID, "rmsnorm_gather: width above 8192");
+    if (pg.t < 2 || pg.t > 8) return fail(LTHN_ERR_INVALID, "rmsnorm_gather: 2 to 8 ranks");
+    const int threads = width >= 2048 ? 1024 : (width >= 512 ? 512 : 256);
+    LTHN_CUDA_TRY(launch_k(rmsnorm_gather_kernel, dim3(rows), dim3(threads), 0, s, pg, h, w_post, w_next, out, width, eps, cols, split));
     return LTHN_OK;
 }
 

@@ -28,6 +28,20 @@ int32_t launch_embed(cudaStream_t s, const int32_t* ids, int rows, const uint32_
                      const uint16_t* biases, int hidden, int vocab, float embed_scale, float* out);
 int32_t launch_rmsnorm(cudaStream_t s, const float* a, float* h, const float* w_post, const float* w_next, float* out,
                        int rows, int width, float eps, int mode, uint16_t* cols = nullptr, int split = 0);
+// Tensor-parallel residual RMSNorm: the row-parallel projection before it left one partial sum
+// per rank; this kernel signals "my partial is complete" to every peer, waits (bounded) for
+// theirs, adds the partials in rank order straight from the peers' memory and then does the
+// residual add and both norms. One kernel instead of all-reduce + norm.
+struct PeerGather {
+    const float* part[8];    // rank r's partial-sum buffer for this call site, as mapped on this GPU
+    uint32_t* flag_out[8];   // rank r's flag array as mapped here; element [rank] is this rank's to write
+    const uint32_t* flag_in; // this rank's flag array (local); element [r] is written by rank r
+    uint32_t* ctr;           // local: [0] sequence number of the last finished exchange, [1] CTA arrivals
+    uint32_t* status;        // device status word (bit 256: a peer's flag did not arrive in time)
+    int t, rank;
+};
+int32_t launch_rmsnorm_gather(cudaStream_t s, const PeerGather& pg, float* h, const float* w_post, const float* w_next,
+                              float* out, int rows, int width, float eps, uint16_t* cols, int split);
 int32_t launch_qknorm_rope_append(cudaStream_t s, const float* qkv, const float* q_norm, const float* k_norm,
                                   const float2* rope_table, const int32_t* row_pos, const int32_t* row_lane,
                                   float* q_out, uint16_t* kcache, uint16_t* vcache, int rows, int Hq, int Hkv, int D,

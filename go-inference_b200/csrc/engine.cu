@@ -112,7 +112,7 @@ struct Model {
     cudaStream_t stream = nullptr;
     // workspace for up to kMaxRows rows
     int32_t *d_ids = nullptr, *d_pos = nullptr, *d_lane = nullptr, *d_next = nullptr;
-    float *h = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *att = nullptr, *a = nullptr, *act = nullptr;
+    float *h = nullptr, *h2 = nullptr, *xn = nullptr, *qkv = nullptr, *q = nullptr, *att = nullptr, *a = nullptr, *act = nullptr;
     uint16_t *xn_cols = nullptr, *att_cols = nullptr;  // bf16 split columns of xn / att for the tensor-core matvec
     float *logits = nullptr, *amax_v = nullptr, *sdpa_part = nullptr, *best_v = nullptr, *gather = nullptr;
     int* amax_i = nullptr;
@@ -126,6 +126,15 @@ struct Model {
     bool graphs_off = false;
     std::mutex mu;
     std::vector<void*> allocs;
+    // tensor-parallel exchange over peer memory (see xchg_setup): one IPC-shared allocation per rank
+    // holding the flag array and one partial-sum buffer per call site (attention output, FFN output)
+    void* x_base = nullptr;
+    void* x_peer[8] = {};
+    uint32_t* x_ctr = nullptr;
+    PeerGather pg[2] = {};
+    float* x_part[2] = {};
+    bool xchg_ready = false;
+    bool fuse_norm = false;  // batch 1-2: norms run inside the matvec that consumes them
 };
 
 template <typename T>
@@ -249,17 +258,32 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
     cudaStream_t s = m->stream;
     const int H = c.hidden, D = c.head_dim;
     int32_t rc;
-    if ((rc = launch_embed(s, m->d_ids, rows, m->embed.wq, m->embed.s, m->embed.b, H, c.vocab, c.embed_scale, m->h))) return rc;
+    // Batch 1-2 on one device: the residual RMSNorm pairs run as the prologue of the matvec that
+    // consumes them (two kernels fewer per block). The residual stream then alternates between
+    // two buffers, because the CTA that stores the updated stream must not overwrite what the
+    // other CTAs of the same kernel are still reading.
+    const bool fn = m->fuse_norm && rows <= 2 && c.tp_size <= 1 && (!want_logits || logit_row0 == 0);
+    float* hcur = m->h;
+    float* halt = m->h2;
+    if ((rc = launch_embed(s, m->d_ids, rows, m->embed.wq, m->embed.s, m->embed.b, H, c.vocab, c.embed_scale, hcur))) return rc;
     const int split = qmv_split_for(rows, LTHN_DTYPE_F32);
-    if ((rc = launch_rmsnorm(s, m->h, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, m->xn, rows, H, c.eps, 0, m->xn_cols, split))) return rc;
+    if (!fn && (rc = launch_rmsnorm(s, m->h, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, m->xn, rows, H, c.eps, 0, m->xn_cols, split))) return rc;
     int chunk_len = 0;
     const int nchunks = sdpa_chunking(max_ctx, D, &chunk_len);
     const size_t need = sdpa_scratch_bytes(rows, m->Hq_l, D, nchunks);
     if (nchunks > 1 && need > m->sdpa_part_bytes) return fail(LTHN_ERR_STATE, "forward: attention scratch too small");
+    NormFuse nf{};
     for (int li = 0; li < c.layers; li++) {
         Layer& L = m->layers[li];
         QmvCall qc{L.qkv.wq, L.qkv.s, L.qkv.b, nullptr, nullptr, nullptr, m->xn, LTHN_DTYPE_F32, m->qkv, LTHN_DTYPE_F32, L.qkv.N, L.qkv.K, rows};
-        qc.x_cols = m->xn_cols; qc.x_split = split;
+        if (fn) {
+            // input norm of this block, preceded (after the first block) by the previous block's post-FFN norm + residual
+            if (li == 0) nf = NormFuse{nullptr, hcur, nullptr, nullptr, L.norm[NORM_INPUT], c.eps};
+            else { nf = NormFuse{m->a, hcur, halt, m->layers[li - 1].norm[NORM_POST_FF], L.norm[NORM_INPUT], c.eps}; std::swap(hcur, halt); }
+            qc.norm = &nf;
+        } else {
+            qc.x_cols = m->xn_cols; qc.x_split = split;
+        }
         if ((rc = qmv_dispatch(s, qc))) return rc;
         uint16_t* kc = m->kcache + (int64_t)li * m->layer_stride;
         uint16_t* vc = m->vcache + (int64_t)li * m->layer_stride;
@@ -268,19 +292,45 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
         SdpaArgs sa{m->q, kc, vc, m->d_pos, m->d_lane, m->att, m->sdpa_part, m->lane_stride, m->Hq_l, m->Hkv_l, nchunks, chunk_len, c.attn_scale};
         sa.cols = m->att_cols; sa.split = split;
         if ((rc = launch_sdpa_decode(s, sa, rows, D))) return rc;
-        QmvCall oc{L.o.wq, L.o.s, L.o.b, nullptr, nullptr, nullptr, m->att, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.o.N, L.o.K, rows};
+        // tensor parallel: row-parallel projections leave partial sums; with the peer-memory exchange
+        // they go to this rank's shared buffer and the norm kernel adds all ranks' partials itself
+        const bool xg = m->xchg_ready;
+        QmvCall oc{L.o.wq, L.o.s, L.o.b, nullptr, nullptr, nullptr, m->att, LTHN_DTYPE_F32, xg ? m->x_part[0] : m->a, LTHN_DTYPE_F32, L.o.N, L.o.K, rows};
         if (nchunks > 1) { oc.x_cols = m->att_cols; oc.x_split = split; }  // the merge stage wrote them
         if ((rc = qmv_dispatch(s, oc))) return rc;
-        if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
-        if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
         QmvCall gc{L.gate.wq, L.gate.s, L.gate.b, L.up.wq, L.up.s, L.up.b, m->xn, LTHN_DTYPE_F32, m->act, LTHN_DTYPE_F32, L.gate.N, L.gate.K, rows};
-        gc.x_cols = m->xn_cols; gc.x_split = split;
+        if (fn) {
+            nf = NormFuse{m->a, hcur, halt, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], c.eps};
+            std::swap(hcur, halt);
+            gc.norm = &nf;
+        } else if (xg) {
+            if ((rc = launch_rmsnorm_gather(s, m->pg[0], m->h, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, m->xn_cols, split))) return rc;
+        } else {
+            if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
+            if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
+        }
+        if (!fn) { gc.x_cols = m->xn_cols; gc.x_split = split; }
         if ((rc = qmv_dispatch(s, gc))) return rc;
-        QmvCall dc{L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, m->act, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.down.N, L.down.K, rows};
+        QmvCall dc{L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, m->act, LTHN_DTYPE_F32, xg ? m->x_part[1] : m->a, LTHN_DTYPE_F32, L.down.N, L.down.K, rows};
         if ((rc = qmv_dispatch(s, dc))) return rc;
-        if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
         const float* next_norm = li + 1 < c.layers ? m->layers[li + 1].norm[NORM_INPUT] : m->final_norm;
-        if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
+        if (fn) {
+            // folded into the next block's QKV matvec (or the lm_head below)
+        } else if (xg) {
+            if ((rc = launch_rmsnorm_gather(s, m->pg[1], m->h, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, m->xn_cols, split))) return rc;
+        } else {
+            if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
+            if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
+        }
+    }
+    if (fn) {
+        if (!want_logits) return LTHN_OK;
+        nf = NormFuse{m->a, hcur, halt, m->layers[c.layers - 1].norm[NORM_POST_FF], m->final_norm, c.eps};
+        QmvCall hc{m->head.wq, m->head.s, m->head.b, nullptr, nullptr, nullptr, m->xn, LTHN_DTYPE_F32, m->logits, LTHN_DTYPE_F32,
+                   m->head.N, m->head.K, rows};
+        hc.norm = &nf;
+        if ((rc = qmv_dispatch(s, hc))) return rc;
+        return launch_argmax(s, m->logits, rows, m->V_l, m->amax_v, m->amax_i, m->d_next, nullptr, 0);
     }
     if (!want_logits) return LTHN_OK;
     const int lr = rows - logit_row0;
@@ -507,7 +557,7 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
     m->lane_used.assign(c.max_lanes, 0);
     const size_t R = kMaxRows;
     if ((rc = dalloc(m, &m->d_ids, R)) || (rc = dalloc(m, &m->d_pos, R)) || (rc = dalloc(m, &m->d_lane, R)) ||
-        (rc = dalloc(m, &m->d_next, R)) || (rc = dalloc(m, &m->h, R * H)) || (rc = dalloc(m, &m->xn, R * H)) ||
+        (rc = dalloc(m, &m->d_next, R)) || (rc = dalloc(m, &m->h, R * H)) || (rc = dalloc(m, &m->h2, R * H)) || (rc = dalloc(m, &m->xn, R * H)) ||
         (rc = dalloc(m, &m->qkv, R * (m->QR_l + 2 * m->KR_l))) || (rc = dalloc(m, &m->q, R * m->QR_l)) ||
         (rc = dalloc(m, &m->att, R * m->QR_l)) || (rc = dalloc(m, &m->a, R * H)) || (rc = dalloc(m, &m->act, R * m->F_l)) ||
         (rc = dalloc(m, &m->xn_cols, R * 3 * H)) || (rc = dalloc(m, &m->att_cols, R * 3 * m->QR_l)) ||
@@ -607,6 +657,87 @@ int32_t lthn_model_synthesize(void* model, uint64_t seed, float sigma) {
     return LTHN_OK;
 }
 
+// Maps every rank's exchange buffer into every other rank (CUDA IPC; one process per GPU) so that
+// the residual RMSNorm can add the ranks' partial sums straight from peer memory. Handles travel
+// through an NCCL all-gather. Any rank that cannot map a peer makes all ranks keep the NCCL
+// all-reduce path (agreed with an all-reduce of a success flag). LTHN_CUDA_TP_NCCL=1 forces that path.
+static int32_t xchg_setup(Model* m) {
+    const auto& c = m->c;
+    const int t = c.tp_size;
+    if (t < 2 || t > 8 || c.hidden > 8192) return LTHN_OK;
+    const char* env = getenv("LTHN_CUDA_TP_NCCL");
+    const bool want = !(env && env[0] == '1');
+    const size_t flag_bytes = 256;
+    const size_t part_bytes = ((size_t)kMaxRows * c.hidden * sizeof(float) + 255) / 256 * 256;
+    const size_t total = flag_bytes + 2 * part_bytes;
+    float ok = want ? 1.f : 0.f;
+    cudaIpcMemHandle_t mine{};
+    if (ok > 0.f) {
+        if (cudaMalloc(&m->x_base, total) != cudaSuccess) { cudaGetLastError(); m->x_base = nullptr; ok = 0.f; }
+    }
+    if (ok > 0.f) {
+        if (cudaMemsetAsync(m->x_base, 0, total, m->stream) != cudaSuccess || cudaIpcGetMemHandle(&mine, m->x_base) != cudaSuccess) {
+            cudaGetLastError();
+            ok = 0.f;
+        }
+    }
+    int32_t rc;
+    // gather the handles (64 bytes = 16 floats per rank) and a success flag
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    float* d_buf = nullptr;
+    const size_t per = 16 + 1;
+    if ((rc = dalloc(m, &d_buf, per * (1 + (size_t)t)))) return rc;
+    float h_send[17];
+    memcpy(h_send, &mine, 64);
+    h_send[16] = ok;
+    LTHN_CUDA_TRY(cudaMemcpyAsync(d_buf, h_send, sizeof(h_send), cudaMemcpyHostToDevice, m->stream));
+    if ((rc = nccl_check(g_nccl.AllGather(d_buf, d_buf + per, per, kNcclFloat32, m->comm, m->stream), "ncclAllGather"))) return rc;
+    std::vector<float> h_all(per * t);
+    LTHN_CUDA_TRY(cudaMemcpyAsync(h_all.data(), d_buf + per, per * t * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    bool all_ok = true;
+    for (int r = 0; r < t; r++) all_ok = all_ok && h_all[per * r + 16] > 0.f;
+    float mapped = all_ok ? 1.f : 0.f;
+    if (all_ok) {
+        for (int r = 0; r < t && mapped > 0.f; r++) {
+            if (r == c.tp_rank) { m->x_peer[r] = m->x_base; continue; }
+            cudaIpcMemHandle_t hd;
+            memcpy(&hd, &h_all[per * r], 64);
+            if (cudaIpcOpenMemHandle(&m->x_peer[r], hd, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                cudaGetLastError();
+                m->x_peer[r] = nullptr;
+                mapped = 0.f;
+            }
+        }
+    }
+    // second round: did every rank map every peer?
+    LTHN_CUDA_TRY(cudaMemcpyAsync(d_buf, &mapped, sizeof(float), cudaMemcpyHostToDevice, m->stream));
+    if ((rc = nccl_check(g_nccl.AllGather(d_buf, d_buf + per, 1, kNcclFloat32, m->comm, m->stream), "ncclAllGather"))) return rc;
+    LTHN_CUDA_TRY(cudaMemcpyAsync(h_all.data(), d_buf + per, t * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    for (int r = 0; r < t; r++) all_ok = all_ok && h_all[r] > 0.f;
+    if (!all_ok) return LTHN_OK;  // NCCL all-reduce path stays in use
+    if ((rc = dalloc(m, &m->x_ctr, 64))) return rc;
+    LTHN_CUDA_TRY(cudaMemsetAsync(m->x_ctr, 0, 256, m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    uint32_t* status = device_status_word();
+    if (!status) return fail(LTHN_ERR_CUDA, "model: no device status word");
+    for (int site = 0; site < 2; site++) {
+        PeerGather& g = m->pg[site];
+        g.t = t; g.rank = c.tp_rank;
+        g.flag_in = (const uint32_t*)m->x_base;
+        g.ctr = m->x_ctr;
+        g.status = status;
+        for (int r = 0; r < t; r++) {
+            g.flag_out[r] = (uint32_t*)m->x_peer[r];
+            g.part[r] = (const float*)((const unsigned char*)m->x_peer[r] + flag_bytes + site * part_bytes);
+        }
+        m->x_part[site] = (float*)((unsigned char*)m->x_base + flag_bytes + site * part_bytes);
+    }
+    m->xchg_ready = true;
+    return LTHN_OK;
+}
+
 int32_t lthn_model_finalize(void* model) {
     clear_error();
     Model* m = (Model*)model;
@@ -615,7 +746,17 @@ int32_t lthn_model_finalize(void* model) {
     for (int li = 0; li < m->c.layers; li++)
         for (int r = 0; r < ROLE_COUNT; r++)
             LTHN_REQUIRE(m->layers[li].have[r], "lthn_model_finalize: a layer is missing a linear");
-    if (m->c.tp_size > 1) LTHN_REQUIRE(m->comm != nullptr, "lthn_model_finalize: tensor-parallel model needs a communicator");
+    if (m->c.tp_size > 1) {
+        LTHN_REQUIRE(m->comm != nullptr, "lthn_model_finalize: tensor-parallel model needs a communicator");
+        int32_t rc = xchg_setup(m);
+        if (rc) return rc;
+    }
+    {
+        const char* env = getenv("LTHN_CUDA_NO_NORM_FUSION");
+        const Layer& L0 = m->layers[0];
+        m->fuse_norm = !(env && env[0] == '1') && m->c.tp_size <= 1 && qmv_can_fuse_norm(L0.qkv.N, L0.qkv.K, 2, false) &&
+                       qmv_can_fuse_norm(L0.gate.N, L0.gate.K, 1, true) && qmv_can_fuse_norm(m->head.N, m->head.K, 2, false);
+    }
     m->finalized = true;
     return LTHN_OK;
 }
@@ -627,6 +768,15 @@ int32_t lthn_model_weight_bytes(void* model, uint64_t* bytes) {
     return LTHN_OK;
 }
 
+int32_t lthn_model_tp_exchange(void* model, int32_t* mode) {
+    clear_error();
+    Model* m = (Model*)model;
+    LTHN_REQUIRE(m && mode, "lthn_model_tp_exchange: NULL argument");
+    LTHN_REQUIRE(m->finalized, "lthn_model_tp_exchange: model is not finalized");
+    *mode = m->c.tp_size <= 1 ? 0 : (m->xchg_ready ? 2 : 1);
+    return LTHN_OK;
+}
+
 int32_t lthn_model_destroy(void* model) {
     clear_error();
     Model* m = (Model*)model;
@@ -634,6 +784,9 @@ int32_t lthn_model_destroy(void* model) {
     cudaStreamSynchronize(m->stream);
     for (auto& g : m->step_graph)
         if (g) cudaGraphExecDestroy(g);
+    for (int r = 0; r < 8; r++)
+        if (m->x_peer[r] && m->x_peer[r] != m->x_base) cudaIpcCloseMemHandle(m->x_peer[r]);
+    if (m->x_base) cudaFree(m->x_base);
     for (void* p : m->allocs) cudaFree(p);
     if (m->h_pinned) cudaFreeHost(m->h_pinned);
     cudaStreamDestroy(m->stream);
@@ -900,6 +1053,35 @@ int32_t lthn_rmsnorm_residual(void* stream, const float* a, float* h, const floa
     if (rows == 0) return LTHN_OK;
     LTHN_REQUIRE(a && h && w_post && w_next && out && rows > 0 && width > 0 && eps >= 0, "lthn_rmsnorm_residual: bad arguments");
     return launch_rmsnorm((cudaStream_t)stream, a, h, w_post, w_next, out, rows, width, eps, 1);
+}
+
+// Test hook for the tensor-parallel norm on one GPU: the t "ranks" are t local buffers
+// ([t][rows*width] in parts) and the flags are preset, so nothing waits; checks the rank-order
+// sum and the fused norms. scratch: at least 512 bytes of device memory.
+int32_t lthn_debug_rmsnorm_gather_local(void* stream, const float* parts, int32_t t, void* scratch, float* h,
+                                        const float* w_post, const float* w_next, float* out, int32_t rows,
+                                        int32_t width, float eps) {
+    clear_error();
+    LTHN_REQUIRE(parts && scratch && h && w_post && w_next && out && rows > 0 && width > 0 && t >= 2 && t <= 8,
+                 "lthn_debug_rmsnorm_gather_local: bad arguments");
+    cudaStream_t s = (cudaStream_t)stream;
+    uint32_t init[128] = {};
+    for (int r = 0; r < 8; r++) init[r] = 1u;  // every "peer" already signalled exchange 1
+    LTHN_CUDA_TRY(cudaMemcpyAsync(scratch, init, sizeof(init), cudaMemcpyHostToDevice, s));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(s));
+    PeerGather g{};
+    g.t = t; g.rank = 0;
+    g.flag_in = (const uint32_t*)scratch;
+    g.ctr = (uint32_t*)scratch + 64;
+    g.status = device_status_word();
+    if (!g.status) return fail(LTHN_ERR_CUDA, "no device status word");
+    for (int r = 0; r < t; r++) {
+        g.part[r] = parts + (size_t)r * rows * width;
+        g.flag_out[r] = (uint32_t*)scratch + 16;  // a dummy line: CTA 0 writes its own signal there
+    }
+    int32_t rc = launch_rmsnorm_gather(s, g, h, w_post, w_next, out, rows, width, eps, nullptr, 0);
+    if (rc) return rc;
+    return check_device_status(s);
 }
 
 int32_t lthn_rmsnorm_rope(void* stream, const float* x, const float* w, const int32_t* positions, float* out,

@@ -521,13 +521,20 @@ int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
     // both other kernels from 2 MB matrices to the 340 MB lm_head).
     if ((g_force_kernel == 3 || g_force_kernel == 0) && c.M <= 2) {
         I8Plan plan;
-        bool aligned = (((uintptr_t)c.wq | (uintptr_t)c.x | (uintptr_t)c.scales | (uintptr_t)c.biases) & 15) == 0;
+        bool aligned = (((uintptr_t)c.wq | (uintptr_t)c.scales | (uintptr_t)c.biases) & 15) == 0;
+        if (c.norm) {
+            const NormFuse& n = *c.norm;
+            aligned = aligned && (((uintptr_t)n.a | (uintptr_t)n.h_in | (uintptr_t)n.h_out | (uintptr_t)n.w_post | (uintptr_t)n.w_next) & 7) == 0;
+        } else {
+            aligned = aligned && ((uintptr_t)c.x & 15) == 0;
+        }
         if (c.wq2) aligned = aligned && (((uintptr_t)c.wq2 | (uintptr_t)c.scales2 | (uintptr_t)c.biases2) & 15) == 0;
         const bool forced = g_force_kernel == 3;
         if (aligned && i8_plan(c.N, c.K, c.M, fuse, forced ? g_force_rt : 0, forced ? g_force_warps : 0, &plan))
             return i8_launch(s, c, plan);
         if (forced && g_force_warps) return fail(LTHN_ERR_INVALID, "affine_qmv: forced integer tensor-core configuration is not available");
     }
+    if (c.norm) return fail(LTHN_ERR_INVALID, "affine_qmv: a fused norm prologue needs the batch-1/2 integer tensor-core kernel for this shape");
     const bool prefer_dp4a = g_force_kernel == 1 || (g_force_kernel == 0 && big);
     if (prefer_dp4a && c.M <= 2) {
         Dp4aPlan plan;
@@ -635,6 +642,27 @@ int32_t lthn_affine_qmv_geglu(void* stream, const void* x, int32_t x_dtype, int3
     LTHN_REQUIRE((((uintptr_t)gate_packed | (uintptr_t)up_packed) & 7) == 0 && ((uintptr_t)x & 15) == 0,
                  "affine_qmv_geglu: packed weights must be 8-byte and x 16-byte aligned");
     QmvCall c{gate_packed, gate_scales, gate_biases, up_packed, up_scales, up_biases, x, x_dtype, y, y_dtype, N, K, M};
+    return qmv_dispatch(s, c);
+}
+
+int32_t lthn_affine_qmv_normed(void* stream, const float* a, const float* h_in, float* h_out, const float* w_post,
+                               const float* w_next, float eps, int32_t M, const uint32_t* packed, const uint16_t* scales,
+                               const uint16_t* biases, const uint32_t* up_packed, const uint16_t* up_scales,
+                               const uint16_t* up_biases, int64_t N, int64_t K, void* y, int32_t y_dtype) {
+    clear_error();
+    cudaStream_t s = (cudaStream_t)stream;
+    LTHN_REQUIRE(M >= 0 && N >= 0 && K >= 0, "affine_qmv_normed: negative dimension");
+    if (M == 0 || N == 0) return LTHN_OK;
+    LTHN_REQUIRE(M <= 2, "affine_qmv_normed: at most 2 rows");
+    LTHN_REQUIRE(h_in && w_next && packed && scales && biases && y, "affine_qmv_normed: NULL pointer");
+    LTHN_REQUIRE(!a || (w_post && h_out && h_out != h_in), "affine_qmv_normed: a needs w_post and an h_out that is not h_in");
+    LTHN_REQUIRE(K > 0 && K % 64 == 0 && eps >= 0, "affine_qmv_normed: K must be a positive multiple of 64 and eps non-negative");
+    LTHN_REQUIRE(y_dtype == LTHN_DTYPE_F32 || y_dtype == LTHN_DTYPE_BF16, "affine_qmv_normed: bad y dtype");
+    LTHN_REQUIRE((up_packed == nullptr) == (up_scales == nullptr) && (up_packed == nullptr) == (up_biases == nullptr),
+                 "affine_qmv_normed: give all three up_* tensors or none");
+    NormFuse nf{a, h_in, h_out, w_post, w_next, eps};
+    QmvCall c{packed, scales, biases, up_packed, up_scales, up_biases, nullptr, LTHN_DTYPE_F32, y, y_dtype, N, K, M};
+    c.norm = &nf;
     return qmv_dispatch(s, c);
 }
 

@@ -5,6 +5,22 @@
 
 namespace lthn {
 
+// Optional prologue of the batch-1/2 kernel: the activations are not read from x but computed
+// as the residual RMSNorm pair of the decoder block,
+//     h_new = h_in + norm(a; w_post)      (skipped when a is NULL: h_new = h_in)
+//     x     = norm(h_new; w_next)
+// with the arithmetic of the stand-alone norm kernel (f64 sum of squares, IEEE divide). Every
+// CTA computes the whole vector (it needs the sums), CTA 0 also stores h_new to h_out, which
+// must not alias h_in. Removes one kernel launch per norm from the decode chain.
+struct NormFuse {
+    const float* a;
+    const float* h_in;
+    float* h_out;
+    const float* w_post;
+    const float* w_next;
+    float eps;
+};
+
 // One decode matvec: y[M,N] = x[M,K] * dequant(W)^T, optionally fused with a second
 // weight set as gelu_tanh(W x) * (W2 x). 4-bit codes, group 64.
 struct QmvCall {
@@ -18,7 +34,11 @@ struct QmvCall {
     // m*x_split+j) by the kernel that produced x; used when the tensor-core kernel is chosen
     const uint16_t* x_cols = nullptr;
     int x_split = 0;
+    const NormFuse* norm = nullptr;  // x is ignored when set (integer tensor-core kernel only)
 };
+
+// true when a call of this shape can carry a fused norm prologue
+bool qmv_can_fuse_norm(int64_t N, int64_t K, int M, bool geglu);
 
 // bf16 columns a tensor-core matvec over f32 activations wants per activation row
 int32_t qmv_split_for(int M, int x_dtype);

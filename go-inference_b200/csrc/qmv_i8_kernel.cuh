@@ -1,0 +1,432 @@
+// qmv_i8_kernel.cuh — affine_qmv for one or two activation rows on the integer tensor-core path
+// (mma.sync m16n8k32, u8 x s8 -> s32), written for B200 (sm_100a).
+//
+// Why this shape of kernel. At batch 1 the matvec is a stream of 4-bit codes from HBM; what
+// limits it on the SM is the number of instructions spent per weight byte. One m16n8k32
+// multiplies 16 rows x 32 codes (256 weight bytes) by 8 columns and B200 retires one per
+// 2.5 SM cycles (measured: 105 G/s over 148 SMs, the same rate as the bf16 m16n8k16), four
+// times the rate the HBM stream needs, while unpacking eight codes to bytes costs three
+// logic ops. The activations are converted once per CTA to block fixed point exactly as in
+// the dp4a kernel: for each group g of 64 consecutive k with amax = max|x|,
+//     x_k = sx * (d0_k + d1_k/128 + d2_k/16384) + e_k,   |e_k| <= amax * 2^-22,
+// three int8 digit planes that occupy three of the eight MMA columns (columns 4..6 hold a
+// second activation row). Integer sums are exact; per group and row
+//     y += scale * sx * (I0 + I1/128 + I2/16384) + bias * sum_k x_k
+// is accumulated in f32.
+//
+// Mapping. A row block is 16*RT consecutive rows over the whole K. The K/64 groups are split
+// over W consumer warps, J consecutive groups each, whose digit fragments stay in registers
+// for the life of the CTA. A producer warp stages row blocks with 1-D bulk (TMA) copies, one
+// per row so that rows can sit at a padded stride in shared memory (row stride = 8 words mod
+// 32: the 8-byte fragment loads of a half-warp then hit 32 different banks), through a ring
+// of stages handed over with full/empty mbarriers. Each warp leaves its partial sums for the
+// block in a ring of buffers published through mbarriers; one warp (rotating) adds the W
+// partials of every output in a fixed order, so results are deterministic.
+#pragma once
+#include "common.cuh"
+#include "qmv.hpp"
+
+#include <algorithm>
+#include <map>
+#include <tuple>
+
+namespace lthn {
+
+struct I8Args {
+    const uint32_t* wq[2];
+    const uint16_t* scales[2];
+    const uint16_t* biases[2];
+    const void* x;
+    void* y;
+    int64_t N, K;
+    int x_dtype, y_dtype;
+    int W;        // consumer warps; warp W is the producer
+    int nblocks;  // row blocks
+    int RS;       // shared-memory row stride in bytes
+    int stg;      // ring stages (2..4)
+    int bs_off, stage_off;  // byte offsets into dynamic shared memory
+    int probe;              // 1: consumers skip the arithmetic (memory pipeline only; measurement aid)
+    int fuse_norm;          // 1: activations come from the fused residual RMSNorm prologue (nf)
+    NormFuse nf;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// first MMA of a group: accumulator input is constant zero (no register moves)
+__device__ __forceinline__ void mma_u8s8_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+__device__ __forceinline__ float gelu_tanh_i8(float x) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    return 0.5f * x * (1.0f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+
+__device__ __forceinline__ float bf16f(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+
+// J groups per warp, RT 16-row tiles per row block, MT activation rows (1 or 2),
+// FUSE=1: two weight sets, output gelu_tanh(W1 x) * (W2 x).
+// LB bounds the block size ((W+1)*32 threads) so that small blocks may use many registers.
+template <int J, int RT, int MT, int FUSE, int LB>
+__global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
+    constexpr int SETS = FUSE ? 2 : 1;
+    constexpr int RB = 16 * RT;
+    const int PR = 2 * a.stg;  // ring of partial-sum buffers, twice the stage count (see below)
+    extern __shared__ __align__(128) unsigned char dsm[];
+    pdl_trigger();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int W = a.W;
+    const int64_t K = a.K;
+    const int G = (int)(K >> 6);
+    const int rowbytes = (int)(K >> 1), sbrow = G * 2, RS = a.RS;
+    const int sb_bytes = (RB * sbrow + 15) & ~15;
+    const int set_bytes = RB * RS + 2 * sb_bytes;
+    const int stage_bytes = SETS * set_bytes;
+    const int stg = a.stg;
+    uint64_t* full = (uint64_t*)dsm;
+    uint64_t* empty = full + 4;
+    uint64_t* pfull = full + 8;                    // [PR], PR <= 8
+    double* nsum = (double*)(dsm + 256);           // [2][16] cross-warp sums of the fused norm prologue
+    float* part = (float*)(dsm + 512);             // [PR][W][SETS][RB*MT]
+    unsigned char* Bs = dsm + a.bs_off;            // [W][MT][3][64] conversion scratch, digit bytes in fragment order
+    unsigned char* stages = dsm + a.stage_off;
+    const int stride = gridDim.x;
+
+    if (tid == 0) {
+        for (int i = 0; i < 4; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], W); }
+        for (int i = 0; i < PR; i++) mbar_init(&pfull[i], W);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp >= W) {
+        // ---- producer: weights do not depend on the previous kernel, start at once ------------
+        if (warp > W) return;
+        int it = 0;
+        for (int b = blockIdx.x; b < a.nblocks; b += stride, it++) {
+            const int st = it % stg;
+            if (!mbar_wait(&empty[st], ((it / stg) & 1) ^ 1)) { if (lane == 0) atomicOr(a.status, 32u); break; }
+            unsigned char* sbase = stages + (size_t)st * stage_bytes;
+            const int64_t row0 = (int64_t)b * RB;
+            const int rows = (int)min((int64_t)RB, a.N - row0);  // a multiple of 16
+            if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)(SETS * rows * (rowbytes + 2 * sbrow)));
+            __syncwarp();
+#pragma unroll
+            for (int s = 0; s < SETS; s++) {
+                unsigned char* d = sbase + (size_t)s * set_bytes;
+                for (int r = lane; r < rows; r += 32)
+                    bulk_g2s(d + (size_t)r * RS, (const unsigned char*)a.wq[s] + (row0 + r) * rowbytes, (uint32_t)rowbytes, &full[st]);
+                if (lane == 0)
+                    bulk_g2s(d + (size_t)RB * RS, (const unsigned char*)a.scales[s] + row0 * sbrow, (uint32_t)(rows * sbrow), &full[st]);
+                if (lane == 1)
+                    bulk_g2s(d + (size_t)RB * RS + sb_bytes, (const unsigned char*)a.biases[s] + row0 * sbrow, (uint32_t)(rows * sbrow), &full[st]);
+            }
+        }
+        return;
+    }
+
+    // ---- consumers: activations -> digit fragments (each warp converts the groups it owns) ----
+    pdl_wait();
+    const int gq = lane >> 2, t = lane & 3;
+    // activations of the owned groups: lane holds elements 2*lane, 2*lane+1 of each group
+    float xr[J][MT][2];
+    if (!a.fuse_norm) {
+#pragma unroll
+        for (int j = 0; j < J; j++)
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                const int g = warp * J + j;
+                if (a.x_dtype == LTHN_DTYPE_BF16) {
+                    const uint32_t v = __ldg((const uint32_t*)((const uint16_t*)a.x + (int64_t)m * K + (int64_t)g * 64) + lane);
+                    xr[j][m][0] = __uint_as_float(v << 16);
+                    xr[j][m][1] = __uint_as_float(v & 0xffff0000u);
+                } else {
+                    const float2 v = __ldg((const float2*)((const float*)a.x + (int64_t)m * K + (int64_t)g * 64) + lane);
+                    xr[j][m][0] = v.x; xr[j][m][1] = v.y;
+                }
+            }
+    } else {
+        // fused residual RMSNorm pair (see NormFuse). The W consumer warps cover the whole vector
+        // between them; sums of squares are f64, reduced over the warps through shared memory
+        // with a named barrier that the producer warp does not join.
+        const NormFuse& nf = a.nf;
+        const int nthr = W * 32;
+        float2 wn[J];
+        float hv[J][MT][2];
+#pragma unroll
+        for (int j = 0; j < J; j++) {
+            const int64_t e0 = (int64_t)(warp * J + j) * 64 + 2 * lane;
+            wn[j] = __ldg((const float2*)(nf.w_next + e0));
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                const float2 v = *(const float2*)(nf.h_in + (int64_t)m * K + e0);
+                hv[j][m][0] = v.x; hv[j][m][1] = v.y;
+            }
+        }
+        double ss[MT];
+        if (nf.a) {
+            float2 wp[J];
+#pragma unroll
+            for (int m = 0; m < MT; m++) ss[m] = 0.0;
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                const int64_t e0 = (int64_t)(warp * J + j) * 64 + 2 * lane;
+                wp[j] = __ldg((const float2*)(nf.w_post + e0));
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    const float2 v = *(const float2*)(nf.a + (int64_t)m * K + e0);
+                    xr[j][m][0] = v.x; xr[j][m][1] = v.y;
+                    ss[m] += (double)__fmul_rn(v.x, v.x);
+                    ss[m] += (double)__fmul_rn(v.y, v.y);
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss[m] += __shfl_xor_sync(0xffffffffu, ss[m], o);
+                if (lane == 0) nsum[m * 16 + warp] = ss[m];
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
+            float rms[MT];
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                double tsum = 0.0;
+                for (int w = 0; w < W; w++) tsum += nsum[m * 16 + w];
+                rms[m] = (float)sqrt(tsum / (double)K + (double)nf.eps);
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                const int64_t e0 = (int64_t)(warp * J + j) * 64 + 2 * lane;
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    hv[j][m][0] = __fadd_rn(hv[j][m][0], __fmul_rn(__fdiv_rn(xr[j][m][0], rms[m]), wp[j].x));
+                    hv[j][m][1] = __fadd_rn(hv[j][m][1], __fmul_rn(__fdiv_rn(xr[j][m][1], rms[m]), wp[j].y));
+                    if (blockIdx.x == 0) *(float2*)(nf.h_out + (int64_t)m * K + e0) = make_float2(hv[j][m][0], hv[j][m][1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MT; m++) ss[m] = 0.0;
+#pragma unroll
+        for (int j = 0; j < J; j++)
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                ss[m] += (double)__fmul_rn(hv[j][m][0], hv[j][m][0]);
+                ss[m] += (double)__fmul_rn(hv[j][m][1], hv[j][m][1]);
+            }
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss[m] += __shfl_xor_sync(0xffffffffu, ss[m], o);
+            if (lane == 0) nsum[m * 16 + warp] = ss[m];
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            double tsum = 0.0;
+            for (int w = 0; w < W; w++) tsum += nsum[m * 16 + w];
+            const float rms2 = (float)sqrt(tsum / (double)K + (double)nf.eps);
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                xr[j][m][0] = __fmul_rn(__fdiv_rn(hv[j][m][0], rms2), wn[j].x);
+                xr[j][m][1] = __fmul_rn(__fdiv_rn(hv[j][m][1], rms2), wn[j].y);
+            }
+        }
+    }
+    // B fragments: column n = lane>>2 carries digit plane n&3 of activation row n>>2;
+    // accumulator columns (2t, 2t+1) are planes (0,1) of row t>>1 for even t and (2, none) for odd t.
+    uint32_t bfrag[J][2][2];
+    float cg[J], xsb[J];
+    {
+        const int bm = gq >> 2, bp = gq & 3, dm = t >> 1;
+        unsigned char* Bw = Bs + (size_t)warp * (MT * 192);  // this warp's scratch: [MT][3][64] digit bytes
+#pragma unroll
+        for (int j = 0; j < J; j++) {
+            float sx_d = 0.f, xs_d = 0.f;
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                const float xv[2] = {xr[j][m][0], xr[j][m][1]};
+                const float amax = warp_max(fmaxf(fabsf(xv[0]), fabsf(xv[1])));
+                const float sx = amax * (1.0f / 127.0f);
+                const float inv = amax > 0.f ? 127.0f / amax : 0.f;
+                const float sx1 = sx * (1.0f / 128.0f);
+                int isum = 0;
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    const float x0 = xv[q];
+                    const float d0 = rintf(x0 * inv);
+                    const float r1 = fmaf(-d0, sx, x0);
+                    const float d1 = rintf(r1 * inv * 128.0f);
+                    const float r2 = fmaf(-d1, sx1, r1);
+                    const float d2 = rintf(r2 * inv * 16384.0f);
+                    const int i0 = (int)d0, i1 = (int)d1, i2 = (int)d2;
+                    isum += i0 * 16384 + i1 * 128 + i2;
+                    // element e of the group: word e>>3 of the row piece, nibble e&7. Thread t of a
+                    // fragment owns words 2t (first MMA) and 2t+1 (second); even nibbles feed the
+                    // low k half, odd nibbles the high k half.
+                    const int e = 2 * lane + q;
+                    const int off = ((((e >> 3) & 1) * 4 + (e >> 4)) * 2 + (e & 1)) * 4 + ((e & 7) >> 1);
+                    Bw[m * 192 + off] = (unsigned char)(i0 & 0xff);
+                    Bw[m * 192 + 64 + off] = (unsigned char)(i1 & 0xff);
+                    Bw[m * 192 + 128 + off] = (unsigned char)(i2 & 0xff);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);
+                if (m == dm) { sx_d = sx; xs_d = (float)isum * (sx * (1.0f / 16384.0f)); }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                uint2 v = make_uint2(0u, 0u);
+                if (bp < 3 && bm < MT) v = *(const uint2*)(Bw + bm * 192 + bp * 64 + (h * 4 + t) * 8);
+                bfrag[j][h][0] = v.x;
+                bfrag[j][h][1] = v.y;
+            }
+            __syncwarp();
+            cg[j] = sx_d * ((t & 1) ? (1.0f / 2097152.0f) : (1.0f / 128.0f));
+            xsb[j] = xs_d;
+        }
+    }
+
+    constexpr uint32_t NIB = 0x0F0F0F0Fu;
+    int it = 0;
+    for (int b = blockIdx.x; b < a.nblocks; b += stride, it++) {
+        const int st = it % stg;
+        if (!mbar_wait(&full[st], (it / stg) & 1)) { if (lane == 0) atomicOr(a.status, 64u); break; }
+        const unsigned char* sbase = stages + (size_t)st * stage_bytes;
+        if (a.probe) {
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[st])) : "memory");
+            continue;
+        }
+        float acc[SETS][RT][2], accb[SETS][RT];
+#pragma unroll
+        for (int s = 0; s < SETS; s++)
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++) {
+                acc[s][rt][0] = 0.f; acc[s][rt][1] = 0.f; accb[s][rt] = 0.f;
+                const unsigned char* setp = sbase + (size_t)s * set_bytes;
+                const unsigned char* rowp = setp + (size_t)(rt * 16 + gq) * RS + t * 8 + warp * J * 32;
+                const uint16_t* sp = (const uint16_t*)(setp + (size_t)RB * RS) + (rt * 16 + gq) * G + warp * J;
+                const uint16_t* bp = (const uint16_t*)(setp + (size_t)RB * RS + sb_bytes) + (rt * 16 + gq + 8 * (t & 1)) * G + warp * J;
+#pragma unroll
+                for (int j = 0; j < J; j++) {
+                    const uint2 wa = *(const uint2*)(rowp + j * 32);
+                    const uint2 wb = *(const uint2*)(rowp + (size_t)8 * RS + j * 32);
+                    int c[4];
+                    mma_u8s8_z(c, wa.x & NIB, wb.x & NIB, (wa.x >> 4) & NIB, (wb.x >> 4) & NIB, bfrag[j][0][0], bfrag[j][0][1]);
+                    mma_u8s8(c, wa.y & NIB, wb.y & NIB, (wa.y >> 4) & NIB, (wb.y >> 4) & NIB, bfrag[j][1][0], bfrag[j][1][1]);
+                    const float s0 = bf16f(sp[j]), s1 = bf16f(sp[8 * G + j]);
+                    const float f0 = (float)(c[0] * 128 + c[1]) * cg[j];
+                    const float f1 = (float)(c[2] * 128 + c[3]) * cg[j];
+                    acc[s][rt][0] = fmaf(s0, f0, acc[s][rt][0]);
+                    acc[s][rt][1] = fmaf(s1, f1, acc[s][rt][1]);
+                    accb[s][rt] = fmaf(bf16f(bp[j]), xsb[j], accb[s][rt]);
+                }
+            }
+        // this warp is done reading the stage: hand it back to the producer
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[st])) : "memory");
+        // Lanes t and t^1 hold the two plane halves of the same outputs; even t finishes row gq,
+        // odd t row gq+8 (each also carries that row's bias term).
+        const int pb = it % PR;
+        float* pw = part + ((size_t)(pb * W + warp) * SETS) * (RB * MT);
+#pragma unroll
+        for (int s = 0; s < SETS; s++)
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++) {
+                const bool odd = t & 1;
+                const float send = odd ? acc[s][rt][0] : acc[s][rt][1];
+                const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                const float res = (odd ? acc[s][rt][1] : acc[s][rt][0]) + recv + accb[s][rt];
+                const int m = t >> 1;
+                if (m < MT) pw[(size_t)s * (RB * MT) + (rt * 16 + gq + 8 * (t & 1)) * MT + m] = res;
+            }
+        // No block-wide barrier: each warp publishes its partials on the buffer's mbarrier and moves
+        // on; one warp (rotating with the block number) waits for all of them and adds the W
+        // partials of every output in a fixed order. A warp can run at most stg blocks ahead of the
+        // slowest one (the weight ring throttles it), so PR >= 2*stg buffers are never overwritten
+        // while they are being summed.
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&pfull[pb])) : "memory");
+        if (warp == it % W) {
+            if (!mbar_wait(&pfull[pb], (it / PR) & 1)) { if (lane == 0) atomicOr(a.status, 128u); break; }
+            for (int o = lane; o < RB * MT; o += 32) {
+                const float* p0 = part + ((size_t)pb * W * SETS) * (RB * MT) + o;
+                float v0 = 0.f, v1 = 0.f;
+                for (int w = 0; w < W; w++) v0 += p0[(size_t)w * SETS * (RB * MT)];
+                if (FUSE) {
+                    for (int w = 0; w < W; w++) v1 += p0[((size_t)w * SETS + 1) * (RB * MT)];
+                    v0 = gelu_tanh_i8(v0) * v1;
+                }
+                const int r = o / MT, m = o - r * MT;
+                const int64_t row = (int64_t)b * RB + r;
+                if (row < a.N) {
+                    if (a.y_dtype == LTHN_DTYPE_BF16) ((uint16_t*)a.y)[(int64_t)m * a.N + row] = f32_to_bf16_bits(v0);
+                    else ((float*)a.y)[(int64_t)m * a.N + row] = v0;
+                }
+            }
+        }
+    }
+}
+
+template <int J, int RT, int MT, int FUSE, int LB>
+inline int32_t launch_i8_t(cudaStream_t st, const I8Args& a, const I8Plan& p) {
+    static int attr_dev = -1;
+    int dev = 0;
+    LTHN_CUDA_TRY(cudaGetDevice(&dev));
+    auto kern = qmv_i8_kernel<J, RT, MT, FUSE, LB>;
+    if (attr_dev != dev) {
+        LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        attr_dev = dev;
+    }
+    static std::map<std::tuple<int, int, size_t>, int> occ_cache;
+    const auto key = std::make_tuple(dev, p.threads, p.smem);
+    auto it = occ_cache.find(key);
+    int occ;
+    if (it == occ_cache.end()) {
+        LTHN_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, p.threads, p.smem));
+        if (occ < 1) return fail(LTHN_ERR_CUDA, "affine_qmv: integer tensor-core kernel does not fit on an SM");
+        occ_cache[key] = occ;
+    } else {
+        occ = it->second;
+    }
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = std::min(p.nblocks, sms * occ);
+    LTHN_CUDA_TRY(launch_k(kern, dim3(grid), dim3(p.threads), p.smem, st, a));
+    return LTHN_OK;
+}
+
+template <int J, int LB>
+inline int32_t launch_i8_j(cudaStream_t st, const I8Args& a, const I8Plan& p, int M, int fuse) {
+    // one 16-row tile per row block: taller blocks measured slower (fewer blocks per SM)
+    if (fuse) return M == 1 ? launch_i8_t<J, 1, 1, 1, LB>(st, a, p) : launch_i8_t<J, 1, 2, 1, LB>(st, a, p);
+    if (M == 1) return launch_i8_t<J, 1, 1, 0, LB>(st, a, p);
+    return launch_i8_t<J, 1, 2, 0, LB>(st, a, p);
+}
+
+// block-size classes: up to 4, 8 and 16 consumer warps (plus the producer warp)
+template <int J>
+int32_t launch_i8_w(cudaStream_t st, const I8Args& a, const I8Plan& p, int M, int fuse) {
+    if (p.W <= 4) return launch_i8_j<J, 160>(st, a, p, M, fuse);
+    if (p.W <= 8) return launch_i8_j<J, 288>(st, a, p, M, fuse);
+    if constexpr (J <= 9) return launch_i8_j<J, 544>(st, a, p, M, fuse);
+    return fail(LTHN_ERR_INVALID, "affine_qmv: no integer tensor-core instantiation for this plan");
+}
+
+
+}  // namespace lthn

@@ -94,8 +94,10 @@ class _Sig:
     lthn_affine_qmv_host = (i32, [vp, sz, vp, sz, vp, sz, vp, sz, i64, i64, i32, i32, vp, sz])
     lthn_affine_qmv_noalloc = (i32, [vp, vp, i32, vp, vp, vp, i64, i64, vp])
     lthn_affine_qmv_geglu = (i32, [vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, i64, i64, vp, i32])
+    lthn_affine_qmv_normed = (i32, [vp, vp, vp, vp, vp, vp, f32, i32, vp, vp, vp, vp, vp, vp, i64, i64, vp, i32])
     lthn_rmsnorm = (i32, [vp, vp, vp, vp, i32, i32, f32])
     lthn_rmsnorm_residual = (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32])
+    lthn_debug_rmsnorm_gather_local = (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32])
     lthn_rmsnorm_rope = (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, f32, i32])
     lthn_sdpa_decode = (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, f32, i32])
     lthn_argmax = (i32, [vp, vp, i32, i32, vp])
@@ -105,6 +107,7 @@ class _Sig:
     lthn_model_synthesize = (i32, [vp, u64, f32])
     lthn_model_finalize = (i32, [vp])
     lthn_model_weight_bytes = (i32, [vp, C.POINTER(u64)])
+    lthn_model_tp_exchange = (i32, [vp, C.POINTER(i32)])
     lthn_model_destroy = (i32, [vp])
     lthn_tp_unique_id = (i32, [vp])
     lthn_tp_init = (i32, [i32, i32, vp, pvp])
@@ -426,6 +429,13 @@ class Model:
     def weight_bytes(self):
         v = C.c_uint64()
         check(lib().lthn_model_weight_bytes(self.h, C.byref(v)))
+        return int(v.value)
+
+    @property
+    def tp_exchange(self):
+        """0 single device, 1 NCCL all-reduce, 2 peer-memory exchange fused into the residual norm."""
+        v = C.c_int32()
+        check(lib().lthn_model_tp_exchange(self.h, C.byref(v)))
         return int(v.value)
 
     def open_session(self) -> "Session":

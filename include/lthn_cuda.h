@@ -138,6 +138,20 @@ int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M,
 int32_t lthn_affine_qmv_noalloc(void* stream, const float* x, int32_t M, const uint32_t* packed,
                                 const uint16_t* scales, const uint16_t* biases, int64_t N, int64_t K, float* y);
 
+/* affine_qmv for 1 or 2 rows with the decoder block's residual RMSNorm pair as its prologue:
+ *     h_new = h_in + rmsnorm(a; w_post)        (a == NULL: h_new = h_in, h_out unused)
+ *     y     = dequant(W) * rmsnorm(h_new; w_next)
+ * and h_new stored to h_out (must not alias h_in). Same arithmetic as lthn_rmsnorm_residual
+ * followed by lthn_affine_qmv (hip_gemma4_q4_oracle_test.go:925-951 norms, the HIP affine
+ * projection for the product) in one launch; up_* non-NULL adds the GeGLU epilogue of
+ * lthn_affine_qmv_geglu. 4-bit, group 64, N a multiple of 16, f32 vectors 8-byte aligned.
+ * Returns LTHN_ERR_INVALID for shapes the batch-1/2 kernel does not serve. The fusion itself
+ * has no counterpart in the reference (it runs these steps as separate kernels). */
+int32_t lthn_affine_qmv_normed(void* stream, const float* a, const float* h_in, float* h_out, const float* w_post,
+                               const float* w_next, float eps, int32_t M, const uint32_t* packed, const uint16_t* scales,
+                               const uint16_t* biases, const uint32_t* up_packed, const uint16_t* up_scales,
+                               const uint16_t* up_biases, int64_t N, int64_t K, void* y, int32_t y_dtype);
+
 /* Fused GeGLU pair: y[M,N] = gelu_tanh(x * dequant(Wgate)^T) * (x * dequant(Wup)^T),
  * both weights [N,K], 4 bit, group 64; gate and up rows are streamed together so
  * the activation is read once and the intermediate never reaches memory.
@@ -242,6 +256,11 @@ int32_t lthn_model_upload_norm(void* model, int32_t layer, int32_t role, const f
 int32_t lthn_model_synthesize(void* model, uint64_t seed, float sigma);
 int32_t lthn_model_finalize(void* model);
 int32_t lthn_model_weight_bytes(void* model, uint64_t* bytes);
+/* How a finalized model combines the partial sums of its row-parallel projections:
+ * 0 single device, 1 NCCL all-reduce, 2 peer-memory exchange fused into the residual RMSNorm
+ * (CUDA IPC mappings of every rank's buffer; chosen when every rank could map every peer,
+ * LTHN_CUDA_TP_NCCL=1 forces mode 1). No counterpart in the reference. */
+int32_t lthn_model_tp_exchange(void* model, int32_t* mode);
 int32_t lthn_model_destroy(void* model);   /* TokenModel.Close (engine/model.go:30) */
 
 /* Tensor parallelism over NCCL (the reference is single-device; new functionality).

@@ -53,6 +53,33 @@ def test_rmsnorm_residual_fusion(oracle):
     assert np.array_equal(out.download(np.float32, (rows, width)).view(np.uint32), out_want.view(np.uint32))
 
 
+@pytest.mark.parametrize("t,rows,width", [(2, 1, 2304), (4, 7, 5376), (8, 3, 512)])
+def test_rmsnorm_gather_rank_order_sum(oracle, t, rows, width):
+    """The tensor-parallel norm with its t ranks emulated as t local buffers (flags preset, nothing
+    waits): partial sums added in rank order, then exactly the fused residual norms."""
+    import lthn
+    rng = np.random.default_rng(t)
+    parts = rng.standard_normal((t, rows, width)).astype(np.float32)
+    h = rng.standard_normal((rows, width)).astype(np.float32) * 5
+    w1 = (1 + 0.1 * rng.standard_normal(width)).astype(np.float32)
+    w2 = (1 + 0.1 * rng.standard_normal(width)).astype(np.float32)
+    a = parts[0].copy()
+    for r in range(1, t):
+        a = (a + parts[r]).astype(np.float32)
+    pb, hb, out, scratch = dev(lthn, parts), dev(lthn, h), lthn.Buf(rows * width * 4), lthn.Buf(512)
+    w1b, w2b = dev(lthn, w1), dev(lthn, w2)
+    lthn.check(lthn.lib().lthn_debug_rmsnorm_gather_local(None, pb.ptr, t, scratch.ptr, hb.ptr, w1b.ptr, w2b.ptr, out.ptr,
+                                                         rows, width, 1e-6))
+    h_want = np.stack([h[r] + oracle.rmsnorm(a[r], w1, 1e-6) for r in range(rows)]).astype(np.float32)
+    out_want = np.stack([oracle.rmsnorm(h_want[r], w2, 1e-6) for r in range(rows)])
+    assert np.array_equal(hb.download(np.float32, (rows, width)).view(np.uint32), h_want.view(np.uint32))
+    assert np.array_equal(out.download(np.float32, (rows, width)).view(np.uint32), out_want.view(np.uint32))
+    # a second exchange on the same scratch must see sequence number 2: flags still say 1, so it would
+    # wait; instead check that the kernel advanced its counter exactly once
+    ctr = scratch.download(np.uint32, (128,))
+    assert ctr[64] == 1 and ctr[65] == 0
+
+
 @pytest.mark.parametrize("heads,D,rotary", [(8, 256, 256), (4, 128, 128), (2, 512, 512), (3, 64, 32), (2, 512, 128)])
 def test_rmsnorm_rope_f32(oracle, heads, D, rotary):
     """Per-head RMSNorm + NeoX RoPE vs hipOracleNormRoPEHeads (oracle_test.go:1103-1118):

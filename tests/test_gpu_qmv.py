@@ -185,6 +185,47 @@ def test_i8_tensor_core_kernel_shapes(oracle, K, N, M):
         L.lthn_debug_qmv_force_kernel(0)
 
 
+@pytest.mark.parametrize("M", [1, 2])
+@pytest.mark.parametrize("N,K,geglu", [(4096, 2304, False), (9216, 2304, True), (65536, 2304, False), (1024, 5376, False),
+                                       (512, 4096, True), (304, 9216, False), (64, 128, False)])
+def test_qmv_with_fused_norm_prologue(oracle, M, N, K, geglu):
+    """lthn_affine_qmv_normed against the separate steps: lthn_rmsnorm_residual (bit-exact against
+    the oracle elsewhere) then the oracle matvec on its output; the stored residual stream must be
+    the norm kernel's (f64 sums in another order may move a value by one ulp at most, rarely)."""
+    import lthn
+    L = lthn.lib()
+    rng = np.random.default_rng(N + K + M)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    h = (rng.standard_normal((M, K)) * 5).astype(np.float32)
+    w1 = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    w2 = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    p, s, b = make_weight(oracle, N, K, seed=N)
+    q = lthn.QuantWeight.from_host(p, s, b)
+    up = q2 = None
+    if geglu:
+        up = make_weight(oracle, N, K, seed=N + 1)
+        q2 = lthn.QuantWeight.from_host(*up)
+    ab, hb, h2b, w1b, w2b = (lthn.Buf.from_array(v) for v in (a, h, np.zeros_like(h), w1, w2))
+    y = lthn.Buf(M * N * 4)
+    for with_a in (True, False):
+        h_want = np.stack([h[r] + oracle.rmsnorm(a[r], w1, 1e-6) for r in range(M)]).astype(np.float32) if with_a else h
+        x_want = np.stack([oracle.rmsnorm(h_want[r], w2, 1e-6) for r in range(M)])
+        want = oracle.matnt_quant_host(x_want, p, s, b, threads=8)
+        if geglu:
+            want = oracle.gelu_tanh(want) * oracle.matnt_quant_host(x_want, *up, threads=8)
+        lthn.check(L.lthn_affine_qmv_normed(None, ab.ptr if with_a else None, hb.ptr, h2b.ptr if with_a else None,
+                                            w1b.ptr if with_a else None, w2b.ptr, 1e-6, M, q.packed.ptr, q.scales.ptr, q.biases.ptr,
+                                            q2.packed.ptr if geglu else None, q2.scales.ptr if geglu else None,
+                                            q2.biases.ptr if geglu else None, N, K, y.ptr, lthn.F32))
+        lthn.sync()
+        got = y.download(np.float32, (M, N))
+        assert rms_err(got, want) <= (1e-4 if geglu else F32_TOL_RMS), with_a
+        if with_a:
+            h_got = h2b.download(np.float32, (M, K))
+            assert np.mean(h_got.view(np.uint32) == h_want.view(np.uint32)) >= 0.999
+            assert np.max(np.abs(h_got - h_want)) <= 1e-6 * np.max(np.abs(h_want))
+
+
 @pytest.mark.parametrize("M", [1, 2, 5])
 @pytest.mark.parametrize("N,K", [(9216, 2304), (1000, 2304), (21504 // 8, 5376)])
 def test_fused_geglu(oracle, M, N, K):

@@ -1,6 +1,6 @@
 """Tensor-parallel decoder on 2 GPUs (skipped on a single-GPU box): both ranks hold row/column
-shards of the same synthetic weights, exchange with NCCL all-reduce, and must produce the
-tokens a single GPU produces."""
+shards of the same synthetic weights, combine partial sums over peer memory (and, second run,
+with NCCL all-reduce), and must produce the tokens a single GPU produces."""
 import os
 import socket
 import sys
@@ -22,7 +22,7 @@ def _free_port():
     return p
 
 
-def _run_model(lthn, rank, world, comm, ids, new):
+def _run_model(lthn, rank, world, comm, ids, new, want_mode=None):
     mc = lthn.make_config(CFG["layers"], CFG["hidden"], CFG["q_heads"], CFG["kv_heads"], CFG["head_dim"], CFG["ffn"],
                           CFG["vocab"], len(ids) + new, 1, tp_rank=rank, tp_size=world)
     m = lthn.Model(mc)
@@ -30,6 +30,8 @@ def _run_model(lthn, rank, world, comm, ids, new):
     if comm is not None:
         m.set_comm(comm)
     m.finalize()
+    if want_mode is not None:
+        assert m.tp_exchange == want_mode
     s = m.open_session()
     s.prefill(ids)
     toks = s.decode_greedy(new)
@@ -50,10 +52,13 @@ def _worker(rank, world, port, out):
     try:
         comm = tp.init_comm(rank, world)
         ids = np.random.default_rng(4).integers(0, CFG["vocab"], 45).astype(np.int32)
-        toks = _run_model(lthn, rank, world, comm, ids, 24)
-        solo = _run_model(lthn, 0, 1, None, ids, 24) if rank == 0 else None
+        toks = _run_model(lthn, rank, world, comm, ids, 24, want_mode=2)   # partial sums read from peer memory
+        os.environ["LTHN_CUDA_TP_NCCL"] = "1"
+        toks_nccl = _run_model(lthn, rank, world, comm, ids, 24, want_mode=1)   # NCCL all-reduce path
+        del os.environ["LTHN_CUDA_TP_NCCL"]
+        solo = _run_model(lthn, 0, 1, None, ids, 24, want_mode=0) if rank == 0 else None
         lthn.check(lthn.lib().lthn_tp_destroy(comm))
-        out.put((rank, toks.tolist(), None if solo is None else solo.tolist()))
+        out.put((rank, toks.tolist(), toks_nccl.tolist(), None if solo is None else solo.tolist()))
     finally:
         dist.destroy_process_group()
 
@@ -73,6 +78,7 @@ def test_tp2_tokens_equal_single_gpu():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    (_, t0, solo), (_, t1, _) = res
-    assert t0 == t1          # every rank returns the same tokens
-    assert t0 == solo        # and they are the single-GPU tokens
+    (_, t0, n0, solo), (_, t1, n1, _) = res
+    assert t0 == t1 and n0 == n1   # every rank returns the same tokens
+    assert t0 == solo              # the peer-memory exchange reproduces the single-GPU tokens
+    assert n0 == solo              # and so does the NCCL all-reduce path
