@@ -35,6 +35,11 @@ struct QmvCall {
     const uint16_t* x_cols = nullptr;
     int x_split = 0;
     const NormFuse* norm = nullptr;  // x is ignored when set (integer tensor-core kernel only)
+    // optional: the caller sums K-slice partials itself. When parts is set the kernel may leave
+    // *nparts (1..8) partial results [nparts][M][N] f32 there instead of y; without it a sliced
+    // plan is followed by a small summing kernel.
+    float* parts = nullptr;
+    int* nparts = nullptr;
 };
 
 // true when a call of this shape can carry a fused norm prologue
@@ -50,9 +55,10 @@ bool dp4a_plan(int64_t N, int64_t K, int M, int fuse, int force_r, int force_s, 
 int32_t dp4a_launch(cudaStream_t st, const QmvCall& c, const Dp4aPlan& p);
 
 // Integer tensor-core kernel (1-2 activation rows, N a multiple of 16).
-struct I8Plan { int J, W, RT, stg, RS, nblocks, threads, bs_off, stage_off; size_t smem; };
+struct I8Plan { int J, W, RT, stg, RS, nblocks, threads, bs_off, stage_off, ks, Gs; size_t smem; };
 extern int g_i8_stg, g_i8_probe;
-bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_rt, int force_w, I8Plan* p);
+// max_slices: 1 = whole rows only; > 1 lets the plan cut K into up to that many slices (partial sums)
+bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I8Plan* p, int max_slices = 1);
 int32_t i8_launch(cudaStream_t st, const QmvCall& c, const I8Plan& p);
 
 // Dispatcher used by the C entry points and by the decoder engine.

@@ -47,6 +47,8 @@ struct I8Args {
     int bs_off, stage_off;  // byte offsets into dynamic shared memory
     int probe;              // 1: consumers skip the arithmetic (memory pipeline only; measurement aid)
     int fuse_norm;          // 1: activations come from the fused residual RMSNorm prologue (nf)
+    int ks, Gs;             // K slices (CTA c works on slice c % ks) and groups per slice
+    float* ypart;           // ks > 1: partial sums [ks][M][N] f32 instead of y
     NormFuse nf;
     uint32_t* status;
 };
@@ -88,8 +90,11 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int W = a.W;
     const int64_t K = a.K;
-    const int G = (int)(K >> 6);
-    const int rowbytes = (int)(K >> 1), sbrow = G * 2, RS = a.RS;
+    // K may be cut into ks slices of Gs groups: CTA c streams slice c % ks of its row blocks and leaves
+    // partial sums (small matrices then fill the GPU, long rows fit the shared-memory ring)
+    const int G = (int)(K >> 6), Gs = a.Gs, ks = a.ks;
+    const int slice = blockIdx.x % ks, cta = blockIdx.x / ks;
+    const int rowbytes = Gs * 32, sbrow = Gs * 2, RS = a.RS;
     const int sb_bytes = (RB * sbrow + 15) & ~15;
     const int set_bytes = RB * RS + 2 * sb_bytes;
     const int stage_bytes = SETS * set_bytes;
@@ -101,10 +106,10 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
     float* part = (float*)(dsm + 512);             // [PR][W][SETS][RB*MT]
     unsigned char* Bs = dsm + a.bs_off;            // [W][MT][3][64] conversion scratch, digit bytes in fragment order
     unsigned char* stages = dsm + a.stage_off;
-    const int stride = gridDim.x;
+    const int stride = gridDim.x / ks;
 
     if (tid == 0) {
-        for (int i = 0; i < 4; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], W); }
+        for (int i = 0; i < 4; i++) { mbar_init(&full[i], ks > 1 ? 2 : 1); mbar_init(&empty[i], W); }
         for (int i = 0; i < PR; i++) mbar_init(&pfull[i], W);
         mbar_fence_init();
     }
@@ -114,23 +119,45 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
         // ---- producer: weights do not depend on the previous kernel, start at once ------------
         if (warp > W) return;
         int it = 0;
-        for (int b = blockIdx.x; b < a.nblocks; b += stride, it++) {
+        for (int b = cta; b < a.nblocks; b += stride, it++) {
             const int st = it % stg;
             if (!mbar_wait(&empty[st], ((it / stg) & 1) ^ 1)) { if (lane == 0) atomicOr(a.status, 32u); break; }
             unsigned char* sbase = stages + (size_t)st * stage_bytes;
             const int64_t row0 = (int64_t)b * RB;
             const int rows = (int)min((int64_t)RB, a.N - row0);  // a multiple of 16
-            if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)(SETS * rows * (rowbytes + 2 * sbrow)));
+            if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)(SETS * rows * (rowbytes + (ks > 1 ? 0 : 2 * sbrow))));
             __syncwarp();
 #pragma unroll
             for (int s = 0; s < SETS; s++) {
                 unsigned char* d = sbase + (size_t)s * set_bytes;
+                const unsigned char* wsrc = (const unsigned char*)a.wq[s] + (size_t)slice * rowbytes;
                 for (int r = lane; r < rows; r += 32)
-                    bulk_g2s(d + (size_t)r * RS, (const unsigned char*)a.wq[s] + (row0 + r) * rowbytes, (uint32_t)rowbytes, &full[st]);
-                if (lane == 0)
-                    bulk_g2s(d + (size_t)RB * RS, (const unsigned char*)a.scales[s] + row0 * sbrow, (uint32_t)(rows * sbrow), &full[st]);
-                if (lane == 1)
-                    bulk_g2s(d + (size_t)RB * RS + sb_bytes, (const unsigned char*)a.biases[s] + row0 * sbrow, (uint32_t)(rows * sbrow), &full[st]);
+                    bulk_g2s(d + (size_t)r * RS, wsrc + (row0 + r) * (K >> 1), (uint32_t)rowbytes, &full[st]);
+                if (ks == 1) {
+                    if (lane == 0)
+                        bulk_g2s(d + (size_t)RB * RS, (const unsigned char*)a.scales[s] + row0 * sbrow, (uint32_t)(rows * sbrow), &full[st]);
+                    if (lane == 1)
+                        bulk_g2s(d + (size_t)RB * RS + sb_bytes, (const unsigned char*)a.biases[s] + row0 * sbrow, (uint32_t)(rows * sbrow), &full[st]);
+                }
+            }
+            if (ks > 1) {
+                // a slice of a scale row is too short and too oddly placed for a bulk copy: plain loads
+                // (4 bytes each; G and Gs are even), published with a second arrival on the barrier
+                const int wpr = Gs >> 1;  // words per row
+#pragma unroll
+                for (int s = 0; s < SETS; s++) {
+                    unsigned char* d = sbase + (size_t)s * set_bytes;
+                    uint32_t* ds = (uint32_t*)(d + (size_t)RB * RS);
+                    uint32_t* db = (uint32_t*)(d + (size_t)RB * RS + sb_bytes);
+                    for (int i = lane; i < rows * wpr; i += 32) {
+                        const int r = i / wpr, w = i - r * wpr;
+                        const int64_t e = (row0 + r) * G + (int64_t)slice * Gs;
+                        ds[i] = __ldg((const uint32_t*)(a.scales[s] + e) + w);
+                        db[i] = __ldg((const uint32_t*)(a.biases[s] + e) + w);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[st])) : "memory");
             }
         }
         return;
@@ -146,7 +173,7 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
         for (int j = 0; j < J; j++)
 #pragma unroll
             for (int m = 0; m < MT; m++) {
-                const int g = warp * J + j;
+                const int g = slice * Gs + warp * J + j;
                 if (a.x_dtype == LTHN_DTYPE_BF16) {
                     const uint32_t v = __ldg((const uint32_t*)((const uint16_t*)a.x + (int64_t)m * K + (int64_t)g * 64) + lane);
                     xr[j][m][0] = __uint_as_float(v << 16);
@@ -302,7 +329,7 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
 
     constexpr uint32_t NIB = 0x0F0F0F0Fu;
     int it = 0;
-    for (int b = blockIdx.x; b < a.nblocks; b += stride, it++) {
+    for (int b = cta; b < a.nblocks; b += stride, it++) {
         const int st = it % stg;
         if (!mbar_wait(&full[st], (it / stg) & 1)) { if (lane == 0) atomicOr(a.status, 64u); break; }
         const unsigned char* sbase = stages + (size_t)st * stage_bytes;
@@ -319,8 +346,8 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
                 acc[s][rt][0] = 0.f; acc[s][rt][1] = 0.f; accb[s][rt] = 0.f;
                 const unsigned char* setp = sbase + (size_t)s * set_bytes;
                 const unsigned char* rowp = setp + (size_t)(rt * 16 + gq) * RS + t * 8 + warp * J * 32;
-                const uint16_t* sp = (const uint16_t*)(setp + (size_t)RB * RS) + (rt * 16 + gq) * G + warp * J;
-                const uint16_t* bp = (const uint16_t*)(setp + (size_t)RB * RS + sb_bytes) + (rt * 16 + gq + 8 * (t & 1)) * G + warp * J;
+                const uint16_t* sp = (const uint16_t*)(setp + (size_t)RB * RS) + (rt * 16 + gq) * Gs + warp * J;
+                const uint16_t* bp = (const uint16_t*)(setp + (size_t)RB * RS + sb_bytes) + (rt * 16 + gq + 8 * (t & 1)) * Gs + warp * J;
 #pragma unroll
                 for (int j = 0; j < J; j++) {
                     const uint2 wa = *(const uint2*)(rowp + j * 32);
@@ -328,7 +355,7 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
                     int c[4];
                     mma_u8s8_z(c, wa.x & NIB, wb.x & NIB, (wa.x >> 4) & NIB, (wb.x >> 4) & NIB, bfrag[j][0][0], bfrag[j][0][1]);
                     mma_u8s8(c, wa.y & NIB, wb.y & NIB, (wa.y >> 4) & NIB, (wb.y >> 4) & NIB, bfrag[j][1][0], bfrag[j][1][1]);
-                    const float s0 = bf16f(sp[j]), s1 = bf16f(sp[8 * G + j]);
+                    const float s0 = bf16f(sp[j]), s1 = bf16f(sp[8 * Gs + j]);
                     const float f0 = (float)(c[0] * 128 + c[1]) * cg[j];
                     const float f1 = (float)(c[2] * 128 + c[3]) * cg[j];
                     acc[s][rt][0] = fmaf(s0, f0, acc[s][rt][0]);
@@ -374,7 +401,8 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
                 const int r = o / MT, m = o - r * MT;
                 const int64_t row = (int64_t)b * RB + r;
                 if (row < a.N) {
-                    if (a.y_dtype == LTHN_DTYPE_BF16) ((uint16_t*)a.y)[(int64_t)m * a.N + row] = f32_to_bf16_bits(v0);
+                    if (ks > 1) a.ypart[((int64_t)slice * MT + m) * a.N + row] = v0;
+                    else if (a.y_dtype == LTHN_DTYPE_BF16) ((uint16_t*)a.y)[(int64_t)m * a.N + row] = f32_to_bf16_bits(v0);
                     else ((float*)a.y)[(int64_t)m * a.N + row] = v0;
                 }
             }
@@ -406,7 +434,7 @@ inline int32_t launch_i8_t(cudaStream_t st, const I8Args& a, const I8Plan& p) {
     }
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int grid = std::min(p.nblocks, sms * occ);
+    const int grid = std::max(1, std::min(p.nblocks, sms * occ / p.ks)) * p.ks;
     LTHN_CUDA_TRY(launch_k(kern, dim3(grid), dim3(p.threads), p.smem, st, a));
     return LTHN_OK;
 }

@@ -24,7 +24,7 @@ void clear_error() { g_err.clear(); }
 static const int kMaxDev = 16;
 static std::mutex g_mu;
 static uint32_t* g_status[kMaxDev];
-static const int kSlots = 4;
+static const int kSlots = 5;
 static void* g_scratch[kMaxDev][kSlots];
 static size_t g_scratch_bytes[kMaxDev][kSlots];
 

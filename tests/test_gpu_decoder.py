@@ -54,6 +54,36 @@ def test_prefill_and_decode_match_oracle(oracle, cfg):
     m.close()
 
 
+@pytest.mark.parametrize("cfg", [SMALL, MID], ids=["small", "mid"])
+def test_fused_decode_chain_equals_separate_kernels(oracle, cfg, monkeypatch):
+    """The decode step with the residual norms inside the matvec against the same step built from
+    the separate kernels (switched off by environment at finalize): same tokens, and the cache rows
+    written during decode equal up to rare one-ulp flips (f64 sums are added in another order)."""
+    import lthn
+    w, norms = synth_weights(oracle, lthn, cfg, seed=5, random_norms=True)
+    ids = np.random.default_rng(1).integers(0, cfg["vocab"], 37).astype(np.int32)
+    outs = []
+    for fused in (True, False):
+        if fused:
+            monkeypatch.delenv("LTHN_CUDA_NO_NORM_FUSION", raising=False)
+        else:
+            monkeypatch.setenv("LTHN_CUDA_NO_NORM_FUSION", "1")
+        m = build_device(lthn, cfg, w, norms, 128)
+        s = m.open_session()
+        s.prefill(ids)
+        toks = s.decode_greedy(40)
+        kv = [oracle.bf16_to_f32(s.kv_export(layer, which)) for layer in range(cfg["layers"]) for which in (0, 1)]
+        outs.append((toks, kv))
+        s.close()
+        m.close()
+    (t0, kv0), (t1, kv1) = outs
+    assert list(t0) == list(t1)
+    for a, b in zip(kv0, kv1):
+        assert a.shape == b.shape
+        assert float(np.mean(a != b)) < 0.1
+        assert np.all(np.abs(a - b) <= 2.0 ** -6 * np.abs(b) + 5e-3 * np.max(np.abs(b)))
+
+
 def test_append_equals_prefill_and_chunked_decode(oracle):
     """AppendTokens extends the cache without replaying the prefix; decoding in small
     chunks (how a yield callback is served) gives the same tokens as one call."""

@@ -153,7 +153,8 @@ def test_dp4a_kernel_shapes(oracle, K, N, M):
 
 
 @pytest.mark.parametrize("K,N", [(2304, 512), (2304, 4112), (9216, 304), (5376, 256), (4096, 128), (2048, 1008),
-                                 (8192, 64), (3072, 96), (128, 48), (64, 16), (1536, 80), (576, 9488)])
+                                 (8192, 64), (3072, 96), (128, 48), (64, 16), (1536, 80), (576, 9488),
+                                 (21504, 64), (21504, 5376), (10752, 2304), (9216, 2304), (14336, 4096), (4096, 5008)])
 @pytest.mark.parametrize("M", [1, 2])
 def test_i8_tensor_core_kernel_shapes(oracle, K, N, M):
     """The integer tensor-core batch-1/2 kernel (forced) over the K of the BASELINE models and
