@@ -61,6 +61,9 @@ extern int g_i8_stg, g_i8_probe;
 bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I8Plan* p, int max_slices = 1);
 int32_t i8_launch(cudaStream_t st, const QmvCall& c, const I8Plan& p);
 
+// y[i] = sum over s < ks of part[s*n + i]
+int32_t launch_sum_parts(cudaStream_t st, const float* part, int ks, int64_t n, void* y, int y_dtype);
+
 // Dispatcher used by the C entry points and by the decoder engine.
 int32_t qmv_dispatch(cudaStream_t st, const QmvCall& c);
 

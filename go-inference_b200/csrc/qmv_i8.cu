@@ -47,7 +47,7 @@ static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_
     for (int stg = g_i8_stg >= 2 && g_i8_stg <= 4 ? g_i8_stg : 2; stg >= 2; stg--) {
         const size_t part_bytes = (size_t)2 * stg * W * sets * RB * M * 4;
         const size_t bs_off = 512 + part_bytes;
-        const size_t stage_off = (bs_off + (size_t)W * M * 192 + 127) / 128 * 128;
+        const size_t stage_off = (bs_off + (size_t)W * (M * 192 + J * 32) + 127) / 128 * 128;
         const size_t smem = stage_off + (size_t)stg * stage;
         if (smem > 200 * 1024) continue;
         p->J = J; p->W = W; p->RT = 1; p->stg = stg; p->RS = RS; p->nblocks = nblocks;

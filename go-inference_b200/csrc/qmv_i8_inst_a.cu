@@ -27,6 +27,11 @@ __global__ void sum_parts_kernel(const float* __restrict__ part, int ks, int64_t
     else ((float*)y)[i] = v;
 }
 
+int32_t launch_sum_parts(cudaStream_t st, const float* part, int ks, int64_t n, void* y, int y_dtype) {
+    LTHN_CUDA_TRY(launch_k(sum_parts_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, part, ks, n, y, y_dtype));
+    return LTHN_OK;
+}
+
 int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p) {
     I8Args a{};
     a.wq[0] = c.wq; a.scales[0] = c.scales; a.biases[0] = c.biases;

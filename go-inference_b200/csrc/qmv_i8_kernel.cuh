@@ -79,9 +79,8 @@ __device__ __forceinline__ float bf16f(uint16_t h) { return __uint_as_float((uin
 
 // J groups per warp, RT 16-row tiles per row block, MT activation rows (1 or 2),
 // FUSE=1: two weight sets, output gelu_tanh(W1 x) * (W2 x).
-// LB bounds the block size ((W+1)*32 threads) so that small blocks may use many registers.
-template <int J, int RT, int MT, int FUSE, int LB>
-__global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
+template <int J, int RT, int MT, int FUSE>
+__device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
     constexpr int SETS = FUSE ? 2 : 1;
     constexpr int RB = 16 * RT;
     const int PR = 2 * a.stg;  // ring of partial-sum buffers, twice the stage count (see below)
@@ -278,7 +277,7 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
     float cg[J], xsb[J];
     {
         const int bm = gq >> 2, bp = gq & 3, dm = t >> 1;
-        unsigned char* Bw = Bs + (size_t)warp * (MT * 192);  // this warp's scratch: [MT][3][64] digit bytes
+        unsigned char* Bw = Bs + (size_t)warp * (MT * 192 + J * 32);  // this warp's scratch: [MT][3][64] digit bytes, then [J][4] constants
 #pragma unroll
         for (int j = 0; j < J; j++) {
             float sx_d = 0.f, xs_d = 0.f;
@@ -327,6 +326,17 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
         }
     }
 
+    // With many groups per warp the per-group constants (plane weight, activation sum) go to shared
+    // memory, one pair per (group, t): measured on the lm_head shape, the loop with fewer live
+    // registers runs 13 % faster (54.4 us against 63.0 us on the same GPU).
+    constexpr bool GC_SMEM = J >= 6;
+    const float2* gconst = (const float2*)(Bs + (size_t)warp * (MT * 192 + J * 32) + MT * 192) + t;
+    if (GC_SMEM && gq == 0) {
+#pragma unroll
+        for (int j = 0; j < J; j++) ((float2*)(Bs + (size_t)warp * (MT * 192 + J * 32) + MT * 192))[j * 4 + t] = make_float2(cg[j], xsb[j]);
+    }
+    __syncwarp();
+
     constexpr uint32_t NIB = 0x0F0F0F0Fu;
     int it = 0;
     for (int b = cta; b < a.nblocks; b += stride, it++) {
@@ -356,11 +366,12 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
                     mma_u8s8_z(c, wa.x & NIB, wb.x & NIB, (wa.x >> 4) & NIB, (wb.x >> 4) & NIB, bfrag[j][0][0], bfrag[j][0][1]);
                     mma_u8s8(c, wa.y & NIB, wb.y & NIB, (wa.y >> 4) & NIB, (wb.y >> 4) & NIB, bfrag[j][1][0], bfrag[j][1][1]);
                     const float s0 = bf16f(sp[j]), s1 = bf16f(sp[8 * Gs + j]);
-                    const float f0 = (float)(c[0] * 128 + c[1]) * cg[j];
-                    const float f1 = (float)(c[2] * 128 + c[3]) * cg[j];
+                    const float2 gc = GC_SMEM ? gconst[j * 4] : make_float2(cg[j], xsb[j]);
+                    const float f0 = (float)(c[0] * 128 + c[1]) * gc.x;
+                    const float f1 = (float)(c[2] * 128 + c[3]) * gc.x;
                     acc[s][rt][0] = fmaf(s0, f0, acc[s][rt][0]);
                     acc[s][rt][1] = fmaf(s1, f1, acc[s][rt][1]);
-                    accb[s][rt] = fmaf(bf16f(bp[j]), xsb[j], accb[s][rt]);
+                    accb[s][rt] = fmaf(bf16f(bp[j]), gc.y, accb[s][rt]);
                 }
             }
         // this warp is done reading the stage: hand it back to the producer
@@ -410,12 +421,19 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) {
     }
 }
 
+// LB bounds the block size ((W+1)*32 threads). The small-block variant (up to 4 consumer warps,
+// the long-stream configuration) asks for five blocks per SM, which holds it to 72 registers.
+template <int J, int RT, int MT, int FUSE, int LB>
+__global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) { qmv_i8_body<J, RT, MT, FUSE>(a); }
+template <int J, int RT, int MT, int FUSE>
+__global__ void __launch_bounds__(160, 5) qmv_i8_kernel_small(const I8Args a) { qmv_i8_body<J, RT, MT, FUSE>(a); }
+
 template <int J, int RT, int MT, int FUSE, int LB>
 inline int32_t launch_i8_t(cudaStream_t st, const I8Args& a, const I8Plan& p) {
     static int attr_dev = -1;
     int dev = 0;
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
-    auto kern = qmv_i8_kernel<J, RT, MT, FUSE, LB>;
+    void (*kern)(const I8Args) = LB == 160 ? qmv_i8_kernel_small<J, RT, MT, FUSE> : qmv_i8_kernel<J, RT, MT, FUSE, LB>;
     if (attr_dev != dev) {
         LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));

@@ -186,6 +186,30 @@ def test_i8_tensor_core_kernel_shapes(oracle, K, N, M):
         L.lthn_debug_qmv_force_kernel(0)
 
 
+@pytest.mark.parametrize("M", [3, 4, 5, 6, 7, 8, 9, 11, 16, 18, 32])
+@pytest.mark.parametrize("K,N", [(2304, 528), (2048, 1008), (9216, 304), (5376, 256), (4096, 128), (3072, 96), (128, 48),
+                                 (64, 16)])
+def test_batched_rows_default_dispatch(oracle, K, N, M):
+    """3..32 rows through the default dispatch (one weight pass for all rows), f32 and bf16
+    activations, f32 and bf16 outputs, tiny and all-zero activation groups."""
+    import lthn
+    p, s, b = make_weight(oracle, N, K, seed=K + N)
+    q = lthn.QuantWeight.from_host(p, s, b)
+    xf, xb = make_x(oracle, M, K, seed=M + K)
+    want = oracle.matnt_quant_host(xf, p, s, b, threads=8)
+    got = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.F32)
+    assert rms_err(got, want) <= F32_TOL_RMS
+    x32 = np.random.default_rng(K + M).standard_normal((M, K)).astype(np.float32)
+    x32[M // 2, :64] *= 1e-4   # a group of tiny activations next to ordinary ones
+    if K >= 128:
+        x32[0, 64:128] = 0.0   # an all-zero group
+    want32 = oracle.matnt_quant_host(x32, p, s, b, threads=8)
+    got32 = run_qmv(lthn, x32, lthn.F32, M, q, lthn.F32)
+    assert rms_err(got32, want32) <= F32_TOL_RMS
+    gotb = run_qmv(lthn, x32, lthn.F32, M, q, lthn.BF16)
+    assert bf16_close(oracle, gotb, want32)
+
+
 @pytest.mark.parametrize("M", [1, 2])
 @pytest.mark.parametrize("N,K,geglu", [(4096, 2304, False), (9216, 2304, True), (65536, 2304, False), (1024, 5376, False),
                                        (512, 4096, True), (304, 9216, False), (64, 128, False)])
@@ -227,7 +251,7 @@ def test_qmv_with_fused_norm_prologue(oracle, M, N, K, geglu):
             assert np.max(np.abs(h_got - h_want)) <= 1e-6 * np.max(np.abs(h_want))
 
 
-@pytest.mark.parametrize("M", [1, 2, 5])
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 16, 19])
 @pytest.mark.parametrize("N,K", [(9216, 2304), (1000, 2304), (21504 // 8, 5376)])
 def test_fused_geglu(oracle, M, N, K):
     """gate/up pair with the GeGLU epilogue against gelu_tanh(gate)*up from the oracle
