@@ -530,7 +530,7 @@ int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
         }
         if (c.wq2) aligned = aligned && (((uintptr_t)c.wq2 | (uintptr_t)c.scales2 | (uintptr_t)c.biases2) & 15) == 0;
         const bool forced = g_force_kernel == 3;
-        if (aligned && i8_plan(c.N, c.K, c.M, fuse, forced ? g_force_rt : 0, forced ? g_force_warps : 0, &plan, (forced && g_force_rt > 1 && !c.norm) ? 8 : 1))
+        if (aligned && i8_plan(c.N, c.K, c.M, fuse, forced ? g_force_rt : 0, forced ? g_force_warps : 0, &plan, (forced && g_force_rt > 1 && !c.norm) ? 8 : 1, c.norm != nullptr))
             return i8_launch(s, c, plan);
         if (forced && g_force_warps) return fail(LTHN_ERR_INVALID, "affine_qmv: forced integer tensor-core configuration is not available");
     }

@@ -17,14 +17,17 @@ int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p);
 int g_i8_stg = 0, g_i8_probe = 0;  // measurement aids
 static const int kI8J[] = {1, 2, 3, 4, 6, 7, 8, 9, 12, 16, 18};
 
-static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_w, I8Plan* p) {
+static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_w, bool has_norm, I8Plan* p) {
     // (J, W): W consumer warps of J groups each. Measured on B200: a long stream (many row blocks
     // per SM) runs fastest with few warps per block and many blocks per SM (less hand-off per row
     // block, more independent pipelines: 5.9 TB/s with 4 warps against 4.4 with 12 on the 340 MB
     // lm_head); a small matrix, where each block sees only a few row blocks, finishes sooner with
     // the groups spread over as many warps as possible.
-    const double per_sm = (double)(N / 16) * ks / 148.0;
-    const int target = per_sm < 10.0 ? 16 : (per_sm < 20.0 ? 7 : 4);
+    const int out_rows = fuse == 2 ? 8 : 16;  // output rows per row block (fuse 2: 8 gate + 8 up rows)
+    const double per_sm = (double)(N / out_rows) * ks / 148.0;
+    // measured crossover: about four row blocks per SM; a fused norm prologue is work per warp that
+    // many warps finish sooner, so it moves the crossover up
+    const int target = per_sm < (has_norm ? 16.0 : 4.0) ? 16 : 4;
     int J = 0, W = 0, best = -1;
     for (int cand : kI8J) {
         if (Gs % cand) continue;
@@ -36,12 +39,12 @@ static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_
         if (score > best) { best = score; J = cand; W = w; }
     }
     if (best < 0) return false;
-    const int sets = fuse ? 2 : 1;
+    const int sets = fuse == 1 ? 2 : 1;
     const int rsw = Gs * 8;
     const int padw = ((8 - rsw % 32) + 32) % 32;
     const int RS = (rsw + padw) * 4;
     const int RB = 16;
-    const int nblocks = (int)((N + RB - 1) / RB);
+    const int nblocks = (int)((N + out_rows - 1) / out_rows);
     const size_t sb = ((size_t)RB * Gs * 2 + 15) / 16 * 16;
     const size_t stage = sets * ((size_t)RB * RS + 2 * sb);
     for (int stg = g_i8_stg >= 2 && g_i8_stg <= 4 ? g_i8_stg : 2; stg >= 2; stg--) {
@@ -53,22 +56,25 @@ static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_
         p->J = J; p->W = W; p->RT = 1; p->stg = stg; p->RS = RS; p->nblocks = nblocks;
         p->threads = (W + 1) * 32;
         p->bs_off = (int)bs_off; p->stage_off = (int)stage_off;
-        p->ks = ks; p->Gs = Gs;
+        p->ks = ks; p->Gs = Gs; p->fuse = fuse;
         p->smem = smem;
         return true;
     }
     return false;
 }
 
-bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I8Plan* p, int max_slices) {
+bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I8Plan* p, int max_slices, bool has_norm) {
     if (M < 1 || M > 2 || K % 64 != 0 || N < 16 || N % 16 != 0) return false;
     const int G = (int)(K / 64);
+    // GeGLU pairs: long rows use the interleaved row block (half the shared memory per stage);
+    // measured: K=5376 42 -> 24 us at N=21504, K=2304 slightly slower than two full sets
+    if (fuse) fuse = K >= 4096 ? 2 : 1;
     // Whole rows whenever a 16-row block of the whole K fits the shared-memory ring (K <= 9216).
     // K slices (partial sums + a summing pass) exist for longer rows but were measured slower than
     // the dp4a kernel on every shape tried (K = 10752..21504: 19-32 us against 16-27 us), and
     // slower than whole rows on small matrices, so the dispatcher only uses them when asked to
     // (max_slices > 1). A GeGLU epilogue needs whole rows.
-    if (force_ks <= 1 && i8_plan_slice(N, G, 1, M, fuse, force_w, p)) return true;
+    if (force_ks <= 1 && i8_plan_slice(N, G, 1, M, fuse, force_w, has_norm, p)) return true;
     if (fuse || max_slices <= 1) return false;
     int best_ks = 0, best_d = 1 << 30;
     for (int ks : {2, 3, 4, 6, 8}) {
@@ -77,7 +83,7 @@ bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I
         const int Gs = G / ks;
         if ((Gs & 1) || (G & 1) || Gs < 16) continue;
         I8Plan q;
-        if (!i8_plan_slice(N, Gs, ks, M, 0, force_w, &q)) continue;
+        if (!i8_plan_slice(N, Gs, ks, M, 0, force_w, false, &q)) continue;
         const int d = std::abs(Gs - 48);
         if (d < best_d) { best_d = d; best_ks = ks; *p = q; }
     }
@@ -86,7 +92,7 @@ bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I
 
 bool qmv_can_fuse_norm(int64_t N, int64_t K, int M, bool geglu) {
     I8Plan p;
-    return i8_plan(N, K, M, geglu ? 1 : 0, 0, 0, &p, 1);
+    return i8_plan(N, K, M, geglu ? 1 : 0, 0, 0, &p, 1, true);
 }
 
 int32_t i8_launch(cudaStream_t st, const QmvCall& c, const I8Plan& p) { return i8_launch_args(st, c, p); }

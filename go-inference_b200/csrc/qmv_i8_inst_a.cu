@@ -60,7 +60,7 @@ int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p) {
     if (c.nparts) *c.nparts = p.ks;
     a.status = device_status_word();
     if (!a.status) return fail(LTHN_ERR_CUDA, "affine_qmv: no device status word");
-    const int fuse = c.wq2 ? 1 : 0;
+    const int fuse = c.wq2 ? p.fuse : 0;  // 1: two full sets per row block, 2: interleaved
     int32_t rc = LTHN_ERR_INVALID;
     switch (p.J) {
         case 1: rc = launch_i8_w<1>(st, a, p, c.M, fuse); break;

@@ -78,10 +78,13 @@ __device__ __forceinline__ float gelu_tanh_i8(float x) {
 __device__ __forceinline__ float bf16f(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
 
 // J groups per warp, RT 16-row tiles per row block, MT activation rows (1 or 2),
-// FUSE=1: two weight sets, output gelu_tanh(W1 x) * (W2 x).
+// FUSE != 0: two weight sets, output gelu_tanh(W1 x) * (W2 x). FUSE=1 stages 16 rows of each set
+// per row block (short rows: fewer, fatter blocks); FUSE=2 stages 8 rows of each set as MMA rows
+// 0-7 and 8-15, so a stage is as large as an unfused one (long rows: more blocks fit an SM).
 template <int J, int RT, int MT, int FUSE>
 __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
-    constexpr int SETS = FUSE ? 2 : 1;
+    constexpr int SETS = FUSE == 1 ? 2 : 1;
+    constexpr int OR = FUSE == 2 ? 8 : 16;  // output rows per row block
     constexpr int RB = 16 * RT;
     const int PR = 2 * a.stg;  // ring of partial-sum buffers, twice the stage count (see below)
     extern __shared__ __align__(128) unsigned char dsm[];
@@ -122,12 +125,24 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
             const int st = it % stg;
             if (!mbar_wait(&empty[st], ((it / stg) & 1) ^ 1)) { if (lane == 0) atomicOr(a.status, 32u); break; }
             unsigned char* sbase = stages + (size_t)st * stage_bytes;
-            const int64_t row0 = (int64_t)b * RB;
-            const int rows = (int)min((int64_t)RB, a.N - row0);  // a multiple of 16
+            const int64_t row0 = (int64_t)b * OR;
+            const int rows = FUSE == 2 ? 16 : (int)min((int64_t)RB, a.N - row0);  // a multiple of 16
             if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)(SETS * rows * (rowbytes + (ks > 1 ? 0 : 2 * sbrow))));
             __syncwarp();
+            if (FUSE == 2) {
+                unsigned char* d = sbase;
+                if (lane < 16) {
+                    const int set = lane >> 3, r = lane & 7;
+                    bulk_g2s(d + (size_t)lane * RS, (const unsigned char*)a.wq[set] + (row0 + r) * (K >> 1), (uint32_t)rowbytes, &full[st]);
+                } else if (lane < 20) {
+                    const int set = lane & 1, which = (lane >> 1) & 1;  // which: 0 scales, 1 biases
+                    const uint16_t* src = which ? a.biases[set] : a.scales[set];
+                    bulk_g2s(d + (size_t)RB * RS + (which ? sb_bytes : 0) + (size_t)set * 8 * sbrow,
+                             (const unsigned char*)src + row0 * sbrow, (uint32_t)(8 * sbrow), &full[st]);
+                }
+            }
 #pragma unroll
-            for (int s = 0; s < SETS; s++) {
+            for (int s = 0; s < (FUSE == 2 ? 0 : SETS); s++) {
                 unsigned char* d = sbase + (size_t)s * set_bytes;
                 const unsigned char* wsrc = (const unsigned char*)a.wq[s] + (size_t)slice * rowbytes;
                 for (int r = lane; r < rows; r += 32)
@@ -401,16 +416,19 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&pfull[pb])) : "memory");
         if (warp == it % W) {
             if (!mbar_wait(&pfull[pb], (it / PR) & 1)) { if (lane == 0) atomicOr(a.status, 128u); break; }
-            for (int o = lane; o < RB * MT; o += 32) {
+            for (int o = lane; o < OR * MT; o += 32) {
                 const float* p0 = part + ((size_t)pb * W * SETS) * (RB * MT) + o;
                 float v0 = 0.f, v1 = 0.f;
                 for (int w = 0; w < W; w++) v0 += p0[(size_t)w * SETS * (RB * MT)];
-                if (FUSE) {
+                if (FUSE == 1) {
                     for (int w = 0; w < W; w++) v1 += p0[((size_t)w * SETS + 1) * (RB * MT)];
+                    v0 = gelu_tanh_i8(v0) * v1;
+                } else if (FUSE == 2) {
+                    for (int w = 0; w < W; w++) v1 += p0[(size_t)w * SETS * (RB * MT) + 8 * MT];  // the up row of this gate row
                     v0 = gelu_tanh_i8(v0) * v1;
                 }
                 const int r = o / MT, m = o - r * MT;
-                const int64_t row = (int64_t)b * RB + r;
+                const int64_t row = (int64_t)b * OR + r;
                 if (row < a.N) {
                     if (ks > 1) a.ypart[((int64_t)slice * MT + m) * a.N + row] = v0;
                     else if (a.y_dtype == LTHN_DTYPE_BF16) ((uint16_t*)a.y)[(int64_t)m * a.N + row] = f32_to_bf16_bits(v0);
@@ -460,7 +478,8 @@ inline int32_t launch_i8_t(cudaStream_t st, const I8Args& a, const I8Plan& p) {
 template <int J, int LB>
 inline int32_t launch_i8_j(cudaStream_t st, const I8Args& a, const I8Plan& p, int M, int fuse) {
     // one 16-row tile per row block: taller blocks measured slower (fewer blocks per SM)
-    if (fuse) return M == 1 ? launch_i8_t<J, 1, 1, 1, LB>(st, a, p) : launch_i8_t<J, 1, 2, 1, LB>(st, a, p);
+    if (fuse == 1) return M == 1 ? launch_i8_t<J, 1, 1, 1, LB>(st, a, p) : launch_i8_t<J, 1, 2, 1, LB>(st, a, p);
+    if (fuse == 2) return M == 1 ? launch_i8_t<J, 1, 1, 2, LB>(st, a, p) : launch_i8_t<J, 1, 2, 2, LB>(st, a, p);
     if (M == 1) return launch_i8_t<J, 1, 1, 0, LB>(st, a, p);
     return launch_i8_t<J, 1, 2, 0, LB>(st, a, p);
 }
