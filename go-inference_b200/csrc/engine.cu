@@ -430,9 +430,7 @@ static int32_t feed_lane(Model* m, Lane* ln, const int32_t* ids, int n) {
         const int rows = std::min(kMaxRows, n - off);
         int32_t* hp = m->h_pinned;
         for (int r = 0; r < rows; r++) { hp[r] = ids[off + r]; hp[kMaxRows + r] = ln->pos + r; hp[2 * kMaxRows + r] = ln->id; }
-        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_ids, hp, rows * 4, cudaMemcpyHostToDevice, m->stream));
-        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_pos, hp + kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
-        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_lane, hp + 2 * kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
+        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_ids, hp, 3 * kMaxRows * 4, cudaMemcpyHostToDevice, m->stream));
         const bool last = off + rows >= n;
         if (n == 1) rc = decode_step(m, 1);
         else rc = forward_full(m, rows, ln->pos + rows, last, rows - 1);
@@ -440,13 +438,14 @@ static int32_t feed_lane(Model* m, Lane* ln, const int32_t* ids, int n) {
         ln->pos += rows;
         if (last) {
             LTHN_CUDA_TRY(cudaMemcpyAsync(hp + 3 * kMaxRows, m->d_next + rows - 1, 4, cudaMemcpyDeviceToHost, m->stream));
+            if ((rc = device_status_read_async(m->stream, (uint32_t*)(hp + 4 * kMaxRows)))) return rc;
         }
         LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));  // the pinned staging is reused by the next chunk
     }
     ln->next_tok = m->h_pinned[3 * kMaxRows];
     ln->have_next = true;
     ln->pending = -1;
-    return check_device_status(m->stream);
+    return device_status_judge((uint32_t)m->h_pinned[4 * kMaxRows], m->stream);
 }
 
 struct Session { Model* m; Lane lane; };
@@ -556,7 +555,8 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
     if ((rc = dalloc(m, &m->vcache, kv_elems))) return bail(rc);
     m->lane_used.assign(c.max_lanes, 0);
     const size_t R = kMaxRows;
-    if ((rc = dalloc(m, &m->d_ids, R)) || (rc = dalloc(m, &m->d_pos, R)) || (rc = dalloc(m, &m->d_lane, R)) ||
+    // ids / positions / lanes of a forward sit in one block, so one copy stages them
+    if ((rc = dalloc(m, &m->d_ids, 3 * R)) ||
         (rc = dalloc(m, &m->d_next, R)) || (rc = dalloc(m, &m->h, R * H)) || (rc = dalloc(m, &m->h2, R * H)) || (rc = dalloc(m, &m->xn, R * H)) ||
         (rc = dalloc(m, &m->qkv, R * (m->QR_l + 2 * m->KR_l))) || (rc = dalloc(m, &m->q, R * m->QR_l)) ||
         (rc = dalloc(m, &m->att, R * m->QR_l)) || (rc = dalloc(m, &m->a, R * H)) || (rc = dalloc(m, &m->act, R * m->F_l)) ||
@@ -565,6 +565,8 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
         (rc = dalloc(m, &m->amax_i, R * ARGMAX_BLOCKS)) || (rc = dalloc(m, &m->best_v, R)) ||
         (rc = dalloc(m, &m->gather, 2 * R * (1 + (size_t)c.tp_size))))
         return bail(rc);
+    m->d_pos = m->d_ids + R;
+    m->d_lane = m->d_ids + 2 * R;
     {
         int chunk_len = 0;
         const int nch = sdpa_chunking(c.max_len, c.head_dim, &chunk_len);
@@ -981,12 +983,11 @@ int32_t lthn_laneset_step(void* set, int32_t* lane_handles, int32_t* tokens, int
             hp[r] = feed[r]->pending; hp[kMaxRows + r] = feed[r]->pos; hp[2 * kMaxRows + r] = feed[r]->id;
             max_ctx = std::max(max_ctx, feed[r]->pos + 1);
         }
-        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_ids, hp, rows * 4, cudaMemcpyHostToDevice, m->stream));
-        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_pos, hp + kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
-        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_lane, hp + 2 * kMaxRows, rows * 4, cudaMemcpyHostToDevice, m->stream));
+        LTHN_CUDA_TRY(cudaMemcpyAsync(m->d_ids, hp, 3 * kMaxRows * 4, cudaMemcpyHostToDevice, m->stream));
         int32_t rc = decode_step(m, rows);
         if (rc) return rc;
         LTHN_CUDA_TRY(cudaMemcpyAsync(hp + 3 * kMaxRows, m->d_next, rows * 4, cudaMemcpyDeviceToHost, m->stream));
+        if ((rc = device_status_read_async(m->stream, (uint32_t*)(hp + 4 * kMaxRows)))) return rc;
         LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
         for (int r = 0; r < rows; r++) {
             feed[r]->pos += 1;
@@ -995,7 +996,7 @@ int32_t lthn_laneset_step(void* set, int32_t* lane_handles, int32_t* tokens, int
             feed[r]->pending = -1;
         }
         ls->forwards++;
-        if ((rc = check_device_status(m->stream))) return rc;
+        if ((rc = device_status_judge((uint32_t)hp[4 * kMaxRows], m->stream))) return rc;
     }
     for (auto& ln : ls->lanes) {
         if (ln.terminal || !ln.have_next) continue;

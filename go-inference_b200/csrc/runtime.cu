@@ -52,6 +52,21 @@ int32_t check_device_status(cudaStream_t s) {
     return LTHN_OK;
 }
 
+// Split form for callers that already have a pinned word and a synchronisation point of their
+// own: queue the read, synchronise once for everything, then judge the value.
+int32_t device_status_read_async(cudaStream_t s, uint32_t* pinned_dst) {
+    uint32_t* w = device_status_word();
+    if (!w) return fail(LTHN_ERR_CUDA, "no device status word");
+    LTHN_CUDA_TRY(cudaMemcpyAsync(pinned_dst, w, 4, cudaMemcpyDeviceToHost, s));
+    return LTHN_OK;
+}
+int32_t device_status_judge(uint32_t v, cudaStream_t s) {
+    if (v == 0) return LTHN_OK;
+    uint32_t* w = device_status_word();
+    if (w) cudaMemsetAsync(w, 0, 4, s);
+    return fail(LTHN_ERR_DEVICE_WAIT, "a device-side bounded wait ran out (status " + std::to_string(v) + ")");
+}
+
 int32_t scratch_get(size_t bytes, void** out, int slot) {
     int dev = 0;
     LTHN_CUDA_TRY(cudaGetDevice(&dev));

@@ -143,7 +143,8 @@ int32_t lthn_affine_qmv_noalloc(void* stream, const float* x, int32_t M, const u
  *     y     = dequant(W) * rmsnorm(h_new; w_next)
  * and h_new stored to h_out (must not alias h_in). Same arithmetic as lthn_rmsnorm_residual
  * followed by lthn_affine_qmv (hip_gemma4_q4_oracle_test.go:925-951 norms, the HIP affine
- * projection for the product) in one launch; up_* non-NULL adds the GeGLU epilogue of
+ * projection for the product) in one launch - the role of the reference's fused RMSNorm->qmv
+ * kernel (engine/metal/kernels/quant/lthn_rms_qmv.metal:23-146), with the residual add included; up_* non-NULL adds the GeGLU epilogue of
  * lthn_affine_qmv_geglu. 4-bit, group 64, N a multiple of 16, f32 vectors 8-byte aligned.
  * Returns LTHN_ERR_INVALID for shapes the batch-1/2 kernel does not serve. The fusion itself
  * has no counterpart in the reference (it runs these steps as separate kernels). */
