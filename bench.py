@@ -197,6 +197,7 @@ def run_decode(lthn, cfg, name, prompt_len, new_tokens, batch, peak, comm=None, 
     t2 = time.perf_counter()
     s.close()
     tps1 = (len(toks) - 1) / (t2 - t1)   # new_tokens-1 forwards: the first token comes from the prefill
+    out["decode_graph"] = {0: "not captured", 1: "cuda graph", 2: "eager (capture failed)"}[m.graph_state]
     out["batch1"] = {"prefill_tok_s": round(prompt_len / (t1 - t0), 1), "decode_tok_s": round(tps1, 1),
                      "ms_per_token": round(1e3 / tps1, 4),
                      "frac_of_measured_hbm": round(tps1 * out["weight_bytes_per_token_per_gpu"] / 1e9 / peak, 4)}

@@ -95,6 +95,18 @@ struct Layer {
 
 constexpr int kMaxRows = 32;  // rows per forward (the batched matvec serves up to 32)
 
+// lm_head (value, index) gather over peer memory (see tp_pair_gather_kernel)
+struct PairGather {
+    float* pairs_out[8];        // rank r's pair area as mapped here: [t][kMaxRows][2] floats
+    const float* pairs_in;      // this rank's pair area (local)
+    uint32_t* flag_out[8];
+    const uint32_t* flag_in;
+    uint32_t* ctr;
+    uint32_t* status;
+    int t, rank, max_rows;
+};
+
+
 struct Model {
     lthn_model_config c{};
     int Hq_l = 0, Hkv_l = 0, QR_l = 0, KR_l = 0, F_l = 0, V_l = 0, v0 = 0;
@@ -132,6 +144,7 @@ struct Model {
     void* x_peer[8] = {};
     uint32_t* x_ctr = nullptr;
     PeerGather pg[2] = {};
+    PairGather pairg = {};
     float* x_part[2] = {};
     bool xchg_ready = false;
     bool fuse_norm = false;  // batch 1-2: norms run inside the matvec that consumes them
@@ -236,6 +249,53 @@ static int32_t all_reduce(Model* m, float* buf, size_t n) {
 __global__ void tp_pack_kernel(const float* v, const int32_t* idx, float* out, int rows) {
     const int r = threadIdx.x;
     if (r < rows) { out[2 * r] = v[r]; out[2 * r + 1] = __int_as_float(idx[r]); }
+}
+// The same gather over peer memory (no NCCL call on the decode path, so the whole step can live in
+// a CUDA graph): every rank pushes its (value, index) pairs into its slot of every peer's pair
+// area, signals with the exchange's sequence number, waits (bounded) for the others and picks.
+// One block; protocol and counters are those of rmsnorm_gather_kernel.
+__global__ void tp_pair_gather_kernel(const PairGather pg, const float* v, int32_t* idx, int rows) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ uint32_t seq_s;
+    const int tid = threadIdx.x;
+    if (tid == 0) seq_s = *(volatile uint32_t*)&pg.ctr[0] + 1u;
+    __syncthreads();
+    const uint32_t seq = seq_s;
+    for (int i = tid; i < rows * pg.t; i += blockDim.x) {
+        const int r = i % rows, p = i / rows;
+        float* dst = pg.pairs_out[p] + ((size_t)pg.rank * pg.max_rows + r) * 2;
+        asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(dst), "f"(v[r]) : "memory");
+        asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(dst + 1), "f"(__int_as_float(idx[r])) : "memory");
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < pg.t) {
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pg.flag_out[tid] + pg.rank), "r"(seq) : "memory");
+        bool ok = false;
+        for (uint32_t it = 0; it < (1u << 21); ++it) {
+            uint32_t f;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(pg.flag_in + tid) : "memory");
+            if ((int32_t)(f - seq) >= 0) { ok = true; break; }
+            __nanosleep(it < 64 ? 20 : 500);
+        }
+        if (!ok) atomicOr(pg.status, 256u);
+    }
+    __syncthreads();
+    if (tid < rows) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int k = 0; k < pg.t; k++) {
+            float pv, pi;
+            const float* src = pg.pairs_in + ((size_t)k * pg.max_rows + tid) * 2;
+            asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(pv) : "l"(src) : "memory");
+            asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(pi) : "l"(src + 1) : "memory");
+            const int i = __float_as_int(pi);
+            if (pv > bv || (pv == bv && i < bi)) { bv = pv; bi = i; }
+        }
+        idx[tid] = bi;
+    }
+    __syncthreads();
+    if (tid == 0) *(volatile uint32_t*)&pg.ctr[0] = seq;
 }
 __global__ void tp_pick_kernel(const float* gathered, int ranks, int rows, int32_t* out_idx) {
     const int r = threadIdx.x;
@@ -342,6 +402,10 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
         return launch_argmax(s, m->logits, lr, m->V_l, m->amax_v, m->amax_i, m->d_next + logit_row0, nullptr, 0);
     // vocab-sharded head: local best (value, global index) per row, gathered from all ranks
     if ((rc = launch_argmax(s, m->logits, lr, m->V_l, m->amax_v, m->amax_i, m->d_next + logit_row0, m->best_v, m->v0))) return rc;
+    if (m->xchg_ready) {
+        LTHN_CUDA_TRY(launch_k(tp_pair_gather_kernel, dim3(1), dim3(64), 0, s, m->pairg, (const float*)m->best_v, m->d_next + logit_row0, lr));
+        return LTHN_OK;
+    }
     tp_pack_kernel<<<1, 32, 0, s>>>(m->best_v, m->d_next + logit_row0, m->gather, lr);
     LTHN_CUDA_TRY(cudaGetLastError());
     float* all = m->gather + 2 * kMaxRows;
@@ -671,7 +735,8 @@ static int32_t xchg_setup(Model* m) {
     const bool want = !(env && env[0] == '1');
     const size_t flag_bytes = 256;
     const size_t part_bytes = ((size_t)kMaxRows * c.hidden * sizeof(float) + 255) / 256 * 256;
-    const size_t total = flag_bytes + 2 * part_bytes;
+    const size_t pair_bytes = ((size_t)8 * kMaxRows * 2 * sizeof(float) + 255) / 256 * 256;
+    const size_t total = flag_bytes + 2 * part_bytes + pair_bytes;
     float ok = want ? 1.f : 0.f;
     cudaIpcMemHandle_t mine{};
     if (ok > 0.f) {
@@ -736,6 +801,18 @@ static int32_t xchg_setup(Model* m) {
         }
         m->x_part[site] = (float*)((unsigned char*)m->x_base + flag_bytes + site * part_bytes);
     }
+    {
+        PairGather& g = m->pairg;
+        g.t = t; g.rank = c.tp_rank; g.max_rows = kMaxRows;
+        g.flag_in = (const uint32_t*)m->x_base;
+        g.ctr = m->x_ctr;
+        g.status = status;
+        g.pairs_in = (const float*)((const unsigned char*)m->x_base + flag_bytes + 2 * part_bytes);
+        for (int r = 0; r < t; r++) {
+            g.flag_out[r] = (uint32_t*)m->x_peer[r];
+            g.pairs_out[r] = (float*)((unsigned char*)m->x_peer[r] + flag_bytes + 2 * part_bytes);
+        }
+    }
     m->xchg_ready = true;
     return LTHN_OK;
 }
@@ -776,6 +853,17 @@ int32_t lthn_model_tp_exchange(void* model, int32_t* mode) {
     LTHN_REQUIRE(m && mode, "lthn_model_tp_exchange: NULL argument");
     LTHN_REQUIRE(m->finalized, "lthn_model_tp_exchange: model is not finalized");
     *mode = m->c.tp_size <= 1 ? 0 : (m->xchg_ready ? 2 : 1);
+    return LTHN_OK;
+}
+
+// 0: decode steps have not been captured (yet), 1: they replay a CUDA graph, 2: capture was not
+// possible and steps are launched kernel by kernel
+int32_t lthn_model_graph_state(void* model, int32_t* state) {
+    clear_error();
+    Model* m = (Model*)model;
+    LTHN_REQUIRE(m && state, "lthn_model_graph_state: NULL argument");
+    *state = m->graphs_off ? 2 : 0;
+    for (auto g : m->step_graph) if (g) *state = 1;
     return LTHN_OK;
 }
 

@@ -108,6 +108,7 @@ class _Sig:
     lthn_model_finalize = (i32, [vp])
     lthn_model_weight_bytes = (i32, [vp, C.POINTER(u64)])
     lthn_model_tp_exchange = (i32, [vp, C.POINTER(i32)])
+    lthn_model_graph_state = (i32, [vp, C.POINTER(i32)])
     lthn_model_destroy = (i32, [vp])
     lthn_tp_unique_id = (i32, [vp])
     lthn_tp_init = (i32, [i32, i32, vp, pvp])
@@ -436,6 +437,13 @@ class Model:
         """0 single device, 1 NCCL all-reduce, 2 peer-memory exchange fused into the residual norm."""
         v = C.c_int32()
         check(lib().lthn_model_tp_exchange(self.h, C.byref(v)))
+        return int(v.value)
+
+    @property
+    def graph_state(self):
+        """0 decode steps not captured yet, 1 replaying a CUDA graph, 2 capture impossible (eager)."""
+        v = C.c_int32()
+        check(lib().lthn_model_graph_state(self.h, C.byref(v)))
         return int(v.value)
 
     def open_session(self) -> "Session":

@@ -262,6 +262,9 @@ int32_t lthn_model_weight_bytes(void* model, uint64_t* bytes);
  * (CUDA IPC mappings of every rank's buffer; chosen when every rank could map every peer,
  * LTHN_CUDA_TP_NCCL=1 forces mode 1). No counterpart in the reference. */
 int32_t lthn_model_tp_exchange(void* model, int32_t* mode);
+/* Whether decode steps replay a captured CUDA graph: 0 not captured yet, 1 graph, 2 capture was
+ * not possible (kernel-by-kernel launches; LTHN_CUDA_NO_GRAPH=1 forces this). No counterpart in the reference. */
+int32_t lthn_model_graph_state(void* model, int32_t* state);
 int32_t lthn_model_destroy(void* model);   /* TokenModel.Close (engine/model.go:30) */
 
 /* Tensor parallelism over NCCL (the reference is single-device; new functionality).
