@@ -451,27 +451,36 @@ static int32_t launch_qmv(cudaStream_t s, const QmvArgs& a, int rt, int nwarps) 
 // Picks rows-per-CTA and warps-per-CTA. Small matrices want every SM busy with
 // the whole matrix in flight at once (RT=1, many K-splitting warps); large ones
 // amortise the activation reads and the epilogue over more rows.
+// Tiles per CTA (rt) and K-splitting warps for the bf16 tensor-core kernel, from a sweep on B200
+// (f32 activations, C = bf16 columns = rows * split; times for the lm_head / 9216x2304 / 4096x2304
+// matrices): long streams want few warps and several tiles per CTA (lm_head, 8 rows: 139 us with
+// (4,2) against 230 us with (1,8)); matrices of a few tiles per SM want two tiles and 4-8 warps;
+// one tile per SM or less wants every group in flight at once.
 void qmv_pick_config(int64_t N, int64_t K, int C, int sets, int* rt, int* nwarps) {
     const int64_t tiles16 = (N + 15) / 16;
     const int G = (int)(K / 64);
-    int r = 1;
+    const double tps = (double)tiles16 / 148.0;  // 16-row tiles per SM
+    int r = 1, w = 8;
     if (C <= 16) {
-        if (tiles16 >= 148 * 16) r = 4;
-        else if (tiles16 >= 148 * 4) r = 2;
+        if (tps >= 16.0) { r = 4; w = 2; }
+        else if (tps >= 3.0) { r = 2; w = 8; if (sets == 2 && C > 8) { r = 1; w = 4; } }
+        else if (C <= 8) {
+            // as many K-splitting warps as still let every 16-row tile be resident in one wave
+            const int maxw = sets == 2 ? 16 : 32;
+            for (int cand = maxw; cand >= 8; cand >>= 1) {
+                const int per_sm = std::max(1, std::min(2048 / (32 * cand), 65536 / (80 * 32 * cand)));
+                if (tiles16 <= (int64_t)148 * per_sm || cand == 8) { w = cand; break; }
+            }
+        }
     } else if (C <= 32) {
-        if (tiles16 >= 148 * 4) r = 2;
+        if (tps >= 16.0) { r = 2; w = 2; }
+        else if (tps >= 3.0) { r = 2; w = 4; }
+        else if (tps >= 1.5) { r = 2; w = 8; }
+    } else {
+        if (tps >= 3.0) w = 2;
+        else if (tps >= 1.5) w = 4;
     }
     if (sets == 2 && r > 2) r = 2;
-    int w = 8;
-    if (r >= 2 && C <= 8) w = 4;
-    if (r == 1 && C <= 8) {
-        // as many K-splitting warps as still let every 16-row tile be resident in one wave
-        const int maxw = sets == 2 ? 16 : 32;
-        for (int cand = maxw; cand >= 8; cand >>= 1) {
-            const int per_sm = std::max(1, std::min(2048 / (32 * cand), 65536 / (80 * 32 * cand)));
-            if (tiles16 <= (int64_t)148 * per_sm || cand == 8) { w = cand; break; }
-        }
-    }
     while (w > 1 && w > G) w >>= 1;
     *rt = r;
     *nwarps = w;
