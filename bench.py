@@ -327,9 +327,13 @@ def run_ours(args):
         from lthn import tp
         for w in ws:
             w.free()
-        comm = tp.init_comm(rank, world)
-        dec = run_decode(lthn, GEMMA_27B, f"gemma-style 62L/5376 (BASELINE configs[4]), TP{world}", 4096, 512,
-                         32 if args.full else 1, peak, comm=comm, rank=rank, world=world)
+        # the headline line above does not depend on this section: a failure here is reported, not fatal
+        try:
+            comm = tp.init_comm(rank, world)
+            dec = run_decode(lthn, GEMMA_27B, f"gemma-style 62L/5376 (BASELINE configs[4]), TP{world}", 4096, 512,
+                             32 if args.full else 1, peak, comm=comm, rank=rank, world=world)
+        except Exception as e:  # noqa: BLE001
+            dec = {"error": f"{type(e).__name__}: {e}"[:300]}
         if rank == 0:
             line["decode_tp"] = dec
         ws = []
