@@ -145,7 +145,13 @@ struct Model {
     uint32_t* x_ctr = nullptr;
     PeerGather pg[2] = {};
     PairGather pairg = {};
-    float* x_part[2] = {};
+    float* x_part[2] = {};      // this rank's own slot of each call site (pull mode)
+    float* x_site[2] = {};      // slot 0 of each call site in this rank's region (push mode reads all t slots)
+    float* x_push[2][8] = {};   // this rank's slot of each call site in every rank's region
+    int64_t x_stride = 0;       // floats between slots
+    PeerWait* d_pw = nullptr;       // device copy of the exchange's wait descriptor
+    float** d_push[2] = {};         // device arrays of x_push[site]
+    bool site_fused[2] = {};    // tensor parallel: the site's norm runs inside the consuming matvec (push mode)
     bool xchg_ready = false;
     bool fuse_norm = false;  // batch 1-2: norms run inside the matvec that consumes them
 };
@@ -318,28 +324,48 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
     cudaStream_t s = m->stream;
     const int H = c.hidden, D = c.head_dim;
     int32_t rc;
-    // Batch 1-2 on one device: the residual RMSNorm pairs run as the prologue of the matvec that
-    // consumes them (two kernels fewer per block). The residual stream then alternates between
-    // two buffers, because the CTA that stores the updated stream must not overwrite what the
-    // other CTAs of the same kernel are still reading.
-    const bool fn = m->fuse_norm && rows <= 2 && c.tp_size <= 1 && (!want_logits || logit_row0 == 0);
+    // Batch 1-2: the residual RMSNorm pairs run as the prologue of the matvec that consumes them (two
+    // kernels fewer per block). The residual stream then alternates between two buffers, because
+    // the CTA that stores the updated stream must not overwrite what the other CTAs of the same
+    // kernel are still reading. Site 0 is the post-attention pair (consumer: gate/up), site 1 the
+    // post-FFN pair (consumer: the next block's q|k|v, or the lm_head). Under tensor parallelism a
+    // fused site also carries the exchange: the projection pushes its partial sums into every
+    // rank's memory and the consumer waits for the peers' signals and adds the partials itself.
+    const bool tp = c.tp_size > 1;
+    const bool xg = m->xchg_ready;
+    const bool small = rows <= 2 && (!want_logits || logit_row0 == 0);
+    const bool f0 = small && (tp ? (xg && m->site_fused[0]) : m->fuse_norm);
+    const bool f1 = small && (tp ? (xg && m->site_fused[1]) : m->fuse_norm);
     float* hcur = m->h;
     float* halt = m->h2;
     if ((rc = launch_embed(s, m->d_ids, rows, m->embed.wq, m->embed.s, m->embed.b, H, c.vocab, c.embed_scale, hcur))) return rc;
     const int split = qmv_split_for(rows, LTHN_DTYPE_F32);
-    if (!fn && (rc = launch_rmsnorm(s, m->h, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, m->xn, rows, H, c.eps, 0, m->xn_cols, split))) return rc;
+    if (!f1 && (rc = launch_rmsnorm(s, hcur, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, m->xn, rows, H, c.eps, 0, m->xn_cols, split))) return rc;
     int chunk_len = 0;
     const int nchunks = sdpa_chunking(max_ctx, D, &chunk_len);
     const size_t need = sdpa_scratch_bytes(rows, m->Hq_l, D, nchunks);
     if (nchunks > 1 && need > m->sdpa_part_bytes) return fail(LTHN_ERR_STATE, "forward: attention scratch too small");
     NormFuse nf{};
+    // the fused norm of a site: partial sums from the projection (one vector, or one per rank)
+    auto site_norm = [&](int site, const float* w_post, const float* w_next) {
+        NormFuse n{tp ? m->x_site[site] : m->a, hcur, halt, w_post, w_next, c.eps};
+        if (tp) { n.na = c.tp_size; n.a_stride = m->x_stride; n.wait = m->d_pw; }
+        std::swap(hcur, halt);
+        return n;
+    };
+    // where a row-parallel projection leaves its result
+    auto site_out = [&](int site, bool fused, QmvCall& q) {
+        if (!tp) return;
+        if (fused) { q.npush = c.tp_size; q.push = m->d_push[site]; }
+        else if (xg) q.y = m->x_part[site];
+    };
     for (int li = 0; li < c.layers; li++) {
         Layer& L = m->layers[li];
         QmvCall qc{L.qkv.wq, L.qkv.s, L.qkv.b, nullptr, nullptr, nullptr, m->xn, LTHN_DTYPE_F32, m->qkv, LTHN_DTYPE_F32, L.qkv.N, L.qkv.K, rows};
-        if (fn) {
+        if (f1) {
             // input norm of this block, preceded (after the first block) by the previous block's post-FFN norm + residual
             if (li == 0) nf = NormFuse{nullptr, hcur, nullptr, nullptr, L.norm[NORM_INPUT], c.eps};
-            else { nf = NormFuse{m->a, hcur, halt, m->layers[li - 1].norm[NORM_POST_FF], L.norm[NORM_INPUT], c.eps}; std::swap(hcur, halt); }
+            else nf = site_norm(1, m->layers[li - 1].norm[NORM_POST_FF], L.norm[NORM_INPUT]);
             qc.norm = &nf;
         } else {
             qc.x_cols = m->xn_cols; qc.x_split = split;
@@ -352,45 +378,48 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
         SdpaArgs sa{m->q, kc, vc, m->d_pos, m->d_lane, m->att, m->sdpa_part, m->lane_stride, m->Hq_l, m->Hkv_l, nchunks, chunk_len, c.attn_scale};
         sa.cols = m->att_cols; sa.split = split;
         if ((rc = launch_sdpa_decode(s, sa, rows, D))) return rc;
-        // tensor parallel: row-parallel projections leave partial sums; with the peer-memory exchange
-        // they go to this rank's shared buffer and the norm kernel adds all ranks' partials itself
-        const bool xg = m->xchg_ready;
-        QmvCall oc{L.o.wq, L.o.s, L.o.b, nullptr, nullptr, nullptr, m->att, LTHN_DTYPE_F32, xg ? m->x_part[0] : m->a, LTHN_DTYPE_F32, L.o.N, L.o.K, rows};
+        QmvCall oc{L.o.wq, L.o.s, L.o.b, nullptr, nullptr, nullptr, m->att, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.o.N, L.o.K, rows};
         if (nchunks > 1) { oc.x_cols = m->att_cols; oc.x_split = split; }  // the merge stage wrote them
+        site_out(0, f0, oc);
         if ((rc = qmv_dispatch(s, oc))) return rc;
         QmvCall gc{L.gate.wq, L.gate.s, L.gate.b, L.up.wq, L.up.s, L.up.b, m->xn, LTHN_DTYPE_F32, m->act, LTHN_DTYPE_F32, L.gate.N, L.gate.K, rows};
-        if (fn) {
-            nf = NormFuse{m->a, hcur, halt, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], c.eps};
-            std::swap(hcur, halt);
+        if (f0) {
+            nf = site_norm(0, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF]);
             gc.norm = &nf;
-        } else if (xg) {
-            if ((rc = launch_rmsnorm_gather(s, m->pg[0], m->h, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, m->xn_cols, split))) return rc;
         } else {
-            if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
-            if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
+            if (tp && xg) {
+                if ((rc = launch_rmsnorm_gather(s, m->pg[0], hcur, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, m->xn_cols, split))) return rc;
+            } else {
+                if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
+                if ((rc = launch_rmsnorm(s, m->a, hcur, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
+            }
+            gc.x_cols = m->xn_cols; gc.x_split = split;
         }
-        if (!fn) { gc.x_cols = m->xn_cols; gc.x_split = split; }
         if ((rc = qmv_dispatch(s, gc))) return rc;
-        QmvCall dc{L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, m->act, LTHN_DTYPE_F32, xg ? m->x_part[1] : m->a, LTHN_DTYPE_F32, L.down.N, L.down.K, rows};
+        QmvCall dc{L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, m->act, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.down.N, L.down.K, rows};
+        site_out(1, f1, dc);
         if ((rc = qmv_dispatch(s, dc))) return rc;
         const float* next_norm = li + 1 < c.layers ? m->layers[li + 1].norm[NORM_INPUT] : m->final_norm;
-        if (fn) {
+        if (f1) {
             // folded into the next block's QKV matvec (or the lm_head below)
-        } else if (xg) {
-            if ((rc = launch_rmsnorm_gather(s, m->pg[1], m->h, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, m->xn_cols, split))) return rc;
+        } else if (tp && xg) {
+            if ((rc = launch_rmsnorm_gather(s, m->pg[1], hcur, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, m->xn_cols, split))) return rc;
         } else {
             if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
-            if ((rc = launch_rmsnorm(s, m->a, m->h, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
+            if ((rc = launch_rmsnorm(s, m->a, hcur, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
         }
     }
-    if (fn) {
-        if (!want_logits) return LTHN_OK;
-        nf = NormFuse{m->a, hcur, halt, m->layers[c.layers - 1].norm[NORM_POST_FF], m->final_norm, c.eps};
+    if (f1 && !want_logits) return LTHN_OK;
+    if (f1) {
+        nf = site_norm(1, m->layers[c.layers - 1].norm[NORM_POST_FF], m->final_norm);
         QmvCall hc{m->head.wq, m->head.s, m->head.b, nullptr, nullptr, nullptr, m->xn, LTHN_DTYPE_F32, m->logits, LTHN_DTYPE_F32,
                    m->head.N, m->head.K, rows};
         hc.norm = &nf;
         if ((rc = qmv_dispatch(s, hc))) return rc;
-        return launch_argmax(s, m->logits, rows, m->V_l, m->amax_v, m->amax_i, m->d_next, nullptr, 0);
+        if (!tp) return launch_argmax(s, m->logits, rows, m->V_l, m->amax_v, m->amax_i, m->d_next, nullptr, 0);
+        if ((rc = launch_argmax(s, m->logits, rows, m->V_l, m->amax_v, m->amax_i, m->d_next, m->best_v, m->v0))) return rc;
+        LTHN_CUDA_TRY(launch_k(tp_pair_gather_kernel, dim3(1), dim3(64), 0, s, m->pairg, (const float*)m->best_v, m->d_next, rows));
+        return LTHN_OK;
     }
     if (!want_logits) return LTHN_OK;
     const int lr = rows - logit_row0;
@@ -736,7 +765,8 @@ static int32_t xchg_setup(Model* m) {
     const size_t flag_bytes = 256;
     const size_t part_bytes = ((size_t)kMaxRows * c.hidden * sizeof(float) + 255) / 256 * 256;
     const size_t pair_bytes = ((size_t)8 * kMaxRows * 2 * sizeof(float) + 255) / 256 * 256;
-    const size_t total = flag_bytes + 2 * part_bytes + pair_bytes;
+    const size_t site_bytes = 8 * part_bytes;  // one slot per rank
+    const size_t total = flag_bytes + 2 * site_bytes + pair_bytes;
     float ok = want ? 1.f : 0.f;
     cudaIpcMemHandle_t mine{};
     if (ok > 0.f) {
@@ -797,9 +827,11 @@ static int32_t xchg_setup(Model* m) {
         g.status = status;
         for (int r = 0; r < t; r++) {
             g.flag_out[r] = (uint32_t*)m->x_peer[r];
-            g.part[r] = (const float*)((const unsigned char*)m->x_peer[r] + flag_bytes + site * part_bytes);
+            g.part[r] = (const float*)((const unsigned char*)m->x_peer[r] + flag_bytes + site * site_bytes + r * part_bytes);
+            m->x_push[site][r] = (float*)((unsigned char*)m->x_peer[r] + flag_bytes + site * site_bytes + c.tp_rank * part_bytes);
         }
-        m->x_part[site] = (float*)((unsigned char*)m->x_base + flag_bytes + site * part_bytes);
+        m->x_part[site] = (float*)((unsigned char*)m->x_base + flag_bytes + site * site_bytes + c.tp_rank * part_bytes);
+        m->x_site[site] = (float*)((unsigned char*)m->x_base + flag_bytes + site * site_bytes);
     }
     {
         PairGather& g = m->pairg;
@@ -807,11 +839,34 @@ static int32_t xchg_setup(Model* m) {
         g.flag_in = (const uint32_t*)m->x_base;
         g.ctr = m->x_ctr;
         g.status = status;
-        g.pairs_in = (const float*)((const unsigned char*)m->x_base + flag_bytes + 2 * part_bytes);
+        g.pairs_in = (const float*)((const unsigned char*)m->x_base + flag_bytes + 2 * site_bytes);
         for (int r = 0; r < t; r++) {
             g.flag_out[r] = (uint32_t*)m->x_peer[r];
-            g.pairs_out[r] = (float*)((unsigned char*)m->x_peer[r] + flag_bytes + 2 * part_bytes);
+            g.pairs_out[r] = (float*)((unsigned char*)m->x_peer[r] + flag_bytes + 2 * site_bytes);
         }
+    }
+    m->x_stride = (int64_t)(part_bytes / sizeof(float));
+    {
+        PeerWait pw{};
+        pw.t = t; pw.rank = c.tp_rank; pw.flag_in = (const uint32_t*)m->x_base; pw.ctr = m->x_ctr;
+        for (int r = 0; r < t; r++) pw.flag_out[r] = (uint32_t*)m->x_peer[r];
+        if ((rc = dalloc(m, &m->d_pw, 1))) return rc;
+        LTHN_CUDA_TRY(cudaMemcpy(m->d_pw, &pw, sizeof(pw), cudaMemcpyHostToDevice));
+        for (int site = 0; site < 2; site++) {
+            if ((rc = dalloc(m, &m->d_push[site], 8))) return rc;
+            LTHN_CUDA_TRY(cudaMemcpy(m->d_push[site], m->x_push[site], sizeof(float*) * 8, cudaMemcpyHostToDevice));
+        }
+    }
+    {
+        // a site can run in push mode when its projection and the matvecs that consume its norm are
+        // all served by the batch-1/2 integer tensor-core kernel
+        const char* env = getenv("LTHN_CUDA_NO_NORM_FUSION");
+        const bool want_f = !(env && env[0] == '1');
+        const Layer& L0 = m->layers[0];
+        I8Plan pl;
+        m->site_fused[0] = want_f && i8_plan(L0.o.N, L0.o.K, 2, 0, 0, 0, &pl) && qmv_can_fuse_norm(L0.gate.N, L0.gate.K, 2, true);
+        m->site_fused[1] = want_f && i8_plan(L0.down.N, L0.down.K, 2, 0, 0, 0, &pl) && qmv_can_fuse_norm(L0.qkv.N, L0.qkv.K, 2, false) &&
+                           qmv_can_fuse_norm(m->head.N, m->head.K, 2, false);
     }
     m->xchg_ready = true;
     return LTHN_OK;

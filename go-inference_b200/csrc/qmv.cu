@@ -480,6 +480,8 @@ void qmv_pick_config(int64_t N, int64_t K, int C, int sets, int* rt, int* nwarps
         if (tps >= 3.0) w = 2;
         else if (tps >= 1.5) w = 4;
     }
+    // the table was measured at K = 2304 (36 groups): keep at most ~18 groups per warp on longer rows
+    while (w < 8 && G > 18 * w) w <<= 1;
     if (sets == 2 && r > 2) r = 2;
     while (w > 1 && w > G) w >>= 1;
     *rt = r;

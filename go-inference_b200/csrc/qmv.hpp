@@ -12,6 +12,18 @@ namespace lthn {
 // with the arithmetic of the stand-alone norm kernel (f64 sum of squares, IEEE divide). Every
 // CTA computes the whole vector (it needs the sums), CTA 0 also stores h_new to h_out, which
 // must not alias h_in. Removes one kernel launch per norm from the decode chain.
+//
+// Tensor parallel form (wait != NULL): a is the sum of na partial vectors a[r*a_stride + ...], one
+// per rank, that the ranks' projection kernels pushed into this GPU's memory. CTA 0 signals the
+// exchange's sequence number to every peer, every CTA waits (bounded polling) until all peers have
+// signalled, then the partials are added in rank order. Same protocol and counters as the
+// stand-alone tensor-parallel norm kernel.
+struct PeerWait {
+    uint32_t* flag_out[8];    // rank r's flag line as mapped here; element [rank] is this rank's
+    const uint32_t* flag_in;  // this rank's flag line
+    uint32_t* ctr;            // [0] sequence number of the last finished exchange, [1] CTA arrivals
+    int t, rank;
+};
 struct NormFuse {
     const float* a;
     const float* h_in;
@@ -19,6 +31,9 @@ struct NormFuse {
     const float* w_post;
     const float* w_next;
     float eps;
+    int na = 1;
+    int64_t a_stride = 0;
+    const PeerWait* wait = nullptr;  // in device memory
 };
 
 // One decode matvec: y[M,N] = x[M,K] * dequant(W)^T, optionally fused with a second
@@ -40,6 +55,10 @@ struct QmvCall {
     // plan is followed by a small summing kernel.
     float* parts = nullptr;
     int* nparts = nullptr;
+    // optional (integer tensor-core kernel, f32 output): store the result to npush buffers instead
+    // of y - a tensor-parallel rank pushing its partial sums into every peer's memory
+    float* const* push = nullptr;  // array of npush pointers, in device memory
+    int npush = 0;
 };
 
 // true when a call of this shape can carry a fused norm prologue

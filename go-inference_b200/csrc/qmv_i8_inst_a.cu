@@ -42,6 +42,9 @@ int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p) {
     a.probe = g_i8_probe;
     a.fuse_norm = c.norm ? 1 : 0;
     if (c.norm) a.nf = *c.norm;
+    a.npush = c.npush;
+    a.push = c.push;
+    if (c.npush && (c.y_dtype != LTHN_DTYPE_F32 || p.ks != 1 || c.wq2)) return fail(LTHN_ERR_INVALID, "affine_qmv: pushed results are f32, whole rows, no GeGLU");
     a.ks = p.ks; a.Gs = p.Gs;
     if (c.norm && p.ks != 1) return fail(LTHN_ERR_INVALID, "affine_qmv: a fused norm prologue needs whole rows");
     if (p.ks > 1) {

@@ -50,6 +50,8 @@ struct I8Args {
     int ks, Gs;             // K slices (CTA c works on slice c % ks) and groups per slice
     float* ypart;           // ks > 1: partial sums [ks][M][N] f32 instead of y
     NormFuse nf;
+    float* const* push;     // npush > 0: f32 results go to these buffers (array in device memory) instead of y
+    int npush;
     uint32_t* status;
 };
 
@@ -203,6 +205,37 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
         // with a named barrier that the producer warp does not join.
         const NormFuse& nf = a.nf;
         const int nthr = W * 32;
+        if (nf.wait) {
+            // tensor parallel: signal this exchange to the peers, wait for theirs (bounded)
+            const PeerWait& pw = *nf.wait;  // in device memory
+            uint32_t* seq_s = (uint32_t*)(dsm + 192);  // spare word of the barrier header
+            if (tid == 0) *seq_s = *(volatile uint32_t*)&pw.ctr[0] + 1u;
+            asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
+            const uint32_t seq = *seq_s;
+            if (warp == 0 && lane < pw.t) {
+                if (blockIdx.x == 0) {
+                    __threadfence_system();
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pw.flag_out[lane] + pw.rank), "r"(seq) : "memory");
+                }
+                bool ok = false;
+                for (uint32_t it = 0; it < (1u << 21); ++it) {
+                    uint32_t f;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(pw.flag_in + lane) : "memory");
+                    if ((int32_t)(f - seq) >= 0) { ok = true; break; }
+                    __nanosleep(it < 64 ? 20 : 500);
+                }
+                if (!ok) atomicOr(a.status, 256u);
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
+            // the last CTA past this point advances the sequence number (every CTA read it above)
+            if (tid == 0) {
+                if (atomicAdd(&pw.ctr[1], 1u) == gridDim.x - 1) {
+                    pw.ctr[1] = 0u;
+                    __threadfence();
+                    *(volatile uint32_t*)&pw.ctr[0] = seq;
+                }
+            }
+        }
         float2 wn[J];
         float hv[J][MT][2];
 #pragma unroll
@@ -220,17 +253,52 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
             float2 wp[J];
 #pragma unroll
             for (int m = 0; m < MT; m++) ss[m] = 0.0;
+            if (nf.na == 1) {
 #pragma unroll
-            for (int j = 0; j < J; j++) {
-                const int64_t e0 = (int64_t)(warp * J + j) * 64 + 2 * lane;
-                wp[j] = __ldg((const float2*)(nf.w_post + e0));
+                for (int j = 0; j < J; j++) {
+                    const int64_t e0 = (int64_t)(warp * J + j) * 64 + 2 * lane;
+                    wp[j] = __ldg((const float2*)(nf.w_post + e0));
 #pragma unroll
-                for (int m = 0; m < MT; m++) {
-                    const float2 v = *(const float2*)(nf.a + (int64_t)m * K + e0);
-                    xr[j][m][0] = v.x; xr[j][m][1] = v.y;
-                    ss[m] += (double)__fmul_rn(v.x, v.x);
-                    ss[m] += (double)__fmul_rn(v.y, v.y);
+                    for (int m = 0; m < MT; m++) {
+                        const float2 v = *(const float2*)(nf.a + (int64_t)m * K + e0);
+                        xr[j][m][0] = v.x; xr[j][m][1] = v.y;
+                        ss[m] += (double)__fmul_rn(v.x, v.x);
+                        ss[m] += (double)__fmul_rn(v.y, v.y);
+                    }
                 }
+            } else {
+                // tensor parallel: one partial vector per rank, added in rank order, one rank (one
+                // batch of independent loads) at a time
+#pragma unroll
+                for (int j = 0; j < J; j++) {
+                    const int64_t e0 = (int64_t)(warp * J + j) * 64 + 2 * lane;
+                    wp[j] = __ldg((const float2*)(nf.w_post + e0));
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        const float2 v = *(const float2*)(nf.a + (int64_t)m * K + e0);
+                        xr[j][m][0] = v.x; xr[j][m][1] = v.y;
+                    }
+                }
+                for (int r = 1; r < nf.na; r++) {
+                    const float* ar = nf.a + (int64_t)r * nf.a_stride;
+#pragma unroll
+                    for (int j = 0; j < J; j++) {
+                        const int64_t e0 = (int64_t)(warp * J + j) * 64 + 2 * lane;
+#pragma unroll
+                        for (int m = 0; m < MT; m++) {
+                            const float2 u = *(const float2*)(ar + (int64_t)m * K + e0);
+                            xr[j][m][0] = __fadd_rn(xr[j][m][0], u.x);
+                            xr[j][m][1] = __fadd_rn(xr[j][m][1], u.y);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < J; j++)
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        ss[m] += (double)__fmul_rn(xr[j][m][0], xr[j][m][0]);
+                        ss[m] += (double)__fmul_rn(xr[j][m][1], xr[j][m][1]);
+                    }
             }
 #pragma unroll
             for (int m = 0; m < MT; m++) {
@@ -431,7 +499,9 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
                 const int64_t row = (int64_t)b * OR + r;
                 if (row < a.N) {
                     if (ks > 1) a.ypart[((int64_t)slice * MT + m) * a.N + row] = v0;
-                    else if (a.y_dtype == LTHN_DTYPE_BF16) ((uint16_t*)a.y)[(int64_t)m * a.N + row] = f32_to_bf16_bits(v0);
+                    else if (a.npush) {
+                        for (int p = 0; p < a.npush; p++) a.push[p][(int64_t)m * a.N + row] = v0;
+                    } else if (a.y_dtype == LTHN_DTYPE_BF16) ((uint16_t*)a.y)[(int64_t)m * a.N + row] = f32_to_bf16_bits(v0);
                     else ((float*)a.y)[(int64_t)m * a.N + row] = v0;
                 }
             }

@@ -11,7 +11,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "liblthn_cuda.so")
+LIB_PATH = os.environ.get("LTHN_CUDA_LIB") or os.path.join(os.path.dirname(_HERE), "liblthn_cuda.so")
 
 OK = 0
 F32, BF16 = 0, 1
