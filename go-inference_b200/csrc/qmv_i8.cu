@@ -15,7 +15,9 @@ int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p);
 // ---- host side --------------------------------------------------------------------
 
 int g_i8_stg = 0, g_i8_probe = 0;  // measurement aids
-static const int kI8J[] = {1, 2, 3, 4, 6, 7, 8, 9, 12, 16, 18};
+// dynamic shared memory a block may ask for (the SM has 227 KB for one block)
+static const size_t kI8MaxSmem = 224 * 1024;
+static const int kI8J[] = {1, 2, 3, 4, 6, 7, 8, 9, 12, 16, 18, 21};
 
 static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_w, bool has_norm, I8Plan* p) {
     // (J, W): W consumer warps of J groups each. Measured on B200: a long stream (many row blocks
@@ -52,7 +54,7 @@ static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_
         const size_t bs_off = 512 + part_bytes;
         const size_t stage_off = (bs_off + (size_t)W * (M * 192 + J * 32) + 127) / 128 * 128;
         const size_t smem = stage_off + (size_t)stg * stage;
-        if (smem > 200 * 1024) continue;
+        if (smem > kI8MaxSmem) continue;
         p->J = J; p->W = W; p->RT = 1; p->stg = stg; p->RS = RS; p->nblocks = nblocks;
         p->threads = (W + 1) * 32;
         p->bs_off = (int)bs_off; p->stage_off = (int)stage_off;

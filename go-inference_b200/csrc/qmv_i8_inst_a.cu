@@ -14,6 +14,7 @@ extern template int32_t launch_i8_w<9>(cudaStream_t, const I8Args&, const I8Plan
 extern template int32_t launch_i8_w<12>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
 extern template int32_t launch_i8_w<16>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
 extern template int32_t launch_i8_w<18>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
+extern template int32_t launch_i8_w<21>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
 
 // y[i] = sum over the K slices of part[s][i], slices added in order
 __global__ void sum_parts_kernel(const float* __restrict__ part, int ks, int64_t n, void* __restrict__ y, int y_dtype) {
@@ -77,6 +78,7 @@ int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p) {
         case 12: rc = launch_i8_w<12>(st, a, p, c.M, fuse); break;
         case 16: rc = launch_i8_w<16>(st, a, p, c.M, fuse); break;
         case 18: rc = launch_i8_w<18>(st, a, p, c.M, fuse); break;
+        case 21: rc = launch_i8_w<21>(st, a, p, c.M, fuse); break;
         default: return fail(LTHN_ERR_INVALID, "affine_qmv: no integer tensor-core instantiation for this plan");
     }
     if (rc) return rc;

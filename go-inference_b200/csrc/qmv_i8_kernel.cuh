@@ -523,7 +523,7 @@ inline int32_t launch_i8_t(cudaStream_t st, const I8Args& a, const I8Plan& p) {
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
     void (*kern)(const I8Args) = LB == 160 ? qmv_i8_kernel_small<J, RT, MT, FUSE> : qmv_i8_kernel<J, RT, MT, FUSE, LB>;
     if (attr_dev != dev) {
-        LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         attr_dev = dev;
     }
