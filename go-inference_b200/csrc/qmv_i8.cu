@@ -71,9 +71,9 @@ bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I
     // GeGLU pairs: long rows use the interleaved row block (half the shared memory per stage);
     // measured: K=5376 42 -> 24 us at N=21504, K=2304 slightly slower than two full sets
     if (fuse) fuse = K >= 4096 ? 2 : 1;
-    // Whole rows whenever a 16-row block of the whole K fits the shared-memory ring (K <= 9216).
+    // Whole rows whenever a 16-row block of the whole K fits the shared-memory ring (K <= 10752).
     // K slices (partial sums + a summing pass) exist for longer rows but were measured slower than
-    // the dp4a kernel on every shape tried (K = 10752..21504: 19-32 us against 16-27 us), and
+    // the dp4a kernel on the shapes tried (K = 14336..21504), and
     // slower than whole rows on small matrices, so the dispatcher only uses them when asked to
     // (max_slices > 1). A GeGLU epilogue needs whole rows.
     if (force_ks <= 1 && i8_plan_slice(N, G, 1, M, fuse, force_w, has_norm, p)) return true;
