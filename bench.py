@@ -323,7 +323,8 @@ def run_ours(args):
                      "kernel_us": round(us_kernel, 3), "frac_of_nominal_8TBps": round(achieved / 8000.0, 4)},
     }
     if world > 1 and not args.no_decode:
-        # tensor-parallel decoder (BASELINE configs[4]): every rank holds its shard, NCCL all-reduce per block
+        # tensor-parallel decoder (BASELINE configs[4]): every rank holds its shard; partial sums are exchanged over
+        # peer memory inside the norm / consuming matvec (NCCL all-reduce where peers cannot be mapped)
         from lthn import tp
         for w in ws:
             w.free()
