@@ -4,7 +4,11 @@
 
 The shared library is the product: a plain C ABI (include/lthn_cuda.h) over the
 hand-written kernels in csrc/. Sources are compiled one object per file so an
-edit only recompiles what changed."""
+edit only recompiles what changed.
+
+A second library, liblthn_cuda_hooks.so, is linked from the very same objects plus
+csrc/test_hooks.cu: it adds the lthn_debug_* entry points the parity tests use to force
+each kernel variant. The product library does not contain them."""
 from __future__ import annotations
 
 import os
@@ -15,6 +19,8 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "liblthn_cuda.so")
+OUT_HOOKS = os.path.join(HERE, "liblthn_cuda_hooks.so")
+HOOK_SOURCES = ("test_hooks.cu",)
 OBJ = os.path.join(HERE, "build")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
@@ -51,13 +57,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=8) as ex:
         list(ex.map(run, jobs))
-    objs = [os.path.join(OBJ, os.path.splitext(s)[0] + ".o") for s in sources()]
-    if jobs or force or not os.path.exists(OUT):
-        cmd = [NVCC, "-shared", "-o", OUT] + objs + ["-lcudart", "-ldl", "-lpthread"]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            sys.stderr.write(r.stdout + r.stderr)
-            raise RuntimeError("link failed")
+    for out, srcs in ((OUT, [s for s in sources() if s not in HOOK_SOURCES]), (OUT_HOOKS, sources())):
+        objs = [os.path.join(OBJ, os.path.splitext(s)[0] + ".o") for s in srcs]
+        if jobs or force or not os.path.exists(out):
+            cmd = [NVCC, "-shared", "-o", out] + objs + ["-lcudart", "-ldl", "-lpthread"]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                sys.stderr.write(r.stdout + r.stderr)
+                raise RuntimeError("link failed")
     return OUT
 
 

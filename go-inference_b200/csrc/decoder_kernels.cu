@@ -221,7 +221,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_gather_kernel(const PeerGather p
             st_release_sys(pg.flag_out[threadIdx.x] + pg.rank, seq);
         }
         bool ok = false;
-        for (uint32_t it = 0; it < (1u << 21); ++it) {
+        const uint32_t limit = pg.poll_limit ? pg.poll_limit : (1u << 21);
+        for (uint32_t it = 0; it < limit; ++it) {
             if ((int32_t)(ld_acquire_sys(pg.flag_in + threadIdx.x) - seq) >= 0) { ok = true; break; }
             __nanosleep(it < 64 ? 20 : 500);
         }

@@ -39,6 +39,7 @@ struct PeerGather {
     uint32_t* ctr;           // local: [0] sequence number of the last finished exchange, [1] CTA arrivals
     uint32_t* status;        // device status word (bit 256: a peer's flag did not arrive in time)
     int t, rank;
+    uint32_t poll_limit = 0; // polls before the wait gives up (0: the default, about a second)
 };
 int32_t launch_rmsnorm_gather(cudaStream_t s, const PeerGather& pg, float* h, const float* w_post, const float* w_next,
                               float* out, int rows, int width, float eps, uint16_t* cols, int split);

@@ -154,6 +154,10 @@ struct Model {
     bool site_fused[2] = {};    // tensor parallel: the site's norm runs inside the consuming matvec (push mode)
     bool xchg_ready = false;
     bool fuse_norm = false;  // batch 1-2: norms run inside the matvec that consumes them
+    // The logits buffer is shared by every session and lane set of the model: each forward that
+    // computes logits takes the next serial number, and a lane remembers the serial of its own
+    // last forward, so a read-out can tell whether the buffer still holds that lane's row.
+    uint64_t logits_serial = 0;
 };
 
 template <typename T>
@@ -494,6 +498,8 @@ struct Lane {
     int pending = -1;  // generated token not yet fed
     bool have_next = false;  // d_next of the last forward holds this lane's next token
     int next_tok = -1;
+    uint64_t logits_serial = 0;  // Model::logits_serial of the forward that produced this lane's logits
+    int logits_row = 0;          // its row in the logits buffer
     // lane-set bookkeeping
     int handle = 0, produced = 0, max_new = 0;
     bool terminal = false;
@@ -538,6 +544,8 @@ static int32_t feed_lane(Model* m, Lane* ln, const int32_t* ids, int n) {
     ln->next_tok = m->h_pinned[3 * kMaxRows];
     ln->have_next = true;
     ln->pending = -1;
+    ln->logits_serial = ++m->logits_serial;
+    ln->logits_row = 0;
     return device_status_judge((uint32_t)m->h_pinned[4 * kMaxRows], m->stream);
 }
 
@@ -1023,7 +1031,10 @@ int32_t lthn_session_logits(void* session, float* logits_host, int64_t n) {
     LTHN_REQUIRE(s->lane.have_next, "lthn_session_logits: no forward has been run since the last token was taken");
     LTHN_REQUIRE(n == s->m->V_l, "lthn_session_logits: buffer must hold the (local) vocabulary");
     std::lock_guard<std::mutex> lk(s->m->mu);
-    LTHN_CUDA_TRY(cudaMemcpyAsync(logits_host, s->m->logits, (size_t)n * 4, cudaMemcpyDeviceToHost, s->m->stream));
+    if (s->lane.logits_serial != s->m->logits_serial)
+        return fail(LTHN_ERR_STATE, "lthn_session_logits: a later forward of another session or lane set of this model has "
+                                    "overwritten the logits; read them before the next forward on the model");
+    LTHN_CUDA_TRY(cudaMemcpyAsync(logits_host, s->m->logits + (size_t)s->lane.logits_row * n, (size_t)n * 4, cudaMemcpyDeviceToHost, s->m->stream));
     LTHN_CUDA_TRY(cudaStreamSynchronize(s->m->stream));
     return LTHN_OK;
 }
@@ -1132,11 +1143,14 @@ int32_t lthn_laneset_step(void* set, int32_t* lane_handles, int32_t* tokens, int
         LTHN_CUDA_TRY(cudaMemcpyAsync(hp + 3 * kMaxRows, m->d_next, rows * 4, cudaMemcpyDeviceToHost, m->stream));
         if ((rc = device_status_read_async(m->stream, (uint32_t*)(hp + 4 * kMaxRows)))) return rc;
         LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+        ++m->logits_serial;
         for (int r = 0; r < rows; r++) {
             feed[r]->pos += 1;
             feed[r]->next_tok = hp[3 * kMaxRows + r];
             feed[r]->have_next = true;
             feed[r]->pending = -1;
+            feed[r]->logits_serial = m->logits_serial;
+            feed[r]->logits_row = r;
         }
         ls->forwards++;
         if ((rc = device_status_judge((uint32_t)hp[4 * kMaxRows], m->stream))) return rc;
@@ -1197,35 +1211,6 @@ int32_t lthn_rmsnorm_residual(void* stream, const float* a, float* h, const floa
     if (rows == 0) return LTHN_OK;
     LTHN_REQUIRE(a && h && w_post && w_next && out && rows > 0 && width > 0 && eps >= 0, "lthn_rmsnorm_residual: bad arguments");
     return launch_rmsnorm((cudaStream_t)stream, a, h, w_post, w_next, out, rows, width, eps, 1);
-}
-
-// Test hook for the tensor-parallel norm on one GPU: the t "ranks" are t local buffers
-// ([t][rows*width] in parts) and the flags are preset, so nothing waits; checks the rank-order
-// sum and the fused norms. scratch: at least 512 bytes of device memory.
-int32_t lthn_debug_rmsnorm_gather_local(void* stream, const float* parts, int32_t t, void* scratch, float* h,
-                                        const float* w_post, const float* w_next, float* out, int32_t rows,
-                                        int32_t width, float eps) {
-    clear_error();
-    LTHN_REQUIRE(parts && scratch && h && w_post && w_next && out && rows > 0 && width > 0 && t >= 2 && t <= 8,
-                 "lthn_debug_rmsnorm_gather_local: bad arguments");
-    cudaStream_t s = (cudaStream_t)stream;
-    uint32_t init[128] = {};
-    for (int r = 0; r < 8; r++) init[r] = 1u;  // every "peer" already signalled exchange 1
-    LTHN_CUDA_TRY(cudaMemcpyAsync(scratch, init, sizeof(init), cudaMemcpyHostToDevice, s));
-    LTHN_CUDA_TRY(cudaStreamSynchronize(s));
-    PeerGather g{};
-    g.t = t; g.rank = 0;
-    g.flag_in = (const uint32_t*)scratch;
-    g.ctr = (uint32_t*)scratch + 64;
-    g.status = device_status_word();
-    if (!g.status) return fail(LTHN_ERR_CUDA, "no device status word");
-    for (int r = 0; r < t; r++) {
-        g.part[r] = parts + (size_t)r * rows * width;
-        g.flag_out[r] = (uint32_t*)scratch + 16;  // a dummy line: CTA 0 writes its own signal there
-    }
-    int32_t rc = launch_rmsnorm_gather(s, g, h, w_post, w_next, out, rows, width, eps, nullptr, 0);
-    if (rc) return rc;
-    return check_device_status(s);
 }
 
 int32_t lthn_rmsnorm_rope(void* stream, const float* x, const float* w, const int32_t* positions, float* out,

@@ -32,6 +32,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <mutex>
 
 namespace lthn {
 
@@ -313,11 +314,15 @@ static EncodeTiledFn encode_fn() {
 template <int NT>
 static int32_t launch_qmm(cudaStream_t s, const CUtensorMap& map, const QmmArgs& a) {
     static int attr_dev = -1;
+    static std::mutex mu;
     int dev = 0;
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
-    if (attr_dev != dev) {
-        LTHN_CUDA_TRY(cudaFuncSetAttribute(qmm_tcgen05_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, QmmSmem<NT>::TOTAL));
-        attr_dev = dev;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (attr_dev != dev) {
+            LTHN_CUDA_TRY(cudaFuncSetAttribute(qmm_tcgen05_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, QmmSmem<NT>::TOTAL));
+            attr_dev = dev;
+        }
     }
     dim3 grid((a.N + NT - 1) / NT, (a.M + QMM_MT - 1) / QMM_MT);
     qmm_tcgen05_kernel<NT><<<grid, QMM_THREADS, QmmSmem<NT>::TOTAL, s>>>(map, a);
@@ -325,15 +330,13 @@ static int32_t launch_qmm(cudaStream_t s, const CUtensorMap& map, const QmmArgs&
     return LTHN_OK;
 }
 
-static int g_force_nt = 0;
+LTHN_HIDDEN int g_force_nt = 0;  // tile override: zero in the product library (setter: test_hooks.cu)
 
 }  // namespace lthn
 
 using namespace lthn;
 
 extern "C" {
-
-void lthn_debug_qmm_force_tile(int32_t nt) { g_force_nt = nt; }
 
 int32_t lthn_affine_qmm(void* stream, const uint16_t* x, int32_t M, const uint32_t* packed, const uint16_t* scales,
                         const uint16_t* biases, int64_t N, int64_t K, int32_t gs, int32_t bits, uint16_t* y) {

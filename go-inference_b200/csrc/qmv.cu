@@ -417,15 +417,17 @@ static int32_t launch_one(cudaStream_t s, const QmvArgs& a, int nwarps) {
     const int G = (int)(a.K / 64);
     const size_t smem = qmv_smem_bytes(RT, NT, FUSE == 1 ? 2 : 1, G, nwarps);
     if (smem > 200 * 1024) return fail(LTHN_ERR_INVALID, "affine_qmv: K too large for the shared scale/bias tile");
-    static bool attr_set = false;  // per instantiation
-    static int attr_dev = -1;
+    static int attr_dev = -1;  // per instantiation
+    static std::mutex mu;
     int dev = 0;
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
-    if (!attr_set || attr_dev != dev) {
-        LTHN_CUDA_TRY(cudaFuncSetAttribute(qmv_mma_kernel<RT, NT, FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           200 * 1024));
-        attr_set = true;
-        attr_dev = dev;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (attr_dev != dev) {
+            LTHN_CUDA_TRY(cudaFuncSetAttribute(qmv_mma_kernel<RT, NT, FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               200 * 1024));
+            attr_dev = dev;
+        }
     }
     const int64_t tr = 16 * RT;
     const unsigned grid = (unsigned)((a.N + tr - 1) / tr);
@@ -515,8 +517,9 @@ int32_t qmv_split_for(int M, int x_dtype) {
     return M <= 2 ? 3 : 2;  // f32 activations: exact 3-term split while it is free, else 2 terms (16 bits)
 }
 
-// test / tuning hooks (not part of the public header)
-static int g_force_rt = 0, g_force_warps = 0, g_force_kernel = 0;
+// dispatch overrides: always zero in the product library, which exports no way to set them;
+// the test-hook library adds setters (test_hooks.cu)
+LTHN_HIDDEN int g_force_rt = 0, g_force_warps = 0, g_force_kernel = 0;
 
 // Routes one call: 1-2 activation rows go to the dp4a kernel, 3..32 rows to the
 // tensor-core kernel (f32 activations are first split into bf16 columns).
@@ -581,18 +584,6 @@ int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
 using namespace lthn;
 
 extern "C" {
-
-// Tuning hooks used by the benchmark sweep and the tests: 0 restores the defaults.
-// rt: rows per thread (dp4a) / 16-row tiles per CTA (tensor-core kernel); kernel: 1 dp4a, 2 tensor-core.
-void lthn_debug_qmv_force_config(int32_t rt, int32_t nwarps) {
-    g_force_rt = rt;
-    g_force_warps = nwarps;
-}
-void lthn_debug_qmv_force_kernel(int32_t kernel) {
-    g_force_kernel = kernel & 15;
-    g_i8_probe = (kernel >> 4) & 1;
-    g_i8_stg = (kernel >> 8) & 7;
-}
 
 static int32_t qmv_validate(const void* x, int32_t x_dtype, int32_t M, const void* packed, const void* scales,
                             const void* biases, int64_t N, int64_t K, int32_t gs, int32_t bits, void* y,
@@ -688,7 +679,7 @@ int32_t lthn_affine_qmv_normed(void* stream, const float* a, const float* h_in, 
 // The array costs kQmvNoAllocBytes of device memory on every GPU that loads the library,
 // for the life of the process.
 constexpr size_t kQmvNoAllocBytes = 512u << 10;
-constexpr size_t kQmvNoAllocHeader = 256;  // status word, then the bf16 activation columns
+constexpr size_t kQmvNoAllocHeader = 256;  // sticky status word, then the bf16 activation columns
 static __device__ __align__(256) unsigned char g_qmv_noalloc[kQmvNoAllocBytes];
 // g_qmv_noalloc is only a host-side handle here; kernels need the device address, which
 // cudaGetSymbolAddress resolves once per device with that device current.
@@ -721,13 +712,16 @@ int32_t lthn_affine_qmv_noalloc(void* stream, const float* x, int32_t M, const u
         if (!g_qmv_noalloc_addr[dev]) {  // first call on this device: resolve the array's device address
             void* p = nullptr;
             LTHN_CUDA_TRY(cudaGetSymbolAddress(&p, g_qmv_noalloc));
+            // The header's status word must start at zero and is sticky from then on: a kernel
+            // whose bounded wait ran out sets a bit that stays until lthn_device_status reads and
+            // clears it, so a later call cannot hide an earlier failure.
+            LTHN_CUDA_TRY(cudaMemsetAsync(p, 0, kQmvNoAllocHeader, s));
+            device_status_register((uint32_t*)p);
             g_qmv_noalloc_addr[dev] = p;
         }
         base = (unsigned char*)g_qmv_noalloc_addr[dev];
     }
-    // the array keeps the previous call's bytes: the status word must start at zero, the
-    // activation columns are fully rewritten below
-    LTHN_CUDA_TRY(cudaMemsetAsync(base, 0, 4, s));
+    // the array keeps the previous call's bytes; the activation columns are fully rewritten below
     uint16_t* cols = (uint16_t*)(base + kQmvNoAllocHeader);
     int32_t rc = split_f32_launch(s, x, M, K, split, cols);
     if (rc) return rc;
@@ -764,6 +758,10 @@ int32_t lthn_affine_qmv_host(const void* x, size_t x_len, const void* packed, si
     LTHN_REQUIRE(gs == 32 || gs == 64 || gs == 128, "MatVec: this engine serves group sizes 32, 64 and 128");
     LTHN_REQUIRE((in_dim * bits) % 32 == 0, "MatVec: inDim*bits must fill whole 32-bit words");
 
+    // The staging arena (slot 1) and the stream are shared by every caller: concurrent MatVec calls
+    // from several host threads take turns here.
+    static std::mutex host_mu;
+    std::lock_guard<std::mutex> host_lk(host_mu);
     // one allocation, 256-byte aligned sections
     auto up = [](size_t v) { return (v + 255) / 256 * 256; };
     const size_t o_x = 0, o_p = o_x + up(x_len), o_s = o_p + up(packed_len), o_b = o_s + up(scales_len),

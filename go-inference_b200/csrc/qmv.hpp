@@ -75,7 +75,7 @@ int32_t dp4a_launch(cudaStream_t st, const QmvCall& c, const Dp4aPlan& p);
 
 // Integer tensor-core kernel (1-2 activation rows, N a multiple of 16).
 struct I8Plan { int J, W, RT, stg, RS, nblocks, threads, bs_off, stage_off, ks, Gs, fuse; size_t smem; };
-extern int g_i8_stg, g_i8_probe;
+extern __attribute__((visibility("hidden"))) int g_i8_stg;
 // max_slices: 1 = whole rows only; > 1 lets the plan cut K into up to that many slices (partial sums)
 bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I8Plan* p, int max_slices = 1,
              bool has_norm = false);

@@ -33,6 +33,7 @@
 
 #include <algorithm>
 #include <map>
+#include <mutex>
 #include <tuple>
 
 namespace lthn {
@@ -383,16 +384,15 @@ bool dp4a_plan(int64_t N, int64_t K, int M, int fuse, int force_r, int force_s, 
 
 template <int J, int R, int MT, int FUSE>
 static int32_t launch_dp4a_t(cudaStream_t st, const Dp4aArgs& a, const Dp4aPlan& p) {
-    static int cached_dev = -1, cached_occ = 0;
-    static size_t cached_smem = 0;
+    static int cached_dev = -1;
+    static std::mutex mu;  // guards the caches below against concurrent host threads
     int dev = 0;
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
     auto kern = qmv_dp4a_kernel<J, R, MT, FUSE>;
-    if (cached_dev != dev || cached_smem < p.smem) {
+    std::unique_lock<std::mutex> lk(mu);
+    if (cached_dev != dev) {
         LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         cached_dev = dev;
-        cached_smem = 200 * 1024;
-        cached_occ = 0;
     }
     // occupancy depends on the block size and shared memory of this launch
     static std::map<std::tuple<int, int, size_t>, int> occ_cache;
@@ -406,7 +406,7 @@ static int32_t launch_dp4a_t(cudaStream_t st, const Dp4aArgs& a, const Dp4aPlan&
     } else {
         occ = it->second;
     }
-    (void)cached_occ;
+    lk.unlock();
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = std::min(p.nblocks, sms * occ);

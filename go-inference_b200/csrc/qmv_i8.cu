@@ -14,7 +14,7 @@ int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p);
 
 // ---- host side --------------------------------------------------------------------
 
-int g_i8_stg = 0, g_i8_probe = 0;  // measurement aids
+LTHN_HIDDEN int g_i8_stg = 0;  // ring-stage override: zero in the product library (setter: test_hooks.cu)
 // dynamic shared memory a block may ask for (the SM has 227 KB for one block)
 static const size_t kI8MaxSmem = 224 * 1024;
 static const int kI8J[] = {1, 2, 3, 4, 6, 7, 8, 9, 12, 16, 18, 21};

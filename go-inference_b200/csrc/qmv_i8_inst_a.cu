@@ -40,7 +40,6 @@ int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p) {
     a.x = c.x; a.y = c.y; a.N = c.N; a.K = c.K; a.x_dtype = c.x_dtype; a.y_dtype = c.y_dtype;
     a.W = p.W; a.nblocks = p.nblocks; a.RS = p.RS; a.stg = p.stg;
     a.bs_off = p.bs_off; a.stage_off = p.stage_off;
-    a.probe = g_i8_probe;
     a.fuse_norm = c.norm ? 1 : 0;
     if (c.norm) a.nf = *c.norm;
     a.npush = c.npush;

@@ -28,6 +28,7 @@
 
 #include <algorithm>
 #include <map>
+#include <mutex>
 #include <tuple>
 
 namespace lthn {
@@ -45,7 +46,6 @@ struct I8Args {
     int RS;       // shared-memory row stride in bytes
     int stg;      // ring stages (2..4)
     int bs_off, stage_off;  // byte offsets into dynamic shared memory
-    int probe;              // 1: consumers skip the arithmetic (memory pipeline only; measurement aid)
     int fuse_norm;          // 1: activations come from the fused residual RMSNorm prologue (nf)
     int ks, Gs;             // K slices (CTA c works on slice c % ks) and groups per slice
     float* ypart;           // ks > 1: partial sums [ks][M][N] f32 instead of y
@@ -426,11 +426,6 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
         const int st = it % stg;
         if (!mbar_wait(&full[st], (it / stg) & 1)) { if (lane == 0) atomicOr(a.status, 64u); break; }
         const unsigned char* sbase = stages + (size_t)st * stage_bytes;
-        if (a.probe) {
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[st])) : "memory");
-            continue;
-        }
         float acc[SETS][RT][2], accb[SETS][RT];
 #pragma unroll
         for (int s = 0; s < SETS; s++)
@@ -519,9 +514,11 @@ __global__ void __launch_bounds__(160, 5) qmv_i8_kernel_small(const I8Args a) { 
 template <int J, int RT, int MT, int FUSE, int LB>
 inline int32_t launch_i8_t(cudaStream_t st, const I8Args& a, const I8Plan& p) {
     static int attr_dev = -1;
+    static std::mutex mu;  // guards attr_dev and occ_cache: entry points may be called from several host threads
     int dev = 0;
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
     void (*kern)(const I8Args) = LB == 160 ? qmv_i8_kernel_small<J, RT, MT, FUSE> : qmv_i8_kernel<J, RT, MT, FUSE, LB>;
+    std::unique_lock<std::mutex> lk(mu);
     if (attr_dev != dev) {
         LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
@@ -538,6 +535,7 @@ inline int32_t launch_i8_t(cudaStream_t st, const I8Args& a, const I8Plan& p) {
     } else {
         occ = it->second;
     }
+    lk.unlock();
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = std::max(1, std::min(p.nblocks, sms * occ / p.ks)) * p.ks;

@@ -5,7 +5,9 @@
 
 #include <cstring>
 #include <mutex>
+#include <algorithm>
 #include <string>
+#include <vector>
 
 namespace lthn {
 
@@ -67,24 +69,41 @@ int32_t device_status_judge(uint32_t v, cudaStream_t s) {
     return fail(LTHN_ERR_DEVICE_WAIT, "a device-side bounded wait ran out (status " + std::to_string(v) + ")");
 }
 
+// Arenas only grow, and a block that was handed out is never freed while the process lives:
+// kernels in flight, captured CUDA graphs and other host threads may still hold its address.
+// A request beyond the current size allocates a block of at least twice that size (so the
+// retired blocks sum to less than the live one) and keeps the old block until exit.
+static std::vector<void*> g_retired;
+
 int32_t scratch_get(size_t bytes, void** out, int slot) {
     int dev = 0;
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDev || slot < 0 || slot >= kSlots) return fail(LTHN_ERR_INVALID, "scratch: bad device or slot");
     std::lock_guard<std::mutex> lk(g_mu);
     if (g_scratch_bytes[dev][slot] < bytes) {
-        if (g_scratch[dev][slot]) {
-            LTHN_CUDA_TRY(cudaDeviceSynchronize());
-            LTHN_CUDA_TRY(cudaFree(g_scratch[dev][slot]));
-            g_scratch[dev][slot] = nullptr;
-            g_scratch_bytes[dev][slot] = 0;
-        }
-        size_t want = bytes < (size_t)(8u << 20) ? (size_t)(8u << 20) : bytes;
-        LTHN_CUDA_TRY(cudaMalloc(&g_scratch[dev][slot], want));
+        size_t want = std::max(bytes, 2 * g_scratch_bytes[dev][slot]);
+        if (want < (size_t)(8u << 20)) want = (size_t)(8u << 20);
+        void* p = nullptr;
+        LTHN_CUDA_TRY(cudaMalloc(&p, want));
+        if (g_scratch[dev][slot]) g_retired.push_back(g_scratch[dev][slot]);
+        g_scratch[dev][slot] = p;
         g_scratch_bytes[dev][slot] = want;
     }
     *out = g_scratch[dev][slot];
     return LTHN_OK;
+}
+
+// Sticky status words outside the arena (a kernel family that must not allocate keeps its own
+// word in a __device__ array and registers it here); read and cleared by lthn_device_status.
+static uint32_t* g_extra_status[kMaxDev][4];
+void device_status_register(uint32_t* word) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return;
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (auto& w : g_extra_status[dev]) {
+        if (w == word) return;
+        if (!w) { w = word; return; }
+    }
 }
 
 }  // namespace lthn
@@ -139,6 +158,40 @@ int32_t lthn_cuda_mem_info(uint64_t* free_bytes, uint64_t* total_bytes) {
     LTHN_CUDA_TRY(cudaMemGetInfo(&f, &t));
     if (free_bytes) *free_bytes = f;
     if (total_bytes) *total_bytes = t;
+    return LTHN_OK;
+}
+
+// Reads and clears every sticky device status word of the current device after synchronising
+// `stream`: the arena word the asynchronous entry points report into (only if one exists) and
+// the words of allocation-free entry points. Four-byte copies into host memory: allocates
+// nothing on the device.
+int32_t lthn_device_status(void* stream, uint32_t* bits) {
+    clear_error();
+    cudaStream_t s = (cudaStream_t)stream;
+    int dev = 0;
+    LTHN_CUDA_TRY(cudaGetDevice(&dev));
+    LTHN_REQUIRE(dev >= 0 && dev < kMaxDev, "lthn_device_status: device index out of range");
+    uint32_t* words[5];
+    int n = 0;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (g_status[dev]) words[n++] = g_status[dev];
+        for (uint32_t* w : g_extra_status[dev]) if (w) words[n++] = w;
+    }
+    LTHN_CUDA_TRY(cudaStreamSynchronize(s));
+    uint32_t all = 0;
+    for (int i = 0; i < n; i++) {
+        uint32_t v = 0;
+        LTHN_CUDA_TRY(cudaMemcpyAsync(&v, words[i], 4, cudaMemcpyDeviceToHost, s));
+        LTHN_CUDA_TRY(cudaStreamSynchronize(s));
+        if (v) {
+            LTHN_CUDA_TRY(cudaMemsetAsync(words[i], 0, 4, s));
+            LTHN_CUDA_TRY(cudaStreamSynchronize(s));
+        }
+        all |= v;
+    }
+    if (bits) *bits = all;
+    if (all) return fail(LTHN_ERR_DEVICE_WAIT, "a device-side bounded wait ran out (status " + std::to_string(all) + ")");
     return LTHN_OK;
 }
 

@@ -50,7 +50,12 @@ def lib() -> C.CDLL:
         _lib.lthn_last_error.restype = C.c_char_p
         for name in dir(_Sig):
             if name.startswith("lthn_"):
-                fn = getattr(_lib, name)
+                try:
+                    fn = getattr(_lib, name)
+                except AttributeError:
+                    if name.startswith("lthn_debug_"):
+                        continue   # only the test-hook build (liblthn_cuda_hooks.so) has these
+                    raise
                 fn.restype, fn.argtypes = getattr(_Sig, name)
     return _lib
 
@@ -65,6 +70,7 @@ class _Sig:
     lthn_cuda_set_device = (i32, [i32])
     lthn_cuda_device_info = (i32, [i32, C.POINTER(DeviceInfo)])
     lthn_cuda_mem_info = (i32, [C.POINTER(u64), C.POINTER(u64)])
+    lthn_device_status = (i32, [vp, C.POINTER(C.c_uint32)])
     lthn_malloc = (i32, [pvp, sz])
     lthn_free = (i32, [vp])
     lthn_host_alloc = (i32, [pvp, sz])
@@ -97,7 +103,7 @@ class _Sig:
     lthn_affine_qmv_normed = (i32, [vp, vp, vp, vp, vp, vp, f32, i32, vp, vp, vp, vp, vp, vp, i64, i64, vp, i32])
     lthn_rmsnorm = (i32, [vp, vp, vp, vp, i32, i32, f32])
     lthn_rmsnorm_residual = (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32])
-    lthn_debug_rmsnorm_gather_local = (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32])
+    lthn_debug_rmsnorm_gather_local = (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, i32, C.c_uint32])
     lthn_rmsnorm_rope = (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, f32, i32])
     lthn_sdpa_decode = (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, f32, i32])
     lthn_argmax = (i32, [vp, vp, i32, i32, vp])
@@ -168,6 +174,21 @@ def device_info(i: int = 0) -> DeviceInfo:
 
 def sync():
     check(lib().lthn_device_sync())
+
+
+def mem_info():
+    """(free, total) bytes of the current device."""
+    f, t = C.c_uint64(), C.c_uint64()
+    check(lib().lthn_cuda_mem_info(C.byref(f), C.byref(t)))
+    return int(f.value), int(t.value)
+
+
+def device_status(stream=None) -> int:
+    """Reads and clears the sticky device status words; raises LthnError (code 5) when a bounded
+    device-side wait ran out since the last read, else returns 0."""
+    bits = C.c_uint32()
+    check(lib().lthn_device_status(stream.h if stream else None, C.byref(bits)))
+    return int(bits.value)
 
 
 class Stream:

@@ -57,6 +57,15 @@ int32_t lthn_cuda_device_count(void);
 int32_t lthn_cuda_set_device(int32_t device);   /* binds the calling thread (cf. engine/hip/hip_driver_cgo.go:208) */
 int32_t lthn_cuda_device_info(int32_t device, lthn_device_info* out);
 int32_t lthn_cuda_mem_info(uint64_t* free_bytes, uint64_t* total_bytes); /* engine/memory_reporter.go */
+/* Device-side waits (mbarrier phases, peer flags) are bounded: a kernel whose wait runs out sets a
+ * bit in a sticky status word and returns, so the context stays usable. The host-buffer entry
+ * point, the sessions and the lane sets check that word themselves; after the asynchronous
+ * entry points (lthn_affine_qmv, _geglu, _normed, _noalloc, lthn_affine_qmm, lthn_sdpa_decode)
+ * call this to learn of it: synchronises `stream`, reads and clears the status words of the
+ * current device into *bits (may be NULL) and returns LTHN_ERR_DEVICE_WAIT when any bit was set.
+ * Copies four bytes per word to the host; allocates nothing. No counterpart in the reference
+ * (its HIP shim reports launch failures through hipGetLastError, engine/hip/hip_driver_cgo.go). */
+int32_t lthn_device_status(void* stream, uint32_t* bits);
 
 /* ---- device memory / streams / events: the thin driver wrappers a cgo shim
  * needs (cf. engine/hip/hip_driver_cgo.go:7-670 malloc/free/memcpy/events). ---- */
@@ -134,7 +143,9 @@ int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M,
  * rejected with LTHN_ERR_INVALID. The first call on a device resolves the array's device
  * address (cudaGetSymbolAddress) and should therefore come before any stream capture.
  * All calls on a device share the one array: calls whose kernels can overlap on the GPU
- * (different streams without ordering) race; order them. */
+ * (different streams without ordering) race; order them. The array's first word is a sticky
+ * status word (a bounded wait that ran out inside the kernel sets it; y is then not valid):
+ * lthn_device_status reads and clears it, also without allocating. */
 int32_t lthn_affine_qmv_noalloc(void* stream, const float* x, int32_t M, const uint32_t* packed,
                                 const uint16_t* scales, const uint16_t* biases, int64_t N, int64_t K, float* y);
 
@@ -285,7 +296,9 @@ int32_t lthn_session_pos(void* session);                                     /* 
  * stop decision to the caller (the Go side calls this in small chunks so `yield` can
  * stop it). The last produced token stays pending and is fed by the next call. */
 int32_t lthn_session_decode_greedy(void* session, int32_t max_new, int32_t eos_id, int32_t* out_ids, int32_t* n_out);
-/* Logits after the last fed token, for GenerateSampledFromCacheEach's host-side sampler. */
+/* Logits after the last fed token, for GenerateSampledFromCacheEach's host-side sampler. The
+ * buffer behind it belongs to the model: LTHN_ERR_STATE when another session or lane set of the
+ * model has run a forward since this session's last one. */
 int32_t lthn_session_logits(void* session, float* logits_host, int64_t n);
 /* CaptureKVWithOptions / RestoreFromKV payloads (kv/snapshot.go:98-143): one layer's keys
  * (which=0) or values (which=1) as bf16 [pos, kv_heads_local*head_dim]. */

@@ -7,6 +7,12 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# The tests run against the test-hook build of the library: the product's objects plus the
+# lthn_debug_* entry points that force each kernel variant (go-inference_b200/build.py links
+# both). Child processes of the multi-GPU tests inherit the choice through the environment.
+_HOOKS = os.path.join(ROOT, "go-inference_b200", "liblthn_cuda_hooks.so")
+if "LTHN_CUDA_LIB" not in os.environ and os.path.exists(_HOOKS):
+    os.environ["LTHN_CUDA_LIB"] = _HOOKS
 for p in (ROOT, os.path.join(ROOT, "go-inference_b200")):
     if p not in sys.path:
         sys.path.insert(0, p)

@@ -24,6 +24,20 @@ def test_library_exports_every_declared_symbol():
     assert not missing, missing
 
 
+def test_product_library_has_no_test_hooks():
+    """liblthn_cuda.so (what bench.py, smoke() and a cgo shim load) exports every declared symbol
+    and none of the lthn_debug_* hooks; those exist only in liblthn_cuda_hooks.so."""
+    import ctypes
+    prod = ctypes.CDLL(os.path.join(ROOT, "go-inference_b200", "liblthn_cuda.so"))
+    missing = [n for n in declared_symbols() if not hasattr(prod, n)]
+    assert not missing, missing
+    for hook in ("lthn_debug_qmv_force_config", "lthn_debug_qmv_force_kernel", "lthn_debug_qmm_force_tile",
+                 "lthn_debug_rmsnorm_gather_local"):
+        assert not hasattr(prod, hook), hook
+    hooks = ctypes.CDLL(os.path.join(ROOT, "go-inference_b200", "liblthn_cuda_hooks.so"))
+    assert hasattr(hooks, "lthn_debug_qmv_force_kernel")
+
+
 def test_binding_covers_every_declared_symbol():
     import lthn
     bound = {n for n in dir(lthn._Sig) if n.startswith("lthn_")}

@@ -108,6 +108,30 @@ def test_append_equals_prefill_and_chunked_decode(oracle):
     a.close(); b.close(); m.close()
 
 
+def test_logits_belong_to_the_session_that_ran_last(oracle):
+    """Two sessions of one model share the model's logits buffer. A read-out after another
+    session's forward must fail (LTHN_ERR_STATE) instead of returning the other session's
+    logits; after its own next forward it succeeds again."""
+    import lthn
+    cfg = SMALL
+    w, norms = synth_weights(oracle, lthn, cfg, seed=8)
+    m = build_device(lthn, cfg, w, norms, 64, max_lanes=2)
+    rng = np.random.default_rng(5)
+    ia, ib = (rng.integers(0, cfg["vocab"], n).astype(np.int32) for n in (12, 20))
+    a, b = m.open_session(), m.open_session()
+    a.prefill(ia)
+    la = a.logits()
+    b.prefill(ib)
+    lb = b.logits()
+    assert not np.array_equal(la, lb)
+    with pytest.raises(lthn.LthnError) as e:
+        a.logits()
+    assert e.value.code == 4
+    a.prefill(ia)
+    assert np.array_equal(a.logits(), la)
+    a.close(); b.close(); m.close()
+
+
 def test_kv_export_import_round_trip(oracle):
     """CaptureKV / RestoreFromKV payloads: a session restored from another's exported
     cache continues with the same tokens (enginetest/session.go:54-155 restore subtest)."""

@@ -69,7 +69,7 @@ def test_rmsnorm_gather_rank_order_sum(oracle, t, rows, width):
     pb, hb, out, scratch = dev(lthn, parts), dev(lthn, h), lthn.Buf(rows * width * 4), lthn.Buf(512)
     w1b, w2b = dev(lthn, w1), dev(lthn, w2)
     lthn.check(lthn.lib().lthn_debug_rmsnorm_gather_local(None, pb.ptr, t, scratch.ptr, hb.ptr, w1b.ptr, w2b.ptr, out.ptr,
-                                                         rows, width, 1e-6))
+                                                         rows, width, 1e-6, 1, 0))
     h_want = np.stack([h[r] + oracle.rmsnorm(a[r], w1, 1e-6) for r in range(rows)]).astype(np.float32)
     out_want = np.stack([oracle.rmsnorm(h_want[r], w2, 1e-6) for r in range(rows)])
     assert np.array_equal(hb.download(np.float32, (rows, width)).view(np.uint32), h_want.view(np.uint32))
@@ -78,6 +78,42 @@ def test_rmsnorm_gather_rank_order_sum(oracle, t, rows, width):
     # wait; instead check that the kernel advanced its counter exactly once
     ctr = scratch.download(np.uint32, (128,))
     assert ctr[64] == 1 and ctr[65] == 0
+
+
+def test_bounded_device_wait_runs_out_and_is_reported(oracle):
+    """A peer that never signals: the tensor-parallel norm polls its flag line a bounded number of
+    times (here 1024 polls, a fraction of a millisecond), records the time-out in the device
+    status word and returns by itself; the host turns that into LTHN_ERR_DEVICE_WAIT with the
+    peer-wait bit (256). The context stays usable: the status reads clean afterwards and the
+    same kernel, with its flags set, gives the exact result."""
+    import lthn
+    t, rows, width = 2, 2, 512
+    rng = np.random.default_rng(9)
+    parts = rng.standard_normal((t, rows, width)).astype(np.float32)
+    h = rng.standard_normal((rows, width)).astype(np.float32)
+    w1 = np.ones(width, dtype=np.float32)
+    w2 = np.ones(width, dtype=np.float32)
+    pb, out, scratch = dev(lthn, parts), lthn.Buf(rows * width * 4), lthn.Buf(512)
+    w1b, w2b = dev(lthn, w1), dev(lthn, w2)
+    assert lthn.device_status() == 0
+    hb = dev(lthn, h)
+    with pytest.raises(lthn.LthnError) as e:
+        lthn.check(lthn.lib().lthn_debug_rmsnorm_gather_local(None, pb.ptr, t, scratch.ptr, hb.ptr, w1b.ptr, w2b.ptr,
+                                                             out.ptr, rows, width, 1e-6, 0, 1024))
+    assert e.value.code == 5 and "256" in e.value.msg
+    assert lthn.device_status() == 0            # read-and-clear: the failure is reported once
+    hb = dev(lthn, h)
+    lthn.check(lthn.lib().lthn_debug_rmsnorm_gather_local(None, pb.ptr, t, scratch.ptr, hb.ptr, w1b.ptr, w2b.ptr,
+                                                         out.ptr, rows, width, 1e-6, 1, 0))
+    a = (parts[0] + parts[1]).astype(np.float32)
+    h_want = np.stack([h[r] + oracle.rmsnorm(a[r], w1, 1e-6) for r in range(rows)]).astype(np.float32)
+    assert np.array_equal(hb.download(np.float32, (rows, width)).view(np.uint32), h_want.view(np.uint32))
+    # the asynchronous entry points report through the same word: a clean matvec leaves it clean
+    from gpu_util import make_weight
+    q = lthn.QuantWeight.from_host(*make_weight(oracle, 64, 128, seed=1))
+    x, y = dev(lthn, np.ones((1, 128), dtype=np.float32)), lthn.Buf(64 * 4)
+    lthn.qmv(x, lthn.F32, 1, q, y, lthn.F32)
+    assert lthn.device_status() == 0
 
 
 @pytest.mark.parametrize("heads,D,rotary", [(8, 256, 256), (4, 128, 128), (2, 512, 512), (3, 64, 32), (2, 512, 128)])

@@ -42,6 +42,29 @@ def test_noalloc_matches_existing_entry_point_twice_in_a_row(oracle):
         assert rms_err(got, want) <= (TOL if M <= 2 else 4e-5), (call, M)
 
 
+def test_noalloc_allocates_no_device_memory_and_reports_its_status(oracle):
+    """The property in the name: calls of the entry point leave the device's free memory untouched
+    (cudaMemGetInfo before and after), for both kernel shapes (1-2 rows, 3-32 rows). One call per
+    shape comes first, untimed: the CUDA runtime loads a kernel's code into device memory at its
+    first launch, which is the runtime's doing and happens once per process. Its status word,
+    which lives in the same fixed array, reads clean through lthn_device_status."""
+    import lthn
+    N, K = 1024, 2304
+    q = lthn.QuantWeight.from_host(*make_weight(oracle, N, K, seed=3))
+    xs = {M: lthn.Buf.from_array(np.random.default_rng(M).standard_normal((M, K)).astype(np.float32)) for M in (1, 8)}
+    ys = {M: lthn.Buf(M * N * 4) for M in (1, 8)}
+    for M in (1, 8):
+        lthn.qmv_noalloc(xs[M], M, q, ys[M])
+    lthn.sync()
+    free0, _ = lthn.mem_info()
+    for _ in range(2):
+        for M in (1, 8):
+            lthn.qmv_noalloc(xs[M], M, q, ys[M])
+    assert lthn.device_status() == 0
+    free1, _ = lthn.mem_info()
+    assert free1 == free0, (free0, free1)
+
+
 def test_noalloc_rejects_sizes_beyond_its_fixed_scratch(oracle):
     import lthn
     q = lthn.QuantWeight.from_host(*make_weight(oracle, 16, 64, seed=1))
