@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--full]
 
-Workload (BASELINE.json configs[1], the decode sweep): affine_qmv at batch 1 on
+Headline workload (the decode sweep's largest matrix): affine_qmv at batch 1 on
 the lm_head shape (N=262144, K=2304), uint4 weights, group 64, bf16 scales/biases,
 weights ~ N(0, 0.02) generated on the device by the seeded synthetic source that
 the CPU oracle shares, bf16 activations ~ N(0, 1). A "step" is one pass of the hot
@@ -12,7 +12,11 @@ bytes / step time with everything resident in HBM; three weight copies (1 GB, fa
 larger than the 126 MB L2) are rotated between steps. `e2e` is the same metric
 through the reference-facing call (model.QuantMatVec.MatVec semantics: host byte
 buffers in, host bytes out) with the host<->device copies inside the timed region.
-The other shapes and batch sizes of the sweep are reported under `sweep`.
+Reported beside it, from the same run: `sweep` (every shape and batch size of the
+decode sweep), `qmm` (the prefill matmul, M in {512, 2048, 8192}, TFLOP/s against the
+measured dense bf16 peak), `decode` (greedy tokens/s of the 26-layer decoder at batch 1
+and 16 and of the 62-layer decoder at batch 1 and 32; under torchrun the 62-layer decoder
+is tensor-parallel over the N GPUs and carries `tokens_equal_tp1`) and the CPU baselines.
 
 With --gpus N (launched by torch.distributed.run) every rank runs the same
 per-GPU workload on its own device (row-sharded weights need no collective), so
@@ -142,7 +146,7 @@ def time_graph(lthn, st, fn, iters):
 def run_sweep(lthn, st, peak, full):
     """Per-shape GB/s for the decode sweep; small shapes rotate >= 600 MB of weight copies."""
     out = []
-    ms = SWEEP_M if full else [1, 8, 32]
+    ms = SWEEP_M
     for (N, K) in SWEEP_SHAPES:
         wbytes = N * K * 9 // 16
         copies = max(3, min(64, int(np.ceil(600e6 / wbytes))))
@@ -162,6 +166,49 @@ def run_sweep(lthn, st, peak, full):
     return out
 
 
+QMM_SHAPES = [(9216, 2304), (2304, 9216), (21504, 5376)]
+QMM_M = [512, 2048, 8192]
+
+
+def measured_bf16_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["bf16_tflops"]), "measured burst"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
+
+
+def run_qmm(lthn, st):
+    """affine_qmm (prefill): TFLOP/s of 2*M*N*K per launch against the measured dense bf16 peak.
+    bf16 activations ~ N(0,1); weight / activation / output sets are rotated so that consecutive
+    launches touch more than the 126 MB L2 holds."""
+    peak, kind = measured_bf16_peak()
+    out = []
+    for (N, K) in QMM_SHAPES:
+        for M in QMM_M:
+            per_call = N * K * 9 // 16 + 2 * M * K + 2 * M * N
+            copies = max(2, min(16, int(np.ceil(300e6 / per_call))))
+            ws = [lthn.QuantWeight.synth(2000 + i, 0.02, N, K, stream=st) for i in range(copies)]
+            xh = bf16_bits(np.random.default_rng(M + K).standard_normal((M, K)))
+            xs = [lthn.Buf.from_array(xh) for _ in range(copies)]
+            ys = [lthn.Buf(M * N * 2) for _ in range(copies)]
+            flops = 2.0 * M * N * K
+            iters = int(max(4, min(60, 30e-3 / (flops / 0.8e15))))
+            us = time_graph(lthn, st, lambda i: lthn.qmm(xs[i % copies], M, ws[i % copies], ys[i % copies], st), iters)
+            tf = flops / us / 1e6
+            out.append({"M": M, "N": N, "K": K, "us": round(us, 2), "TFLOPs": round(tf, 1),
+                        "frac_of_bf16_peak": round(tf / peak, 4), "algorithmic_bytes": per_call,
+                        "GBps": round(per_call / us / 1e3, 1)})
+            for b in ws:
+                b.free()
+            for b in xs + ys:
+                b.free()
+    return {"peak_tflops": peak, "peak_kind": f"of {kind}", "unit": "TFLOP/s", "flops": "2*M*N*K",
+            "l2": "rotated operand sets, >= 300 MB per rotation", "cases": out}
+
+
 GEMMA_2B = dict(layers=26, hidden=2304, q_heads=8, kv_heads=4, head_dim=256, ffn=9216, vocab=262144)
 GEMMA_27B = dict(layers=62, hidden=5376, q_heads=32, kv_heads=16, head_dim=128, ffn=21504, vocab=262144)
 
@@ -172,9 +219,12 @@ def decode_weight_bytes(cfg, tp=1):
     return (cfg["layers"] * per_layer + cfg["vocab"] * H * 9 // 16) // tp
 
 
-def run_decode(lthn, cfg, name, prompt_len, new_tokens, batch, peak, comm=None, rank=0, world=1):
-    """Greedy decode tokens/s of a synthetic Gemma-style 4-bit decoder (BASELINE configs[3]/[4]):
-    random prompt, then `new_tokens` greedy tokens at batch 1 (Session) and at `batch` lanes (LaneSet)."""
+def run_decode(lthn, cfg, name, prompt_len, new_tokens, batch, peak, comm=None, rank=0, world=1, check_tp1=False,
+               dist=None):
+    """Greedy decode tokens/s of a synthetic Gemma-style 4-bit decoder: random prompt, then
+    `new_tokens` greedy tokens at batch 1 (Session) and at `batch` lanes (LaneSet). With
+    check_tp1 (tensor-parallel runs) the ranks also decode 64 tokens from a 32-token prompt and
+    rank 0 compares them with the same model held whole on its own GPU."""
     mc = lthn.make_config(cfg["layers"], cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"],
                           cfg["vocab"], prompt_len + new_tokens, batch + 1, tp_rank=rank, tp_size=world)
     m = lthn.Model(mc)
@@ -190,6 +240,12 @@ def run_decode(lthn, cfg, name, prompt_len, new_tokens, batch, peak, comm=None, 
     ids = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
     s.prefill(ids[:64])          # warm-up (first use allocates scratch)
     s.decode_greedy(4)
+    short_toks = None
+    if check_tp1:
+        # a prompt of at most 32 tokens is fed through the f32 decode kernels on every rank count,
+        # where identical tokens are a fair demand
+        s.prefill(ids[:32])
+        short_toks = s.decode_greedy(64).tolist()
     t0 = time.perf_counter()
     s.prefill(ids)
     t1 = time.perf_counter()
@@ -215,6 +271,25 @@ def run_decode(lthn, cfg, name, prompt_len, new_tokens, batch, peak, comm=None, 
                                 "batch_forwards": ls.batch_forward_count}
         ls.close()
     m.close()
+    if check_tp1:
+        if dist is not None:
+            dist.barrier()
+        if rank == 0:
+            mc1 = lthn.make_config(cfg["layers"], cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"],
+                                   cfg["ffn"], cfg["vocab"], 32 + 64, 1)
+            m1 = lthn.Model(mc1)
+            m1.synthesize(0, 0.02)
+            m1.finalize()
+            s1 = m1.open_session()
+            s1.prefill(ids[:32])
+            want = s1.decode_greedy(64).tolist()
+            s1.close()
+            m1.close()
+            same = next((i for i in range(64) if want[i] != short_toks[i]), 64)
+            out["tokens_equal_tp1"] = {"equal": same == 64, "first_difference": None if same == 64 else same,
+                                       "tokens": 64, "prompt": 32}
+        if dist is not None:
+            dist.barrier()
     return out
 
 
@@ -312,52 +387,62 @@ def run_ours(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u4*bf16->f32",
         "data": "synthetic",
-        "config": {"workload": "affine_qmv decode sweep (BASELINE configs[1]): lm_head N=262144 K=2304 M=1, "
+        "config": {"workload": "affine_qmv decode sweep, largest matrix: lm_head N=262144 K=2304 M=1, "
                                "uint4 g64 bf16 scale/bias, weights N(0,0.02), x bf16 N(0,1)",
                    "l2": "3 rotated weight copies of 340 MB each (inputs larger than the 126 MB L2)",
                    "sharding": "independent row shards per GPU, no collective"},
         "clocks": clk.summary(), "e2e": e2e, "gpu_launches": args.steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                     "frac": round(achieved / peak, 4), "traffic": traffic_bytes_per_launch(),
                      "peak_kind": f"of {peak_kind}", "algorithmic_bytes": bytes_step,
                      "kernel_us": round(us_kernel, 3), "frac_of_nominal_8TBps": round(achieved / 8000.0, 4)},
     }
-    if world > 1 and not args.no_decode:
-        # tensor-parallel decoder (BASELINE configs[4]): every rank holds its shard; partial sums are exchanged over
-        # peer memory inside the norm / consuming matvec (NCCL all-reduce where peers cannot be mapped)
-        from lthn import tp
-        for w in ws:
-            w.free()
-        # the headline line above does not depend on this section: a failure here is reported, not fatal
-        try:
-            comm = tp.init_comm(rank, world)
-            dec = run_decode(lthn, GEMMA_27B, f"gemma-style 62L/5376 (BASELINE configs[4]), TP{world}", 4096, 512,
-                             32 if args.full else 1, peak, comm=comm, rank=rank, world=world)
-        except Exception as e:  # noqa: BLE001
-            dec = {"error": f"{type(e).__name__}: {e}"[:300]}
-        if rank == 0:
-            line["decode_tp"] = dec
-        ws = []
+    for w in ws:
+        w.free()
+    ws = []
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline(sample_rows=65536, threads=1)
+        if world == 1:
+            line["cpu_baseline_single_linear"] = cpu_single_linear()
         if not args.no_sweep and world == 1:
             line["sweep"] = run_sweep(lthn, st, peak, args.full)
-        if not args.no_decode and world == 1:
-            for w in ws:
-                w.free()
-            ws = []
-            line["decode"] = [run_decode(lthn, GEMMA_2B, "gemma-style 26L/2304 (BASELINE configs[3])", 1024, 256, 16, peak)]
-            if args.full:
-                line["decode"].append(run_decode(lthn, GEMMA_27B, "gemma-style 62L/5376 (BASELINE configs[4])", 4096, 512, 32, peak))
+            line["qmm"] = run_qmm(lthn, st)
+    if not args.no_decode:
+        dec = []
+        if world == 1:
+            dec.append(run_decode(lthn, GEMMA_2B, "gemma-style 26L/2304, 1024-token prompt, 256 new tokens", 1024, 256,
+                                  16, peak))
+        # the 62-layer decoder: whole on one GPU, or tensor-parallel over the ranks (partial sums
+        # exchanged over peer memory inside the norm / consuming matvec; NCCL where peers cannot map)
+        try:
+            comm = None
+            if world > 1:
+                from lthn import tp
+                comm = tp.init_comm(rank, world)
+            dec.append(run_decode(lthn, GEMMA_27B, f"gemma-style 62L/5376, 4096-token prompt, 512 new tokens, TP{world}",
+                                  4096, 512, 32, peak, comm=comm, rank=rank, world=world, check_tp1=world > 1, dist=dist))
+        except Exception as e:  # noqa: BLE001 - the headline line does not depend on this section
+            dec.append({"model": f"gemma-style 62L/5376 TP{world}", "error": f"{type(e).__name__}: {e}"[:300]})
+        if rank == 0:
+            line["decode"] = dec
+            if world > 1:
+                line["decode_tp"] = dec[-1]
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one lm_head launch (ncu capture
-# summarised in profiles/affine_qmv_i8mma_lm_head_M1.md)
-TRAFFIC_BYTES_PER_LAUNCH = 344690944
+def traffic_bytes_per_launch():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one lm_head launch, from the figures file
+    kept beside the ncu summary of that kernel (null when it is absent)."""
+    p = os.path.join(ROOT, "profiles", "affine_qmv_i8mma_lm_head_M1.json")
+    try:
+        d = json.load(open(p))
+        return int(d["dram_bytes_read"]) + int(d["dram_bytes_write"])
+    except Exception:
+        return None
 
 
 # ------------------------------------------------------------- reference ----
@@ -385,13 +470,42 @@ def cpu_baseline(sample_rows, threads):
             "ms_per_sample": round(dt * 1e3, 3)}
 
 
+def cpu_single_linear():
+    """The reference's own CPU-runnable case: one affine-4bit linear, W [8192, 2048] ~ N(0, 0.02)
+    seed 0 rounded to bf16, x [1, 2048] ~ N(0, 1): quantise (both rules) and y = x * dequant(W)^T on
+    the host cores, single thread as the reference's serial Go loop and on all cores."""
+    from oracle import oracle as o
+    o.build()
+    N, K = 8192, 2048
+    w = (np.random.default_rng(0).standard_normal((N, K)) * 0.02).astype(np.float32)
+    w = o.bf16_to_f32(o.f32_to_bf16(w))
+    x = o.bf16_to_f32(bf16_bits(np.random.default_rng(1).standard_normal((1, K))))
+    out = {"shape": [N, K], "kind": "port"}
+    for variant, name in ((0, "quantize_reference_rule_ms"), (1, "quantize_literal_minmax_ms")):
+        t0 = time.perf_counter()
+        p, s, b = o.quantize(w, 4, 64, variant)
+        out[name] = round((time.perf_counter() - t0) * 1e3, 2)
+    cores = os.cpu_count() or 1
+    for threads, name in ((1, "matvec_1_thread"), (cores, f"matvec_{cores}_threads")):
+        o.matnt_quant_host(x, p, s, b, threads=threads)
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 1.0:
+            o.matnt_quant_host(x, p, s, b, threads=threads)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        out[name] = {"ms": round(dt * 1e3, 3), "GBps": round(algo_bytes(N, K, 1) / dt / 1e9, 3), "cores": threads}
+    return out
+
+
 def run_reference(args):
     rank, _, world = dist_env()
     if rank != 0:
         return
     from oracle import oracle as o
     o.build()
-    threads = o.lib().lthn_o_num_threads()
+    # every host core, stated explicitly: a launcher may have set OMP_NUM_THREADS=1 for its ranks
+    threads = os.cpu_count() or 1
     steps = max(args.steps, 1)
     N, K, M = 65536, HEAD_K, HEAD_M
     w = o.synth_normal(7, 0, N * K, 0.02).reshape(N, K)
@@ -409,7 +523,7 @@ def run_reference(args):
         "impl": "reference", "metric": "affine_qmv_4bit_GBps", "value": v, "unit": "GB/s", "n_gpus": world,
         "steps": steps, "warmup": max(args.warmup, 1), "ms_per_step": round(dt * 1e3, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u4*f32->f64", "data": "synthetic",
-        "config": {"workload": "affine_qmv decode sweep (BASELINE configs[1]): lm_head N=262144 K=2304 M=1 "
+        "config": {"workload": "affine_qmv decode sweep, largest matrix: lm_head N=262144 K=2304 M=1 "
                                "(bounded sample of rows), CPU restatement of attn.matNTQuantHost"},
         "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -422,7 +536,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--full", action="store_true", help="report every batch size of the sweep")
+    ap.add_argument("--full", action="store_true", help="kept for compatibility: the default run already reports everything")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     args = ap.parse_args()

@@ -38,6 +38,27 @@ def synth_weights(oracle, lthn, cfg, seed, sigma=0.02, random_norms=False):
     return w, norms
 
 
+def synth_weights_from_device(lthn, cfg, seed, sigma=0.02):
+    """The same tensors for models too large to generate on the CPU in seconds: drawn and quantised
+    by the device generator (tests/test_gpu_codec.py holds it bit-identical to the oracle's) and
+    downloaded. Norm weights are 1, as lthn_model_synthesize sets them."""
+    w = {}
+    shapes = linear_shapes(cfg)
+    for li in range(cfg["layers"]):
+        for ri, role in enumerate(ROLES):
+            n, k = shapes[role]
+            q = lthn.QuantWeight.synth(lthn.tensor_seed(seed, li, ri), sigma, n, k)
+            w[(li, role)] = q.to_host()
+            q.free()
+    q = lthn.QuantWeight.synth(lthn.tensor_seed(seed, -1, 0), sigma, cfg["vocab"], cfg["hidden"])
+    w["embed"] = q.to_host()
+    q.free()
+    norms = {(li, role): np.ones(cfg["head_dim"] if role in ("q_norm", "k_norm") else cfg["hidden"], dtype=np.float32)
+             for li in range(cfg["layers"]) for role in NORMS}
+    norms["final"] = np.ones(cfg["hidden"], dtype=np.float32)
+    return w, norms
+
+
 def build_oracle(oracle, cfg, w, norms, max_len):
     embed_scale = float(oracle.bf16_to_f32(oracle.f32_to_bf16(np.array([np.sqrt(cfg["hidden"])], dtype=np.float32)))[0])
     oc = oracle.DecoderConfig(layers=cfg["layers"], hidden=cfg["hidden"], q_heads=cfg["q_heads"],
@@ -75,7 +96,7 @@ def build_device(lthn, cfg, w, norms, max_len, max_lanes=1, tp_rank=0, tp_size=1
 
 SMALL = dict(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1024)
 MID = dict(layers=3, hidden=512, q_heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=4096)
-# BASELINE configs[3]: 26 layers, hidden 2304, 8 q / 4 kv heads x 256, GeGLU 9216, vocab 262144
+# the 26-layer decoder of the single-GPU decode benchmark: hidden 2304, 8 q / 4 kv heads x 256, GeGLU 9216, vocab 262144
 GEMMA_2B = dict(layers=26, hidden=2304, q_heads=8, kv_heads=4, head_dim=256, ffn=9216, vocab=262144)
-# BASELINE configs[4]: 62 layers, hidden 5376, 32 q / 16 kv heads x 128, GeGLU 21504, vocab 262144
+# the 62-layer decoder of the tensor-parallel benchmark: hidden 5376, 32 q / 16 kv heads x 128, GeGLU 21504, vocab 262144
 GEMMA_27B = dict(layers=62, hidden=5376, q_heads=32, kv_heads=16, head_dim=128, ffn=21504, vocab=262144)

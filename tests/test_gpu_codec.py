@@ -55,7 +55,7 @@ def test_synth_weight_matches_oracle_generator(oracle):
 
 
 def test_quantize_full_size_round_trip_property(oracle):
-    """BASELINE-size tensor (8192 x 2048): device quantise -> device dequantise stays
+    """The single-linear reference case (8192 x 2048): device quantise -> device dequantise stays
     inside the reference's group error bound (mlxaffine_test.go:63-64) and the codes
     of a sample of rows equal the oracle's."""
     import lthn

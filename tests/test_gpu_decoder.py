@@ -247,7 +247,7 @@ def test_rejected_arguments(oracle):
 
 
 def test_gemma_2b_shape_greedy_256_tokens(oracle):
-    """BASELINE configs[3]: the 26-layer decoder (hidden 2304, 8/4 heads x 256, GeGLU 9216,
+    """The 26-layer decoder of the single-GPU decode benchmark (hidden 2304, 8/4 heads x 256, GeGLU 9216,
     vocab 262144), synthetic N(0,0.02) 4-bit weights, a 1024-token random prompt, then 256
     greedy tokens: the device must reproduce the CPU reference's token sequence. Where the
     sequences part, the reference's top-1/top-2 logit margin at that step is reported."""

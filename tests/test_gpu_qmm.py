@@ -41,7 +41,7 @@ def test_qmm_matches_oracle(oracle, tile, M, N, K):
 
 
 def test_qmm_baseline_shape_m512(oracle):
-    """BASELINE configs[2] smallest case at full size: M=512, (N,K)=(9216,2304)."""
+    """The smallest prefill benchmark case at full size: M=512, (N,K)=(9216,2304), every output against the oracle."""
     import lthn
     M, N, K = 512, 9216, 2304
     p, s, b = make_weight(oracle, N, K, seed=1)
@@ -51,23 +51,32 @@ def test_qmm_baseline_shape_m512(oracle):
     assert bf16_close(oracle, got16, oracle.bf16_to_f32(want16))
 
 
-def test_qmm_large_shape_agrees_with_decode_kernel(oracle):
-    """BASELINE configs[2] large case (M=2048, N=21504, K=5376): too big for the CPU
-    oracle in seconds, so sampled token rows are checked against affine_qmv (itself
-    oracle-checked), which multiplies the unrounded weights: agreement within 1e-2."""
+def _sampled_check(lthn, oracle, M, N, K, seed):
+    """Full-size launch, oracle on sampled (token row, weight row) pairs: weights come from the
+    device generator (identical to the oracle's), the CPU restates only the sampled rows."""
+    q = lthn.QuantWeight.synth(seed, 0.02, N, K)
+    p, s, b = q.to_host()
+    xb = oracle.f32_to_bf16(np.random.default_rng(seed).standard_normal((M, K)).astype(np.float32))
+    got16 = run_qmm(lthn, xb, M, q)
+    assert np.isfinite(oracle.bf16_to_f32(got16)).all()
+    rng = np.random.default_rng(seed + 1)
+    trows = np.unique(np.concatenate([[0, 1, 127, 128, 255, 256, M - 1], rng.integers(0, M, 9)]))
+    wrows = np.unique(np.concatenate([np.arange(0, 40), np.arange(N - 40, N), rng.integers(0, N, 400)]))
+    want16 = oracle.qmm_bf16(xb[trows], p[wrows], s[wrows], b[wrows])
+    assert bf16_close(oracle, got16[np.ix_(trows, wrows)], oracle.bf16_to_f32(want16))
+    ref = oracle.matnt_quant_host(oracle.bf16_to_f32(xb[trows]), p[wrows], s[wrows], b[wrows], threads=8)
+    assert rel_err(oracle.bf16_to_f32(got16[np.ix_(trows, wrows)]), ref) <= 1e-2
+    q.free()
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 21504, 5376), (8192, 9216, 2304), (2048, 2304, 9216)])
+def test_qmm_prefill_shapes_at_full_size(oracle, M, N, K):
+    """The large prefill shapes (2048 tokens on the 21504 x 5376 projection, 8192 tokens on
+    9216 x 2304, the K = 9216 down projection) are too big for the CPU oracle as a whole, so
+    sampled token rows x sampled weight rows are held to the same two bounds as the small cases:
+    one bf16 ulp of the bf16-contract oracle, 1e-2 of the f64 reference on unrounded weights."""
     import lthn
-    M, N, K = 2048, 21504, 5376
-    q = lthn.QuantWeight.synth(9, 0.02, N, K)
-    xb = oracle.f32_to_bf16(np.random.default_rng(3).standard_normal((M, K)).astype(np.float32))
-    got = oracle.bf16_to_f32(run_qmm(lthn, xb, M, q))
-    rows = np.array([0, 1, 127, 128, 255, 256, 1000, 2047])
-    xs = lthn.Buf.from_array(xb[rows])
-    y = lthn.Buf(len(rows) * N * 4)
-    lthn.qmv(xs, lthn.BF16, len(rows), q, y, lthn.F32)
-    lthn.sync()
-    ref = y.download(np.float32, (len(rows), N))
-    assert rel_err(got[rows], ref) <= 1e-2
-    assert np.isfinite(got).all()
+    _sampled_check(lthn, oracle, M, N, K, seed=9)
 
 
 def test_qmm_small_m_and_other_widths_route_to_decode_kernels(oracle):

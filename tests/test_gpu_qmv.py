@@ -15,6 +15,7 @@ pytestmark = pytest.mark.gpu
 
 F32_TOL_RMS = 2e-5   # f32 output vs f64 oracle, relative to output RMS
 REF_TOL = 1e-2       # the reference's tolerance form
+BATCH_TOL_RMS = 2e-5  # 3..32 activation rows
 
 
 def run_qmv(lthn, x_arr, x_dtype, M, q, y_dtype):
@@ -59,7 +60,7 @@ def test_seam_fixture_shapes(oracle, M, K, N, bits, gs):
 @pytest.mark.parametrize("N,K", [(2304, 2304), (9216, 2304), (2304, 9216)])
 @pytest.mark.parametrize("M", [1, 2, 4, 8, 16, 32])
 def test_decode_sweep_shapes_bf16(oracle, N, K, M):
-    """BASELINE decode sweep shapes, bf16 activations ~ N(0,1), weights ~ N(0,0.02)."""
+    """The decode sweep shapes, bf16 activations ~ N(0,1), weights ~ N(0,0.02)."""
     import lthn
     p, s, b = make_weight(oracle, N, K, seed=N + K)
     xf, xb = make_x(oracle, M, K, seed=M)
@@ -130,7 +131,7 @@ def test_every_kernel_configuration_agrees(oracle):
                                  (128, 40), (64, 5), (1536, 77)])
 @pytest.mark.parametrize("M", [1, 2])
 def test_dp4a_kernel_shapes(oracle, K, N, M):
-    """The batch-1/2 kernel over every K of the BASELINE models (2304, 9216, 5376, 21504,
+    """The batch-1/2 kernel over every K of the two benchmark decoders (2304, 9216, 5376, 21504,
     4096, 2048) and awkward small ones, f32 and bf16 activations."""
     import lthn
     p, s, b = make_weight(oracle, N, K, seed=K + N)
@@ -157,7 +158,7 @@ def test_dp4a_kernel_shapes(oracle, K, N, M):
                                  (21504, 64), (21504, 5376), (10752, 2304), (9216, 2304), (14336, 4096), (4096, 5008)])
 @pytest.mark.parametrize("M", [1, 2])
 def test_i8_tensor_core_kernel_shapes(oracle, K, N, M):
-    """The integer tensor-core batch-1/2 kernel (forced) over the K of the BASELINE models and
+    """The integer tensor-core batch-1/2 kernel (forced) over the K of the two benchmark decoders and
     awkward small ones, f32 and bf16 activations, both tile heights, ragged last row block."""
     import lthn
     p, s, b = make_weight(oracle, N, K, seed=K + N)
@@ -288,7 +289,7 @@ def test_negative_scales_and_literal_variant(oracle):
 
 
 def test_lm_head_full_size(oracle):
-    """Full BASELINE lm_head shape (262144 x 2304), weights generated on the device:
+    """Full-size lm_head shape (262144 x 2304), weights generated on the device:
     compared row-for-row with the oracle, plus linearity as a size-independent check."""
     import lthn
     N, K = 262144, 2304
@@ -303,6 +304,16 @@ def test_lm_head_full_size(oracle):
     xs = (xf[0] + xf[1])[None, :].astype(np.float32)
     got_sum = run_qmv(lthn, xs, lthn.F32, 1, q, lthn.F32)
     assert rms_err(got_sum[0], got[0].astype(np.float64) + got[1]) <= 5e-5
+    # the batched row counts of the decode sweep on the same matrix, against the oracle on a sample
+    # of weight rows (both ends, every tile phase, a random spread)
+    rows = np.unique(np.concatenate([np.arange(0, 96), np.arange(N - 96, N),
+                                     np.random.default_rng(1).integers(0, N, 4096)]))
+    for M in (4, 8, 16, 32):
+        xf, xb = make_x(oracle, M, K, seed=40 + M)
+        want = oracle.matnt_quant_host(xf, p[rows], s[rows], b[rows], threads=8)
+        got = run_qmv(lthn, xb, lthn.BF16, M, q, lthn.F32)[:, rows]
+        assert rel_err(got, want) <= REF_TOL, M
+        assert rms_err(got, want) <= BATCH_TOL_RMS, M
 
 
 def test_zero_sized_and_rejected_arguments(oracle):
