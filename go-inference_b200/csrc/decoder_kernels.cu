@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
     const int row = blockIdx.x;
     const float* ar = a + (int64_t)row * width;
     float* hr = h ? h + (int64_t)row * width : nullptr;
-    float* orow = out + (int64_t)row * width;
+    float* orow = out ? out + (int64_t)row * width : nullptr;  // the f32 output is optional when cols is given
     double ss = 0.0;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float v = ar[i];
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
     if (mode == 0) {
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
             const float v = __fmul_rn(__fdiv_rn(ar[i], rms), w_post[i]);
-            orow[i] = v;
+            if (orow) orow[i] = v;
             if (cols) store_split(cols, split, row, width, i, v);
         }
         return;
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
     const float rms2 = (float)sqrt(ss2 / (double)width + (double)eps);
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float v = __fmul_rn(__fdiv_rn(hr[i], rms2), w_next[i]);
-        orow[i] = v;
+        if (orow) orow[i] = v;
         if (cols) store_split(cols, split, row, width, i, v);
     }
 }
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_reg_kernel(const float* __restri
     const int row = blockIdx.x;
     const float* ar = a + (int64_t)row * width;
     float* hr = h ? h + (int64_t)row * width : nullptr;
-    float* orow = out + (int64_t)row * width;
+    float* orow = out ? out + (int64_t)row * width : nullptr;  // optional when cols is given
     float av[MAXE], hv[MAXE], wp[MAXE], wn[MAXE];
 #pragma unroll
     for (int k = 0; k < MAXE; k++) {
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_reg_kernel(const float* __restri
         if (i >= width) continue;
         const float n = __fmul_rn(__fdiv_rn(av[k], rms), wp[k]);
         if (mode == 0) {
-            orow[i] = n;
+            if (orow) orow[i] = n;
             if (cols) store_split(cols, split, row, width, i, n);
         } else {
             hv[k] = __fadd_rn(hv[k], n);
@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_reg_kernel(const float* __restri
         const int i = threadIdx.x + k * blockDim.x;
         if (i >= width) continue;
         const float v = __fmul_rn(__fdiv_rn(hv[k], rms2), wn[k]);
-        orow[i] = v;
+        if (orow) orow[i] = v;
         if (cols) store_split(cols, split, row, width, i, v);
     }
 }

@@ -52,6 +52,16 @@ int32_t launch_rmsnorm_rope(cudaStream_t s, const float* x, const float* w, cons
 int sdpa_chunking(int max_ctx, int D, int* chunk_len);
 size_t sdpa_scratch_bytes(int rows, int Hq, int D, int nchunks);
 int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D);
+// Causal attention of `rows` consecutive prompt positions pos0.. of one cache lane (prefill).
+struct PrefillAttnArgs {
+    const float* q;          // [rows, Hq, D] f32, normed and rotated
+    const uint16_t* kc;      // this lane's and layer's cache: [max_len][Hkv*D] bf16, rows 0..pos0+rows-1 valid
+    const uint16_t* vc;
+    uint16_t* out;           // [rows, Hq, D] bf16
+    int rows, pos0, Hq, Hkv;
+    float scale_log2e;       // softmax scale times log2(e)
+};
+int32_t launch_prefill_attn(cudaStream_t s, const PrefillAttnArgs& a, int D);
 int32_t launch_argmax(cudaStream_t s, const float* logits, int rows, int V, float* pv, int* pi, int32_t* out_idx,
                       float* out_val, int index_offset);
 int32_t launch_advance(cudaStream_t s, int32_t* row_pos, int32_t* ids, const int32_t* next, int rows);

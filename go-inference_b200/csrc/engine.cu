@@ -94,6 +94,9 @@ struct Layer {
 };
 
 constexpr int kMaxRows = 32;  // rows per forward (the batched matvec serves up to 32)
+// Prompt rows per prefill chunk: the reference prefills in 512-token chunks
+// (decode/generate/generate.go:147-150).
+constexpr int kPrefillRows = 512;
 
 // lm_head (value, index) gather over peer memory (see tp_pair_gather_kernel)
 struct PairGather {
@@ -158,6 +161,11 @@ struct Model {
     // computes logits takes the next serial number, and a lane remembers the serial of its own
     // last forward, so a read-out can tell whether the buffer still holds that lane's row.
     uint64_t logits_serial = 0;
+    // prefill on the tensor cores (prompts longer than kMaxRows): chunk workspace for kPrefillRows rows
+    bool prefill_tc = false;
+    int32_t *p_ids = nullptr, *p_pos = nullptr, *p_lane = nullptr, *p_pinned = nullptr;
+    float *p_h = nullptr, *p_qkv = nullptr, *p_q = nullptr, *p_a = nullptr, *p_xnf = nullptr;
+    uint16_t *p_xn = nullptr, *p_att = nullptr, *p_act = nullptr;
 };
 
 template <typename T>
@@ -319,6 +327,36 @@ __global__ void tp_pick_kernel(const float* gathered, int ranks, int rows, int32
     out_idx[r] = bi;
 }
 
+// lm_head + greedy pick for rows [logit_row0, rows) of the final-normed hidden rows in xn (their
+// bf16 split columns in xn_cols when `split` matches what the matvec wants): logits land in
+// m->logits rows 0.., tokens in d_next[logit_row0..]. Vocab-sharded under tensor parallelism: the
+// local best (value, global index) per row is gathered from all ranks.
+static int32_t lm_head_pick(Model* m, int rows, int logit_row0, int split) {
+    const auto& c = m->c;
+    cudaStream_t s = m->stream;
+    const int H = c.hidden;
+    int32_t rc;
+    const int lr = rows - logit_row0;
+    QmvCall hc{m->head.wq, m->head.s, m->head.b, nullptr, nullptr, nullptr, m->xn + (int64_t)logit_row0 * H, LTHN_DTYPE_F32,
+               m->logits, LTHN_DTYPE_F32, m->head.N, m->head.K, lr};
+    if (split > 0 && qmv_split_for(lr, LTHN_DTYPE_F32) == split) { hc.x_cols = m->xn_cols + (int64_t)logit_row0 * split * H; hc.x_split = split; }
+    if ((rc = qmv_dispatch(s, hc))) return rc;
+    if (c.tp_size <= 1)
+        return launch_argmax(s, m->logits, lr, m->V_l, m->amax_v, m->amax_i, m->d_next + logit_row0, nullptr, 0);
+    if ((rc = launch_argmax(s, m->logits, lr, m->V_l, m->amax_v, m->amax_i, m->d_next + logit_row0, m->best_v, m->v0))) return rc;
+    if (m->xchg_ready) {
+        LTHN_CUDA_TRY(launch_k(tp_pair_gather_kernel, dim3(1), dim3(64), 0, s, m->pairg, (const float*)m->best_v, m->d_next + logit_row0, lr));
+        return LTHN_OK;
+    }
+    tp_pack_kernel<<<1, 32, 0, s>>>(m->best_v, m->d_next + logit_row0, m->gather, lr);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    float* all = m->gather + 2 * kMaxRows;
+    if ((rc = nccl_check(g_nccl.AllGather(m->gather, all, (size_t)2 * lr, kNcclFloat32, m->comm, s), "ncclAllGather"))) return rc;
+    tp_pick_kernel<<<1, 32, 0, s>>>(all, c.tp_size, lr, m->d_next + logit_row0);
+    LTHN_CUDA_TRY(cudaGetLastError());
+    return LTHN_OK;
+}
+
 // One forward over `rows` (<= kMaxRows) tokens whose ids / positions / lanes are already in
 // d_ids / d_pos / d_lane. max_ctx bounds pos+1 over the rows (host knowledge, sizes the
 // split-KV grid). Leaves the final-normed hidden rows in xn; computes logits + greedy
@@ -426,26 +464,7 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
         return LTHN_OK;
     }
     if (!want_logits) return LTHN_OK;
-    const int lr = rows - logit_row0;
-    QmvCall hc{m->head.wq, m->head.s, m->head.b, nullptr, nullptr, nullptr, m->xn + (int64_t)logit_row0 * H, LTHN_DTYPE_F32,
-               m->logits, LTHN_DTYPE_F32, m->head.N, m->head.K, lr};
-    if (qmv_split_for(lr, LTHN_DTYPE_F32) == split) { hc.x_cols = m->xn_cols + (int64_t)logit_row0 * split * H; hc.x_split = split; }
-    if ((rc = qmv_dispatch(s, hc))) return rc;
-    if (c.tp_size <= 1)
-        return launch_argmax(s, m->logits, lr, m->V_l, m->amax_v, m->amax_i, m->d_next + logit_row0, nullptr, 0);
-    // vocab-sharded head: local best (value, global index) per row, gathered from all ranks
-    if ((rc = launch_argmax(s, m->logits, lr, m->V_l, m->amax_v, m->amax_i, m->d_next + logit_row0, m->best_v, m->v0))) return rc;
-    if (m->xchg_ready) {
-        LTHN_CUDA_TRY(launch_k(tp_pair_gather_kernel, dim3(1), dim3(64), 0, s, m->pairg, (const float*)m->best_v, m->d_next + logit_row0, lr));
-        return LTHN_OK;
-    }
-    tp_pack_kernel<<<1, 32, 0, s>>>(m->best_v, m->d_next + logit_row0, m->gather, lr);
-    LTHN_CUDA_TRY(cudaGetLastError());
-    float* all = m->gather + 2 * kMaxRows;
-    if ((rc = nccl_check(g_nccl.AllGather(m->gather, all, (size_t)2 * lr, kNcclFloat32, m->comm, s), "ncclAllGather"))) return rc;
-    tp_pick_kernel<<<1, 32, 0, s>>>(all, c.tp_size, lr, m->d_next + logit_row0);
-    LTHN_CUDA_TRY(cudaGetLastError());
-    return LTHN_OK;
+    return lm_head_pick(m, rows, logit_row0, split);
 }
 
 static int32_t forward_full(Model* m, int rows, int max_ctx, bool want_logits, int logit_row0) {
@@ -456,6 +475,54 @@ static int32_t forward_full(Model* m, int rows, int max_ctx, bool want_logits, i
     const int32_t rc = forward(m, rows, max_ctx, want_logits, logit_row0);
     pdl_set(false);
     return rc;
+}
+
+// Prefill of one chunk on the tensor cores: `rows` (<= kPrefillRows) consecutive tokens of one
+// lane starting at position pos0, ids / positions / lane in p_ids / p_pos / p_lane. The
+// reference routes more than one row through affine_qmm_t (engine/metal/quant_seam_backend.go:
+// 37-68) in chunks of 512 (decode/generate/generate.go:147-150); this is that path with the Metal
+// engine's bf16 contract: the residual stream, norms and projection outputs stay f32, the
+// activations entering a projection are rounded to bf16 (the bf16 copy the norm kernel writes,
+// the attention output, the GeGLU product) and the weights are dequantised to bf16 inside
+// affine_qmm. Layer order as forward(). `last` computes the logits and the greedy token of the
+// chunk's final row (into row 0 of the logits buffer and d_next[0]).
+static int32_t prefill_chunk(Model* m, int lane, int rows, int pos0, bool last) {
+    const auto& c = m->c;
+    cudaStream_t s = m->stream;
+    const int H = c.hidden, D = c.head_dim;
+    const bool tp = c.tp_size > 1;
+    int32_t rc;
+    if ((rc = launch_embed(s, m->p_ids, rows, m->embed.wq, m->embed.s, m->embed.b, H, c.vocab, c.embed_scale, m->p_h))) return rc;
+    if ((rc = launch_rmsnorm(s, m->p_h, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, nullptr, rows, H, c.eps, 0, m->p_xn, 1))) return rc;
+    const float scale_log2e = (float)((double)c.attn_scale * 1.4426950408889634);
+    for (int li = 0; li < c.layers; li++) {
+        Layer& L = m->layers[li];
+        QmmCall qc{m->p_xn, rows, L.qkv.wq, L.qkv.s, L.qkv.b, nullptr, nullptr, nullptr, L.qkv.N, L.qkv.K, m->p_qkv, 1};
+        if ((rc = qmm_launch(s, qc))) return rc;
+        uint16_t* kc = m->kcache + (int64_t)li * m->layer_stride;
+        uint16_t* vc = m->vcache + (int64_t)li * m->layer_stride;
+        if ((rc = launch_qknorm_rope_append(s, m->p_qkv, L.norm[NORM_Q], L.norm[NORM_K], m->rope, m->p_pos, m->p_lane, m->p_q, kc, vc,
+                                            rows, m->Hq_l, m->Hkv_l, D, c.eps, m->lane_stride, c.max_len))) return rc;
+        PrefillAttnArgs pa{m->p_q, kc + (int64_t)lane * m->lane_stride, vc + (int64_t)lane * m->lane_stride, m->p_att, rows, pos0,
+                           m->Hq_l, m->Hkv_l, scale_log2e};
+        if ((rc = launch_prefill_attn(s, pa, D))) return rc;
+        QmmCall oc{m->p_att, rows, L.o.wq, L.o.s, L.o.b, nullptr, nullptr, nullptr, L.o.N, L.o.K, m->p_a, 1};
+        if ((rc = qmm_launch(s, oc))) return rc;
+        if (tp && (rc = all_reduce(m, m->p_a, (size_t)rows * H))) return rc;
+        if ((rc = launch_rmsnorm(s, m->p_a, m->p_h, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], nullptr, rows, H, c.eps, 1, m->p_xn, 1))) return rc;
+        QmmCall gc{m->p_xn, rows, L.gate.wq, L.gate.s, L.gate.b, L.up.wq, L.up.s, L.up.b, L.gate.N, L.gate.K, m->p_act, 0};
+        if ((rc = qmm_launch(s, gc))) return rc;
+        QmmCall dc{m->p_act, rows, L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, L.down.N, L.down.K, m->p_a, 1};
+        if ((rc = qmm_launch(s, dc))) return rc;
+        if (tp && (rc = all_reduce(m, m->p_a, (size_t)rows * H))) return rc;
+        const bool final_layer = li + 1 == c.layers;
+        const float* next_norm = final_layer ? m->final_norm : m->layers[li + 1].norm[NORM_INPUT];
+        if ((rc = launch_rmsnorm(s, m->p_a, m->p_h, L.norm[NORM_POST_FF], next_norm, final_layer && last ? m->p_xnf : nullptr, rows, H,
+                                 c.eps, 1, final_layer ? nullptr : m->p_xn, final_layer ? 0 : 1))) return rc;
+    }
+    if (!last) return LTHN_OK;
+    LTHN_CUDA_TRY(cudaMemcpyAsync(m->xn, m->p_xnf + (int64_t)(rows - 1) * H, (size_t)H * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    return lm_head_pick(m, 1, 0, 0);
 }
 
 // One decode step for `rows` lanes (ids / positions / lanes already in the device buffers),
@@ -525,6 +592,29 @@ static int32_t feed_lane(Model* m, Lane* ln, const int32_t* ids, int n) {
     for (int i = 0; i < n; i++) LTHN_REQUIRE(ids[i] >= 0 && ids[i] < m->c.vocab, "session: token id outside the vocabulary");
     std::lock_guard<std::mutex> lk(m->mu);
     int32_t rc;
+    if (m->prefill_tc && n > kMaxRows) {
+        // more rows than one decode forward takes: 512-row chunks through affine_qmm and the causal prefill attention
+        for (int off = 0; off < n; off += kPrefillRows) {
+            const int rows = std::min(kPrefillRows, n - off);
+            int32_t* hp = m->p_pinned;
+            for (int r = 0; r < rows; r++) { hp[r] = ids[off + r]; hp[kPrefillRows + r] = ln->pos + r; hp[2 * kPrefillRows + r] = ln->id; }
+            LTHN_CUDA_TRY(cudaMemcpyAsync(m->p_ids, hp, 3 * kPrefillRows * 4, cudaMemcpyHostToDevice, m->stream));
+            const bool last = off + rows >= n;
+            if ((rc = prefill_chunk(m, ln->id, rows, ln->pos, last))) return rc;
+            ln->pos += rows;
+            if (last) {
+                LTHN_CUDA_TRY(cudaMemcpyAsync(m->h_pinned + 3 * kMaxRows, m->d_next, 4, cudaMemcpyDeviceToHost, m->stream));
+                if ((rc = device_status_read_async(m->stream, (uint32_t*)(m->h_pinned + 4 * kMaxRows)))) return rc;
+            }
+            LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));  // the pinned staging is reused by the next chunk
+        }
+        ln->next_tok = m->h_pinned[3 * kMaxRows];
+        ln->have_next = true;
+        ln->pending = -1;
+        ln->logits_serial = ++m->logits_serial;
+        ln->logits_row = 0;
+        return device_status_judge((uint32_t)m->h_pinned[4 * kMaxRows], m->stream);
+    }
     for (int off = 0; off < n; off += kMaxRows) {
         const int rows = std::min(kMaxRows, n - off);
         int32_t* hp = m->h_pinned;
@@ -614,6 +704,7 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
         const std::string keep = lthn_last_error();
         for (void* p : m->allocs) cudaFree(p);
         if (m->h_pinned) cudaFreeHost(m->h_pinned);
+        if (m->p_pinned) cudaFreeHost(m->p_pinned);
         cudaStreamDestroy(m->stream);
         delete m;
         return fail(code, keep);
@@ -676,6 +767,25 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
     }
     e = cudaHostAlloc((void**)&m->h_pinned, 4 * kMaxRows * sizeof(int32_t) + 256, cudaHostAllocDefault);
     if (e != cudaSuccess) { cuda_fail(e, "cudaHostAlloc"); return bail(LTHN_ERR_CUDA); }
+    {
+        // LTHN_CUDA_PREFILL_F32=1 keeps every prompt on the f32 decode kernels (32 rows per forward);
+        // the tensor-core prefill attention serves head_dim up to 256
+        const char* env = getenv("LTHN_CUDA_PREFILL_F32");
+        m->prefill_tc = !(env && env[0] == '1') && c.head_dim <= 256 && c.max_len > kMaxRows;
+    }
+    if (m->prefill_tc) {
+        const size_t P = (size_t)std::min(kPrefillRows, c.max_len);
+        const size_t QKV = (size_t)m->QR_l + 2 * m->KR_l;
+        if ((rc = dalloc(m, &m->p_ids, 3 * (size_t)kPrefillRows)) || (rc = dalloc(m, &m->p_h, P * H)) ||
+            (rc = dalloc(m, &m->p_xn, P * H)) || (rc = dalloc(m, &m->p_xnf, P * H)) || (rc = dalloc(m, &m->p_qkv, P * QKV)) ||
+            (rc = dalloc(m, &m->p_q, P * m->QR_l)) || (rc = dalloc(m, &m->p_att, P * m->QR_l)) ||
+            (rc = dalloc(m, &m->p_a, P * H)) || (rc = dalloc(m, &m->p_act, P * m->F_l)))
+            return bail(rc);
+        m->p_pos = m->p_ids + kPrefillRows;
+        m->p_lane = m->p_ids + 2 * kPrefillRows;
+        e = cudaHostAlloc((void**)&m->p_pinned, 3 * kPrefillRows * sizeof(int32_t), cudaHostAllocDefault);
+        if (e != cudaSuccess) { cuda_fail(e, "cudaHostAlloc"); return bail(LTHN_ERR_CUDA); }
+    }
     *model = m;
     return LTHN_OK;
 }
@@ -942,6 +1052,7 @@ int32_t lthn_model_destroy(void* model) {
     if (m->x_base) cudaFree(m->x_base);
     for (void* p : m->allocs) cudaFree(p);
     if (m->h_pinned) cudaFreeHost(m->h_pinned);
+    if (m->p_pinned) cudaFreeHost(m->p_pinned);
     cudaStreamDestroy(m->stream);
     delete m;
     return LTHN_OK;
@@ -1243,6 +1354,19 @@ int32_t lthn_sdpa_decode(void* stream, const float* q, const uint16_t* kcache, c
     }
     SdpaArgs a{q, kcache, vcache, row_pos, row_lane, out, (float*)part, lane_stride, q_heads, kv_heads, nchunks, chunk_len, scale};
     return launch_sdpa_decode((cudaStream_t)stream, a, rows, head_dim);
+}
+
+int32_t lthn_prefill_attention(void* stream, const float* q, const uint16_t* kcache, const uint16_t* vcache, uint16_t* out,
+                               int32_t rows, int32_t pos0, int32_t q_heads, int32_t kv_heads, int32_t head_dim, float scale) {
+    clear_error();
+    if (rows == 0) return LTHN_OK;
+    LTHN_REQUIRE(q && kcache && vcache && out, "lthn_prefill_attention: NULL pointer");
+    LTHN_REQUIRE(rows > 0 && pos0 >= 0 && q_heads > 0 && kv_heads > 0, "lthn_prefill_attention: dimensions must be positive");
+    LTHN_REQUIRE((((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache) & 15) == 0 && ((uintptr_t)out & 3) == 0,
+                 "lthn_prefill_attention: q and the caches must be 16-byte aligned");
+    if (scale <= 0) scale = (float)(1.0 / std::sqrt((double)head_dim));
+    PrefillAttnArgs a{q, kcache, vcache, out, rows, pos0, q_heads, kv_heads, (float)((double)scale * 1.4426950408889634)};
+    return launch_prefill_attn((cudaStream_t)stream, a, head_dim);
 }
 
 int32_t lthn_argmax(void* stream, const float* logits, int32_t rows, int32_t vocab, int32_t* out_idx) {

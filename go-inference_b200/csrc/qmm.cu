@@ -54,9 +54,15 @@ struct QmmArgs {
     const uint32_t* wq;
     const uint16_t* scales;
     const uint16_t* biases;
-    uint16_t* y;
+    // GeGLU pair (wq2 != NULL): a CTA's weight tile holds NT/2 rows of the gate matrix followed by
+    // the same NT/2 rows of the up matrix, and the epilogue stores gelu_tanh(gate) * up
+    const uint32_t* wq2;
+    const uint16_t* scales2;
+    const uint16_t* biases2;
+    void* y;       // [M, N] bf16, or f32 when y_f32
     uint32_t* status;
-    int M, N, K;
+    int M, N, K;   // N = output columns
+    int y_f32;
 };
 
 // ---- tcgen05 / TMA wrappers -----------------------------------------------------------
@@ -139,10 +145,18 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t w, uint32_t s2, uint32_t 
     return o;
 }
 
-template <int NT>
+__device__ __forceinline__ float qmm_gelu_tanh(float x) {
+    // gelu_tanh as hipGemma4Q4HostGELU (engine/hip/hip_gemma4_q4_layer.go:3582-3597)
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    return 0.5f * x * (1.0f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+
+// GEGLU: 0 plain, 1 gate/up pair (see QmmArgs)
+template <int NT, int GEGLU>
 __global__ void __launch_bounds__(QMM_THREADS, 1)
 qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
     using S = QmmSmem<NT>;
+    constexpr int NO = GEGLU ? NT / 2 : NT;   // output columns per CTA
     constexpr int STAGES = S::STAGES;
     constexpr int TPR = QMM_DQ_THREADS / NT;  // dequant threads per weight row: 1 (NT=256) or 2 (NT=128)
     constexpr int WORDS = 8 / TPR;            // packed words (of the 8 in a group) per thread
@@ -156,7 +170,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
     uint32_t* tmem_slot = (uint32_t*)(bars + 3 * STAGES + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * NT, m0 = blockIdx.y * QMM_MT;
+    const int n0 = blockIdx.x * NO, m0 = blockIdx.y * QMM_MT;
     const int KB = a.K / QMM_BK;
     bool ok = true;
 
@@ -216,10 +230,11 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
         // ---- dequantisers, then epilogue -------------------------------------------------
         const int t = threadIdx.x - 64;
         const int row = t / TPR, part = t - row * TPR;
-        const int64_t grow = min(n0 + row, a.N - 1);  // tail tiles re-read the last row; never stored
-        const uint32_t* wp = a.wq + grow * (a.K >> 3) + part * WORDS;
-        const uint16_t* sp = a.scales + grow * KB;
-        const uint16_t* bp = a.biases + grow * KB;
+        const bool second = GEGLU && row >= NO;       // tile rows NO.. come from the up matrix
+        const int64_t grow = min(n0 + (second ? row - NO : row), a.N - 1);  // tail tiles re-read the last row; never stored
+        const uint32_t* wp = (second ? a.wq2 : a.wq) + grow * (a.K >> 3) + part * WORDS;
+        const uint16_t* sp = (second ? a.scales2 : a.scales) + grow * KB;
+        const uint16_t* bp = (second ? a.biases2 : a.biases) + grow * KB;
         uint32_t wcur[WORDS], wnxt[WORDS];
         uint32_t sbcur, sbnxt = 0;
         auto load_kb = [&](int kb, uint32_t (&w)[WORDS], uint32_t& sb) {
@@ -263,12 +278,33 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
             const int m = m0 + half * 128 + quad * 32 + lane;
             const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + half * NT;
 #pragma unroll 1
-            for (int c0 = 0; c0 < NT; c0 += 32) {
+            for (int c0 = 0; c0 < NO; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tbase + c0, r);
-                tmem_ld_wait();
+                if (GEGLU) {
+                    uint32_t u[32];
+                    tmem_ld32(tbase + NO + c0, u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; e++)
+                        r[e] = __float_as_uint(qmm_gelu_tanh(__uint_as_float(r[e])) * __uint_as_float(u[e]));
+                } else {
+                    tmem_ld_wait();
+                }
                 if (m < a.M) {
-                    uint16_t* yrow = a.y + (int64_t)m * a.N + n0 + c0;
+                    if (a.y_f32) {
+                        float* yrow = (float*)a.y + (int64_t)m * a.N + n0 + c0;
+                        if (n0 + c0 + 32 <= a.N && (((uintptr_t)yrow) & 15) == 0) {
+#pragma unroll
+                            for (int v = 0; v < 8; v++)
+                                *(uint4*)(yrow + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+                        } else {
+                            for (int e = 0; e < 32; e++)
+                                if (n0 + c0 + e < a.N) yrow[e] = __uint_as_float(r[e]);
+                        }
+                        continue;
+                    }
+                    uint16_t* yrow = (uint16_t*)a.y + (int64_t)m * a.N + n0 + c0;
                     if (n0 + c0 + 32 <= a.N && (((uintptr_t)yrow) & 15) == 0) {
 #pragma unroll
                         for (int v = 0; v < 4; v++) {
@@ -311,7 +347,7 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int NT>
+template <int NT, int GEGLU>
 static int32_t launch_qmm(cudaStream_t s, const CUtensorMap& map, const QmmArgs& a) {
     static int attr_dev = -1;
     static std::mutex mu;
@@ -320,17 +356,48 @@ static int32_t launch_qmm(cudaStream_t s, const CUtensorMap& map, const QmmArgs&
     {
         std::lock_guard<std::mutex> lk(mu);
         if (attr_dev != dev) {
-            LTHN_CUDA_TRY(cudaFuncSetAttribute(qmm_tcgen05_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, QmmSmem<NT>::TOTAL));
+            LTHN_CUDA_TRY(cudaFuncSetAttribute(qmm_tcgen05_kernel<NT, GEGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, QmmSmem<NT>::TOTAL));
             attr_dev = dev;
         }
     }
-    dim3 grid((a.N + NT - 1) / NT, (a.M + QMM_MT - 1) / QMM_MT);
-    qmm_tcgen05_kernel<NT><<<grid, QMM_THREADS, QmmSmem<NT>::TOTAL, s>>>(map, a);
+    constexpr int NO = GEGLU ? NT / 2 : NT;
+    dim3 grid((a.N + NO - 1) / NO, (a.M + QMM_MT - 1) / QMM_MT);
+    qmm_tcgen05_kernel<NT, GEGLU><<<grid, QMM_THREADS, QmmSmem<NT>::TOTAL, s>>>(map, a);
     LTHN_CUDA_TRY(cudaGetLastError());
     return LTHN_OK;
 }
 
 LTHN_HIDDEN int g_force_nt = 0;  // tile override: zero in the product library (setter: test_hooks.cu)
+
+// The tensor-core path for any M >= 1 (rows past M are zero-filled by the TMA load and never
+// stored): 4-bit codes, group 64, x and packed 16-byte aligned.
+int32_t qmm_launch(cudaStream_t s, const QmmCall& c) {
+    if (!encode_fn()) return fail(LTHN_ERR_UNAVAILABLE, "affine_qmm: cuTensorMapEncodeTiled is not available from this driver");
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)c.K, (cuuint64_t)c.M};
+    const cuuint64_t strides[1] = {(cuuint64_t)c.K * 2};
+    const cuuint32_t box[2] = {QMM_BK, QMM_MT};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)c.x, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(LTHN_ERR_CUDA, "affine_qmm: cuTensorMapEncodeTiled failed (" + std::to_string((int)cr) + ")");
+    QmmArgs a{c.wq, c.scales, c.biases, c.wq2, c.scales2, c.biases2, c.y, device_status_word(), c.M, (int)c.N, (int)c.K, c.y_f32};
+    if (!a.status) return fail(LTHN_ERR_CUDA, "affine_qmm: no device status word");
+    const int64_t mt = (c.M + QMM_MT - 1) / QMM_MT;
+    if (c.wq2) {
+        // a 256-row tile holds 128 gate + 128 up rows
+        const int64_t tiles = ((c.N + 127) / 128) * mt;
+        int nt = tiles >= 148 ? 256 : 128;
+        if (g_force_nt == 128 || g_force_nt == 256) nt = g_force_nt;
+        return nt == 256 ? launch_qmm<256, 1>(s, map, a) : launch_qmm<128, 1>(s, map, a);
+    }
+    // 256-row weight tiles when that still fills the GPU, else 128
+    const int64_t tiles256 = ((c.N + 255) / 256) * mt;
+    int nt = tiles256 >= 148 ? 256 : 128;
+    if (g_force_nt == 128 || g_force_nt == 256) nt = g_force_nt;
+    return nt == 256 ? launch_qmm<256, 0>(s, map, a) : launch_qmm<128, 0>(s, map, a);
+}
 
 }  // namespace lthn
 
@@ -365,22 +432,24 @@ int32_t lthn_affine_qmm(void* stream, const uint16_t* x, int32_t M, const uint32
         }
         return LTHN_OK;
     }
-    CUtensorMap map;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {QMM_BK, QMM_MT};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult cr = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)x, dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cr != CUDA_SUCCESS) return fail(LTHN_ERR_CUDA, "affine_qmm: cuTensorMapEncodeTiled failed (" + std::to_string((int)cr) + ")");
-    QmmArgs a{packed, scales, biases, y, device_status_word(), M, (int)N, (int)K};
-    if (!a.status) return fail(LTHN_ERR_CUDA, "affine_qmm: no device status word");
-    // 256-row weight tiles when that still fills the GPU, else 128
-    const int64_t tiles256 = ((N + 255) / 256) * ((M + QMM_MT - 1) / QMM_MT);
-    int nt = tiles256 >= 148 ? 256 : 128;
-    if (g_force_nt == 128 || g_force_nt == 256) nt = g_force_nt;
-    return nt == 256 ? launch_qmm<256>(s, map, a) : launch_qmm<128>(s, map, a);
+    QmmCall c{x, M, packed, scales, biases, nullptr, nullptr, nullptr, N, K, y, 0};
+    return qmm_launch(s, c);
+}
+
+int32_t lthn_affine_qmm_geglu(void* stream, const uint16_t* x, int32_t M, const uint32_t* gate_packed,
+                              const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
+                              const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, uint16_t* y) {
+    clear_error();
+    LTHN_REQUIRE(M >= 0 && N >= 0 && K >= 0, "affine_qmm_geglu: negative dimension");
+    if (M == 0 || N == 0) return LTHN_OK;
+    LTHN_REQUIRE(x && gate_packed && gate_scales && gate_biases && up_packed && up_scales && up_biases && y,
+                 "affine_qmm_geglu: NULL pointer");
+    LTHN_REQUIRE(K > 0 && K % 64 == 0, "affine_qmm_geglu: K must be a positive multiple of 64 (4-bit, group 64 only)");
+    LTHN_REQUIRE(N < (int64_t)1 << 31 && K < (int64_t)1 << 31, "affine_qmm_geglu: dimension too large");
+    LTHN_REQUIRE((((uintptr_t)x | (uintptr_t)gate_packed | (uintptr_t)up_packed) & 15) == 0,
+                 "affine_qmm_geglu: x and the packed weights must be 16-byte aligned");
+    QmmCall c{x, M, gate_packed, gate_scales, gate_biases, up_packed, up_scales, up_biases, N, K, y, 0};
+    return qmm_launch((cudaStream_t)stream, c);
 }
 
 }  // extern "C"

@@ -84,6 +84,17 @@ int32_t i8_launch(cudaStream_t st, const QmvCall& c, const I8Plan& p);
 // y[i] = sum over s < ks of part[s*n + i]
 int32_t launch_sum_parts(cudaStream_t st, const float* part, int ks, int64_t n, void* y, int y_dtype);
 
+// One prefill matmul on the tensor cores: y[M,N] = x[M,K] (bf16) * dequant(W)^T, or with a second
+// weight set gelu_tanh(x Wgate^T) * (x Wup^T). y is bf16, or f32 when y_f32.
+struct QmmCall {
+    const uint16_t* x; int M;
+    const uint32_t* wq; const uint16_t* scales; const uint16_t* biases;
+    const uint32_t* wq2; const uint16_t* scales2; const uint16_t* biases2;
+    int64_t N, K;
+    void* y; int y_f32;
+};
+int32_t qmm_launch(cudaStream_t st, const QmmCall& c);
+
 // Dispatcher used by the C entry points and by the decoder engine.
 int32_t qmv_dispatch(cudaStream_t st, const QmvCall& c);
 

@@ -36,6 +36,10 @@ static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_
         const int w = Gs / cand;
         if (w < 1 || w > 16) continue;
         if (cand > 9 && w > 8) continue;  // many groups per warp only in small blocks (registers)
+        // the five-blocks-per-SM build of the 4-warp class holds 72 registers: the digit fragments of
+        // more than 9 groups (4 registers each) do not fit and spill (K = 5376 as 4 x 21 groups
+        // measured 94 us for the 130 MB gate/up pair, 1.4 TB/s)
+        if (cand > 9 && w <= 4) continue;
         int score = 1000 - 10 * std::abs(w - target) + (target >= 8 ? w : -w);
         if (force_w > 0) score = (w == force_w) ? 5000 : -1;
         if (score > best) { best = score; J = cand; W = w; }

@@ -138,6 +138,8 @@ class _Sig:
     lthn_laneset_batch_forward_count = (u64, [vp])
     lthn_laneset_close = (i32, [vp])
     lthn_affine_qmm = (i32, [vp, vp, i32, vp, vp, vp, i64, i64, i32, i32, vp])
+    lthn_affine_qmm_geglu = (i32, [vp, vp, i32, vp, vp, vp, vp, vp, vp, i64, i64, vp])
+    lthn_prefill_attention = (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32])
     lthn_debug_qmm_force_tile = (None, [i32])
     lthn_debug_qmv_force_config = (None, [i32, i32])
     lthn_debug_qmv_force_kernel = (None, [i32])
@@ -383,6 +385,17 @@ def qmv_noalloc(x_f32: Buf, M, q: QuantWeight, y_f32: Buf, stream=None):
 def qmm(x: Buf, M, q: QuantWeight, y: Buf, stream=None):
     check(lib().lthn_affine_qmm(_s(stream), x.ptr, M, q.packed.ptr, q.scales.ptr, q.biases.ptr, q.N, q.K, q.gs, q.bits,
                                 y.ptr))
+
+
+def qmm_geglu(x: Buf, M, gate: QuantWeight, up: QuantWeight, y: Buf, stream=None):
+    check(lib().lthn_affine_qmm_geglu(_s(stream), x.ptr, M, gate.packed.ptr, gate.scales.ptr, gate.biases.ptr,
+                                      up.packed.ptr, up.scales.ptr, up.biases.ptr, gate.N, gate.K, y.ptr))
+
+
+def prefill_attention(q: Buf, kcache: Buf, vcache: Buf, out: Buf, rows, pos0, q_heads, kv_heads, head_dim, scale=0.0,
+                      stream=None):
+    check(lib().lthn_prefill_attention(_s(stream), q.ptr, kcache.ptr, vcache.ptr, out.ptr, rows, pos0, q_heads,
+                                       kv_heads, head_dim, scale))
 
 
 def qmv_geglu(x: Buf, x_dtype, M, gate: QuantWeight, up: QuantWeight, y: Buf, y_dtype, stream=None):

@@ -187,6 +187,15 @@ int32_t lthn_affine_qmv_geglu(void* stream, const void* x, int32_t x_dtype, int3
 int32_t lthn_affine_qmm(void* stream, const uint16_t* x, int32_t M, const uint32_t* packed, const uint16_t* scales,
                         const uint16_t* biases, int64_t N, int64_t K, int32_t gs, int32_t bits, uint16_t* y);
 
+/* Prefill GeGLU pair: y[M,N] (bf16) = gelu_tanh(x Wgate^T) * (x Wup^T), both weights [N,K], 4 bit,
+ * group 64. One tensor-core pass: a CTA's weight tile holds rows of both matrices, and the
+ * epilogue multiplies the two f32 accumulators before the single bf16 rounding, so the
+ * intermediate never reaches memory. Replaces rocm_mlx_q4_gelu_tanh_multiply's batched use in
+ * prefill (engine/hip/kernels/quant/affine_gelu_tanh.hipinc:3-180). Any M >= 1. */
+int32_t lthn_affine_qmm_geglu(void* stream, const uint16_t* x, int32_t M, const uint32_t* gate_packed,
+                              const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
+                              const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, uint16_t* y);
+
 /* model.QuantMatVec.MatVec (model/quant.go:35-38): bf16 LE bytes in HOST memory
  * in, bf16 LE bytes out; lengths are validated like the reference
  * (enginetest/quant_reference.go:79-104). Copies in, launches, copies out,
@@ -228,6 +237,18 @@ int32_t lthn_rmsnorm_rope(void* stream, const float* x, const float* w, const in
 int32_t lthn_sdpa_decode(void* stream, const float* q, const uint16_t* kcache, const uint16_t* vcache,
                          const int32_t* row_pos, const int32_t* row_lane, float* out, int32_t rows, int32_t q_heads,
                          int32_t kv_heads, int32_t head_dim, int64_t lane_stride, float scale, int32_t max_ctx);
+/* lthn_prefill_attention: causal attention for `rows` consecutive prompt positions pos0 ..
+ * pos0+rows-1 of one cache lane, whose K and V rows (the chunk's own included) are already in the
+ * cache: row r attends keys 0 .. pos0+r. Same cache layout and head map as lthn_sdpa_decode
+ * (kcache/vcache point at the lane's first row; row stride kv_heads*head_dim). Tensor-core
+ * kernel with the bf16 contract of the reference's Metal prefill: q and the softmax weights are
+ * rounded to bf16 for the two products, scores and output accumulate in f32; out is bf16
+ * [rows, q_heads*head_dim], ready to be the next affine_qmm's x. Stands where the reference
+ * prefills with its batched chunked attention (engine/hip/kernels/attention/chunked.hipinc) /
+ * MLX's sdpa over the chunk; CPU ref hipReferenceSingleHeadAttentionWithScale
+ * (hip_transformer_reference.go:295-330). head_dim in {64,128,256}; scale<=0 means 1/sqrt(head_dim). */
+int32_t lthn_prefill_attention(void* stream, const float* q, const uint16_t* kcache, const uint16_t* vcache, uint16_t* out,
+                               int32_t rows, int32_t pos0, int32_t q_heads, int32_t kv_heads, int32_t head_dim, float scale);
 /* Greedy pick per row: strict '>', lowest index wins ties (model.Greedy, model/sample.go:
  * 29-50; hipReferenceGreedySample). logits [rows, vocab] f32. */
 int32_t lthn_argmax(void* stream, const float* logits, int32_t rows, int32_t vocab, int32_t* out_idx);
@@ -285,7 +306,14 @@ int32_t lthn_tp_init(int32_t rank, int32_t world, const void* id128, void** comm
 int32_t lthn_tp_destroy(void* comm);
 int32_t lthn_model_set_comm(void* model, void* comm);
 
-/* engine.Session (engine/session.go:40-61). One session is driven by one host thread at
+/* Prompts of more than 32 tokens are prefilled in 512-row chunks (decode/generate/generate.go:
+ * 147-150) through lthn_affine_qmm and lthn_prefill_attention, the route the reference takes for
+ * M > 1 (engine/metal/quant_seam_backend.go:37-68), with that engine's bf16 contract: activations
+ * entering a projection and the dequantised weights are bf16, everything else f32. Shorter prompts
+ * and appended pieces go through the f32 decode kernels, 32 rows per forward, as every prompt
+ * does when LTHN_CUDA_PREFILL_F32=1 is set at lthn_model_create (or head_dim is 512).
+ *
+ * engine.Session (engine/session.go:40-61). One session is driven by one host thread at
  * a time (SessionHandle.mu, engine/session.go:105-117); sessions of one model serialise
  * on the model's stream. */
 int32_t lthn_session_open(void* model, void** session);                      /* TokenModel.OpenEngineSession */

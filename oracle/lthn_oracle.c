@@ -393,6 +393,42 @@ int lthn_o_qmm_bf16(const uint16_t *x, const uint8_t *packed, const uint16_t *sc
     return LTHN_O_OK;
 }
 
+/* The same contract with f32 activations in (rounded to bf16 here) and the f64 sums returned as
+ * f32 without an output rounding: what a prefill projection computes when the caller keeps its
+ * outputs in f32. x: [tokens, cols] f32; out: [tokens, rows] f32. */
+int lthn_o_proj_bf16_contract(const float *x, long tokens, const uint32_t *weights, const uint16_t *scales,
+                              const uint16_t *biases, long rows, long cols, int gs, int bits, float *out) {
+    if (!supported_bits(bits) || cols <= 0 || gs <= 0 || cols % gs != 0 || tokens <= 0 || rows <= 0) return LTHN_O_EINVAL;
+    long wpr = cols * bits / 32, gpr = cols / gs;
+    int epw = 32 / bits;
+    uint32_t mask = (1u << bits) - 1u;
+    float *xb = (float *)malloc(sizeof(float) * (size_t)tokens * (size_t)cols);
+    for (long i = 0; i < tokens * cols; i++) xb[i] = lthn_o_bf16_to_f32(lthn_o_f32_to_bf16(x[i]));
+#pragma omp parallel
+    {
+        float *wr = (float *)malloc(sizeof(float) * (size_t)cols);
+#pragma omp for schedule(static)
+        for (long n = 0; n < rows; n++) {
+            const uint32_t *words = weights + n * wpr;
+            for (long j = 0; j < cols; j++) {
+                uint32_t code = (words[j / epw] >> ((j % epw) * bits)) & mask;
+                float scale = lthn_o_bf16_to_f32(scales[n * gpr + j / gs]);
+                float bias = lthn_o_bf16_to_f32(biases[n * gpr + j / gs]);
+                wr[j] = lthn_o_bf16_to_f32(lthn_o_f32_to_bf16(scale * (float)code + bias));
+            }
+            for (long m = 0; m < tokens; m++) {
+                const float *xr = xb + m * cols;
+                double acc = 0;
+                for (long k = 0; k < cols; k++) acc += (double)xr[k] * (double)wr[k];
+                out[m * rows + n] = (float)acc;
+            }
+        }
+        free(wr);
+    }
+    free(xb);
+    return LTHN_O_OK;
+}
+
 /* -------------------------------------- a13: RMSNorm / RoPE references --- */
 
 /* engine/hip/hip_transformer_reference.go:171-194 hipReferenceRMSNorm:

@@ -46,6 +46,12 @@ typedef struct {
     int32_t layers, hidden, q_heads, kv_heads, head_dim, ffn, vocab, gs, bits, max_len;
     float eps, rope_base, attn_scale, embed_scale;
     int32_t kv_bf16; /* 1: round K/V to bf16 when appended */
+    /* 1: forwards of more than 32 tokens follow the prefill contract of the reference's Metal
+     * engine, which routes M > 1 through affine_qmm_t with bf16 operands (engine/metal/
+     * quant_seam_backend.go:37-68,84-110): the activations entering a projection and the
+     * dequantised weights are rounded to bf16, products accumulate in f64, outputs stay f32;
+     * the attention query is rounded to bf16 too. Shorter forwards (decode) stay f32. */
+    int32_t prefill_bf16;
 } lthn_o_decoder_config;
 
 enum { L_Q = 0, L_K, L_V, L_O, L_GATE, L_UP, L_DOWN, L_COUNT };
@@ -111,8 +117,12 @@ void lthn_o_decoder_set_tap(void *h, int layer, int which, float *buf) {
     if (which >= 0 && which < 8) d->tap[which] = buf;
 }
 
+int lthn_o_proj_bf16_contract(const float *x, long tokens, const uint32_t *weights, const uint16_t *scales,
+                              const uint16_t *biases, long rows, long cols, int gs, int bits, float *out);
+static int g_bf16_contract = 0; /* set per forward call (the oracle is driven from one thread) */
 static void proj(const lin_t *l, const float *x, long tokens, int gs, int bits, float *out) {
-    lthn_o_hip_affine_projection_rows(x, tokens, l->w, l->s, l->b, l->rows, l->cols, gs, bits, out);
+    if (g_bf16_contract) lthn_o_proj_bf16_contract(x, tokens, l->w, l->s, l->b, l->rows, l->cols, gs, bits, out);
+    else lthn_o_hip_affine_projection_rows(x, tokens, l->w, l->s, l->b, l->rows, l->cols, gs, bits, out);
 }
 static void norm_rows(const float *in, const float *w, long rows, long width, float eps, float *out) {
     /* oracle_test.go:981-990 hipOracleReferenceNormRows */
@@ -129,6 +139,7 @@ int lthn_o_decoder_forward(void *h, const int32_t *ids, long n, float *logits, f
     dec_t *d = (dec_t *)h;
     const lthn_o_decoder_config *c = &d->c;
     if (n <= 0 || d->pos + n > c->max_len) return 1;
+    g_bf16_contract = c->prefill_bf16 && n > 32;
     long H = c->hidden, D = c->head_dim, QR = (long)c->q_heads * D, KR = (long)c->kv_heads * D, F = c->ffn;
     float *hid = (float *)malloc(sizeof(float) * n * H);
     float *xn = (float *)malloc(sizeof(float) * n * H);
@@ -174,6 +185,7 @@ int lthn_o_decoder_forward(void *h, const int32_t *ids, long n, float *logits, f
             memcpy(vc + p * KR, v + t * KR, sizeof(float) * KR);
             if (c->kv_bf16) { lthn_o_round_bf16_inplace(kc + p * KR, KR); lthn_o_round_bf16_inplace(vc + p * KR, KR); }
         }
+        if (g_bf16_contract) lthn_o_round_bf16_inplace(q, n * QR);
         tapcpy(d, L, 7, q, n * QR);
         /* oracle_test.go:907-924: causal attention per token, GQA head map */
 #pragma omp parallel
@@ -207,6 +219,7 @@ int lthn_o_decoder_forward(void *h, const int32_t *ids, long n, float *logits, f
         tapcpy(d, L, 6, hid, n * H);
     }
     d->pos += n;
+    g_bf16_contract = 0; /* the lm_head of the last row is a single-row matvec: f32 like decode */
     if (logits || hidden_last) {
         lthn_o_rmsnorm(hid + (n - 1) * H, d->final_norm, H, c->eps, xn);
         if (hidden_last) memcpy(hidden_last, xn, sizeof(float) * H);

@@ -186,6 +186,39 @@ def test_sdpa_decode_matches_reference(oracle, Hq, Hkv, D, ctxs):
             np.testing.assert_allclose(got[r, h], want, rtol=0, atol=3e-6 * max(1.0, np.abs(want).max()) + 2e-6)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,rows,pos0", [(4, 2, 64, 70, 0), (8, 4, 256, 130, 0), (4, 2, 128, 64, 37), (2, 1, 128, 33, 480),
+                                              (8, 4, 256, 512, 512), (4, 4, 64, 1, 5)])
+def test_prefill_attention_matches_reference(oracle, Hq, Hkv, D, rows, pos0):
+    """Causal attention of a prompt chunk (rows positions from pos0, keys 0..pos0+r) against
+    hipReferenceSingleHeadAttentionWithScale per row and head with the GQA head map. The oracle is
+    given the query rounded to bf16, which is what the kernel multiplies; the kernel also rounds
+    its softmax weights to bf16 and stores bf16, which bounds the difference at a few bf16 ulps of
+    the output scale (stated below), not at f32 noise."""
+    import lthn
+    KR = Hkv * D
+    ctx = pos0 + rows
+    rng = np.random.default_rng(Hq * 1000 + D + rows)
+    kf = oracle.bf16_to_f32(oracle.f32_to_bf16(rng.standard_normal((ctx, KR)).astype(np.float32)))
+    vf = oracle.bf16_to_f32(oracle.f32_to_bf16(rng.standard_normal((ctx, KR)).astype(np.float32)))
+    q = (rng.standard_normal((rows, Hq * D)) * 2).astype(np.float32)
+    qb = oracle.bf16_to_f32(oracle.f32_to_bf16(q))
+    out = lthn.Buf(rows * Hq * D * 2)
+    scale = float(np.float32(1.0 / np.sqrt(D)))
+    lthn.prefill_attention(dev(lthn, q), dev(lthn, oracle.f32_to_bf16(kf)), dev(lthn, oracle.f32_to_bf16(vf)), out, rows, pos0,
+                           Hq, Hkv, D, scale)
+    lthn.sync()
+    got = oracle.bf16_to_f32(out.download(np.uint16, (rows, Hq, D)))
+    check_rows = sorted({r for r in [0, 1, rows // 2, rows - 1] + list(rng.integers(0, rows, 6)) if r < rows})
+    for r in check_rows:
+        for h in range(Hq):
+            kvh = int(oracle.lib().lthn_o_kv_head_for_query(h, Hq, Hkv))
+            n = pos0 + r + 1
+            want = oracle.attention_single_head(qb[r, h * D:(h + 1) * D], kf[:n, kvh * D:(kvh + 1) * D],
+                                                vf[:n, kvh * D:(kvh + 1) * D], scale)
+            # bf16 output (2^-9 relative) + bf16 softmax weights (2^-9 each, averaged over the keys)
+            np.testing.assert_allclose(got[r, h], want, rtol=2.0 ** -7, atol=2.0 ** -7 * max(np.abs(want).max(), 1e-3))
+
+
 def test_argmax_lowest_index_wins_ties(oracle):
     """model.Greedy (model/sample.go:33-50): strict '>' from -inf, so ties go to the lowest index."""
     import lthn

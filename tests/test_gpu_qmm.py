@@ -79,6 +79,39 @@ def test_qmm_prefill_shapes_at_full_size(oracle, M, N, K):
     _sampled_check(lthn, oracle, M, N, K, seed=9)
 
 
+@pytest.mark.parametrize("tile", [128, 256])
+@pytest.mark.parametrize("M,N,K", [(1, 64, 128), (40, 200, 256), (300, 1152, 2304), (512, 2688, 5376)])
+def test_qmm_geglu_pair(oracle, tile, M, N, K):
+    """gelu_tanh(x Wgate^T) * (x Wup^T) in one tensor-core pass against the same product formed
+    from the bf16-contract operands in f64 (x bf16, weights dequantised and rounded to bf16), one
+    bf16 rounding at the end; and against the f64 reference on unrounded weights."""
+    import lthn
+    gp = make_weight(oracle, N, K, seed=N + 1)
+    up = make_weight(oracle, N, K, seed=N + 2)
+    xf, xb = make_x(oracle, M, K, seed=M)
+    wg = oracle.bf16_to_f32(oracle.f32_to_bf16(oracle.dequantize(*gp))).astype(np.float64)
+    wu = oracle.bf16_to_f32(oracle.f32_to_bf16(oracle.dequantize(*up))).astype(np.float64)
+    g = (xf.astype(np.float64) @ wg.T).astype(np.float32)
+    u = (xf.astype(np.float64) @ wu.T).astype(np.float32)
+    want = oracle.gelu_tanh(g) * u
+    gq, uq = lthn.QuantWeight.from_host(*gp), lthn.QuantWeight.from_host(*up)
+    x, y = lthn.Buf.from_array(xb), lthn.Buf(M * N * 2)
+    lthn.lib().lthn_debug_qmm_force_tile(tile)
+    try:
+        lthn.qmm_geglu(x, M, gq, uq, y)
+        lthn.sync()
+    finally:
+        lthn.lib().lthn_debug_qmm_force_tile(0)
+    got16 = y.download(np.uint16, (M, N))
+    # gelu_tanh runs on tanhf here and on the reference's f32 formula in the oracle: a few f32 ulps
+    # ahead of the bf16 rounding, inside bf16_close's allowance for values near a rounding boundary
+    assert bf16_close(oracle, got16, want)
+    ref = oracle.gelu_tanh(oracle.matnt_quant_host(xf, *gp, threads=8)) * oracle.matnt_quant_host(xf, *up, threads=8)
+    # against unrounded weights the 1e-2 bound holds per projection; the product of two
+    # projections (values up to ~10 here) carries both factors' error
+    assert rel_err(oracle.bf16_to_f32(got16), ref) <= 3e-2
+
+
 def test_qmm_small_m_and_other_widths_route_to_decode_kernels(oracle):
     import lthn
     for (M, N, K, bits, gs) in [(5, 128, 256, 4, 64), (40, 64, 256, 8, 64), (3, 24, 256, 2, 128)]:
