@@ -175,6 +175,69 @@ __global__ void __launch_bounds__(1024) rmsnorm_reg_kernel(const float* __restri
     }
 }
 
+// The same arithmetic for many rows at once (prefill chunks): one warp per row, shuffles only, no
+// block barrier. The row (a few KB) is read three times from L1/L2 instead of being held in
+// registers, so any width is served; sums of squares stay f64 as above.
+__global__ void __launch_bounds__(128) rmsnorm_rows_kernel(const float* __restrict__ a, float* __restrict__ h,
+                                                          const float* __restrict__ w_post,
+                                                          const float* __restrict__ w_next, float* __restrict__ out,
+                                                          int rows, int width, float eps, int mode,
+                                                          uint16_t* __restrict__ cols, int split) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const float* ar = a + (int64_t)row * width;
+    float* hr = h ? h + (int64_t)row * width : nullptr;
+    float* orow = out ? out + (int64_t)row * width : nullptr;
+    const int w4 = width >> 2;  // width is a multiple of 4 (checked by the launcher)
+    double ss = 0.0;
+    for (int i = lane; i < w4; i += 32) {
+        const float4 v = ((const float4*)ar)[i];
+        ss += (double)__fmul_rn(v.x, v.x) + (double)__fmul_rn(v.y, v.y) + (double)__fmul_rn(v.z, v.z) + (double)__fmul_rn(v.w, v.w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rms = (float)sqrt(ss / (double)width + (double)eps);
+    auto emit = [&](int i, float4 v) {
+        if (orow) ((float4*)orow)[i] = v;
+        if (cols) {
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; k++) store_split(cols, split, row, width, 4 * i + k, e[k]);
+        }
+    };
+    if (mode == 0) {
+        for (int i = lane; i < w4; i += 32) {
+            const float4 v = ((const float4*)ar)[i], w = ((const float4*)w_post)[i];
+            emit(i, make_float4(__fmul_rn(__fdiv_rn(v.x, rms), w.x), __fmul_rn(__fdiv_rn(v.y, rms), w.y),
+                                __fmul_rn(__fdiv_rn(v.z, rms), w.z), __fmul_rn(__fdiv_rn(v.w, rms), w.w)));
+        }
+        return;
+    }
+    double ss2 = 0.0;
+    for (int i = lane; i < w4; i += 32) {
+        const float4 v = ((const float4*)ar)[i], w = ((const float4*)w_post)[i];
+        float4 hv = ((float4*)hr)[i];
+        hv.x = __fadd_rn(hv.x, __fmul_rn(__fdiv_rn(v.x, rms), w.x));
+        hv.y = __fadd_rn(hv.y, __fmul_rn(__fdiv_rn(v.y, rms), w.y));
+        hv.z = __fadd_rn(hv.z, __fmul_rn(__fdiv_rn(v.z, rms), w.z));
+        hv.w = __fadd_rn(hv.w, __fmul_rn(__fdiv_rn(v.w, rms), w.w));
+        ((float4*)hr)[i] = hv;
+        ss2 += (double)__fmul_rn(hv.x, hv.x) + (double)__fmul_rn(hv.y, hv.y) + (double)__fmul_rn(hv.z, hv.z) + (double)__fmul_rn(hv.w, hv.w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss2 += __shfl_xor_sync(0xffffffffu, ss2, o);
+    const float rms2 = (float)sqrt(ss2 / (double)width + (double)eps);
+    if (!orow && !cols) return;
+    for (int i = lane; i < w4; i += 32) {
+        const float4 hv = ((const float4*)hr)[i], w = ((const float4*)w_next)[i];
+        emit(i, make_float4(__fmul_rn(__fdiv_rn(hv.x, rms2), w.x), __fmul_rn(__fdiv_rn(hv.y, rms2), w.y),
+                            __fmul_rn(__fdiv_rn(hv.z, rms2), w.z), __fmul_rn(__fdiv_rn(hv.w, rms2), w.w)));
+    }
+}
+
 // ---- tensor-parallel residual RMSNorm over peer memory ---------------------------------
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -650,7 +713,10 @@ int32_t launch_rmsnorm(cudaStream_t s, const float* a, float* h, const float* w_
     // one CTA per row; enough threads that each handles two or three elements (the f64 sum of
     // squares and the IEEE divisions are latency, not throughput, so parallelism is what helps)
     const int threads = width >= 2048 ? 1024 : (width >= 512 ? 512 : 256);
-    if (width <= 8 * threads)
+    const bool aligned = (((uintptr_t)a | (uintptr_t)h | (uintptr_t)w_post | (uintptr_t)w_next | (uintptr_t)out) & 15) == 0;
+    if (rows > 64 && width % 4 == 0 && aligned)  // many rows (prefill): a warp per row
+        LTHN_CUDA_TRY(launch_k(rmsnorm_rows_kernel, dim3((rows + 3) / 4), dim3(128), 0, s, a, h, w_post, w_next, out, rows, width, eps, mode, cols, split));
+    else if (width <= 8 * threads)
         LTHN_CUDA_TRY(launch_k(rmsnorm_reg_kernel, dim3(rows), dim3(threads), 0, s, a, h, w_post, w_next, out, width, eps, mode, cols, split));
     else
         LTHN_CUDA_TRY(launch_k(rmsnorm_kernel, dim3(rows), dim3(threads), 0, s, a, h, w_post, w_next, out, width, eps, mode, cols, split));

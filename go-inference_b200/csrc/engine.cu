@@ -94,9 +94,10 @@ struct Layer {
 };
 
 constexpr int kMaxRows = 32;  // rows per forward (the batched matvec serves up to 32)
-// Prompt rows per prefill chunk: the reference prefills in 512-token chunks
-// (decode/generate/generate.go:147-150).
-constexpr int kPrefillRows = 512;
+// Prompt rows per prefill chunk. The reference prefills in 512-token chunks
+// (decode/generate/generate.go:147-150); a chunk here is four times that, because a 512-row
+// projection is only 2 x N/128 tiles for 148 SMs and 512 rows x 8 heads of attention only 64 CTAs.
+constexpr int kPrefillRows = 2048;
 
 // lm_head (value, index) gather over peer memory (see tp_pair_gather_kernel)
 struct PairGather {
@@ -163,6 +164,7 @@ struct Model {
     uint64_t logits_serial = 0;
     // prefill on the tensor cores (prompts longer than kMaxRows): chunk workspace for kPrefillRows rows
     bool prefill_tc = false;
+    int prefill_rows = 0;  // rows per chunk (kPrefillRows unless LTHN_CUDA_PREFILL_CHUNK asks for fewer)
     int32_t *p_ids = nullptr, *p_pos = nullptr, *p_lane = nullptr, *p_pinned = nullptr;
     float *p_h = nullptr, *p_qkv = nullptr, *p_q = nullptr, *p_a = nullptr, *p_xnf = nullptr;
     uint16_t *p_xn = nullptr, *p_att = nullptr, *p_act = nullptr;
@@ -593,9 +595,9 @@ static int32_t feed_lane(Model* m, Lane* ln, const int32_t* ids, int n) {
     std::lock_guard<std::mutex> lk(m->mu);
     int32_t rc;
     if (m->prefill_tc && n > kMaxRows) {
-        // more rows than one decode forward takes: 512-row chunks through affine_qmm and the causal prefill attention
-        for (int off = 0; off < n; off += kPrefillRows) {
-            const int rows = std::min(kPrefillRows, n - off);
+        // more rows than one decode forward takes: chunks of kPrefillRows through affine_qmm and the causal prefill attention
+        for (int off = 0; off < n; off += m->prefill_rows) {
+            const int rows = std::min(m->prefill_rows, n - off);
             int32_t* hp = m->p_pinned;
             for (int r = 0; r < rows; r++) { hp[r] = ids[off + r]; hp[kPrefillRows + r] = ln->pos + r; hp[2 * kPrefillRows + r] = ln->id; }
             LTHN_CUDA_TRY(cudaMemcpyAsync(m->p_ids, hp, 3 * kPrefillRows * 4, cudaMemcpyHostToDevice, m->stream));
@@ -772,9 +774,13 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
         // the tensor-core prefill attention serves head_dim up to 256
         const char* env = getenv("LTHN_CUDA_PREFILL_F32");
         m->prefill_tc = !(env && env[0] == '1') && c.head_dim <= 256 && c.max_len > kMaxRows;
+        // LTHN_CUDA_PREFILL_CHUNK=n: smaller chunks (64..2048 rows), e.g. to bound the workspace
+        const char* ch = getenv("LTHN_CUDA_PREFILL_CHUNK");
+        const int want = ch ? atoi(ch) : kPrefillRows;
+        m->prefill_rows = std::max(64, std::min(kPrefillRows, want));
     }
     if (m->prefill_tc) {
-        const size_t P = (size_t)std::min(kPrefillRows, c.max_len);
+        const size_t P = (size_t)std::min(m->prefill_rows, c.max_len);
         const size_t QKV = (size_t)m->QR_l + 2 * m->KR_l;
         if ((rc = dalloc(m, &m->p_ids, 3 * (size_t)kPrefillRows)) || (rc = dalloc(m, &m->p_h, P * H)) ||
             (rc = dalloc(m, &m->p_xn, P * H)) || (rc = dalloc(m, &m->p_xnf, P * H)) || (rc = dalloc(m, &m->p_qkv, P * QKV)) ||

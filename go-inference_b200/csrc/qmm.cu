@@ -385,17 +385,21 @@ int32_t qmm_launch(cudaStream_t s, const QmmCall& c) {
     QmmArgs a{c.wq, c.scales, c.biases, c.wq2, c.scales2, c.biases2, c.y, device_status_word(), c.M, (int)c.N, (int)c.K, c.y_f32};
     if (!a.status) return fail(LTHN_ERR_CUDA, "affine_qmm: no device status word");
     const int64_t mt = (c.M + QMM_MT - 1) / QMM_MT;
-    if (c.wq2) {
-        // a 256-row tile holds 128 gate + 128 up rows
-        const int64_t tiles = ((c.N + 127) / 128) * mt;
-        int nt = tiles >= 148 ? 256 : 128;
-        if (g_force_nt == 128 || g_force_nt == 256) nt = g_force_nt;
-        return nt == 256 ? launch_qmm<256, 1>(s, map, a) : launch_qmm<128, 1>(s, map, a);
+    // Tile width by wave efficiency: one CTA per SM, so a grid of T tiles takes ceil(T/SMs) waves
+    // and the last wave may be nearly empty (N = 5376 with 2048 tokens is 168 tiles of 256 =
+    // 1.13 waves). The narrower tile does the same work in more, smaller pieces, at about 0.9 of
+    // the wide tile's rate per SM (measured ratio at full waves).
+    int sms = 148;
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     }
-    // 256-row weight tiles when that still fills the GPU, else 128
-    const int64_t tiles256 = ((c.N + 255) / 256) * mt;
-    int nt = tiles256 >= 148 ? 256 : 128;
+    auto eff = [&](int64_t tiles) { return (double)tiles / (double)(((tiles + sms - 1) / sms) * sms); };
+    const int no256 = c.wq2 ? 128 : 256, no128 = c.wq2 ? 64 : 128;  // output columns per tile (a GeGLU tile is half gate, half up)
+    const double e256 = eff(((c.N + no256 - 1) / no256) * mt), e128 = 0.9 * eff(((c.N + no128 - 1) / no128) * mt);
+    int nt = e256 >= e128 ? 256 : 128;
     if (g_force_nt == 128 || g_force_nt == 256) nt = g_force_nt;
+    if (c.wq2) return nt == 256 ? launch_qmm<256, 1>(s, map, a) : launch_qmm<128, 1>(s, map, a);
     return nt == 256 ? launch_qmm<256, 0>(s, map, a) : launch_qmm<128, 0>(s, map, a);
 }
 

@@ -306,8 +306,9 @@ int32_t lthn_tp_init(int32_t rank, int32_t world, const void* id128, void** comm
 int32_t lthn_tp_destroy(void* comm);
 int32_t lthn_model_set_comm(void* model, void* comm);
 
-/* Prompts of more than 32 tokens are prefilled in 512-row chunks (decode/generate/generate.go:
- * 147-150) through lthn_affine_qmm and lthn_prefill_attention, the route the reference takes for
+/* Prompts of more than 32 tokens are prefilled in chunks of up to 2048 rows (the reference's
+ * chunks are 512, decode/generate/generate.go:147-150; a B200 wants more tiles in flight) through
+ * lthn_affine_qmm and lthn_prefill_attention, the route the reference takes for
  * M > 1 (engine/metal/quant_seam_backend.go:37-68), with that engine's bf16 contract: activations
  * entering a projection and the dequantised weights are bf16, everything else f32. Shorter prompts
  * and appended pieces go through the f32 decode kernels, 32 rows per forward, as every prompt

@@ -128,10 +128,12 @@ def _margin_aware_tokens(got, want, margin, tol):
     return len(want)
 
 
-@pytest.mark.parametrize("cfg,prompt", [(SMALL, 33), (SMALL, 200), (MID, 130), (MID, 600)], ids=["small33", "small200", "mid130", "mid600"])
-def test_tensor_core_prefill_matches_bf16_contract_oracle(oracle, cfg, prompt):
-    """Prompts of more than 32 tokens are prefilled in 512-row chunks through affine_qmm and the
-    causal prefill attention (600 tokens: two chunks, the second attending the first's keys).
+@pytest.mark.parametrize("cfg,prompt,chunk", [(SMALL, 33, 0), (SMALL, 200, 0), (MID, 130, 0), (MID, 600, 256), (MID, 2100, 0)],
+                         ids=["small33", "small200", "mid130", "mid600x256", "mid2100"])
+def test_tensor_core_prefill_matches_bf16_contract_oracle(oracle, cfg, prompt, chunk, monkeypatch):
+    """Prompts of more than 32 tokens are prefilled in chunks of up to 2048 rows through affine_qmm
+    and the causal prefill attention (600 tokens with LTHN_CUDA_PREFILL_CHUNK=256: three chunks,
+    the later ones attending the earlier ones' keys; 2100 tokens: two chunks at the default).
     Oracle: the CPU reference decoder with the prefill contract of the reference's Metal engine
     (projection inputs and dequantised weights rounded to bf16, query rounded to bf16, everything
     else f32). What the oracle does not model is the kernel's bf16 softmax weights and f32 (not
@@ -139,6 +141,8 @@ def test_tensor_core_prefill_matches_bf16_contract_oracle(oracle, cfg, prompt):
     KV within 2^-6 relative (two bf16 ulps) plus a small absolute term, and greedy tokens equal
     wherever the reference's top-1/top-2 margin exceeds 2e-2 of the logit RMS."""
     import lthn
+    if chunk:
+        monkeypatch.setenv("LTHN_CUDA_PREFILL_CHUNK", str(chunk))
     w, norms = synth_weights(oracle, lthn, cfg, seed=13, random_norms=True)
     new = 24
     max_len = prompt + new
@@ -343,7 +347,7 @@ def test_gemma_2b_shape_greedy_256_tokens(oracle, monkeypatch):
     s.prefill(ids)
     f32_logits = s.logits()
     got = s.decode_greedy(new)
-    # the same prompt through the tensor-core prefill (two 512-row chunks) on a second session of a
+    # the same prompt through the tensor-core prefill (one 1024-row chunk) on a second session of a
     # second model: logits against the f32 path's, which the CPU reference pins below
     monkeypatch.delenv("LTHN_CUDA_PREFILL_F32")
     m2 = lthn.Model(mc)
