@@ -512,9 +512,17 @@ int32_t split_f32_launch(cudaStream_t s, const float* x, int64_t M, int64_t K, i
     return LTHN_OK;
 }
 
+bool qmv_batch_f32() {
+    const char* e = getenv("LTHN_CUDA_BATCH_F32");
+    return e && e[0] == '1';
+}
+
+// bf16 columns per f32 activation row that producers write for the matvec serving M rows: an
+// exact 3-term split at M <= 2, else 2 terms (16 mantissa bits). The tcgen05 kernel reads only the
+// first term, which is the bf16 rounding of the value.
 int32_t qmv_split_for(int M, int x_dtype) {
     if (x_dtype == LTHN_DTYPE_BF16) return 1;
-    return M <= 2 ? 3 : 2;  // f32 activations: exact 3-term split while it is free, else 2 terms (16 bits)
+    return M <= 2 ? 3 : 2;
 }
 
 // dispatch overrides: always zero in the product library, which exports no way to set them;
@@ -549,6 +557,28 @@ int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
         if (forced && g_force_warps) return fail(LTHN_ERR_INVALID, "affine_qmv: forced integer tensor-core configuration is not available");
     }
     if (c.norm) return fail(LTHN_ERR_INVALID, "affine_qmv: a fused norm prologue needs the batch-1/2 integer tensor-core kernel for this shape");
+    // 17..32 rows of a large matrix: the tcgen05 streaming kernel (bf16 activations and bf16-rounded
+    // weights, the contract of affine_qmm). Measured on B200 against the bf16 mma.sync kernel below:
+    // its time does not depend on the row count (lm_head 262144 x 2304: 161 us at 4..32 rows, against
+    // 108 / 111 / 143 / 295 / 314 us at 4 / 8 / 16 / 24 / 32 rows; 21504 x 5376: 55 us against 31 / 31 /
+    // 46 / 70 / 72 us), so it takes over where the mma.sync kernel runs out of issue slots; matrices
+    // of a few MB finish sooner on the mma.sync kernel at every row count.
+    const double welems = (double)c.N * (double)c.K * (fuse ? 2 : 1);
+    const bool tc_pays = c.M > 16 && welems >= 64e6;
+    if (c.M >= 3 && (g_force_kernel == 4 || (g_force_kernel == 0 && tc_pays && !qmv_batch_f32())) && qmv_tc_available(c)) {
+        const uint16_t* xb = nullptr;
+        int64_t ld = c.K;
+        if (c.x_dtype == LTHN_DTYPE_BF16) xb = (const uint16_t*)c.x;
+        else if (c.x_cols && c.x_split >= 1) { xb = c.x_cols; ld = (int64_t)c.x_split * c.K; }  // first split term = bf16(x)
+        else {
+            void* scratch = nullptr;
+            int32_t rc = scratch_get((size_t)c.M * c.K * 2, &scratch);
+            if (rc) return rc;
+            if ((rc = split_f32_launch(s, (const float*)c.x, c.M, c.K, 1, (uint16_t*)scratch))) return rc;
+            xb = (const uint16_t*)scratch;
+        }
+        if (((uintptr_t)xb & 15) == 0) return qmv_tc_launch(s, c, xb, ld);
+    }
     const bool prefer_dp4a = g_force_kernel == 1 || (g_force_kernel == 0 && big);
     if (prefer_dp4a && c.M <= 2) {
         Dp4aPlan plan;
@@ -561,7 +591,7 @@ int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
     a.wq = c.wq; a.scales = c.scales; a.biases = c.biases;
     a.wq2 = c.wq2; a.scales2 = c.scales2; a.biases2 = c.biases2;
     a.y = c.y; a.N = c.N; a.K = c.K; a.M = c.M; a.y_dtype = c.y_dtype; a.y_split = 0;
-    a.split = qmv_split_for(c.M, c.x_dtype);
+    a.split = c.x_dtype == LTHN_DTYPE_BF16 ? 1 : (c.M <= 2 ? 3 : 2);  // what this kernel wants (see qmv_split_for)
     a.C = c.M * a.split;
     if (c.x_dtype == LTHN_DTYPE_BF16) {
         a.x = (const uint16_t*)c.x;
@@ -696,7 +726,7 @@ int32_t lthn_affine_qmv_noalloc(void* stream, const float* x, int32_t M, const u
     LTHN_REQUIRE(M <= 32, "affine_qmv_noalloc: M must be at most 32");
     LTHN_REQUIRE(K > 0 && K % 64 == 0, "affine_qmv_noalloc: K must be a positive multiple of 64 (4-bit, group 64 only)");
     LTHN_REQUIRE(((uintptr_t)packed & 7) == 0 && ((uintptr_t)x & 3) == 0, "affine_qmv_noalloc: misaligned pointer");
-    const int split = qmv_split_for(M, LTHN_DTYPE_F32);
+    const int split = M <= 2 ? 3 : 2;  // the bf16 mma.sync kernel's exact / 16-bit split of f32 activations
     const size_t need = kQmvNoAllocHeader + (size_t)M * split * (size_t)K * 2;
     if (need > kQmvNoAllocBytes)
         return fail(LTHN_ERR_INVALID, "affine_qmv_noalloc: M*" + std::to_string(split) + "*K*2 bytes of activation columns (" +

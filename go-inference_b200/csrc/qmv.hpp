@@ -95,6 +95,14 @@ struct QmmCall {
 };
 int32_t qmm_launch(cudaStream_t st, const QmmCall& c);
 
+// Tensor-core streaming kernel for up to 32 activation rows (qmv_tc.cu): bf16 activations (row
+// pitch x_ld elements), weights dequantised to bf16 (the numeric contract of affine_qmm), f32
+// accumulation in TMEM.
+bool qmv_tc_available(const QmvCall& c);
+int32_t qmv_tc_launch(cudaStream_t st, const QmvCall& c, const uint16_t* x_bf16, int64_t x_ld);
+// LTHN_CUDA_BATCH_F32=1 keeps every row count on the f32-grade kernels (read at every call)
+bool qmv_batch_f32();
+
 // Dispatcher used by the C entry points and by the decoder engine.
 int32_t qmv_dispatch(cudaStream_t st, const QmvCall& c);
 

@@ -10,6 +10,8 @@
 namespace lthn {
 extern LTHN_HIDDEN int g_force_rt, g_force_warps, g_force_kernel;  // qmv.cu
 extern LTHN_HIDDEN int g_force_nt;                                 // qmm.cu
+extern LTHN_HIDDEN int g_tc_dbg;                                   // qmv_tc.cu
+extern LTHN_HIDDEN long long* g_tc_prof;
 }  // namespace lthn
 
 using namespace lthn;
@@ -22,13 +24,15 @@ void lthn_debug_qmv_force_config(int32_t rt, int32_t nwarps) {
     g_force_rt = rt;
     g_force_warps = nwarps;
 }
-// kernel: 0 default dispatch, 1 dp4a, 2 bf16 tensor-core, 3 integer tensor-core; bits 8-10: ring stages of the
+// kernel: 0 default dispatch, 1 dp4a, 2 bf16 mma.sync, 3 integer tensor-core, 4 tcgen05 streaming; bits 8-10: ring stages of the
 // integer kernel (0 default)
 void lthn_debug_qmv_force_kernel(int32_t kernel) {
     g_force_kernel = kernel & 15;
     g_i8_stg = (kernel >> 8) & 7;
+    g_tc_dbg = (kernel >> 12) & 255;
 }
 void lthn_debug_qmm_force_tile(int32_t nt) { g_force_nt = nt; }
+void lthn_debug_tc_profile(void* dptr) { g_tc_prof = (long long*)dptr; }
 
 // The tensor-parallel residual norm on one GPU: the t "ranks" are t local buffers ([t][rows*width]
 // in parts). flags_preset != 0: every "peer" has already signalled, nothing waits, and the call

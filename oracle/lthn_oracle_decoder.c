@@ -139,7 +139,8 @@ int lthn_o_decoder_forward(void *h, const int32_t *ids, long n, float *logits, f
     dec_t *d = (dec_t *)h;
     const lthn_o_decoder_config *c = &d->c;
     if (n <= 0 || d->pos + n > c->max_len) return 1;
-    g_bf16_contract = c->prefill_bf16 && n > 32;
+    const int long_prefill = c->prefill_bf16 && n > 32;
+    g_bf16_contract = long_prefill;
     long H = c->hidden, D = c->head_dim, QR = (long)c->q_heads * D, KR = (long)c->kv_heads * D, F = c->ffn;
     float *hid = (float *)malloc(sizeof(float) * n * H);
     float *xn = (float *)malloc(sizeof(float) * n * H);
@@ -185,7 +186,7 @@ int lthn_o_decoder_forward(void *h, const int32_t *ids, long n, float *logits, f
             memcpy(vc + p * KR, v + t * KR, sizeof(float) * KR);
             if (c->kv_bf16) { lthn_o_round_bf16_inplace(kc + p * KR, KR); lthn_o_round_bf16_inplace(vc + p * KR, KR); }
         }
-        if (g_bf16_contract) lthn_o_round_bf16_inplace(q, n * QR);
+        if (long_prefill) lthn_o_round_bf16_inplace(q, n * QR); /* the prefill attention multiplies bf16 queries */
         tapcpy(d, L, 7, q, n * QR);
         /* oracle_test.go:907-924: causal attention per token, GQA head map */
 #pragma omp parallel
@@ -225,6 +226,7 @@ int lthn_o_decoder_forward(void *h, const int32_t *ids, long n, float *logits, f
         if (hidden_last) memcpy(hidden_last, xn, sizeof(float) * H);
         if (logits) proj(&d->embed, xn, 1, c->gs, c->bits, logits);
     }
+    g_bf16_contract = 0;
     free(hid); free(xn); free(q); free(k); free(v); free(att); free(ao); free(h1); free(gate); free(up); free(tmp); free(sc);
     return 0;
 }

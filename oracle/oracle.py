@@ -73,6 +73,7 @@ def _declare(l):
     l.lthn_o_matnt_quant_host.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32]
     l.lthn_o_matnt.argtypes = [vp, vp, i64, i64, i64, vp]
     l.lthn_o_qmm_bf16.argtypes = [vp, vp, vp, vp, i64, i64, i64, i32, i32, vp]
+    l.lthn_o_proj_bf16_contract.argtypes = [vp, i64, vp, vp, vp, i64, i64, i32, i32, vp]
     l.lthn_o_rmsnorm.argtypes = [vp, vp, i64, f32, vp]
     l.lthn_o_rope_neox.argtypes = [vp, i64, i64, f64, i64, i64, f64, vp]
     l.lthn_o_rope_interleaved.argtypes = [vp, i64, i64, f64, i64, f64, vp]
@@ -276,6 +277,22 @@ def qmm_bf16(x_bf16, packed, scales, biases, gs=64, bits=4) -> np.ndarray:
     out = np.empty((m, n), dtype=np.uint16)
     _check(lib().lthn_o_qmm_bf16(_p(x), _p(pk), _p(np.ascontiguousarray(scales, dtype=np.uint16)),
                                  _p(np.ascontiguousarray(biases, dtype=np.uint16)), m, k, n, gs, bits, _p(out)), "qmm_bf16")
+    return out
+
+
+def proj_bf16_contract(x_f32, packed, scales, biases, gs=64, bits=4) -> np.ndarray:
+    """The tensor-core contract with f32 results: x and the dequantised weights rounded to bf16,
+    f64 accumulation, no output rounding (lthn_o_proj_bf16_contract). out [M, N] f32."""
+    x = np.ascontiguousarray(x_f32, dtype=np.float32)
+    if x.ndim == 1:
+        x = x[None, :]
+    pk = np.ascontiguousarray(packed, dtype=np.uint32)
+    m, k = x.shape
+    n = pk.shape[0]
+    out = np.empty((m, n), dtype=np.float32)
+    _check(lib().lthn_o_proj_bf16_contract(_p(x), m, _p(pk), _p(np.ascontiguousarray(scales, dtype=np.uint16)),
+                                           _p(np.ascontiguousarray(biases, dtype=np.uint16)), n, k, gs, bits, _p(out)),
+           "proj_bf16_contract")
     return out
 
 

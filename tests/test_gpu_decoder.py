@@ -26,6 +26,7 @@ def test_prefill_and_decode_match_oracle(oracle, cfg, monkeypatch):
     reference decoder."""
     import lthn
     monkeypatch.setenv("LTHN_CUDA_PREFILL_F32", "1")
+    monkeypatch.setenv("LTHN_CUDA_BATCH_F32", "1")   # and the 32-row forwards on the f32-grade matvec
     w, norms = synth_weights(oracle, lthn, cfg, seed=3, random_norms=True)
     max_len = 160
     od = build_oracle(oracle, cfg, w, norms, max_len)
@@ -95,6 +96,7 @@ def test_append_equals_prefill_and_chunked_decode(oracle, monkeypatch):
     20 + 30 split stays on the decode kernels.)"""
     import lthn
     monkeypatch.setenv("LTHN_CUDA_PREFILL_F32", "1")
+    monkeypatch.setenv("LTHN_CUDA_BATCH_F32", "1")
     cfg = SMALL
     w, norms = synth_weights(oracle, lthn, cfg, seed=5, random_norms=True)
     m = build_device(lthn, cfg, w, norms, 128, max_lanes=2)
@@ -234,11 +236,13 @@ def test_kv_export_import_round_trip(oracle):
     a.close(); b.close(); m.close()
 
 
-def test_lane_set_matches_single_sessions(oracle):
+def test_lane_set_matches_single_sessions(oracle, monkeypatch):
     """inference.LaneSet: K lanes with ragged prompts advanced by ONE batched forward per
     Step produce the tokens each prompt gets alone; BatchForwardCount advances by one per
-    Step (batch_step.go:112-116)."""
+    Step (batch_step.go:112-116). With the f32 prefill on both sides the batched rows compute
+    what the single rows compute, so the tokens are identical."""
     import lthn
+    monkeypatch.setenv("LTHN_CUDA_PREFILL_F32", "1")
     cfg = MID
     w, norms = synth_weights(oracle, lthn, cfg, seed=7, random_norms=True)
     K = 5
@@ -335,6 +339,7 @@ def test_gemma_2b_shape_greedy_256_tokens(oracle, monkeypatch):
     sequences part, the reference's top-1/top-2 logit margin at that step is reported."""
     import lthn
     monkeypatch.setenv("LTHN_CUDA_PREFILL_F32", "1")   # token identity is asked of the f32 path
+    monkeypatch.setenv("LTHN_CUDA_BATCH_F32", "1")
     cfg = GEMMA_2B
     seed, prompt_len, new = 0, 1024, 256
     mc = lthn.make_config(cfg["layers"], cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"],
@@ -350,6 +355,7 @@ def test_gemma_2b_shape_greedy_256_tokens(oracle, monkeypatch):
     # the same prompt through the tensor-core prefill (one 1024-row chunk) on a second session of a
     # second model: logits against the f32 path's, which the CPU reference pins below
     monkeypatch.delenv("LTHN_CUDA_PREFILL_F32")
+    monkeypatch.delenv("LTHN_CUDA_BATCH_F32")
     m2 = lthn.Model(mc)
     m2.synthesize(seed, 0.02)
     m2.finalize()
