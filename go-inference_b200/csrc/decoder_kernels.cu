@@ -597,9 +597,12 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
 }
 
 // stage 2: merge chunk partials with their log-sum-exp weights. One CTA per (head, row), four
-// warps; warp w takes chunks w, w+4, ... and each lane D/32 consecutive dimensions, so the
-// partial accumulators are read with independent 16-byte loads (several chunks in flight per
-// lane); the four warps' sums meet in shared memory.
+// warps; warp w takes chunks w, w+4, ... and each lane D/32 consecutive dimensions. A single pass:
+// a warp issues the loads of (max, sum, accumulator slice) of up to MERGE_BATCH of its chunks
+// together, folds them into a running (max, sum, accumulator) of its own, and the four warps' states
+// meet once in shared memory - one memory round trip per MERGE_BATCH*4 chunks instead of the three
+// dependent passes (maxima, weights, accumulators) of a two-level softmax merge.
+constexpr int MERGE_BATCH = 8;
 template <int D>
 __global__ void __launch_bounds__(128) sdpa_merge_kernel(const float* __restrict__ part,
                                                          const int32_t* __restrict__ row_pos, int Hq, int nchunks,
@@ -608,45 +611,59 @@ __global__ void __launch_bounds__(128) sdpa_merge_kernel(const float* __restrict
     pdl_trigger();
     pdl_wait();
     constexpr int DL = D / 32;  // dimensions per lane (2, 4, 8 or 16)
-    __shared__ float wgt[1024];
-    __shared__ float sden[4];
+    __shared__ float sm_m[4], sm_l[4];
     __shared__ float acc_s[4][D];
     const int row = blockIdx.y, qh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int ctx = row_pos[row] + 1;
     const int used = min(nchunks, (ctx + chunk_len - 1) / chunk_len);
     const float* pa = part + ((int64_t)row * Hq + qh) * nchunks * (D + 2);
-    float m = -INFINITY;  // every warp finds the global maximum itself (cheap, no extra barrier)
-    for (int c = lane; c < used; c += 32) m = fmaxf(m, pa[(int64_t)c * (D + 2) + D]);
-    m = warp_max(m);
-    float den = 0.f;
-    for (int c = tid; c < used; c += 128) {
-        const float e = __expf(pa[(int64_t)c * (D + 2) + D] - m);
-        wgt[c] = e;
-        den += pa[(int64_t)c * (D + 2) + D + 1] * e;
-    }
-    den = warp_sum(den);
-    if (lane == 0) sden[warp] = den;
-    __syncthreads();
-    float acc[DL];
+    float m = -INFINITY, l = 0.f, acc[DL];
 #pragma unroll
     for (int i = 0; i < DL; i++) acc[i] = 0.f;
-#pragma unroll 4
-    for (int c = warp; c < used; c += 4) {
-        const float w = wgt[c];
-        const float2* src = (const float2*)(pa + (int64_t)c * (D + 2) + lane * DL);  // rows are 8-byte aligned
+    for (int c0 = warp; c0 < used; c0 += 4 * MERGE_BATCH) {
+        float cm[MERGE_BATCH], cl[MERGE_BATCH];
+        float2 cv[MERGE_BATCH][DL / 2];
 #pragma unroll
-        for (int i = 0; i < DL / 2; i++) {
-            const float2 v = src[i];
-            acc[2 * i] = fmaf(v.x, w, acc[2 * i]);
-            acc[2 * i + 1] = fmaf(v.y, w, acc[2 * i + 1]);
+        for (int b = 0; b < MERGE_BATCH; b++) {
+            const int c = c0 + 4 * b;
+            const bool live = c < used;
+            const float* p = pa + (int64_t)(live ? c : c0) * (D + 2);
+            cm[b] = live ? p[D] : -INFINITY;
+            cl[b] = live ? p[D + 1] : 0.f;
+            const float2* src = (const float2*)(p + lane * DL);  // rows are 8-byte aligned
+#pragma unroll
+            for (int i = 0; i < DL / 2; i++) cv[b][i] = src[i];
         }
+        float bm = m;
+#pragma unroll
+        for (int b = 0; b < MERGE_BATCH; b++) bm = fmaxf(bm, cm[b]);
+        if (bm == -INFINITY) continue;
+        const float rescale = __expf(m - bm);  // m = -inf -> 0
+        l *= rescale;
+#pragma unroll
+        for (int i = 0; i < DL; i++) acc[i] *= rescale;
+#pragma unroll
+        for (int b = 0; b < MERGE_BATCH; b++) {
+            const float w = __expf(cm[b] - bm);  // dead slots: exp(-inf) = 0
+            l = fmaf(cl[b], w, l);
+#pragma unroll
+            for (int i = 0; i < DL / 2; i++) {
+                acc[2 * i] = fmaf(cv[b][i].x, w, acc[2 * i]);
+                acc[2 * i + 1] = fmaf(cv[b][i].y, w, acc[2 * i + 1]);
+            }
+        }
+        m = bm;
     }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
 #pragma unroll
     for (int i = 0; i < DL; i++) acc_s[warp][lane * DL + i] = acc[i];
     __syncthreads();
-    const float denom = sden[0] + sden[1] + sden[2] + sden[3];
+    const float gm = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+    float w4[4], denom = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) { w4[w] = __expf(sm_m[w] - gm); denom = fmaf(sm_l[w], w4[w], denom); }
     for (int d = tid; d < D; d += 128) {
-        const float o = (acc_s[0][d] + acc_s[1][d] + acc_s[2][d] + acc_s[3][d]) / denom;
+        const float o = (acc_s[0][d] * w4[0] + acc_s[1][d] * w4[1] + acc_s[2][d] * w4[2] + acc_s[3][d] * w4[3]) / denom;
         out[((int64_t)row * Hq + qh) * D + d] = o;
         if (cols) store_split(cols, split, row, Hq * D, qh * D + d, o);
     }
@@ -778,7 +795,6 @@ int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D) {
     if (a.Hq % a.Hkv != 0) return fail(LTHN_ERR_INVALID, "sdpa_decode: Hq must be a multiple of Hkv");
     const int GQ = a.Hq / a.Hkv;
     if (a.nchunks > 1 && !a.part) return fail(LTHN_ERR_INVALID, "sdpa_decode: split-KV needs a scratch buffer");
-    if (a.nchunks > 1024) return fail(LTHN_ERR_INVALID, "sdpa_decode: context too long for the merge stage (more than 1024 chunks)");
     // register budget: bundle * D/8 accumulators and as many query values per lane
     const int max_bundle = D <= 128 ? 4 : (D <= 256 ? 2 : 1);
     int bundle = 1;

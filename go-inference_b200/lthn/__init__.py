@@ -30,6 +30,11 @@ class DeviceInfo(C.Structure):
                 ("sm_count", C.c_int32), ("compute_major", C.c_int32), ("compute_minor", C.c_int32)]
 
 
+class LoadOptions(C.Structure):
+    _fields_ = [("max_len", C.c_int32), ("max_lanes", C.c_int32), ("tp_rank", C.c_int32), ("tp_size", C.c_int32),
+                ("comm", C.c_void_p), ("uniform_attention", C.c_int32)]
+
+
 class ModelConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab",
                                          "group_size", "bits", "max_len", "max_lanes")] + \
@@ -108,6 +113,8 @@ class _Sig:
     lthn_sdpa_decode = (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, f32, i32])
     lthn_argmax = (i32, [vp, vp, i32, i32, vp])
     lthn_model_create = (i32, [C.POINTER(ModelConfig), pvp])
+    lthn_model_load_dir = (i32, [C.c_char_p, C.POINTER(LoadOptions), pvp])
+    lthn_checkpoint_inspect = (i32, [C.c_char_p, C.c_char_p, sz])
     lthn_model_upload_linear = (i32, [vp, i32, i32, vp, vp, vp, i64, i64])
     lthn_model_upload_norm = (i32, [vp, i32, i32, vp, i64])
     lthn_model_synthesize = (i32, [vp, u64, f32])
@@ -429,6 +436,14 @@ def make_config(layers, hidden, q_heads, kv_heads, head_dim, ffn, vocab, max_len
                        rope_base=rope_base, attn_scale=0.0, embed_scale=0.0, tp_rank=tp_rank, tp_size=tp_size)
 
 
+def checkpoint_inspect(path: str) -> dict:
+    """Host-side summary of a checkpoint directory (config.json + safetensors headers)."""
+    import json
+    buf = C.create_string_buffer(4096)
+    check(lib().lthn_checkpoint_inspect(os.fsencode(path), buf, len(buf)))
+    return json.loads(buf.value.decode())
+
+
 class Model:
     """engine.TokenModel: resident weights + KV lanes (lthn_model_*)."""
 
@@ -437,6 +452,20 @@ class Model:
         h = C.c_void_p()
         check(lib().lthn_model_create(C.byref(cfg), C.byref(h)))
         self.h = h
+
+    @classmethod
+    def load_dir(cls, path: str, max_len=0, max_lanes=1, tp_rank=0, tp_size=1, comm=None, uniform_attention=False) -> "Model":
+        """Backend.LoadModel for a checkpoint directory (lthn_model_load_dir)."""
+        info = checkpoint_inspect(path)
+        opts = LoadOptions(max_len=max_len, max_lanes=max_lanes, tp_rank=tp_rank, tp_size=tp_size, comm=comm,
+                           uniform_attention=int(uniform_attention))
+        h = C.c_void_p()
+        check(lib().lthn_model_load_dir(os.fsencode(path), C.byref(opts), C.byref(h)))
+        m = cls.__new__(cls)
+        m.h = h
+        m.cfg = make_config(info["layers"], info["hidden"], info["q_heads"], info["kv_heads"], info["head_dim"], info["ffn"],
+                            info["vocab"], max_len, max_lanes, tp_rank=tp_rank, tp_size=tp_size)
+        return m
 
     def upload_linear(self, layer, role, packed, scales, biases):
         pk = np.ascontiguousarray(packed, dtype=np.uint32)

@@ -299,6 +299,31 @@ int32_t lthn_model_tp_exchange(void* model, int32_t* mode);
 int32_t lthn_model_graph_state(void* model, int32_t* state);
 int32_t lthn_model_destroy(void* model);   /* TokenModel.Close (engine/model.go:30) */
 
+/* model.Load (model/load.go:19-108) for a gemma3-style MLX-affine checkpoint directory: reads
+ * config.json (text fields at top level or under "text_config"; "quantization" block with
+ * group_size / bits and per-module overrides, model/quant_config.go:39-88) and the safetensors
+ * directory (model.safetensors, or the shards model.safetensors.index.json names; tensor names of
+ * model/assemble.go:56-75, an optional "language_model." prefix stripped), checks every linear's
+ * geometry against the quantization block as affineGeometry does (model/linear.go:91-102), widens
+ * F16 scales/biases/norms to bf16 (model/safetensors/widen.go), applies the gemma (1+w) norm fold
+ * in the tensor's dtype (model/norm_bias.go:22-49), uploads this rank's shard of every tensor and
+ * finalizes. The files are mapped read-only for the duration of the call. Linears other than
+ * 4-bit / group 64 (e.g. an 8-bit per-module override) and checkpoints that declare
+ * sliding-window layers are rejected with the tensor or field named; uniform_attention = 1 loads
+ * the latter anyway, every layer with full attention and the checkpoint's rope_theta. */
+typedef struct {
+    int32_t max_len;            /* KV positions per lane; 0 -> min(max_position_embeddings, 4096) */
+    int32_t max_lanes;          /* 0 -> 1 */
+    int32_t tp_rank, tp_size;   /* tensor-parallel shard to keep (tp_size 0 or 1: everything) */
+    void* comm;                 /* communicator from lthn_tp_init when tp_size > 1 */
+    int32_t uniform_attention;
+} lthn_load_options;
+int32_t lthn_model_load_dir(const char* dir, const lthn_load_options* opts, void** model);
+/* The host half of the same: parses config.json and the safetensors directories and writes a
+ * one-line JSON summary (dimensions, quantization, tensor and shard counts) into json_out. Needs
+ * no device. */
+int32_t lthn_checkpoint_inspect(const char* dir, char* json_out, size_t json_len);
+
 /* Tensor parallelism over NCCL (the reference is single-device; new functionality).
  * Rank 0 makes the id, the host distributes its 128 bytes, every rank joins. */
 int32_t lthn_tp_unique_id(void* out128);

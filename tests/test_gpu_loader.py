@@ -1,0 +1,79 @@
+"""lthn_model_load_dir: a checkpoint directory loaded by the library gives the model that uploading
+the same tensors through lthn_model_upload_* gives (model.Load, model/load.go:19-108, followed by
+the engine's binding of model.LoadedModel)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from checkpoint_util import effective_norms, write_checkpoint
+from decoder_util import MID, SMALL, build_device, build_oracle, synth_weights
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("norm_dtype,shards,prefix,nest", [("BF16", 1, "", False), ("F32", 3, "language_model.", True),
+                                                           ("F16", 2, "", False)])
+def test_loaded_checkpoint_equals_uploaded_tensors(oracle, tmp_path, norm_dtype, shards, prefix, nest):
+    import lthn
+    cfg = SMALL
+    w, norms = synth_weights(oracle, lthn, cfg, seed=31, random_norms=True)
+    d = str(tmp_path / "ck")
+    write_checkpoint(d, cfg, w, norms, norm_dtype=norm_dtype, shards=shards, prefix=prefix, nest_text_config=nest)
+    loaded = lthn.Model.load_dir(d, max_len=96)
+    # the uploaded twin gets the norm weights the (1+w) fold produces from what the file stores
+    eff = effective_norms(oracle, norms, norm_dtype)
+    up = build_device(lthn, cfg, w, eff, 96)
+    ids = np.random.default_rng(2).integers(0, cfg["vocab"], 20).astype(np.int32)
+    a, b = loaded.open_session(), up.open_session()
+    a.prefill(ids)
+    la = a.logits()
+    ta = a.decode_greedy(16)
+    b.prefill(ids)
+    assert np.array_equal(la, b.logits())
+    assert np.array_equal(ta, b.decode_greedy(16))
+    # and the CPU reference decoder on the folded norms agrees with the loaded model
+    od = build_oracle(oracle, cfg, w, eff, 96)
+    want_logits = od.forward(ids)
+    rms = float(np.sqrt(np.mean(want_logits.astype(np.float64) ** 2)))
+    assert float(np.max(np.abs(la - want_logits))) <= 1e-2 * rms
+    a.close(); b.close(); loaded.close(); up.close()
+
+
+def test_load_rejects_what_the_engine_does_not_serve(oracle, tmp_path):
+    import lthn
+    cfg = SMALL
+    w, norms = synth_weights(oracle, lthn, cfg, seed=31)
+    d = str(tmp_path / "ck")
+    # an 8-bit per-module override (QAT packs keep MLP projections at 8 bit): named and refused
+    write_checkpoint(d, cfg, w, norms, quant_extra={"model.layers.1.mlp.down_proj": {"group_size": 64, "bits": 8}})
+    with pytest.raises(lthn.LthnError) as e:
+        lthn.Model.load_dir(d, max_len=32)
+    assert "model.layers.1.mlp.down_proj" in str(e.value)
+    # a missing tensor
+    write_checkpoint(d, cfg, w, norms)
+    import checkpoint_util as cu
+    t = cu.checkpoint_tensors(cfg, w, norms)
+    del t["model.layers.0.self_attn.k_norm.weight"]
+    cu.write_safetensors(os.path.join(d, "model.safetensors"), t)
+    with pytest.raises(lthn.LthnError) as e:
+        lthn.Model.load_dir(d, max_len=32)
+    assert "k_norm" in str(e.value)
+    # sliding-window layers: refused unless every layer may run with full attention
+    write_checkpoint(d, cfg, w, norms, extra_config={"sliding_window": 512, "sliding_window_pattern": 6})
+    with pytest.raises(lthn.LthnError) as e:
+        lthn.Model.load_dir(d, max_len=32)
+    assert "sliding" in str(e.value)
+    m = lthn.Model.load_dir(d, max_len=32, uniform_attention=True)
+    s = m.open_session()
+    s.prefill(np.arange(5, dtype=np.int32))
+    assert len(s.decode_greedy(3)) == 3
+    s.close(); m.close()
+    # geometry that contradicts the quantization block
+    cfgj = json.load(open(os.path.join(d, "config.json")))
+    cfgj["quantization"]["group_size"] = 32
+    json.dump(cfgj, open(os.path.join(d, "config.json"), "w"))
+    with pytest.raises(lthn.LthnError) as e:
+        lthn.Model.load_dir(d, max_len=32, uniform_attention=True)
+    assert "geometry" in str(e.value)
