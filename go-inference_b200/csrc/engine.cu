@@ -23,12 +23,14 @@
 #include "common.cuh"
 #include "decoder_kernels.hpp"
 #include "qmv.hpp"
+#include "sampler.hpp"
 
 #include <dlfcn.h>
 
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -168,6 +170,11 @@ struct Model {
     int32_t *p_ids = nullptr, *p_pos = nullptr, *p_lane = nullptr, *p_pinned = nullptr;
     float *p_h = nullptr, *p_qkv = nullptr, *p_q = nullptr, *p_a = nullptr, *p_xnf = nullptr;
     uint16_t *p_xn = nullptr, *p_att = nullptr, *p_act = nullptr;
+    // sampling workspace (first sampled call): bf16 row, candidate window, id lists
+    uint16_t *s_bits = nullptr, *s_cbits = nullptr;
+    int32_t *s_cidx = nullptr, *s_lists = nullptr;
+    float* s_gather = nullptr;
+    std::vector<uint16_t> s_host_bits;
 };
 
 template <typename T>
@@ -573,7 +580,105 @@ struct Lane {
     int handle = 0, produced = 0, max_new = 0;
     bool terminal = false;
     std::vector<int32_t> stop;
+    std::shared_ptr<struct SampleState> samp;  // set for lanes that sample (LaneSpec.Sampler)
 };
+
+// Per-lane (or per-call) sampling state: the reference keeps one Sampler per request and a history
+// of the tokens generated so far for the repeat penalty (model/token.go:263-305).
+struct SampleState {
+    HostSampler own;            // lane sets: the lane's own RNG stream
+    HostSampler* rng = nullptr; // the stream in use (sessions: the caller's sampler)
+    lthn_sample_params p{};
+    std::vector<int32_t> suppress, history;
+    int generated = 0;
+};
+constexpr int kSampleListCap = 1 << 16;
+
+static int32_t sample_workspace(Model* m) {
+    if (m->s_bits) return LTHN_OK;
+    int32_t rc;
+    const size_t t = (size_t)std::max(1, m->c.tp_size);
+    if ((rc = dalloc(m, &m->s_bits, (size_t)m->V_l)) || (rc = dalloc(m, &m->s_cbits, (size_t)SAMPLE_KMAX)) ||
+        (rc = dalloc(m, &m->s_cidx, (size_t)SAMPLE_KMAX)) || (rc = dalloc(m, &m->s_lists, (size_t)2 * kSampleListCap)) ||
+        (rc = dalloc(m, &m->s_gather, 2 * (size_t)SAMPLE_KMAX * (1 + t))))
+        return rc;
+    return LTHN_OK;
+}
+
+__global__ void sample_pack_kernel(const int32_t* idx, const uint16_t* bits, int k, float* out) {
+    const int i = threadIdx.x;
+    if (i < k) { out[2 * i] = __uint_as_float((uint32_t)bits[i] << 16); out[2 * i + 1] = __int_as_float(idx[i]); }
+}
+
+// One token for the row `row` of the model's logits buffer (which must still hold that lane's
+// logits). stop: the request's stop tokens (suppressed until min_tokens_before_stop tokens exist).
+static int32_t sample_row(Model* m, int row, SampleState& st, const std::vector<int32_t>& stop, int32_t* token) {
+    int32_t rc;
+    if ((rc = sample_workspace(m))) return rc;
+    cudaStream_t s = m->stream;
+    const auto& c = m->c;
+    lthn_sample_params p = st.p;
+    std::vector<int32_t> sup = st.suppress;
+    if (p.min_tokens_before_stop > 0 && st.generated < p.min_tokens_before_stop)  // appendSuppressionTokens (model/token.go:645-655)
+        for (int32_t tk : stop) if (std::find(sup.begin(), sup.end(), tk) == sup.end()) sup.push_back(tk);
+    p.suppress = sup.data();
+    p.n_suppress = (int)sup.size();
+    const bool penal = p.repeat_penalty > 1.0f && !st.history.empty();
+    const int nh = penal ? (int)st.history.size() : 0;
+    if (nh > kSampleListCap || (int)sup.size() > kSampleListCap) return fail(LTHN_ERR_INVALID, "sampler: history or suppress list longer than 65536 ids");
+    if (nh) LTHN_CUDA_TRY(cudaMemcpyAsync(m->s_lists, st.history.data(), (size_t)nh * 4, cudaMemcpyHostToDevice, s));
+    if (!sup.empty()) LTHN_CUDA_TRY(cudaMemcpyAsync(m->s_lists + kSampleListCap, sup.data(), sup.size() * 4, cudaMemcpyHostToDevice, s));
+    const float* logits = m->logits + (size_t)row * m->V_l;
+    if ((rc = sample_prepare_device(s, logits, m->V_l, m->v0, m->s_lists, nh, p.repeat_penalty, m->s_lists + kSampleListCap, (int)sup.size(), m->s_bits))) return rc;
+    // the lists were applied on the device: the host sampler sees plain logits
+    lthn_sample_params hp = p;
+    hp.suppress = nullptr; hp.n_suppress = 0; hp.repeat_penalty = 0;
+    const bool greedy = p.temperature <= 0 && p.min_p <= 0;
+    const int k = greedy ? 1 : p.top_k;
+    if (k >= 1 && k <= SAMPLE_KMAX && k < c.vocab) {
+        const int kl = std::min(k, m->V_l);
+        if ((rc = sample_topk_device(s, m->s_bits, 1, m->V_l, kl, m->v0, m->s_cidx, m->s_cbits))) return rc;
+        std::vector<std::pair<uint16_t, int32_t>> cand;
+        if (c.tp_size > 1) {
+            // every rank contributes its shard's best kl; all ranks merge the same list and draw the same token
+            sample_pack_kernel<<<1, SAMPLE_KMAX, 0, s>>>(m->s_cidx, m->s_cbits, kl, m->s_gather);
+            LTHN_CUDA_TRY(cudaGetLastError());
+            float* all = m->s_gather + 2 * SAMPLE_KMAX;
+            if ((rc = nccl_check(g_nccl.AllGather(m->s_gather, all, (size_t)2 * kl, kNcclFloat32, m->comm, s), "ncclAllGather"))) return rc;
+            std::vector<float> h((size_t)2 * kl * c.tp_size);
+            LTHN_CUDA_TRY(cudaMemcpyAsync(h.data(), all, h.size() * 4, cudaMemcpyDeviceToHost, s));
+            LTHN_CUDA_TRY(cudaStreamSynchronize(s));
+            for (size_t i = 0; i < h.size() / 2; i++) {
+                uint32_t vb, ib;
+                memcpy(&vb, &h[2 * i], 4); memcpy(&ib, &h[2 * i + 1], 4);
+                cand.emplace_back((uint16_t)(vb >> 16), (int32_t)ib);
+            }
+        } else {
+            std::vector<int32_t> hi(kl);
+            std::vector<uint16_t> hb(kl);
+            LTHN_CUDA_TRY(cudaMemcpyAsync(hi.data(), m->s_cidx, (size_t)kl * 4, cudaMemcpyDeviceToHost, s));
+            LTHN_CUDA_TRY(cudaMemcpyAsync(hb.data(), m->s_cbits, (size_t)kl * 2, cudaMemcpyDeviceToHost, s));
+            LTHN_CUDA_TRY(cudaStreamSynchronize(s));
+            for (int i = 0; i < kl; i++) cand.emplace_back(hb[i], hi[i]);
+        }
+        // best first: value descending, id ascending (the order a stable descending sort of the row gives)
+        std::sort(cand.begin(), cand.end(), [](const std::pair<uint16_t, int32_t>& a, const std::pair<uint16_t, int32_t>& b) {
+            const float va = bf16_bits_to_f32(a.first), vb = bf16_bits_to_f32(b.first);
+            if (va != vb) return va > vb;
+            return a.second < b.second;
+        });
+        if ((int)cand.size() > k) cand.resize(k);
+        std::vector<uint16_t> cb(cand.size());
+        std::vector<int32_t> ci(cand.size());
+        for (size_t i = 0; i < cand.size(); i++) { cb[i] = cand[i].first; ci[i] = cand[i].second; }
+        return st.rng->sample(cb.data(), ci.data(), (int)cand.size(), hp, token);
+    }
+    if (c.tp_size > 1) return fail(LTHN_ERR_INVALID, "sampler: a tensor-parallel model samples through the device top-k window: set 1 <= top_k <= 256");
+    m->s_host_bits.resize((size_t)m->V_l);
+    LTHN_CUDA_TRY(cudaMemcpyAsync(m->s_host_bits.data(), m->s_bits, (size_t)m->V_l * 2, cudaMemcpyDeviceToHost, s));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(s));
+    return st.rng->sample(m->s_host_bits.data(), nullptr, m->V_l, hp, token);
+}
 
 static int lane_acquire(Model* m) {
     std::lock_guard<std::mutex> lk(m->mu);
@@ -1139,6 +1244,50 @@ int32_t lthn_session_decode_greedy(void* session, int32_t max_new, int32_t eos_i
     return LTHN_OK;
 }
 
+// GenerateSampledFromCacheEach (engine/session.go:51): the loop of model/token.go:263-305 with the
+// pick made by the sampler. The repeat-penalty history is the tokens of this call.
+int32_t lthn_session_decode_sampled(void* session, void* sampler, const lthn_sample_params* params, int32_t max_new,
+                                    const int32_t* stop, int32_t n_stop, int32_t* out_ids, int32_t* n_out) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && sampler && params && out_ids && n_out, "lthn_session_decode_sampled: NULL argument");
+    LTHN_REQUIRE(n_stop >= 0 && (n_stop == 0 || stop), "lthn_session_decode_sampled: bad stop list");
+    LTHN_REQUIRE(params->n_suppress >= 0 && (params->n_suppress == 0 || params->suppress), "lthn_session_decode_sampled: bad suppress list");
+    *n_out = 0;
+    LTHN_REQUIRE(s->lane.pos > 0, "lthn_session_decode_sampled: the session has no prefilled state");
+    Model* m = s->m;
+    SampleState st;
+    st.rng = (HostSampler*)sampler;
+    st.p = *params;
+    if (params->n_suppress) st.suppress.assign(params->suppress, params->suppress + params->n_suppress);
+    const std::vector<int32_t> stops(stop, stop + n_stop);
+    for (int i = 0; i < max_new; i++) {
+        if (!s->lane.have_next) {  // the last picked token has not been fed yet: its logits are needed now
+            LTHN_REQUIRE(s->lane.pending >= 0, "lthn_session_decode_sampled: no pending token");
+            if (s->lane.pos + 1 > m->c.max_len) return fail(LTHN_ERR_STATE, "lthn_session_decode_sampled: context length exceeded");
+            const int32_t t = s->lane.pending;
+            int32_t rc = feed_lane(m, &s->lane, &t, 1);
+            if (rc) return rc;
+        }
+        int32_t tok = -1;
+        {
+            std::lock_guard<std::mutex> lk(m->mu);
+            if (s->lane.logits_serial != m->logits_serial)
+                return fail(LTHN_ERR_STATE, "lthn_session_decode_sampled: a later forward of another session or lane set of this model has "
+                                            "overwritten the logits");
+            int32_t rc = sample_row(m, s->lane.logits_row, st, stops, &tok);
+            if (rc) return rc;
+        }
+        out_ids[(*n_out)++] = tok;
+        st.generated++;
+        if (st.p.repeat_penalty > 1.0f) st.history.push_back(tok);
+        s->lane.pending = tok;
+        s->lane.have_next = false;
+        if (std::find(stops.begin(), stops.end(), tok) != stops.end()) break;
+    }
+    return LTHN_OK;
+}
+
 // Logits of the last fed token (vocab floats; local shard under tensor parallelism) for
 // host-side sampling (engine/session.go:51 GenerateSampledFromCacheEach).
 int32_t lthn_session_logits(void* session, float* logits_host, int64_t n) {
@@ -1211,12 +1360,11 @@ int32_t lthn_laneset_open(void* model, int32_t max_lanes, void** set) {
     return LTHN_OK;
 }
 
-int32_t lthn_laneset_prepare(void* set, const int32_t* ids, int32_t n, int32_t max_new, const int32_t* stop,
-                             int32_t n_stop, int32_t* lane_handle) {
-    clear_error();
-    LaneSet* ls = (LaneSet*)set;
+static int32_t laneset_prepare(LaneSet* ls, const int32_t* ids, int32_t n, int32_t max_new, const int32_t* stop, int32_t n_stop,
+                               const lthn_sample_params* params, uint64_t seed, int32_t* lane_handle) {
     LTHN_REQUIRE(ls && ids && lane_handle, "lthn_laneset_prepare: NULL argument");
     LTHN_REQUIRE((int)ls->lanes.size() < ls->max_lanes, "lthn_laneset_prepare: the lane set is at MaxLanes");
+    LTHN_REQUIRE(!params || (params->n_suppress >= 0 && (params->n_suppress == 0 || params->suppress)), "lthn_laneset_prepare: bad suppress list");
     const int id = lane_acquire(ls->m);
     if (id < 0) return fail(LTHN_ERR_STATE, "lthn_laneset_prepare: every KV lane of the model is in use");
     Lane ln;
@@ -1225,10 +1373,38 @@ int32_t lthn_laneset_prepare(void* set, const int32_t* ids, int32_t n, int32_t m
     if (stop && n_stop > 0) ln.stop.assign(stop, stop + n_stop);
     int32_t rc = feed_lane(ls->m, &ln, ids, n);
     if (rc) { lane_release(ls->m, id); return rc; }
+    if (params) {
+        // the lane's own sampler state; its first token is drawn now, from the prompt's logits,
+        // before another lane's forward overwrites the model's logits buffer
+        ln.samp = std::make_shared<SampleState>();
+        ln.samp->own.state = seed;
+        ln.samp->rng = &ln.samp->own;
+        ln.samp->p = *params;
+        if (params->n_suppress) ln.samp->suppress.assign(params->suppress, params->suppress + params->n_suppress);
+        std::lock_guard<std::mutex> lk(ls->m->mu);
+        int32_t tok = -1;
+        if ((rc = sample_row(ls->m, ln.logits_row, *ln.samp, ln.stop, &tok))) { lane_release(ls->m, id); return rc; }
+        ln.next_tok = tok;
+        ln.samp->generated++;
+        if (params->repeat_penalty > 1.0f) ln.samp->history.push_back(tok);
+    }
     ln.handle = ls->next_handle++;
     ls->lanes.push_back(ln);
     *lane_handle = ln.handle;
     return LTHN_OK;
+}
+
+int32_t lthn_laneset_prepare(void* set, const int32_t* ids, int32_t n, int32_t max_new, const int32_t* stop,
+                             int32_t n_stop, int32_t* lane_handle) {
+    clear_error();
+    return laneset_prepare((LaneSet*)set, ids, n, max_new, stop, n_stop, nullptr, 0, lane_handle);
+}
+
+int32_t lthn_laneset_prepare_sampled(void* set, const int32_t* ids, int32_t n, int32_t max_new, const int32_t* stop,
+                                     int32_t n_stop, const lthn_sample_params* params, uint64_t seed, int32_t* lane_handle) {
+    clear_error();
+    LTHN_REQUIRE(params != nullptr, "lthn_laneset_prepare_sampled: params is NULL");
+    return laneset_prepare((LaneSet*)set, ids, n, max_new, stop, n_stop, params, seed, lane_handle);
 }
 
 // One batched forward for every active, non-terminal lane (inference.LaneSet.Step).
@@ -1271,6 +1447,17 @@ int32_t lthn_laneset_step(void* set, int32_t* lane_handles, int32_t* tokens, int
         }
         ls->forwards++;
         if ((rc = device_status_judge((uint32_t)hp[4 * kMaxRows], m->stream))) return rc;
+        // lanes with a sampler draw their token from their row of this forward's logits
+        for (int r = 0; r < rows; r++) {
+            if (!feed[r]->samp) continue;
+            SampleState& st = *feed[r]->samp;
+            st.rng = &st.own;
+            int32_t tok = -1;
+            if ((rc = sample_row(m, r, st, feed[r]->stop, &tok))) return rc;
+            feed[r]->next_tok = tok;
+            st.generated++;
+            if (st.p.repeat_penalty > 1.0f) st.history.push_back(tok);
+        }
     }
     for (auto& ln : ls->lanes) {
         if (ln.terminal || !ln.have_next) continue;

@@ -35,6 +35,47 @@ class LoadOptions(C.Structure):
                 ("comm", C.c_void_p), ("uniform_attention", C.c_int32)]
 
 
+class SampleParams(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("min_p", C.c_float),
+                ("repeat_penalty", C.c_float), ("min_tokens_before_stop", C.c_int32), ("suppress", C.POINTER(C.c_int32)),
+                ("n_suppress", C.c_int32)]
+
+
+def sample_params(temperature=0.0, top_k=0, top_p=0.0, min_p=0.0, repeat_penalty=0.0, min_tokens_before_stop=0, suppress=()):
+    sup = np.ascontiguousarray(suppress, dtype=np.int32)
+    p = SampleParams(temperature, top_k, top_p, min_p, repeat_penalty, min_tokens_before_stop,
+                     sup.ctypes.data_as(C.POINTER(C.c_int32)) if sup.size else None, sup.size)
+    p._keep = sup   # the struct borrows the array
+    return p
+
+
+class Sampler:
+    """model.Sampler: a reproducible splitmix64 stream plus the sampling arithmetic (lthn_sampler_*)."""
+
+    def __init__(self, seed: int):
+        h = C.c_void_p()
+        check(lib().lthn_sampler_create(seed, C.byref(h)))
+        self.h = h
+
+    def draw(self) -> float:
+        return float(lib().lthn_sampler_draw(self.h))
+
+    def sample(self, logits_bf16: np.ndarray, params: SampleParams, ids=None) -> int:
+        a = np.ascontiguousarray(logits_bf16, dtype=np.uint16)
+        tok = C.c_int32()
+        if ids is None:
+            check(lib().lthn_sampler_sample(self.h, a.ctypes.data, a.size, C.byref(params), C.byref(tok)))
+        else:
+            i = np.ascontiguousarray(ids, dtype=np.int32)
+            check(lib().lthn_sampler_sample_candidates(self.h, a.ctypes.data, i.ctypes.data, a.size, C.byref(params), C.byref(tok)))
+        return int(tok.value)
+
+    def close(self):
+        if self.h:
+            lib().lthn_sampler_destroy(self.h)
+            self.h = None
+
+
 class ModelConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab",
                                          "group_size", "bits", "max_len", "max_lanes")] + \
@@ -133,6 +174,14 @@ class _Sig:
     lthn_session_pos = (i32, [vp])
     lthn_session_decode_greedy = (i32, [vp, i32, i32, vp, C.POINTER(i32)])
     lthn_session_logits = (i32, [vp, vp, i64])
+    lthn_session_decode_sampled = (i32, [vp, vp, C.POINTER(SampleParams), i32, vp, i32, vp, C.POINTER(i32)])
+    lthn_sampler_create = (i32, [u64, pvp])
+    lthn_sampler_destroy = (i32, [vp])
+    lthn_sampler_draw = (f32, [vp])
+    lthn_sampler_sample = (i32, [vp, vp, i32, C.POINTER(SampleParams), C.POINTER(i32)])
+    lthn_sampler_sample_candidates = (i32, [vp, vp, vp, i32, C.POINTER(SampleParams), C.POINTER(i32)])
+    lthn_topk_candidates = (i32, [vp, vp, i32, i32, i32, vp, vp, vp])
+    lthn_laneset_prepare_sampled = (i32, [vp, vp, i32, i32, vp, i32, C.POINTER(SampleParams), u64, C.POINTER(i32)])
     lthn_session_kv_export = (i32, [vp, i32, i32, vp, sz])
     lthn_session_kv_import = (i32, [vp, i32, i32, vp, i32])
     lthn_session_set_state = (i32, [vp, i32, i32])
@@ -405,6 +454,11 @@ def prefill_attention(q: Buf, kcache: Buf, vcache: Buf, out: Buf, rows, pos0, q_
                                        kv_heads, head_dim, scale))
 
 
+def topk_candidates(logits_f32: Buf, rows, vocab, k, scratch_bf16: Buf, out_ids: Buf, out_bf16: Buf, stream=None):
+    """k best entries of each row after bf16 rounding, at out_ids / out_bf16 + row*256 (unordered within the k)."""
+    check(lib().lthn_topk_candidates(_s(stream), logits_f32.ptr, rows, vocab, k, scratch_bf16.ptr, out_ids.ptr, out_bf16.ptr))
+
+
 def qmv_geglu(x: Buf, x_dtype, M, gate: QuantWeight, up: QuantWeight, y: Buf, y_dtype, stream=None):
     check(lib().lthn_affine_qmv_geglu(_s(stream), x.ptr, x_dtype, M, gate.packed.ptr, gate.scales.ptr, gate.biases.ptr,
                                       up.packed.ptr, up.scales.ptr, up.biases.ptr, gate.N, gate.K, y.ptr, y_dtype))
@@ -548,6 +602,14 @@ class Session:
         check(lib().lthn_session_decode_greedy(self.h, max_new, eos_id, out.ctypes.data, C.byref(n)))
         return out[:n.value].copy()
 
+    def decode_sampled(self, sampler: "Sampler", params: SampleParams, max_new, stop=()):
+        out = np.empty(max(max_new, 1), dtype=np.int32)
+        st = np.ascontiguousarray(stop, dtype=np.int32)
+        n = C.c_int32()
+        check(lib().lthn_session_decode_sampled(self.h, sampler.h, C.byref(params), max_new, st.ctypes.data if st.size else None,
+                                                st.size, out.ctypes.data, C.byref(n)))
+        return out[:n.value].copy()
+
     def logits(self):
         n = self.model.cfg.vocab // max(1, self.model.cfg.tp_size)
         out = np.empty(n, dtype=np.float32)
@@ -588,6 +650,14 @@ class LaneSet:
         lane = C.c_int32()
         check(lib().lthn_laneset_prepare(self.h, a.ctypes.data, a.size, max_new, st.ctypes.data if st.size else None,
                                          st.size, C.byref(lane)))
+        return int(lane.value)
+
+    def prepare_sampled(self, ids, params: SampleParams, seed: int, max_new=0, stop=()):
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        st = np.ascontiguousarray(stop, dtype=np.int32)
+        lane = C.c_int32()
+        check(lib().lthn_laneset_prepare_sampled(self.h, a.ctypes.data, a.size, max_new, st.ctypes.data if st.size else None,
+                                                 st.size, C.byref(params), seed, C.byref(lane)))
         return int(lane.value)
 
     def step(self):

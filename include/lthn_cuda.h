@@ -361,11 +361,53 @@ int32_t lthn_session_kv_import(void* session, int32_t layer, int32_t which, cons
 int32_t lthn_session_set_state(void* session, int32_t pos, int32_t pending_token);
 int32_t lthn_session_close(void* session);
 
+/* ---- sampling: model.Sampler / model.SampleParams (model/sample.go:52-400) ------------------
+ * The reference's sampler draws from bf16 logits with a splitmix64 stream that advances once per
+ * stochastic token: temperature (<= 0: greedy), top-k, top-p, min-p, suppressed tokens, and a
+ * repeat penalty over the tokens generated so far (sample.go:449-508; > 1 engages it).
+ * lthn_sampler_* is that sampler on host buffers, operation for operation, so a given seed gives
+ * the reference's tokens. */
+typedef struct {
+    float temperature;
+    int32_t top_k;
+    float top_p, min_p;
+    float repeat_penalty;
+    int32_t min_tokens_before_stop;   /* stop tokens are suppressed until this many tokens were generated */
+    const int32_t* suppress;          /* SuppressTokens */
+    int32_t n_suppress;
+} lthn_sample_params;
+int32_t lthn_sampler_create(uint64_t seed, void** sampler);           /* model.NewSampler */
+int32_t lthn_sampler_destroy(void* sampler);
+float lthn_sampler_draw(void* sampler);                               /* Sampler.Draw */
+/* Sampler.Sample: logits = vocab bf16 values in host memory. */
+int32_t lthn_sampler_sample(void* sampler, const uint16_t* logits_bf16, int32_t vocab, const lthn_sample_params* params, int32_t* token);
+/* Sampler.SampleCandidates: n candidate values with the token ids they belong to. */
+int32_t lthn_sampler_sample_candidates(void* sampler, const uint16_t* logits_bf16, const int32_t* ids, int32_t n,
+                                       const lthn_sample_params* params, int32_t* token);
+/* Device half: the k best entries of each f32 logit row after rounding to bf16, by (value
+ * descending, index ascending) - the order of selectTopKDesc (sample.go:339-366) - as k ids and
+ * bf16 values per row at out_ids / out_bf16 + row*256, unordered within the k. k <= min(256, vocab).
+ * scratch_bf16: rows*vocab bf16 values of device memory. Replaces the reference's device top-k
+ * (engine/hip/kernels/sampling/topk.hipinc). */
+int32_t lthn_topk_candidates(void* stream, const float* logits, int32_t rows, int32_t vocab, int32_t k, uint16_t* scratch_bf16,
+                             int32_t* out_ids, uint16_t* out_bf16);
+/* GenerateSampledFromCacheEach (engine/session.go:51, loop of model/token.go:263-305): up to max_new
+ * tokens drawn with `sampler` from the session's logits; the repeat penalty sees the tokens of this
+ * call; a token in `stop` ends the call after it is emitted (and is suppressed while fewer than
+ * min_tokens_before_stop tokens were generated). With 1 < top_k <= 256 only the top-k window leaves
+ * the device each step; other settings read the bf16 row back. The last token is not fed. */
+int32_t lthn_session_decode_sampled(void* session, void* sampler, const lthn_sample_params* params, int32_t max_new,
+                                    const int32_t* stop, int32_t n_stop, int32_t* out_ids, int32_t* n_out);
+
 /* inference.LaneSet (batch_step.go:97-119) behind engine.LaneSetOpener
  * (engine/batch_step.go:21-23). Single host thread per set. */
 int32_t lthn_laneset_open(void* model, int32_t max_lanes, void** set);
 int32_t lthn_laneset_prepare(void* set, const int32_t* ids, int32_t n, int32_t max_new, const int32_t* stop,
                              int32_t n_stop, int32_t* lane_handle);           /* lane ids start at 1 */
+/* LaneSpec.Sampler / SampleSeed (batch_step.go:55-71): a lane with its own sampler state, token-identical
+ * to lthn_session_decode_sampled at the same seed and parameters. */
+int32_t lthn_laneset_prepare_sampled(void* set, const int32_t* ids, int32_t n, int32_t max_new, const int32_t* stop,
+                                     int32_t n_stop, const lthn_sample_params* params, uint64_t seed, int32_t* lane_handle);
 int32_t lthn_laneset_step(void* set, int32_t* lane_handles, int32_t* tokens, int32_t* flags, int32_t* n);
 int32_t lthn_laneset_retire(void* set, int32_t lane_handle);
 int32_t lthn_laneset_active(void* set);

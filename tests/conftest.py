@@ -45,3 +45,10 @@ def oracle():
     o.build()
     o.lib()
     return o
+
+
+@pytest.fixture(scope="session")
+def lthn():
+    import lthn as m
+    m.lib()
+    return m

@@ -72,8 +72,15 @@ def test_load_rejects_what_the_engine_does_not_serve(oracle, tmp_path):
     s.close(); m.close()
     # geometry that contradicts the quantization block
     cfgj = json.load(open(os.path.join(d, "config.json")))
+    cfgj["quantization"]["language_model.model.layers.0.mlp.gate_proj"] = {"group_size": 32, "bits": 4}
+    json.dump(cfgj, open(os.path.join(d, "config.json"), "w"))
+    with pytest.raises(lthn.LthnError) as e:
+        lthn.Model.load_dir(d, max_len=32, uniform_attention=True)
+    assert "geometry" in str(e.value) and "gate_proj" in str(e.value)
+    # a checkpoint quantised at another group size altogether
+    del cfgj["quantization"]["language_model.model.layers.0.mlp.gate_proj"]
     cfgj["quantization"]["group_size"] = 32
     json.dump(cfgj, open(os.path.join(d, "config.json"), "w"))
     with pytest.raises(lthn.LthnError) as e:
         lthn.Model.load_dir(d, max_len=32, uniform_attention=True)
-    assert "geometry" in str(e.value)
+    assert "group-64" in str(e.value)
