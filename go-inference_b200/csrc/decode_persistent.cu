@@ -1,0 +1,874 @@
+// decode_persistent.cu — every decoder block of one token in ONE kernel (batch 1, one GPU), sm_100a.
+//
+// Why. A batch-1 decode step of a Gemma-style block is five small kernels' worth of work
+// (q|k|v matvec, head norms + RoPE + attention, o matvec, gate|up GeGLU matvec, down matvec), each
+// of which moves only a few MB of 4-bit weights. Launched one by one (even inside a CUDA graph,
+// even with programmatic dependent launch) every kernel pays its own ramp: the weight stream
+// stops at each boundary and restarts from a cold pipeline. Here one cooperative grid of one CTA
+// per SM walks all blocks; phases are separated by grid-wide barriers, and the weight stream is
+// decoupled from them:
+//
+//  * warp 8 of every CTA is a producer. It knows the CTA's whole work list for the token (weights
+//    do not depend on activations) and keeps a ring of shared-memory slots full with 1-D bulk
+//    (TMA) copies of 16-row x <=44-group weight pieces plus cp.async copies of their scales and
+//    biases, running ahead of the consumers across phase boundaries and grid barriers. While the
+//    grid is synchronising and the next phase's activations are being prepared, the weights of
+//    that phase are already landing.
+//  * warps 0..7 are consumers. Per phase they turn the activation vector into the three int8
+//    digit planes of the integer tensor-core matvec (x = sx*(d0 + d1/128 + d2/16384), exact
+//    integer dot products, f32 per-group scaling; the arithmetic of qmv_i8_kernel.cuh) in
+//    shared memory, then multiply ring slots with mma.sync.m16n8k32.u8.s8 and add the eight
+//    warps' partial sums in a fixed order. The residual RMSNorm pairs are part of the activation
+//    preparation (every CTA computes them redundantly from L2; CTA 0 stores the residual stream).
+//  * attention runs as two 128-thread groups per CTA over (kv head, key chunk) items: the head
+//    norms, RoPE and the KV append of the new token are folded into the items, and the last item
+//    of a kv head to finish merges that head's chunk partials (a counter per kv head), so the
+//    phase needs no barrier of its own.
+//
+// Every wait (ring slot, grid barrier) is bounded in time. A wait that runs out sets a bit in the
+// device status word and an abort flag; from then on every wait returns at once, the CTAs fall
+// through the remaining control flow without touching data, the producer waits (bounded) for its
+// copies in flight, and the kernel returns by itself. The host reports LTHN_ERR_DEVICE_WAIT.
+//
+// The reference decodes a token through per-op kernels chained by its engine
+// (engine/metal/decode_step.go, engine/hip/hip_gemma4_q4_forward.go); this kernel replaces that
+// chain for one row on one GPU and leaves the same buffers behind (the last down-projection
+// output and the residual stream), so the lm_head with its fused final norm follows unchanged.
+#include "common.cuh"
+#include "decoder_kernels.hpp"
+
+#include <algorithm>
+#include <mutex>
+
+namespace lthn {
+
+constexpr int PK_CW = 8;                  // consumer warps
+constexpr int PK_CT = PK_CW * 32;         // consumer threads
+constexpr int PK_THREADS = PK_CT + 32;    // plus the producer warp
+constexpr int PK_RS_MAX = 1440;           // bytes between weight rows of a slot (44 groups * 32 B + pad)
+constexpr int PK_SB_OFF = 16 * PK_RS_MAX; // scales of a slot
+constexpr int PK_SB_HALF = 16 * PERSIST_SLOT_G * 2;             // biases follow the scales
+constexpr int PK_SLOT_BYTES = PK_SB_OFF + 2 * PK_SB_HALF;       // 25856
+constexpr int PK_MAX_SLOTS = 8;
+constexpr int PK_PART_OFF = 1024;         // [2][PK_CW][16] f32 partial sums
+constexpr int PK_DIG_OFF = 2048;          // activation digits (per phase), attention scratch
+constexpr uint64_t PK_WAIT_NS = 50ull * 1000 * 1000;
+
+// status bits of this kernel (device status word)
+constexpr uint32_t PK_ST_SLOT_EMPTY = 1u << 13, PK_ST_SLOT_FULL = 1u << 14, PK_ST_GRID = 1u << 15;
+
+// shared-memory row stride of a slot holding ks groups per row: 8 words mod 32, so the 8-byte
+// fragment loads of a half-warp (8 rows x 4 pieces) fall into 32 different banks
+__host__ __device__ inline int pk_row_stride(int ks) { return ks * 32 + ((32 - ks * 32) & 127); }
+
+__device__ __forceinline__ void pk_mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void pk_mma_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void pk_cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+// one (pre-counted) arrival on the mbarrier once every cp.async this thread has issued has landed
+__device__ __forceinline__ void pk_cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void pk_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint64_t pk_now() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void pk_bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(PK_CT) : "memory"); }
+__device__ __forceinline__ void pk_bar_group(int g) { asm volatile("bar.sync %0, 128;" ::"r"(2 + g) : "memory"); }
+__device__ __forceinline__ float pk_gelu(float x) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    return 0.5f * x * (1.0f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+
+// Bounded mbarrier wait. `abort` is the CTA's abort word in shared memory: once set, nothing waits.
+__device__ __forceinline__ bool pk_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort, const PersistArgs& a, uint32_t bit) {
+    if (*abort) return false;
+    uint32_t done = 0;
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (done) return true;
+        if ((it & 63) == 63) {
+            if (*abort) return false;
+            const uint64_t now = pk_now();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > PK_WAIT_NS) break;
+        }
+    }
+    *abort = 1u;
+    atomicExch(a.sync + 2, 1u);
+    atomicOr(a.status, bit);
+    return false;
+}
+
+// Grid-wide barrier of the consumer warps of every CTA (the producers never join: they touch only
+// weights). sync[0] counts arrivals and grows for the life of the launch; sync[2] is the abort flag.
+__device__ __forceinline__ bool pk_grid_barrier(const PersistArgs& a, uint32_t& epoch, volatile uint32_t* abort, volatile uint32_t* okflag) {
+    pk_bar_consumers();
+    if (threadIdx.x == 0) {
+        uint32_t ok = 0;
+        if (!*abort) {
+            __threadfence();
+            atomicAdd(a.sync, 1u);
+            const uint32_t target = (epoch + 1u) * gridDim.x;
+            const uint64_t t0 = pk_now();
+            for (uint32_t it = 0;; ++it) {
+                uint32_t v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.sync) : "memory");
+                if (v >= target) { ok = 1; break; }
+                if ((it & 15) == 15) {
+                    uint32_t ab;
+                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ab) : "l"(a.sync + 2) : "memory");
+                    if (ab) break;
+                    if (pk_now() - t0 > PK_WAIT_NS) { atomicOr(a.status, PK_ST_GRID); break; }
+                }
+            }
+            if (!ok) { *abort = 1u; atomicExch(a.sync + 2, 1u); }
+            __threadfence();
+        }
+        *okflag = ok;
+    }
+    epoch++;
+    pk_bar_consumers();
+    return *okflag != 0;
+}
+
+// f64 sum over the consumer threads (sh: 8 doubles)
+__device__ __forceinline__ double pk_block_sum(double v, double* sh, int lane, int warp) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    pk_bar_consumers();
+    if (lane == 0) sh[warp] = v;
+    pk_bar_consumers();
+    double t = 0.0;
+#pragma unroll
+    for (int w = 0; w < PK_CW; w++) t += sh[w];
+    return t;
+}
+
+// Digit planes of U groups at once (independent dependency chains interleave). x[u][q]: elements
+// 2*lane+q of group u. dg: 192 bytes per group - three planes of 64 digit bytes in MMA fragment
+// order; gc: (sx, sx-weighted sum of the group's activations) per group.
+template <int U>
+__device__ __forceinline__ void pk_digitise(const float (&x)[U][2], const bool (&live)[U], int lane, unsigned char* const (&dg)[U], float2* const (&gc)[U]) {
+    float amax[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) amax[u] = fmaxf(fabsf(x[u][0]), fabsf(x[u][1]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int u = 0; u < U; u++) amax[u] = fmaxf(amax[u], __shfl_xor_sync(0xffffffffu, amax[u], o));
+    int isum[U];
+    float sxv[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const float sx = amax[u] * (1.0f / 127.0f);
+        const float inv = amax[u] > 0.f ? 127.0f / amax[u] : 0.f;
+        const float sx1 = sx * (1.0f / 128.0f);
+        sxv[u] = sx;
+        isum[u] = 0;
+#pragma unroll
+        for (int q = 0; q < 2; q++) {
+            const float x0 = x[u][q];
+            const float d0 = rintf(x0 * inv);
+            const float r1 = fmaf(-d0, sx, x0);
+            const float d1 = rintf(r1 * inv * 128.0f);
+            const float r2 = fmaf(-d1, sx1, r1);
+            const float d2 = rintf(r2 * inv * 16384.0f);
+            const int i0 = (int)d0, i1 = (int)d1, i2 = (int)d2;
+            isum[u] += i0 * 16384 + i1 * 128 + i2;
+            // element e of the group: word e>>3 of the row piece, nibble e&7. Thread t of a fragment
+            // owns words 2t (first MMA) and 2t+1 (second); even nibbles feed the low k half, odd
+            // nibbles the high k half.
+            const int e = 2 * lane + q;
+            const int off = ((((e >> 3) & 1) * 4 + (e >> 4)) * 2 + (e & 1)) * 4 + ((e & 7) >> 1);
+            if (live[u]) {
+                dg[u][off] = (unsigned char)(i0 & 0xff);
+                dg[u][64 + off] = (unsigned char)(i1 & 0xff);
+                dg[u][128 + off] = (unsigned char)(i2 & 0xff);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int u = 0; u < U; u++) isum[u] += __shfl_xor_sync(0xffffffffu, isum[u], o);
+#pragma unroll
+    for (int u = 0; u < U; u++)
+        if (live[u] && lane == 0) *gc[u] = make_float2(sxv[u], (float)isum[u] * (sxv[u] * (1.0f / 16384.0f)));
+}
+
+struct PkSmem {
+    uint64_t* full;
+    uint64_t* empty;
+    double* nsum;
+    volatile uint32_t* abort;
+    volatile uint32_t* okflag;
+    float* part;
+    unsigned char* dig;
+    unsigned char* ring;
+};
+
+// Activation vector of a matvec phase -> digit planes. src: G*64 f32 values; `scale_w` (optional):
+// per-element weights applied after dividing by rms (the trailing RMSNorm of a residual pair).
+__device__ __forceinline__ void pk_prepare_digits(const PkSmem& sm, const float* src, bool src_smem, int G, float rms, const float* w_next, int lane,
+                                                  int warp) {
+    constexpr int U = 4;
+    float2* gcb = (float2*)(sm.dig + (size_t)G * 192);
+    for (int g0 = warp; g0 < G; g0 += PK_CW * U) {
+        float x[U][2];
+        bool live[U];
+        unsigned char* dg[U];
+        float2* gc[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int g = g0 + u * PK_CW;
+            live[u] = g < G;
+            const int gg = live[u] ? g : g0;
+            const int e = gg * 64 + 2 * lane;
+            float2 v = src_smem ? *(const float2*)(src + e) : __ldcg((const float2*)(src + e));
+            if (w_next) {
+                const float2 wn = __ldg((const float2*)(w_next + e));
+                v.x = __fmul_rn(__fdiv_rn(v.x, rms), wn.x);
+                v.y = __fmul_rn(__fdiv_rn(v.y, rms), wn.y);
+            }
+            x[u][0] = v.x; x[u][1] = v.y;
+            dg[u] = sm.dig + (size_t)gg * 192;
+            gc[u] = gcb + gg;
+        }
+        pk_digitise<U>(x, live, lane, dg, gc);
+    }
+    pk_bar_consumers();
+}
+
+// Residual RMSNorm pair in front of a matvec (every CTA computes it; CTA 0 stores the stream):
+//   h_out = h_in + rmsnorm(avec) * w_post   (skipped when avec == nullptr: h_out is h_in)
+//   x     = rmsnorm(h_out) * w_next  -> digits
+__device__ __forceinline__ void pk_norm_prologue(const PkSmem& sm, const PersistArgs& a, const float* avec, const float* h_in, float* h_out,
+                                                 const float* w_post, const float* w_next, int lane, int warp) {
+    const int H = a.H, G = H >> 6, tid = threadIdx.x;
+    float* xs = (float*)(sm.dig + (((size_t)G * 200 + 15) & ~(size_t)15));
+    double ss2 = 0.0;
+    if (avec) {
+        double ss = 0.0;
+#pragma unroll 4
+        for (int e = 2 * tid; e < H; e += 2 * PK_CT) {
+            const float2 v = __ldcg((const float2*)(avec + e));
+            ss += (double)__fmul_rn(v.x, v.x);
+            ss += (double)__fmul_rn(v.y, v.y);
+        }
+        ss = pk_block_sum(ss, sm.nsum, lane, warp);
+        const float rms = (float)sqrt(ss / (double)H + (double)a.eps);
+#pragma unroll 4
+        for (int e = 2 * tid; e < H; e += 2 * PK_CT) {
+            const float2 v = __ldcg((const float2*)(avec + e));
+            const float2 h = __ldcg((const float2*)(h_in + e));
+            const float2 wp = __ldg((const float2*)(w_post + e));
+            float2 o;
+            o.x = __fadd_rn(h.x, __fmul_rn(__fdiv_rn(v.x, rms), wp.x));
+            o.y = __fadd_rn(h.y, __fmul_rn(__fdiv_rn(v.y, rms), wp.y));
+            *(float2*)(xs + e) = o;
+            if (blockIdx.x == 0) *(float2*)(h_out + e) = o;
+            ss2 += (double)__fmul_rn(o.x, o.x);
+            ss2 += (double)__fmul_rn(o.y, o.y);
+        }
+    } else {
+#pragma unroll 4
+        for (int e = 2 * tid; e < H; e += 2 * PK_CT) {
+            const float2 h = __ldcg((const float2*)(h_in + e));
+            *(float2*)(xs + e) = h;
+            ss2 += (double)__fmul_rn(h.x, h.x);
+            ss2 += (double)__fmul_rn(h.y, h.y);
+        }
+    }
+    ss2 = pk_block_sum(ss2, sm.nsum, lane, warp);  // its barriers also publish xs
+    const float rms2 = (float)sqrt(ss2 / (double)H + (double)a.eps);
+    pk_prepare_digits(sm, xs, true, G, rms2, w_next, lane, warp);
+}
+
+// One matvec phase of the consumers: this CTA's row blocks (b = cta, cta+grid, ...), each of
+// ph.nsl ring slots. FUSE: rows 0-7 of a slot are gate rows, rows 8-15 the same rows of up;
+// out[row] = gelu_tanh(gate) * up.
+__device__ __forceinline__ void pk_matvec(const PkSmem& sm, const PersistArgs& a, const PersistPhase& ph, bool fuse, float* out, int nslots,
+                                          uint32_t& it, uint32_t& rbi, int lane, int warp) {
+    const int gq = lane >> 2, t = lane & 3;
+    const float2* gcb = (const float2*)(sm.dig + (size_t)ph.G * 192);
+    constexpr uint32_t NIB = 0x0F0F0F0Fu;
+    const float planew = (t & 1) ? (1.0f / 2097152.0f) : (1.0f / 128.0f);
+    const bool colrow = t < 2;  // columns of activation row 0 (the only row)
+    for (int b = blockIdx.x; b < ph.nblk; b += gridDim.x) {
+        float acc0 = 0.f, acc1 = 0.f, accb = 0.f;
+        for (int sl = 0; sl < ph.nsl; sl++, it++) {
+            const int slot = it % nslots;
+            const bool ok = __all_sync(0xffffffffu, pk_wait(&sm.full[slot], (it / nslots) & 1, sm.abort, a, PK_ST_SLOT_FULL));
+            const int g0 = sl * ph.KS, ks = min(ph.KS, ph.G - g0), RS = pk_row_stride(ks);
+            const unsigned char* sb = sm.ring + (size_t)slot * PK_SLOT_BYTES;
+            if (ok) {
+                const uint16_t* sp = (const uint16_t*)(sb + PK_SB_OFF) + gq * ks;
+                const uint16_t* bp = (const uint16_t*)(sb + PK_SB_OFF + PK_SB_HALF) + (gq + 8 * (t & 1)) * ks;
+                const unsigned char* rowp = sb + (size_t)gq * RS + t * 8;
+                // two groups per trip (g and g + 8): two independent load -> unpack -> MMA chains per warp
+                for (int g = warp; g < ks; g += 2 * PK_CW) {
+                    const int gB = g + PK_CW;
+                    const bool hasB = gB < ks;
+                    const int gb = hasB ? gB : g;
+                    const unsigned char* dA = sm.dig + (size_t)(g0 + g) * 192;
+                    const unsigned char* dB = sm.dig + (size_t)(g0 + gb) * 192;
+                    uint2 bA0 = make_uint2(0u, 0u), bA1 = bA0, bB0 = bA0, bB1 = bA0;
+                    if (gq < 3) {
+                        bA0 = *(const uint2*)(dA + gq * 64 + t * 8);
+                        bA1 = *(const uint2*)(dA + gq * 64 + (4 + t) * 8);
+                        bB0 = *(const uint2*)(dB + gq * 64 + t * 8);
+                        bB1 = *(const uint2*)(dB + gq * 64 + (4 + t) * 8);
+                    }
+                    const uint2 waA = *(const uint2*)(rowp + g * 32), wbA = *(const uint2*)(rowp + (size_t)8 * RS + g * 32);
+                    const uint2 waB = *(const uint2*)(rowp + gb * 32), wbB = *(const uint2*)(rowp + (size_t)8 * RS + gb * 32);
+                    const float2 gcA = gcb[g0 + g], gcB = gcb[g0 + gb];
+                    int cA[4], cB[4];
+                    pk_mma_z(cA, waA.x & NIB, wbA.x & NIB, (waA.x >> 4) & NIB, (wbA.x >> 4) & NIB, bA0.x, bA0.y);
+                    pk_mma_z(cB, waB.x & NIB, wbB.x & NIB, (waB.x >> 4) & NIB, (wbB.x >> 4) & NIB, bB0.x, bB0.y);
+                    pk_mma(cA, waA.y & NIB, wbA.y & NIB, (waA.y >> 4) & NIB, (wbA.y >> 4) & NIB, bA1.x, bA1.y);
+                    pk_mma(cB, waB.y & NIB, wbB.y & NIB, (waB.y >> 4) & NIB, (wbB.y >> 4) & NIB, bB1.x, bB1.y);
+                    {
+                        const float cg = colrow ? gcA.x * planew : 0.f;
+                        const float f0 = (float)(cA[0] * 128 + cA[1]) * cg, f1 = (float)(cA[2] * 128 + cA[3]) * cg;
+                        acc0 = fmaf(bf16_bits_to_f32(sp[g]), f0, acc0);
+                        acc1 = fmaf(bf16_bits_to_f32(sp[8 * ks + g]), f1, acc1);
+                        accb = fmaf(bf16_bits_to_f32(bp[g]), colrow ? gcA.y : 0.f, accb);
+                    }
+                    if (hasB) {
+                        const float cg = colrow ? gcB.x * planew : 0.f;
+                        const float f0 = (float)(cB[0] * 128 + cB[1]) * cg, f1 = (float)(cB[2] * 128 + cB[3]) * cg;
+                        acc0 = fmaf(bf16_bits_to_f32(sp[gB]), f0, acc0);
+                        acc1 = fmaf(bf16_bits_to_f32(sp[8 * ks + gB]), f1, acc1);
+                        accb = fmaf(bf16_bits_to_f32(bp[gB]), colrow ? gcB.y : 0.f, accb);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) pk_arrive(&sm.empty[slot]);  // this warp is done with the slot
+        }
+        // lanes t and t^1 hold the two plane halves of the same outputs; even t finishes row gq,
+        // odd t row gq+8 (each also carries that row's bias term)
+        const bool odd = t & 1;
+        const float send = odd ? acc0 : acc1;
+        const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+        const float res = (odd ? acc1 : acc0) + recv + accb;
+        float* pw = sm.part + ((size_t)(rbi & 1) * PK_CW + warp) * 16;
+        if (colrow) pw[gq + 8 * (t & 1)] = res;
+        pk_bar_consumers();
+        if (warp == (int)(rbi % PK_CW)) {
+            const float* p0 = sm.part + (size_t)(rbi & 1) * PK_CW * 16;
+            if (!fuse) {
+                if (lane < 16) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int w = 0; w < PK_CW; w++) v += p0[w * 16 + lane];
+                    out[(size_t)b * 16 + lane] = v;
+                }
+            } else if (lane < 8) {
+                float g = 0.f, u = 0.f;
+#pragma unroll
+                for (int w = 0; w < PK_CW; w++) { g += p0[w * 16 + lane]; u += p0[w * 16 + 8 + lane]; }
+                out[(size_t)b * 8 + lane] = pk_gelu(g) * u;
+            }
+        }
+        rbi++;
+    }
+}
+
+// ---- attention: one (kv head, key chunk) item on a 128-thread group ----------------------------
+// The arithmetic of sdpa_decode_kernel / sdpa_merge_kernel (decoder_kernels.cu) with the per-head
+// RMSNorm + RoPE of q (and of the new key) and the KV append folded in.
+template <int D, int GQ>
+struct alignas(16) PkAttSmem {
+    float red[4][GQ][D + 2];
+    float q[GQ][D];
+    float smax[GQ][4], ssum[GQ][4];
+    double sh[4][GQ + 1];
+    uint32_t last;
+};
+
+template <int D, int GQ>
+__device__ __forceinline__ void pk_attention_item(const PersistArgs& a, const PersistLayer& L, PkAttSmem<D, GQ>& s, int grp, int kvh, int chunk,
+                                                  int used, int pos, int64_t lane_off) {
+    constexpr int E = D / 8, V8 = E / 8, NIT = 512 / D > 0 ? 512 / D : 1, CH = 16 * NIT, half = D / 2;
+    const int gt = threadIdx.x & 127, lane = gt & 31, warp = gt >> 5;
+    const int l8 = lane & 7, pg = warp * 4 + (lane >> 3);
+    const int ctx = pos + 1, p0 = chunk * CH, KR = a.Hkv * D, qh0 = kvh * GQ;
+    uint16_t* kbase = L.kcache + lane_off + (int64_t)kvh * D;
+    uint16_t* vbase = L.vcache + lane_off + (int64_t)kvh * D;
+    const float2 cs = gt < half ? __ldg(a.rope + (int64_t)min(pos, a.max_len - 1) * half + gt) : make_float2(1.f, 0.f);
+    const bool has_new = pos >= p0 && pos < p0 + CH;  // this chunk holds the token being decoded: append its key and value first
+    // sums of squares of the GQ query heads (and the new key head)
+    float x0[GQ + 1], x1[GQ + 1];
+    double ss[GQ + 1];
+#pragma unroll
+    for (int h = 0; h <= GQ; h++) {
+        x0[h] = 0.f; x1[h] = 0.f; ss[h] = 0.0;
+        if (h == GQ && !has_new) continue;
+        const float* src = a.qkv + (int64_t)(h < GQ ? qh0 + h : a.Hq + kvh) * D;
+        if (gt < half) {
+            x0[h] = __ldcg(src + gt);
+            x1[h] = __ldcg(src + gt + half);
+            ss[h] = (double)__fmul_rn(x0[h], x0[h]) + (double)__fmul_rn(x1[h], x1[h]);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h <= GQ; h++)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], o);
+    pk_bar_group(grp);  // the previous item's readers of this scratch are done
+    if (lane == 0)
+#pragma unroll
+        for (int h = 0; h <= GQ; h++) s.sh[warp][h] = ss[h];
+    pk_bar_group(grp);
+#pragma unroll
+    for (int h = 0; h <= GQ; h++) {
+        if (h == GQ && !has_new) continue;
+        const double tsum = s.sh[0][h] + s.sh[1][h] + s.sh[2][h] + s.sh[3][h];
+        const float rms = (float)sqrt(tsum / (double)D + (double)a.eps);
+        if (gt < half) {
+            const float* w = h < GQ ? L.n_q : L.n_k;
+            const float n0 = __fmul_rn(__fdiv_rn(x0[h], rms), __ldg(w + gt));
+            const float n1 = __fmul_rn(__fdiv_rn(x1[h], rms), __ldg(w + gt + half));
+            const float r0 = __fsub_rn(__fmul_rn(n0, cs.x), __fmul_rn(n1, cs.y));
+            const float r1 = __fadd_rn(__fmul_rn(n0, cs.y), __fmul_rn(n1, cs.x));
+            if (h < GQ) {
+                s.q[h][gt] = r0 * a.attn_scale;
+                s.q[h][gt + half] = r1 * a.attn_scale;
+            } else {
+                uint16_t* dst = kbase + (int64_t)pos * KR;
+                dst[gt] = f32_to_bf16_bits(r0);
+                dst[gt + half] = f32_to_bf16_bits(r1);
+            }
+        }
+    }
+    if (has_new && gt < half) {
+        const float* src = a.qkv + (int64_t)(a.Hq + a.Hkv + kvh) * D;
+        uint16_t* dst = vbase + (int64_t)pos * KR;
+        dst[gt] = f32_to_bf16_bits(__ldcg(src + gt));
+        dst[gt + half] = f32_to_bf16_bits(__ldcg(src + gt + half));
+    }
+    pk_bar_group(grp);  // q in shared memory; the appended row visible to the group's loads below
+
+    // ---- every load of the chunk goes out first -------------------------------------------------
+    uint4 kreg[NIT][V8], vreg[NIT][V8];
+    bool valid[NIT];
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
+        const int p = p0 + pg + 16 * i;
+        valid[i] = p < ctx;
+        const int64_t off = (int64_t)(valid[i] ? p : p0) * KR;
+#pragma unroll
+        for (int v = 0; v < V8; v++) {
+            kreg[i][v] = __ldcg((const uint4*)(kbase + off + (v * 8 + l8) * 8));
+            vreg[i][v] = __ldcg((const uint4*)(vbase + off + (v * 8 + l8) * 8));
+        }
+    }
+    float q[GQ][E];
+#pragma unroll
+    for (int h = 0; h < GQ; h++)
+#pragma unroll
+        for (int v = 0; v < V8; v++) {
+            const float4 qa = *(const float4*)(&s.q[h][(v * 8 + l8) * 8]);
+            const float4 qb = *(const float4*)(&s.q[h][(v * 8 + l8) * 8 + 4]);
+            q[h][v * 8 + 0] = qa.x; q[h][v * 8 + 1] = qa.y; q[h][v * 8 + 2] = qa.z; q[h][v * 8 + 3] = qa.w;
+            q[h][v * 8 + 4] = qb.x; q[h][v * 8 + 5] = qb.y; q[h][v * 8 + 6] = qb.z; q[h][v * 8 + 7] = qb.w;
+        }
+    float sc[NIT][GQ], mx[GQ];
+#pragma unroll
+    for (int h = 0; h < GQ; h++) mx[h] = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
+        float dot[GQ];
+#pragma unroll
+        for (int h = 0; h < GQ; h++) dot[h] = 0.f;
+#pragma unroll
+        for (int v = 0; v < V8; v++) {
+            const uint32_t kw[4] = {kreg[i][v].x, kreg[i][v].y, kreg[i][v].z, kreg[i][v].w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float k0 = __uint_as_float(kw[e] << 16), k1 = __uint_as_float(kw[e] & 0xffff0000u);
+#pragma unroll
+                for (int h = 0; h < GQ; h++) dot[h] = fmaf(q[h][v * 8 + 2 * e + 1], k1, fmaf(q[h][v * 8 + 2 * e], k0, dot[h]));
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < GQ; h++) {
+            float d = dot[h];
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            sc[i][h] = valid[i] ? d : -INFINITY;
+            mx[h] = fmaxf(mx[h], sc[i][h]);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < GQ; h++) {
+        const float m = warp_max(mx[h]);
+        if (lane == 0) s.smax[h][warp] = m;
+    }
+    pk_bar_group(grp);
+    float cmax[GQ];
+#pragma unroll
+    for (int h = 0; h < GQ; h++) cmax[h] = fmaxf(fmaxf(s.smax[h][0], s.smax[h][1]), fmaxf(s.smax[h][2], s.smax[h][3]));
+    float acc[GQ][E], lsum[GQ];
+#pragma unroll
+    for (int h = 0; h < GQ; h++) {
+        lsum[h] = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; e++) acc[h][e] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
+        float w[GQ];
+#pragma unroll
+        for (int h = 0; h < GQ; h++) { w[h] = valid[i] ? __expf(sc[i][h] - cmax[h]) : 0.f; lsum[h] += w[h]; }
+#pragma unroll
+        for (int v = 0; v < V8; v++) {
+            const uint32_t vw[4] = {vreg[i][v].x, vreg[i][v].y, vreg[i][v].z, vreg[i][v].w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float v0 = __uint_as_float(vw[e] << 16), v1 = __uint_as_float(vw[e] & 0xffff0000u);
+#pragma unroll
+                for (int h = 0; h < GQ; h++) {
+                    acc[h][v * 8 + 2 * e] = fmaf(w[h], v0, acc[h][v * 8 + 2 * e]);
+                    acc[h][v * 8 + 2 * e + 1] = fmaf(w[h], v1, acc[h][v * 8 + 2 * e + 1]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < GQ; h++) {
+#pragma unroll
+        for (int e = 0; e < E; e++) {
+            float v = acc[h][e];
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            acc[h][e] = v;
+        }
+        float l = (l8 == 0) ? lsum[h] : 0.f;
+        l = warp_sum(l);
+        if (lane == 0) s.ssum[h][warp] = l;
+        if (lane < 8) {
+#pragma unroll
+            for (int v = 0; v < V8; v++)
+#pragma unroll
+                for (int e = 0; e < 8; e++) s.red[warp][h][(v * 8 + l8) * 8 + e] = acc[h][v * 8 + e];
+        }
+    }
+    pk_bar_group(grp);
+    for (int idx = gt; idx < GQ * D; idx += 128) {
+        const int h = idx / D, d = idx - h * D;
+        const float v = s.red[0][h][d] + s.red[1][h][d] + s.red[2][h][d] + s.red[3][h][d];
+        const float l = s.ssum[h][0] + s.ssum[h][1] + s.ssum[h][2] + s.ssum[h][3];
+        const int qh = qh0 + h;
+        if (used == 1) {
+            a.att[(int64_t)qh * D + d] = v / l;
+        } else {
+            float* pa = a.part + ((int64_t)qh * a.nchunks_cap + chunk) * (D + 2);
+            pa[d] = v;
+            if (d == 0) { pa[D] = cmax[h]; pa[D + 1] = l; }
+        }
+    }
+    if (used == 1) return;
+    // ---- the last item of this kv head to finish merges the head's chunk partials ----------------
+    __threadfence();
+    pk_bar_group(grp);
+    if (gt == 0) {
+        const uint32_t n = atomicAdd(a.sync + 16 + kvh, 1u);
+        s.last = (n == (uint32_t)used - 1u) ? 1u : 0u;
+        if (s.last) { a.sync[16 + kvh] = 0u; __threadfence(); }
+    }
+    pk_bar_group(grp);
+    if (!s.last) return;
+    constexpr int DL = D / 32, MB = 8;
+    for (int h = 0; h < GQ; h++) {
+        const int qh = qh0 + h;
+        const float* pa = a.part + (int64_t)qh * a.nchunks_cap * (D + 2);
+        float m = -INFINITY, l = 0.f, macc[DL];
+#pragma unroll
+        for (int i = 0; i < DL; i++) macc[i] = 0.f;
+        for (int c0 = warp; c0 < used; c0 += 4 * MB) {
+            float cm[MB], cl[MB];
+            float2 cv[MB][DL / 2];
+#pragma unroll
+            for (int b = 0; b < MB; b++) {
+                const int c = c0 + 4 * b;
+                const bool live = c < used;
+                const float* p = pa + (int64_t)(live ? c : c0) * (D + 2);
+                cm[b] = live ? __ldcg(p + D) : -INFINITY;
+                cl[b] = live ? __ldcg(p + D + 1) : 0.f;
+                const float2* src = (const float2*)(p + lane * DL);
+#pragma unroll
+                for (int i = 0; i < DL / 2; i++) cv[b][i] = __ldcg(src + i);
+            }
+            float bm = m;
+#pragma unroll
+            for (int b = 0; b < MB; b++) bm = fmaxf(bm, cm[b]);
+            if (bm == -INFINITY) continue;
+            const float rescale = __expf(m - bm);
+            l *= rescale;
+#pragma unroll
+            for (int i = 0; i < DL; i++) macc[i] *= rescale;
+#pragma unroll
+            for (int b = 0; b < MB; b++) {
+                const float w = __expf(cm[b] - bm);
+                l = fmaf(cl[b], w, l);
+#pragma unroll
+                for (int i = 0; i < DL / 2; i++) {
+                    macc[2 * i] = fmaf(cv[b][i].x, w, macc[2 * i]);
+                    macc[2 * i + 1] = fmaf(cv[b][i].y, w, macc[2 * i + 1]);
+                }
+            }
+            m = bm;
+        }
+        pk_bar_group(grp);  // the previous head's readers of this scratch are done
+        if (lane == 0) { s.smax[0][warp] = m; s.ssum[0][warp] = l; }
+#pragma unroll
+        for (int i = 0; i < DL; i++) s.red[warp][0][lane * DL + i] = macc[i];
+        pk_bar_group(grp);
+        const float gm = fmaxf(fmaxf(s.smax[0][0], s.smax[0][1]), fmaxf(s.smax[0][2], s.smax[0][3]));
+        float w4[4], denom = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) { w4[w] = __expf(s.smax[0][w] - gm); denom = fmaf(s.ssum[0][w], w4[w], denom); }
+        for (int d = gt; d < D; d += 128)
+            a.att[(int64_t)qh * D + d] =
+                (s.red[0][0][d] * w4[0] + s.red[1][0][d] * w4[1] + s.red[2][0][d] * w4[2] + s.red[3][0][d] * w4[3]) / denom;
+    }
+}
+
+template <int D, int GQ>
+__global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(const PersistArgs a) {
+    extern __shared__ __align__(128) unsigned char psm[];
+    PkSmem sm;
+    sm.full = (uint64_t*)psm;
+    sm.empty = sm.full + PK_MAX_SLOTS;
+    sm.nsum = (double*)(psm + 128);
+    sm.abort = (volatile uint32_t*)(psm + 192);
+    sm.okflag = (volatile uint32_t*)(psm + 196);
+    sm.part = (float*)(psm + PK_PART_OFF);
+    sm.dig = psm + PK_DIG_OFF;
+    sm.ring = psm + a.ring_off;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nslots = a.nslots;
+    if (tid == 0) {
+        for (int i = 0; i < nslots; i++) { mbar_init(&sm.full[i], 33); mbar_init(&sm.empty[i], PK_CW); }
+        mbar_fence_init();
+        *sm.abort = 0u;
+        *sm.okflag = 0u;
+    }
+    __syncthreads();
+
+    if (warp == PK_CW) {
+        // ---- producer: the whole token's weight pieces of this CTA, in the consumers' order --------
+        uint32_t it = 0;
+        bool ok = true;
+        for (int li = 0; li < a.nlayers && ok; li++) {
+            const PersistLayer& L = a.layers[li];
+            for (int p = 0; p < 4 && ok; p++) {
+                const PersistPhase ph = a.ph[p];
+                const bool fuse = p == 2;
+                const uint32_t* w0 = p == 0 ? L.qkv_w : p == 1 ? L.o_w : p == 2 ? L.gate_w : L.down_w;
+                const uint16_t* s0 = p == 0 ? L.qkv_s : p == 1 ? L.o_s : p == 2 ? L.gate_s : L.down_s;
+                const uint16_t* b0 = p == 0 ? L.qkv_b : p == 1 ? L.o_b : p == 2 ? L.gate_b : L.down_b;
+                const int64_t rowbytes = (int64_t)ph.G * 32;
+                for (int b = blockIdx.x; b < ph.nblk && ok; b += gridDim.x) {
+                    for (int sl = 0; sl < ph.nsl; sl++, it++) {
+                        const int slot = it % nslots;
+                        ok = __all_sync(0xffffffffu, pk_wait(&sm.empty[slot], ((it / nslots) & 1) ^ 1, sm.abort, a, PK_ST_SLOT_EMPTY));
+                        if (!ok) break;
+                        const int g0 = sl * ph.KS, ks = min(ph.KS, ph.G - g0), RS = pk_row_stride(ks);
+                        unsigned char* sb = sm.ring + (size_t)slot * PK_SLOT_BYTES;
+                        if (lane == 0) mbar_expect_tx(&sm.full[slot], (uint32_t)(16 * ks * 32));
+                        __syncwarp();
+                        if (lane < 16) {
+                            const bool second = fuse && lane >= 8;
+                            const int64_t grow = fuse ? (int64_t)b * 8 + (lane & 7) : (int64_t)b * 16 + lane;
+                            const unsigned char* src = (const unsigned char*)(second ? L.up_w : w0) + grow * rowbytes + (int64_t)g0 * 32;
+                            bulk_g2s(sb + (size_t)lane * RS, src, (uint32_t)(ks * 32), &sm.full[slot]);
+                        }
+                        // scales and biases of the piece: ks/2 words per row and tensor, one cp.async each
+                        const int wpr = ks >> 1;
+                        for (int i = lane; i < 16 * wpr; i += 32) {
+                            const int r = i / wpr, w = i - r * wpr;
+                            const bool second = fuse && r >= 8;
+                            const int64_t grow = fuse ? (int64_t)b * 8 + (r & 7) : (int64_t)b * 16 + r;
+                            const int64_t e = grow * ph.G + g0 + 2 * w;
+                            pk_cp_async4(sb + PK_SB_OFF + (size_t)(r * ks + 2 * w) * 2, (second ? L.up_s : s0) + e);
+                            pk_cp_async4(sb + PK_SB_OFF + PK_SB_HALF + (size_t)(r * ks + 2 * w) * 2, (second ? L.up_b : b0) + e);
+                        }
+                        pk_cp_async_arrive(&sm.full[slot]);
+                    }
+                }
+            }
+        }
+        if (!ok) {
+            // gave up: let the copies already issued land before the CTA's shared memory goes away
+            const uint32_t first = it > (uint32_t)nslots ? it - nslots : 0u;
+            for (uint32_t j = first; j < it; j++) {
+                uint32_t done = 0;
+                const uint64_t t0 = pk_now();
+                while (!done && pk_now() - t0 < PK_WAIT_NS) {
+                    asm volatile("{\n\t.reg .pred p;\n\t"
+                                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                                 "selp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(done) : "r"(smem_u32(&sm.full[j % nslots])), "r"((j / nslots) & 1) : "memory");
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- consumers --------------------------------------------------------------------------------
+    using Att = PkAttSmem<D, GQ>;
+    Att* att_s = (Att*)sm.dig;  // two of them; the digits are dead during the attention phase
+    uint32_t it = 0, rbi = 0, epoch = 0;
+    const float* hcur = a.h0;
+    float* halt = a.h1;
+    const int pos = a.row_pos[0];
+    const int64_t lane_off = (int64_t)a.row_lane[0] * a.lane_stride;
+    constexpr int CH = 16 * (512 / D > 0 ? 512 / D : 1);
+    const int used = min(a.nchunks_cap, (pos + CH) / CH);
+    const int Gq = (a.Hq * D) >> 6, Gf = a.F >> 6;
+    for (int li = 0; li < a.nlayers; li++) {
+        const PersistLayer& L = a.layers[li];
+        // q|k|v
+        if (li == 0) {
+            pk_norm_prologue(sm, a, nullptr, hcur, nullptr, nullptr, L.n_input, lane, warp);
+        } else {
+            pk_norm_prologue(sm, a, a.a, hcur, halt, a.layers[li - 1].n_post_ff, L.n_input, lane, warp);
+            const float* t = hcur; hcur = halt; halt = (float*)t;
+        }
+        pk_matvec(sm, a, a.ph[0], false, a.qkv, nslots, it, rbi, lane, warp);
+        const bool live = pk_grid_barrier(a, epoch, sm.abort, sm.okflag);
+        // attention (the barrier's verdict is the same for every thread of the CTA)
+        if (live) {
+            const int grp = warp >> 2;
+            const int nitems = a.Hkv * used;
+            for (int i = blockIdx.x * 2 + grp; i < nitems; i += gridDim.x * 2)
+                pk_attention_item<D, GQ>(a, L, att_s[grp], grp, i % a.Hkv, i / a.Hkv, used, pos, lane_off);
+        }
+        pk_grid_barrier(a, epoch, sm.abort, sm.okflag);
+        // o
+        pk_prepare_digits(sm, a.att, false, Gq, 1.f, nullptr, lane, warp);
+        pk_matvec(sm, a, a.ph[1], false, a.a, nslots, it, rbi, lane, warp);
+        pk_grid_barrier(a, epoch, sm.abort, sm.okflag);
+        // gate | up
+        {
+            pk_norm_prologue(sm, a, a.a, hcur, halt, L.n_post_attn, L.n_pre_ff, lane, warp);
+            const float* t = hcur; hcur = halt; halt = (float*)t;
+        }
+        pk_matvec(sm, a, a.ph[2], true, a.act, nslots, it, rbi, lane, warp);
+        pk_grid_barrier(a, epoch, sm.abort, sm.okflag);
+        // down
+        pk_prepare_digits(sm, a.act, false, Gf, 1.f, nullptr, lane, warp);
+        pk_matvec(sm, a, a.ph[3], false, a.a, nslots, it, rbi, lane, warp);
+        if (li + 1 < a.nlayers) pk_grid_barrier(a, epoch, sm.abort, sm.okflag);
+    }
+}
+
+// ---- host ---------------------------------------------------------------------------------------
+static PersistPhase pk_phase(int64_t N, int64_t K, bool fuse) {
+    PersistPhase p{};
+    p.G = (int)(K >> 6);
+    p.nsl = (p.G + PERSIST_SLOT_G - 1) / PERSIST_SLOT_G;
+    p.KS = ((p.G + p.nsl - 1) / p.nsl + 1) & ~1;
+    p.nsl = (p.G + p.KS - 1) / p.KS;
+    p.nblk = (int)(fuse ? N / 8 : N / 16);
+    return p;
+}
+
+template <int D>
+static size_t pk_att_bytes() { return 2 * sizeof(PkAttSmem<D, 2>); }
+
+bool persist_supported(int H, int Hq, int Hkv, int D, int F, std::string* why) {
+    auto no = [&](const char* m) { if (why) *why = m; return false; };
+    if (D != 64 && D != 128 && D != 256) return no("head_dim must be 64, 128 or 256");
+    if (Hq != 2 * Hkv) return no("two query heads per kv head");
+    if (Hkv > 32) return no("at most 32 kv heads");
+    const int64_t Kq = (int64_t)Hq * D, Nqkv = (int64_t)(Hq + 2 * Hkv) * D;
+    if (H % 128 || Kq % 128 || F % 128) return no("hidden, q width and ffn must be multiples of 128");
+    if (H % 16 || Nqkv % 16 || F % 8) return no("row counts must be multiples of 16");
+    return true;
+}
+
+int32_t persist_plan(int H, int Hq, int Hkv, int D, int F, PersistArgs* a, size_t* smem) {
+    std::string why;
+    if (!persist_supported(H, Hq, Hkv, D, F, &why)) return fail(LTHN_ERR_INVALID, "persistent decode: " + why);
+    const int64_t Kq = (int64_t)Hq * D, Nqkv = (int64_t)(Hq + 2 * Hkv) * D;
+    a->ph[0] = pk_phase(Nqkv, H, false);
+    a->ph[1] = pk_phase(H, Kq, false);
+    a->ph[2] = pk_phase(F, H, true);
+    a->ph[3] = pk_phase(H, F, false);
+    const int Gh = H >> 6, Gmax = std::max({Gh, (int)(Kq >> 6), F >> 6});
+    size_t dig = (size_t)Gmax * 200;
+    dig = std::max(dig, (((size_t)Gh * 200 + 15) & ~(size_t)15) + (size_t)H * 4);
+    dig = std::max(dig, D == 64 ? pk_att_bytes<64>() : D == 128 ? pk_att_bytes<128>() : pk_att_bytes<256>());
+    dig = (dig + 127) & ~(size_t)127;
+    a->ring_off = (int)(PK_DIG_OFF + dig);
+    const size_t budget = 227 * 1024;
+    if ((size_t)a->ring_off + 2 * (size_t)PK_SLOT_BYTES > budget) return fail(LTHN_ERR_INVALID, "persistent decode: the activation digits leave no room for the weight ring");
+    a->nslots = (int)std::min<size_t>(PK_MAX_SLOTS, (budget - a->ring_off) / PK_SLOT_BYTES);
+    *smem = (size_t)a->ring_off + (size_t)a->nslots * PK_SLOT_BYTES;
+    return LTHN_OK;
+}
+
+template <int D>
+static int32_t pk_launch(cudaStream_t s, const PersistArgs& a, size_t smem) {
+    static std::mutex mu;
+    static int attr_dev = -1, grid_cache = 0;
+    int dev = 0;
+    LTHN_CUDA_TRY(cudaGetDevice(&dev));
+    auto kern = decode_persistent_kernel<D, 2>;
+    int grid;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (attr_dev != dev) {
+            LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            int sms = 0, occ = 0, coop = 0;
+            LTHN_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            LTHN_CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+            LTHN_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, PK_THREADS, smem));
+            if (!coop || occ < 1) return fail(LTHN_ERR_CUDA, "persistent decode: the kernel cannot be launched cooperatively on this device");
+            grid_cache = sms;
+            attr_dev = dev;
+        }
+        grid = grid_cache;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(PK_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    LTHN_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a));
+    return LTHN_OK;
+}
+
+// a.sync must be zero when the kernel starts (PERSIST_SYNC_WORDS words): the caller clears it on the same stream
+int32_t launch_decode_persistent(cudaStream_t s, const PersistArgs& a, size_t smem) {
+    LTHN_CUDA_TRY(cudaMemsetAsync(a.sync, 0, PERSIST_SYNC_WORDS * sizeof(uint32_t), s));
+    if (a.D == 64) return pk_launch<64>(s, a, smem);
+    if (a.D == 128) return pk_launch<128>(s, a, smem);
+    if (a.D == 256) return pk_launch<256>(s, a, smem);
+    return fail(LTHN_ERR_INVALID, "persistent decode: unsupported head_dim");
+}
+
+}  // namespace lthn

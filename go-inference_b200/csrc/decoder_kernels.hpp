@@ -4,6 +4,8 @@
 #include <stdint.h>
 #include <stddef.h>
 
+#include <string>
+
 namespace lthn {
 
 constexpr int ARGMAX_BLOCKS = 64;
@@ -62,6 +64,44 @@ struct PrefillAttnArgs {
     float scale_log2e;       // softmax scale times log2(e)
 };
 int32_t launch_prefill_attn(cudaStream_t s, const PrefillAttnArgs& a, int D);
+// ---- all decoder blocks of one token in one cooperative kernel (batch 1, one GPU) -------------
+constexpr int PERSIST_SLOT_G = 44;       // groups of 64 input columns per ring slot at most
+constexpr int PERSIST_SYNC_WORDS = 64;   // [0] grid-barrier arrivals, [2] abort flag, [16 + kv head] attention items done
+struct PersistLayer {
+    const uint32_t *qkv_w, *o_w, *gate_w, *up_w, *down_w;
+    const uint16_t *qkv_s, *qkv_b, *o_s, *o_b, *gate_s, *gate_b, *up_s, *up_b, *down_s, *down_b;
+    const float *n_input, *n_q, *n_k, *n_post_attn, *n_pre_ff, *n_post_ff;
+    uint16_t *kcache, *vcache;           // this block's cache: [lanes][max_len][Hkv*D] bf16
+};
+struct PersistPhase { int nblk, nsl, KS, G; };  // row blocks, ring slots per row block, groups per slot, groups per row
+struct PersistArgs {
+    const PersistLayer* layers;          // device memory
+    int nlayers;
+    int H, Hq, Hkv, D, F;
+    float eps, attn_scale;
+    const int32_t* row_pos;              // [1] position of the token being decoded
+    const int32_t* row_lane;             // [1] its cache lane
+    int64_t lane_stride;
+    int max_len;
+    const float2* rope;                  // [max_len][D/2] (cos, sin)
+    float* h0;                           // residual stream at entry (the embedding row); the two buffers alternate
+    float* h1;                           //   and after 2*nlayers-1 updates the stream is in h1
+    float* qkv;                          // [(Hq+2Hkv)*D]
+    float* att;                          // [Hq*D]
+    float* a;                            // [H]: o / down projection output (the last down output stays here)
+    float* act;                          // [F]
+    float* part;                         // [Hq][nchunks_cap][D+2] split-KV partials
+    int nchunks_cap;
+    uint32_t* sync;                      // PERSIST_SYNC_WORDS words, cleared by the launch wrapper
+    uint32_t* status;                    // device status word
+    PersistPhase ph[4];                  // q|k|v, o, gate|up, down
+    int nslots, ring_off;
+};
+bool persist_supported(int H, int Hq, int Hkv, int D, int F, std::string* why);
+// fills ph / nslots / ring_off and the dynamic shared-memory size
+int32_t persist_plan(int H, int Hq, int Hkv, int D, int F, PersistArgs* a, size_t* smem);
+int32_t launch_decode_persistent(cudaStream_t s, const PersistArgs& a, size_t smem);
+
 int32_t launch_argmax(cudaStream_t s, const float* logits, int rows, int V, float* pv, int* pi, int32_t* out_idx,
                       float* out_val, int index_offset);
 int32_t launch_advance(cudaStream_t s, int32_t* row_pos, int32_t* ids, const int32_t* next, int rows);

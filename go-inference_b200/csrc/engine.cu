@@ -160,6 +160,10 @@ struct Model {
     bool site_fused[2] = {};    // tensor parallel: the site's norm runs inside the consuming matvec (push mode)
     bool xchg_ready = false;
     bool fuse_norm = false;  // batch 1-2: norms run inside the matvec that consumes them
+    // batch 1 on one GPU: every decoder block of a token in one cooperative kernel (decode_persistent.cu)
+    bool persist_ok = false;
+    PersistArgs pk{};
+    size_t pk_smem = 0;
     // The logits buffer is shared by every session and lane set of the model: each forward that
     // computes logits takes the next serial number, and a lane remembers the serial of its own
     // last forward, so a read-out can tell whether the buffer still holds that lane's row.
@@ -390,6 +394,19 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
     float* hcur = m->h;
     float* halt = m->h2;
     if ((rc = launch_embed(s, m->d_ids, rows, m->embed.wq, m->embed.s, m->embed.b, H, c.vocab, c.embed_scale, hcur))) return rc;
+    if (m->persist_ok && rows == 1 && (!want_logits || logit_row0 == 0)) {
+        // one kernel for all blocks; it leaves the last down-projection output in a and the residual
+        // stream in h2 (2*layers-1 updates alternate between h and h2), which is what the lm_head's
+        // fused final norm reads
+        if ((rc = launch_decode_persistent(s, m->pk, m->pk_smem))) return rc;
+        if (!want_logits) return LTHN_OK;
+        NormFuse nf{m->a, m->h2, m->h, m->layers[c.layers - 1].norm[NORM_POST_FF], m->final_norm, c.eps};
+        QmvCall hc{m->head.wq, m->head.s, m->head.b, nullptr, nullptr, nullptr, m->xn, LTHN_DTYPE_F32, m->logits, LTHN_DTYPE_F32,
+                   m->head.N, m->head.K, rows};
+        hc.norm = &nf;
+        if ((rc = qmv_dispatch(s, hc))) return rc;
+        return launch_argmax(s, m->logits, rows, m->V_l, m->amax_v, m->amax_i, m->d_next, nullptr, 0);
+    }
     const int split = qmv_split_for(rows, LTHN_DTYPE_F32);
     if (!f1 && (rc = launch_rmsnorm(s, hcur, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, m->xn, rows, H, c.eps, 0, m->xn_cols, split))) return rc;
     int chunk_len = 0;
@@ -1119,6 +1136,48 @@ int32_t lthn_model_finalize(void* model) {
         const Layer& L0 = m->layers[0];
         m->fuse_norm = !(env && env[0] == '1') && m->c.tp_size <= 1 && qmv_can_fuse_norm(L0.qkv.N, L0.qkv.K, 2, false) &&
                        qmv_can_fuse_norm(L0.gate.N, L0.gate.K, 1, true) && qmv_can_fuse_norm(m->head.N, m->head.K, 2, false);
+    }
+    {
+        // the one-kernel decode step serves one row on one GPU, behind the fused final norm of the lm_head
+        const auto& c = m->c;
+        const char* env = getenv("LTHN_CUDA_NO_PERSIST");
+        std::string why;
+        if (!(env && env[0] == '1') && c.tp_size <= 1 && m->fuse_norm &&
+            persist_supported(c.hidden, m->Hq_l, m->Hkv_l, c.head_dim, m->F_l, &why)) {
+            int32_t rc;
+            PersistArgs& a = m->pk;
+            if ((rc = persist_plan(c.hidden, m->Hq_l, m->Hkv_l, c.head_dim, m->F_l, &a, &m->pk_smem))) return rc;
+            std::vector<PersistLayer> pl(c.layers);
+            for (int li = 0; li < c.layers; li++) {
+                const Layer& L = m->layers[li];
+                PersistLayer& d = pl[li];
+                d.qkv_w = L.qkv.wq; d.qkv_s = L.qkv.s; d.qkv_b = L.qkv.b;
+                d.o_w = L.o.wq; d.o_s = L.o.s; d.o_b = L.o.b;
+                d.gate_w = L.gate.wq; d.gate_s = L.gate.s; d.gate_b = L.gate.b;
+                d.up_w = L.up.wq; d.up_s = L.up.s; d.up_b = L.up.b;
+                d.down_w = L.down.wq; d.down_s = L.down.s; d.down_b = L.down.b;
+                d.n_input = L.norm[NORM_INPUT]; d.n_q = L.norm[NORM_Q]; d.n_k = L.norm[NORM_K];
+                d.n_post_attn = L.norm[NORM_POST_ATTN]; d.n_pre_ff = L.norm[NORM_PRE_FF]; d.n_post_ff = L.norm[NORM_POST_FF];
+                d.kcache = m->kcache + (int64_t)li * m->layer_stride;
+                d.vcache = m->vcache + (int64_t)li * m->layer_stride;
+            }
+            PersistLayer* dl = nullptr;
+            if ((rc = dalloc(m, &dl, pl.size()))) return rc;
+            LTHN_CUDA_TRY(cudaMemcpy(dl, pl.data(), pl.size() * sizeof(PersistLayer), cudaMemcpyHostToDevice));
+            uint32_t* sync = nullptr;
+            if ((rc = dalloc(m, &sync, (size_t)PERSIST_SYNC_WORDS))) return rc;
+            int chunk_len = 0;
+            a.layers = dl; a.nlayers = c.layers;
+            a.H = c.hidden; a.Hq = m->Hq_l; a.Hkv = m->Hkv_l; a.D = c.head_dim; a.F = m->F_l;
+            a.eps = c.eps; a.attn_scale = c.attn_scale;
+            a.row_pos = m->d_pos; a.row_lane = m->d_lane; a.lane_stride = m->lane_stride; a.max_len = c.max_len;
+            a.rope = m->rope;
+            a.h0 = m->h; a.h1 = m->h2; a.qkv = m->qkv; a.att = m->att; a.a = m->a; a.act = m->act; a.part = m->sdpa_part;
+            a.nchunks_cap = sdpa_chunking(c.max_len, c.head_dim, &chunk_len);
+            a.sync = sync;
+            a.status = device_status_word();
+            m->persist_ok = true;
+        }
     }
     m->finalized = true;
     return LTHN_OK;

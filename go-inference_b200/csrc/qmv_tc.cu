@@ -88,21 +88,7 @@ struct TcArgs {
     int M, N, K;
     int ntiles, ks;   // row tiles, K slices per tile
     int y_dtype;
-    long long* prof;
-    int dbg;          // measurement aid: 1 dequantisers skip the arithmetic and the TMEM store, 2 producer skips the weight loads
 };
-LTHN_HIDDEN int g_tc_dbg = 0;
-LTHN_HIDDEN long long* g_tc_prof = nullptr;  // measurement aid: cycles spent in each wait, CTA 0
-
-__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity);
-__device__ __forceinline__ bool tc_wait_fwd(uint64_t* bar, uint32_t parity) { return tc_wait(bar, parity); }
-__device__ __forceinline__ bool tc_wait_t(const TcArgs& a, int slot, uint64_t* bar, uint32_t parity) {
-    if (!a.prof || blockIdx.x != 0 || (threadIdx.x & 31) != 0) return tc_wait_fwd(bar, parity);
-    const long long t0 = clock64();
-    const bool ok = tc_wait_fwd(bar, parity);
-    atomicAdd((unsigned long long*)&a.prof[slot * 16 + (threadIdx.x >> 5)], (unsigned long long)(clock64() - t0));
-    return ok;
-}
 
 // ---- tcgen05 / TMA wrappers (cta_group::1, no multicast) --------------------------------------
 __device__ __forceinline__ void tc_tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
@@ -295,17 +281,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qmv_tc_kernel(const __grid_cons
             tc_slice_range(KB, a.ks, slice, kb0, kb1);
             for (int kb = kb0; kb < kb1 && ok; kb += TC_KC, sit++) {
                 const int st = sit % STAGES, kc = min(TC_KC, kb1 - kb);
-                ok = tc_wait_t(a, 1, &empty[st], ((sit / STAGES) & 1) ^ 1);
+                ok = tc_wait(&empty[st], ((sit / STAGES) & 1) ^ 1);
                 if (!ok) atomicOr(a.status, 1u << 16);  // which wait ran out
                 if (!ok) break;
                 unsigned char* sb = smem + (size_t)st * S::STAGE_BYTES;
                 if (lane == 0) {
                     // the boxes are always whole (k-blocks past K and rows past N or M arrive as zeros)
-                    mbar_expect_tx(&full[st], (uint32_t)(((a.dbg & 2) ? 0 : SETS * TC_PTILE) + ((a.dbg & 8) ? 0 : TC_KC * TC_XTILE)));
-                    if (!(a.dbg & 2)) {
+                    mbar_expect_tx(&full[st], (uint32_t)(SETS * TC_PTILE + TC_KC * TC_XTILE));
                     tc_tma_load_2d(sb, &w_map0, kb * 8, (int)n0, &full[st]);
                     if (SETS == 2) tc_tma_load_2d(sb + TC_PTILE, &w_map1, kb * 8, (int)n0, &full[st]);
-                    }
                 }
                 if (!waited) { pdl_wait(); waited = true; }
                 // Scales and biases of the stage's four k-blocks: 8 bytes per row and tensor, fetched by
@@ -314,7 +298,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qmv_tc_kernel(const __grid_cons
                 // global load. 8-byte copies where the row pitch keeps them aligned (K a multiple
                 // of 256), two 4-byte copies for K a multiple of 128, plain 2-byte loads otherwise.
 #pragma unroll
-                for (int set = 0; set < ((a.dbg & 16) ? 0 : SETS); set++)
+                for (int set = 0; set < SETS; set++)
 #pragma unroll
                     for (int i = 0; i < TC_ROWS / 32; i++) {
                         const int r = lane + 32 * i;
@@ -337,7 +321,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qmv_tc_kernel(const __grid_cons
                 if ((KB & 1) == 0) tc_cp_async_arrive(&full[st]);
                 else tc_arrive(&full[st]);  // plain stores above: an ordinary (releasing) arrival
                 // the stage's four activation k-blocks in one load: x viewed as [k-block][row][64]
-                if (lane == 0 && !(a.dbg & 8)) tc_tma_load_3d(sb + S::X_OFF, &x_map, 0, 0, kb, &full[st]);
+                if (lane == 0) tc_tma_load_3d(sb + S::X_OFF, &x_map, 0, 0, kb, &full[st]);
             }
         }
         if (!ok && lane == 0) atomicOr(a.status, 512u);
@@ -352,7 +336,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qmv_tc_kernel(const __grid_cons
                 int kb0, kb1;
                 tc_slice_range(KB, a.ks, slice, kb0, kb1);
                 const int acc = ait & 1;
-                ok = tc_wait_t(a, 2, &aempty[acc], ((ait >> 1) & 1) ^ 1);  // the epilogue has drained this buffer
+                ok = tc_wait(&aempty[acc], ((ait >> 1) & 1) ^ 1);  // the epilogue has drained this buffer
                 if (!ok) atomicOr(a.status, 2u << 16);  // which wait ran out
                 if (!ok) break;
                 tc_fence_after();
@@ -364,14 +348,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qmv_tc_kernel(const __grid_cons
                     const uint64_t bd0 = tc_desc(smem_u32(smem + (size_t)st * S::STAGE_BYTES + S::X_OFF));
                     for (int g0 = 0; g0 < kc && ok; g0 += S::GR, wit++) {
                         const int ws = wit % WSLOTS;
-                        ok = tc_wait_t(a, 4, &wfull[ws], (wit / WSLOTS) & 1);
+                        ok = tc_wait(&wfull[ws], (wit / WSLOTS) & 1);
                         if (!ok) atomicOr(a.status, 4u << 16);  // which wait ran out
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t slot = tmem_base + S::A_COL0 + ws * S::SLOT_COLS;
 #pragma unroll
                         for (int jj = 0; jj < S::GR; jj++) {
-                            if (g0 + jj < kc && !(a.dbg & 4)) {
+                            if (g0 + jj < kc) {
 #pragma unroll
                                 for (int set = 0; set < SETS; set++)
 #pragma unroll
@@ -382,9 +366,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qmv_tc_kernel(const __grid_cons
                                                    (kb + g0 + jj > kb0 || q > 0) ? 1u : 0u);
                             }
                         }
-                        if (a.dbg & 4) tc_arrive(&wempty[ws]); else tc_commit(&wempty[ws]);
+                        tc_commit(&wempty[ws]);
                     }
-                    if (ok) { if (a.dbg & 4) tc_arrive(&empty[st]); else tc_commit(&empty[st]); }
+                    if (ok) tc_commit(&empty[st]);
                 }
                 if (ok) tc_commit(&afull[acc]);
             }
@@ -434,7 +418,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qmv_tc_kernel(const __grid_cons
 #pragma unroll
                     for (int jj = 0; jj < S::GR; jj++) {
                         const int j = g0 + jj;
-                        if (j < kc && !(a.dbg & 1)) {
+                        if (j < kc) {
 #pragma unroll
                             for (int set = 0; set < SETS; set++) {
                                 const uint32_t sbv = sbc[set][j];
@@ -471,7 +455,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qmv_tc_kernel(const __grid_cons
         for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ait++) {
             const int rt = item / a.ks, slice = item - rt * a.ks;
             const int acc = ait & 1;
-            ok = tc_wait_t(a, 7, &afull[acc], (ait >> 1) & 1);
+            ok = tc_wait(&afull[acc], (ait >> 1) & 1);
             if (!ok) atomicOr(a.status, 32u << 16);  // which wait ran out
             if (!ok) break;
             tc_fence_after();
@@ -629,8 +613,6 @@ int32_t qmv_tc_launch(cudaStream_t st, const QmvCall& c, const uint16_t* x_bf16,
     a.ks = 1;
     if (a.ntiles < sms) a.ks = std::max(1, std::min(std::min(sms / a.ntiles, (KB + TC_KC - 1) / TC_KC), 16));
     a.status = device_status_word();
-    a.dbg = g_tc_dbg;
-    a.prof = g_tc_prof;
     if (!a.status) return fail(LTHN_ERR_CUDA, "affine_qmv: no device status word");
     if (a.ks > 1) {
         void* ws = nullptr;

@@ -10,8 +10,6 @@
 namespace lthn {
 extern LTHN_HIDDEN int g_force_rt, g_force_warps, g_force_kernel;  // qmv.cu
 extern LTHN_HIDDEN int g_force_nt;                                 // qmm.cu
-extern LTHN_HIDDEN int g_tc_dbg;                                   // qmv_tc.cu
-extern LTHN_HIDDEN long long* g_tc_prof;
 }  // namespace lthn
 
 using namespace lthn;
@@ -29,10 +27,8 @@ void lthn_debug_qmv_force_config(int32_t rt, int32_t nwarps) {
 void lthn_debug_qmv_force_kernel(int32_t kernel) {
     g_force_kernel = kernel & 15;
     g_i8_stg = (kernel >> 8) & 7;
-    g_tc_dbg = (kernel >> 12) & 255;
 }
 void lthn_debug_qmm_force_tile(int32_t nt) { g_force_nt = nt; }
-void lthn_debug_tc_profile(void* dptr) { g_tc_prof = (long long*)dptr; }
 
 // The tensor-parallel residual norm on one GPU: the t "ranks" are t local buffers ([t][rows*width]
 // in parts). flags_preset != 0: every "peer" has already signalled, nothing waits, and the call
