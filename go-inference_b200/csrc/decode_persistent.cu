@@ -8,8 +8,8 @@
 // per SM walks all blocks; phases are separated by grid-wide barriers, and the weight stream is
 // decoupled from them:
 //
-//  * warp 8 of every CTA is a producer. It knows the CTA's whole work list for the token (weights
-//    do not depend on activations) and keeps a ring of shared-memory slots full with 1-D bulk
+//  * warps 8 and 9 of every CTA are producers. They know the CTA's whole work list for the token (weights
+//    do not depend on activations) and keep a ring of shared-memory slots full with 1-D bulk
 //    (TMA) copies of 16-row x <=44-group weight pieces plus cp.async copies of their scales and
 //    biases, running ahead of the consumers across phase boundaries and grid barriers. While the
 //    grid is synchronising and the next phase's activations are being prepared, the weights of
@@ -44,7 +44,7 @@ namespace lthn {
 
 constexpr int PK_CW = 8;                  // consumer warps
 constexpr int PK_CT = PK_CW * 32;         // consumer threads
-constexpr int PK_THREADS = PK_CT + 32;    // plus the producer warp
+constexpr int PK_THREADS = PK_CT + 64;    // plus the two producer warps
 constexpr int PK_RS_MAX = 1440;           // bytes between weight rows of a slot (44 groups * 32 B + pad)
 constexpr int PK_SB_OFF = 16 * PK_RS_MAX; // scales of a slot
 constexpr int PK_SB_HALF = 16 * PERSIST_SLOT_G * 2;             // biases follow the scales
@@ -68,6 +68,9 @@ __device__ __forceinline__ void pk_mma(int (&c)[4], uint32_t a0, uint32_t a1, ui
 __device__ __forceinline__ void pk_mma_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void pk_cp_async8(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void pk_cp_async4(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -116,21 +119,26 @@ __device__ __forceinline__ bool pk_wait(uint64_t* bar, uint32_t parity, volatile
 }
 
 // Grid-wide barrier of the consumer warps of every CTA (the producers never join: they touch only
-// weights). sync[0] counts arrivals and grows for the life of the launch; sync[2] is the abort flag.
-__device__ __forceinline__ bool pk_grid_barrier(const PersistArgs& a, uint32_t& epoch, volatile uint32_t* abort, volatile uint32_t* okflag) {
+// weights), split into arrive and wait so that loads which do not depend on the other CTAs can be
+// issued in between. sync[0] counts arrivals and grows for the life of the launch (the waiters poll
+// the counter itself: the last arrival is visible to them one L2 access after it lands); sync[2]
+// is the abort flag.
+__device__ __forceinline__ void pk_grid_arrive(const PersistArgs& a, volatile uint32_t* abort) {
     pk_bar_consumers();
+    // the barrier above ordered the CTA's writes before this thread; the release makes them visible with the count
+    if (threadIdx.x == 0 && !*abort) asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(a.sync), "r"(1u) : "memory");
+}
+__device__ __noinline__ bool pk_grid_wait(const PersistArgs& a, uint32_t& epoch, volatile uint32_t* abort, volatile uint32_t* okflag) {
     if (threadIdx.x == 0) {
         uint32_t ok = 0;
         if (!*abort) {
-            __threadfence();
-            atomicAdd(a.sync, 1u);
             const uint32_t target = (epoch + 1u) * gridDim.x;
             const uint64_t t0 = pk_now();
             for (uint32_t it = 0;; ++it) {
                 uint32_t v;
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.sync) : "memory");
                 if (v >= target) { ok = 1; break; }
-                if ((it & 15) == 15) {
+                if ((it & 31) == 31) {
                     uint32_t ab;
                     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ab) : "l"(a.sync + 2) : "memory");
                     if (ab) break;
@@ -138,7 +146,6 @@ __device__ __forceinline__ bool pk_grid_barrier(const PersistArgs& a, uint32_t& 
                 }
             }
             if (!ok) { *abort = 1u; atomicExch(a.sync + 2, 1u); }
-            __threadfence();
         }
         *okflag = ok;
     }
@@ -167,17 +174,14 @@ template <int U>
 __device__ __forceinline__ void pk_digitise(const float (&x)[U][2], const bool (&live)[U], int lane, unsigned char* const (&dg)[U], float2* const (&gc)[U]) {
     float amax[U];
 #pragma unroll
-    for (int u = 0; u < U; u++) amax[u] = fmaxf(fabsf(x[u][0]), fabsf(x[u][1]));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-        for (int u = 0; u < U; u++) amax[u] = fmaxf(amax[u], __shfl_xor_sync(0xffffffffu, amax[u], o));
+    for (int u = 0; u < U; u++)  // non-negative floats order like their bit patterns
+        amax[u] = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(fabsf(x[u][0]), fabsf(x[u][1])))));
     int isum[U];
     float sxv[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
         const float sx = amax[u] * (1.0f / 127.0f);
-        const float inv = amax[u] > 0.f ? 127.0f / amax[u] : 0.f;
+        const float inv = amax[u] > 0.f ? __fdividef(127.0f, amax[u]) : 0.f;
         const float sx1 = sx * (1.0f / 128.0f);
         sxv[u] = sx;
         isum[u] = 0;
@@ -204,9 +208,7 @@ __device__ __forceinline__ void pk_digitise(const float (&x)[U][2], const bool (
         }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-        for (int u = 0; u < U; u++) isum[u] += __shfl_xor_sync(0xffffffffu, isum[u], o);
+    for (int u = 0; u < U; u++) isum[u] = __reduce_add_sync(0xffffffffu, isum[u]);
 #pragma unroll
     for (int u = 0; u < U; u++)
         if (live[u] && lane == 0) *gc[u] = make_float2(sxv[u], (float)isum[u] * (sxv[u] * (1.0f / 16384.0f)));
@@ -225,7 +227,7 @@ struct PkSmem {
 
 // Activation vector of a matvec phase -> digit planes. src: G*64 f32 values; `scale_w` (optional):
 // per-element weights applied after dividing by rms (the trailing RMSNorm of a residual pair).
-__device__ __forceinline__ void pk_prepare_digits(const PkSmem& sm, const float* src, bool src_smem, int G, float rms, const float* w_next, int lane,
+__device__ __noinline__ void pk_prepare_digits(const PkSmem& sm, const float* src, bool src_smem, int G, float rms, const float* w_next, int lane,
                                                   int warp) {
     constexpr int U = 4;
     float2* gcb = (float2*)(sm.dig + (size_t)G * 192);
@@ -241,11 +243,6 @@ __device__ __forceinline__ void pk_prepare_digits(const PkSmem& sm, const float*
             const int gg = live[u] ? g : g0;
             const int e = gg * 64 + 2 * lane;
             float2 v = src_smem ? *(const float2*)(src + e) : __ldcg((const float2*)(src + e));
-            if (w_next) {
-                const float2 wn = __ldg((const float2*)(w_next + e));
-                v.x = __fmul_rn(__fdiv_rn(v.x, rms), wn.x);
-                v.y = __fmul_rn(__fdiv_rn(v.y, rms), wn.y);
-            }
             x[u][0] = v.x; x[u][1] = v.y;
             dg[u] = sm.dig + (size_t)gg * 192;
             gc[u] = gcb + gg;
@@ -255,112 +252,203 @@ __device__ __forceinline__ void pk_prepare_digits(const PkSmem& sm, const float*
     pk_bar_consumers();
 }
 
+// Static weights of a residual RMSNorm pair, fetched before the grid barrier in front of it is
+// waited for. Thread (warp, lane) owns elements 2*lane, 2*lane+1 of the groups warp, warp+8, ...
+constexpr int PK_NV = 11;  // groups per thread: hidden <= 64 * 8 * 11 = 5632
+struct PkNormW {
+    float2 wp[PK_NV], wn[PK_NV];
+};
+__device__ __noinline__ void pk_norm_prefetch(PkNormW& nw, const float* w_post, const float* w_next, int G, int lane, int warp) {
+#pragma unroll
+    for (int i = 0; i < PK_NV; i++) {
+        const int g = warp + i * PK_CW;
+        const int e = g * 64 + 2 * lane;
+        nw.wp[i] = (w_post && g < G) ? __ldg((const float2*)(w_post + e)) : make_float2(0.f, 0.f);
+        nw.wn[i] = g < G ? __ldg((const float2*)(w_next + e)) : make_float2(0.f, 0.f);
+    }
+}
+
 // Residual RMSNorm pair in front of a matvec (every CTA computes it; CTA 0 stores the stream):
 //   h_out = h_in + rmsnorm(avec) * w_post   (skipped when avec == nullptr: h_out is h_in)
-//   x     = rmsnorm(h_out) * w_next  -> digits
-__device__ __forceinline__ void pk_norm_prologue(const PkSmem& sm, const PersistArgs& a, const float* avec, const float* h_in, float* h_out,
-                                                 const float* w_post, const float* w_next, int lane, int warp) {
-    const int H = a.H, G = H >> 6, tid = threadIdx.x;
-    float* xs = (float*)(sm.dig + (((size_t)G * 200 + 15) & ~(size_t)15));
-    double ss2 = 0.0;
+//   x     = rmsnorm(h_out) * w_next  -> digit planes in shared memory
+// Thread (warp, lane) owns elements 2*lane, 2*lane+1 of the groups warp, warp+8, ...: everything
+// stays in registers (one memory round trip for avec and h_in), every step is branch-free so the
+// groups' arithmetic interleaves, and the sums of squares run on four f64 accumulators.
+__device__ __noinline__ void pk_norm_prologue(const PkSmem& sm, const PersistArgs& a, const float* avec, const float* h_in, float* h_out,
+                                              const PkNormW& nw, int lane, int warp) {
+    const int H = a.H, G = H >> 6;
+    const double inv_h = a.inv_h;
+    float2 av[PK_NV], hv[PK_NV];
+#pragma unroll
+    for (int i = 0; i < PK_NV; i++) {
+        const int g = warp + i * PK_CW;
+        const int e = g * 64 + 2 * lane;
+        hv[i] = g < G ? __ldcg((const float2*)(h_in + e)) : make_float2(0.f, 0.f);
+        av[i] = (avec && g < G) ? __ldcg((const float2*)(avec + e)) : make_float2(0.f, 0.f);
+    }
     if (avec) {
-        double ss = 0.0;
-#pragma unroll 4
-        for (int e = 2 * tid; e < H; e += 2 * PK_CT) {
-            const float2 v = __ldcg((const float2*)(avec + e));
-            ss += (double)__fmul_rn(v.x, v.x);
-            ss += (double)__fmul_rn(v.y, v.y);
+        double s4[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+        for (int i = 0; i < PK_NV; i++) {  // zeros beyond the vector
+            s4[(2 * i) & 3] += (double)__fmul_rn(av[i].x, av[i].x);
+            s4[(2 * i + 1) & 3] += (double)__fmul_rn(av[i].y, av[i].y);
         }
-        ss = pk_block_sum(ss, sm.nsum, lane, warp);
-        const float rms = (float)sqrt(ss / (double)H + (double)a.eps);
-#pragma unroll 4
-        for (int e = 2 * tid; e < H; e += 2 * PK_CT) {
-            const float2 v = __ldcg((const float2*)(avec + e));
-            const float2 h = __ldcg((const float2*)(h_in + e));
-            const float2 wp = __ldg((const float2*)(w_post + e));
-            float2 o;
-            o.x = __fadd_rn(h.x, __fmul_rn(__fdiv_rn(v.x, rms), wp.x));
-            o.y = __fadd_rn(h.y, __fmul_rn(__fdiv_rn(v.y, rms), wp.y));
-            *(float2*)(xs + e) = o;
-            if (blockIdx.x == 0) *(float2*)(h_out + e) = o;
-            ss2 += (double)__fmul_rn(o.x, o.x);
-            ss2 += (double)__fmul_rn(o.y, o.y);
+        const double ss = pk_block_sum((s4[0] + s4[1]) + (s4[2] + s4[3]), sm.nsum, lane, warp);
+        const FastDiv k = fast_div_by(fast_rms(ss, inv_h, a.eps));
+#pragma unroll
+        for (int i = 0; i < PK_NV; i++) {
+            hv[i].x = __fadd_rn(hv[i].x, __fmul_rn(fast_div(av[i].x, k), nw.wp[i].x));
+            hv[i].y = __fadd_rn(hv[i].y, __fmul_rn(fast_div(av[i].y, k), nw.wp[i].y));
         }
-    } else {
-#pragma unroll 4
-        for (int e = 2 * tid; e < H; e += 2 * PK_CT) {
-            const float2 h = __ldcg((const float2*)(h_in + e));
-            *(float2*)(xs + e) = h;
-            ss2 += (double)__fmul_rn(h.x, h.x);
-            ss2 += (double)__fmul_rn(h.y, h.y);
+        if (blockIdx.x == 0) {
+#pragma unroll
+            for (int i = 0; i < PK_NV; i++) {
+                const int g = warp + i * PK_CW;
+                if (g < G) *(float2*)(h_out + g * 64 + 2 * lane) = hv[i];
+            }
         }
     }
-    ss2 = pk_block_sum(ss2, sm.nsum, lane, warp);  // its barriers also publish xs
-    const float rms2 = (float)sqrt(ss2 / (double)H + (double)a.eps);
-    pk_prepare_digits(sm, xs, true, G, rms2, w_next, lane, warp);
+    double s4[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+    for (int i = 0; i < PK_NV; i++) {
+        s4[(2 * i) & 3] += (double)__fmul_rn(hv[i].x, hv[i].x);
+        s4[(2 * i + 1) & 3] += (double)__fmul_rn(hv[i].y, hv[i].y);
+    }
+    const double ss2 = pk_block_sum((s4[0] + s4[1]) + (s4[2] + s4[3]), sm.nsum, lane, warp);
+    const FastDiv k2 = fast_div_by(fast_rms(ss2, inv_h, a.eps));
+    // the normed vector goes through shared memory: one rolled copy of the digit conversion serves every phase
+    float* xs = (float*)(sm.dig + (((size_t)G * 200 + 15) & ~(size_t)15));
+#pragma unroll
+    for (int i = 0; i < PK_NV; i++) {
+        const int g = warp + i * PK_CW;
+        if (g < G)
+            *(float2*)(xs + g * 64 + 2 * lane) = make_float2(__fmul_rn(fast_div(hv[i].x, k2), nw.wn[i].x), __fmul_rn(fast_div(hv[i].y, k2), nw.wn[i].y));
+    }
+    __syncwarp();  // a warp converts the groups it wrote
+    pk_prepare_digits(sm, xs, true, G, 1.f, nullptr, lane, warp);
+}
+
+// Digit planes that another phase left in global memory (G groups: G*192 digit bytes, then G
+// (sx, sum) pairs) -> shared memory. Every load is issued before the first store.
+__device__ __noinline__ void pk_digits_from_global(const PkSmem& sm, const unsigned char* src, int G) {
+    const int n16 = (G * 200) >> 4;
+    const uint4* s4 = (const uint4*)src;
+    uint4* d4 = (uint4*)sm.dig;
+    for (int i0 = threadIdx.x; i0 < n16; i0 += 8 * PK_CT) {
+        uint4 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int i = i0 + k * PK_CT;
+            v[k] = i < n16 ? __ldcg(s4 + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int i = i0 + k * PK_CT;
+            if (i < n16) d4[i] = v[k];
+        }
+    }
+    pk_bar_consumers();
+}
+
+// This CTA's share of a vector in global memory -> digit planes in global memory (groups cta,
+// cta + grid, ...; one warp per group).
+__device__ __noinline__ void pk_digitise_share(const float* src, unsigned char* dst, int G, int lane, int warp) {
+    float2* gcb = (float2*)(dst + (size_t)G * 192);
+    for (int g = blockIdx.x + warp * gridDim.x; g < G; g += PK_CW * gridDim.x) {
+        const float2 v = __ldcg((const float2*)(src + (size_t)g * 64 + 2 * lane));
+        const float x[1][2] = {{v.x, v.y}};
+        const bool live[1] = {true};
+        unsigned char* const dg[1] = {dst + (size_t)g * 192};
+        float2* const gc[1] = {gcb + g};
+        pk_digitise<1>(x, live, lane, dg, gc);
+    }
 }
 
 // One matvec phase of the consumers: this CTA's row blocks (b = cta, cta+grid, ...), each of
 // ph.nsl ring slots. FUSE: rows 0-7 of a slot are gate rows, rows 8-15 the same rows of up;
-// out[row] = gelu_tanh(gate) * up.
-__device__ __forceinline__ void pk_matvec(const PkSmem& sm, const PersistArgs& a, const PersistPhase& ph, bool fuse, float* out, int nslots,
-                                          uint32_t& it, uint32_t& rbi, int lane, int warp) {
+// out[row] = gelu_tanh(gate) * up. it_base: the ring position at entry (the caller advances it by pk_blocks() * nsl).
+// 
+__device__ __forceinline__ uint32_t pk_blocks(const PersistPhase& ph) {
+    return (int)blockIdx.x < ph.nblk ? (uint32_t)((ph.nblk - 1 - (int)blockIdx.x) / (int)gridDim.x + 1) : 0u;
+}
+__device__ __noinline__ void pk_matvec(uint64_t* full, uint64_t* empty, volatile uint32_t* abort, float* part, const unsigned char* dig,
+                                       const unsigned char* ring, const PersistArgs& a, PersistPhase ph, bool fuse, float* out, int nslots,
+                                       uint32_t it_base) {
+    // The eight consumer warps split into T teams that work on different row blocks at the same time, so
+    // that the latency of one ring slot (wait, fragment loads, MMAs, hand-back) overlaps with the others':
+    // T = 4 teams of two warps when the CTA has at least four row blocks in this phase, 2 x 4 or 1 x 8 below.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nrb = (int)pk_blocks(ph);
+    const int tshift = nrb >= 4 ? 2 : nrb >= 2 ? 1 : 0;
+    const int T = 1 << tshift, WT = PK_CW >> tshift;
+    const int team = warp / WT, wt = warp - team * WT;
     const int gq = lane >> 2, t = lane & 3;
-    const float2* gcb = (const float2*)(sm.dig + (size_t)ph.G * 192);
+    const float2* gcb = (const float2*)(dig + (size_t)ph.G * 192);
     constexpr uint32_t NIB = 0x0F0F0F0Fu;
-    const float planew = (t & 1) ? (1.0f / 2097152.0f) : (1.0f / 128.0f);
     const bool colrow = t < 2;  // columns of activation row 0 (the only row)
-    for (int b = blockIdx.x; b < ph.nblk; b += gridDim.x) {
+    const float planew = !colrow ? 0.f : (t & 1) ? (1.0f / 2097152.0f) : (1.0f / 128.0f);
+    int jj = 0;
+    for (int j = team; j < nrb; j += T, jj++) {
+        const int b = blockIdx.x + j * gridDim.x;
         float acc0 = 0.f, acc1 = 0.f, accb = 0.f;
-        for (int sl = 0; sl < ph.nsl; sl++, it++) {
-            const int slot = it % nslots;
-            const bool ok = __all_sync(0xffffffffu, pk_wait(&sm.full[slot], (it / nslots) & 1, sm.abort, a, PK_ST_SLOT_FULL));
+        // ring order: (wave of T row blocks, slice, team), so that the slots in flight always serve every team
+        const int wave = j >> tshift, inwave = min(T, nrb - (wave << tshift));
+        for (int sl = 0; sl < ph.nsl; sl++) {
+            const uint32_t it = it_base + (uint32_t)((wave << tshift) * ph.nsl + sl * inwave + team);
+            const uint32_t lap = it / (uint32_t)nslots;
+            const int slot = (int)(it - lap * (uint32_t)nslots);
+            const bool ok = __all_sync(0xffffffffu, pk_wait(&full[slot], lap & 1, abort, a, PK_ST_SLOT_FULL));
             const int g0 = sl * ph.KS, ks = min(ph.KS, ph.G - g0), RS = pk_row_stride(ks);
-            const unsigned char* sb = sm.ring + (size_t)slot * PK_SLOT_BYTES;
+            const unsigned char* sb = ring + (size_t)slot * PK_SLOT_BYTES;
             if (ok) {
                 const uint16_t* sp = (const uint16_t*)(sb + PK_SB_OFF) + gq * ks;
                 const uint16_t* bp = (const uint16_t*)(sb + PK_SB_OFF + PK_SB_HALF) + (gq + 8 * (t & 1)) * ks;
                 const unsigned char* rowp = sb + (size_t)gq * RS + t * 8;
-                // two groups per trip (g and g + 8): two independent load -> unpack -> MMA chains per warp
-                for (int g = warp; g < ks; g += 2 * PK_CW) {
-                    const int gB = g + PK_CW;
-                    const bool hasB = gB < ks;
-                    const int gb = hasB ? gB : g;
-                    const unsigned char* dA = sm.dig + (size_t)(g0 + g) * 192;
-                    const unsigned char* dB = sm.dig + (size_t)(g0 + gb) * 192;
-                    uint2 bA0 = make_uint2(0u, 0u), bA1 = bA0, bB0 = bA0, bB1 = bA0;
-                    if (gq < 3) {
-                        bA0 = *(const uint2*)(dA + gq * 64 + t * 8);
-                        bA1 = *(const uint2*)(dA + gq * 64 + (4 + t) * 8);
-                        bB0 = *(const uint2*)(dB + gq * 64 + t * 8);
-                        bB1 = *(const uint2*)(dB + gq * 64 + (4 + t) * 8);
+                const unsigned char* dgp = dig + (size_t)g0 * 192 + (gq < 3 ? gq : 0) * 64 + t * 8;
+                // Six groups of the team's share (g = wt, wt+WT, ...) are in flight together: twelve independent
+                // MMAs whose loads and unpacking overlap. No branches: a group past the end of the slot repeats the
+                // warp's first group with weight zero.
+                constexpr int U = 6;
+                for (int gb = wt; gb < ks; gb += U * WT) {
+                    uint2 wa[U], wb[U], b0[U], b1[U];
+                    float gx[U], gy[U], s0[U], s1[U], bb[U];
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        const int g = gb + u * WT;
+                        const bool live = g < ks;
+                        const int gg = live ? g : wt;
+                        b0[u] = *(const uint2*)(dgp + gg * 192);
+                        b1[u] = *(const uint2*)(dgp + gg * 192 + 32);
+                        if (gq >= 3) { b0[u] = make_uint2(0u, 0u); b1[u] = b0[u]; }
+                        wa[u] = *(const uint2*)(rowp + gg * 32);
+                        wb[u] = *(const uint2*)(rowp + (size_t)8 * RS + gg * 32);
+                        const float2 gc = gcb[g0 + gg];
+                        gx[u] = live ? gc.x * planew : 0.f;
+                        gy[u] = (live && colrow) ? gc.y : 0.f;
+                        s0[u] = bf16_bits_to_f32(sp[gg]);
+                        s1[u] = bf16_bits_to_f32(sp[8 * ks + gg]);
+                        bb[u] = bf16_bits_to_f32(bp[gg]);
                     }
-                    const uint2 waA = *(const uint2*)(rowp + g * 32), wbA = *(const uint2*)(rowp + (size_t)8 * RS + g * 32);
-                    const uint2 waB = *(const uint2*)(rowp + gb * 32), wbB = *(const uint2*)(rowp + (size_t)8 * RS + gb * 32);
-                    const float2 gcA = gcb[g0 + g], gcB = gcb[g0 + gb];
-                    int cA[4], cB[4];
-                    pk_mma_z(cA, waA.x & NIB, wbA.x & NIB, (waA.x >> 4) & NIB, (wbA.x >> 4) & NIB, bA0.x, bA0.y);
-                    pk_mma_z(cB, waB.x & NIB, wbB.x & NIB, (waB.x >> 4) & NIB, (wbB.x >> 4) & NIB, bB0.x, bB0.y);
-                    pk_mma(cA, waA.y & NIB, wbA.y & NIB, (waA.y >> 4) & NIB, (wbA.y >> 4) & NIB, bA1.x, bA1.y);
-                    pk_mma(cB, waB.y & NIB, wbB.y & NIB, (waB.y >> 4) & NIB, (wbB.y >> 4) & NIB, bB1.x, bB1.y);
-                    {
-                        const float cg = colrow ? gcA.x * planew : 0.f;
-                        const float f0 = (float)(cA[0] * 128 + cA[1]) * cg, f1 = (float)(cA[2] * 128 + cA[3]) * cg;
-                        acc0 = fmaf(bf16_bits_to_f32(sp[g]), f0, acc0);
-                        acc1 = fmaf(bf16_bits_to_f32(sp[8 * ks + g]), f1, acc1);
-                        accb = fmaf(bf16_bits_to_f32(bp[g]), colrow ? gcA.y : 0.f, accb);
+                    float f0[U], f1[U];
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        int c0[4], c1[4];
+                        pk_mma_z(c0, wa[u].x & NIB, wb[u].x & NIB, (wa[u].x >> 4) & NIB, (wb[u].x >> 4) & NIB, b0[u].x, b0[u].y);
+                        pk_mma_z(c1, wa[u].y & NIB, wb[u].y & NIB, (wa[u].y >> 4) & NIB, (wb[u].y >> 4) & NIB, b1[u].x, b1[u].y);
+                        f0[u] = (float)((c0[0] + c1[0]) * 128 + (c0[1] + c1[1])) * gx[u];
+                        f1[u] = (float)((c0[2] + c1[2]) * 128 + (c0[3] + c1[3])) * gx[u];
                     }
-                    if (hasB) {
-                        const float cg = colrow ? gcB.x * planew : 0.f;
-                        const float f0 = (float)(cB[0] * 128 + cB[1]) * cg, f1 = (float)(cB[2] * 128 + cB[3]) * cg;
-                        acc0 = fmaf(bf16_bits_to_f32(sp[gB]), f0, acc0);
-                        acc1 = fmaf(bf16_bits_to_f32(sp[8 * ks + gB]), f1, acc1);
-                        accb = fmaf(bf16_bits_to_f32(bp[gB]), colrow ? gcB.y : 0.f, accb);
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        acc0 = fmaf(s0[u], f0[u], acc0);
+                        acc1 = fmaf(s1[u], f1[u], acc1);
+                        accb = fmaf(bb[u], gy[u], accb);
                     }
                 }
             }
             __syncwarp();
-            if (lane == 0) pk_arrive(&sm.empty[slot]);  // this warp is done with the slot
+            // this warp is done with the slot: the team's WT warps bring the PK_CW arrivals the barrier expects
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&empty[slot])), "r"(T) : "memory");
         }
         // lanes t and t^1 hold the two plane halves of the same outputs; even t finishes row gq,
         // odd t row gq+8 (each also carries that row's bias term)
@@ -368,43 +456,62 @@ __device__ __forceinline__ void pk_matvec(const PkSmem& sm, const PersistArgs& a
         const float send = odd ? acc0 : acc1;
         const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
         const float res = (odd ? acc1 : acc0) + recv + accb;
-        float* pw = sm.part + ((size_t)(rbi & 1) * PK_CW + warp) * 16;
-        if (colrow) pw[gq + 8 * (t & 1)] = res;
-        pk_bar_consumers();
-        if (warp == (int)(rbi % PK_CW)) {
-            const float* p0 = sm.part + (size_t)(rbi & 1) * PK_CW * 16;
+        float* p0 = part + (size_t)((team * 2 + (jj & 1)) * WT) * 16;  // [T][2][WT][16]
+        if (colrow) p0[wt * 16 + gq + 8 * (t & 1)] = res;
+        asm volatile("bar.sync %0, %1;" ::"r"(4 + team), "r"(WT * 32) : "memory");
+        if (wt == jj % WT) {
             if (!fuse) {
                 if (lane < 16) {
                     float v = 0.f;
-#pragma unroll
-                    for (int w = 0; w < PK_CW; w++) v += p0[w * 16 + lane];
+                    for (int w = 0; w < WT; w++) v += p0[w * 16 + lane];
                     out[(size_t)b * 16 + lane] = v;
                 }
             } else if (lane < 8) {
                 float g = 0.f, u = 0.f;
-#pragma unroll
-                for (int w = 0; w < PK_CW; w++) { g += p0[w * 16 + lane]; u += p0[w * 16 + 8 + lane]; }
+                for (int w = 0; w < WT; w++) { g += p0[w * 16 + lane]; u += p0[w * 16 + 8 + lane]; }
                 out[(size_t)b * 8 + lane] = pk_gelu(g) * u;
             }
         }
-        rbi++;
     }
 }
 
 // ---- attention: one (kv head, key chunk) item on a 128-thread group ----------------------------
 // The arithmetic of sdpa_decode_kernel / sdpa_merge_kernel (decoder_kernels.cu) with the per-head
-// RMSNorm + RoPE of q (and of the new key) and the KV append folded in.
+// RMSNorm + RoPE of q (and of the new key), the KV append and the digit planes of the output (the
+// o projection's activations) folded in. Every global load of an item is issued before anything
+// is computed: one memory round trip per item.
 template <int D, int GQ>
 struct alignas(16) PkAttSmem {
     float red[4][GQ][D + 2];
     float q[GQ][D];
+    uint16_t knew[D], vnew[D];
     float smax[GQ][4], ssum[GQ][4];
     double sh[4][GQ + 1];
     uint32_t last;
 };
 
+// the finished output of the item's heads (s.q[h][d], reused as a staging area) -> digit planes of the o
+// projection's input in global memory; one warp per group of 64
 template <int D, int GQ>
-__device__ __forceinline__ void pk_attention_item(const PersistArgs& a, const PersistLayer& L, PkAttSmem<D, GQ>& s, int grp, int kvh, int chunk,
+__device__ __forceinline__ void pk_att_emit(const PersistArgs& a, PkAttSmem<D, GQ>& s, int qh0, int lane, int warp) {
+    constexpr int GH = D / 64;  // groups per head
+    const int Gq = (a.Hq * D) >> 6;
+    float2* gcb = (float2*)(a.dig_att + (size_t)Gq * 192);
+#pragma unroll 1
+    for (int gi = warp; gi < GQ * GH; gi += 4) {
+        const int h = gi / GH, j = gi - h * GH;
+        const float2 v = *(const float2*)(&s.q[h][j * 64 + 2 * lane]);
+        const float x[1][2] = {{v.x, v.y}};
+        const bool live[1] = {true};
+        const int g = (qh0 + h) * GH + j;
+        unsigned char* const dg[1] = {a.dig_att + (size_t)g * 192};
+        float2* const gc[1] = {gcb + g};
+        pk_digitise<1>(x, live, lane, dg, gc);
+    }
+}
+
+template <int D, int GQ>
+__device__ __noinline__ void pk_attention_item(const PersistArgs& a, const PersistLayer& L, PkAttSmem<D, GQ>& s, int grp, int kvh, int chunk,
                                                   int used, int pos, int64_t lane_off) {
     constexpr int E = D / 8, V8 = E / 8, NIT = 512 / D > 0 ? 512 / D : 1, CH = 16 * NIT, half = D / 2;
     const int gt = threadIdx.x & 127, lane = gt & 31, warp = gt >> 5;
@@ -412,26 +519,52 @@ __device__ __forceinline__ void pk_attention_item(const PersistArgs& a, const Pe
     const int ctx = pos + 1, p0 = chunk * CH, KR = a.Hkv * D, qh0 = kvh * GQ;
     uint16_t* kbase = L.kcache + lane_off + (int64_t)kvh * D;
     uint16_t* vbase = L.vcache + lane_off + (int64_t)kvh * D;
-    const float2 cs = gt < half ? __ldg(a.rope + (int64_t)min(pos, a.max_len - 1) * half + gt) : make_float2(1.f, 0.f);
-    const bool has_new = pos >= p0 && pos < p0 + CH;  // this chunk holds the token being decoded: append its key and value first
-    // sums of squares of the GQ query heads (and the new key head)
-    float x0[GQ + 1], x1[GQ + 1];
+    const bool has_new = pos >= p0 && pos < p0 + CH;  // this chunk holds the token being decoded
+    const bool pair = gt < half;                      // thread owns the rotation pair (gt, gt + half)
+
+    // ---- every load of the item goes out first ---------------------------------------------------
+    uint4 kreg[NIT][V8], vreg[NIT][V8];
+    bool valid[NIT];
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
+        const int p = p0 + pg + 16 * i;
+        valid[i] = p < ctx;
+        const int64_t off = (int64_t)((valid[i] && p != pos) ? p : p0) * KR;  // the new token's row comes from shared memory
+#pragma unroll
+        for (int v = 0; v < V8; v++) {
+            kreg[i][v] = __ldcg((const uint4*)(kbase + off + (v * 8 + l8) * 8));
+            vreg[i][v] = __ldcg((const uint4*)(vbase + off + (v * 8 + l8) * 8));
+        }
+    }
+    float x0[GQ + 1], x1[GQ + 1], w0[2], w1[2], vn0 = 0.f, vn1 = 0.f;
+    float2 cs = make_float2(1.f, 0.f);
+#pragma unroll
+    for (int h = 0; h <= GQ; h++) {
+        x0[h] = 0.f; x1[h] = 0.f;
+        if (pair && (h < GQ || has_new)) {
+            const float* src = a.qkv + (int64_t)(h < GQ ? qh0 + h : a.Hq + kvh) * D;
+            x0[h] = __ldcg(src + gt);
+            x1[h] = __ldcg(src + gt + half);
+        }
+    }
+    w0[0] = w0[1] = w1[0] = w1[1] = 0.f;
+    if (pair) {
+        cs = __ldg(a.rope + (int64_t)min(pos, a.max_len - 1) * half + gt);
+        w0[0] = __ldg(L.n_q + gt); w1[0] = __ldg(L.n_q + gt + half);
+        if (has_new) {
+            w0[1] = __ldg(L.n_k + gt); w1[1] = __ldg(L.n_k + gt + half);
+            const float* src = a.qkv + (int64_t)(a.Hq + a.Hkv + kvh) * D;
+            vn0 = __ldcg(src + gt); vn1 = __ldcg(src + gt + half);
+        }
+    }
+    // ---- head norms + RoPE ---------------------------------------------------------------------------
     double ss[GQ + 1];
 #pragma unroll
     for (int h = 0; h <= GQ; h++) {
-        x0[h] = 0.f; x1[h] = 0.f; ss[h] = 0.0;
-        if (h == GQ && !has_new) continue;
-        const float* src = a.qkv + (int64_t)(h < GQ ? qh0 + h : a.Hq + kvh) * D;
-        if (gt < half) {
-            x0[h] = __ldcg(src + gt);
-            x1[h] = __ldcg(src + gt + half);
-            ss[h] = (double)__fmul_rn(x0[h], x0[h]) + (double)__fmul_rn(x1[h], x1[h]);
-        }
-    }
-#pragma unroll
-    for (int h = 0; h <= GQ; h++)
+        ss[h] = (double)__fmul_rn(x0[h], x0[h]) + (double)__fmul_rn(x1[h], x1[h]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], o);
+    }
     pk_bar_group(grp);  // the previous item's readers of this scratch are done
     if (lane == 0)
 #pragma unroll
@@ -441,44 +574,40 @@ __device__ __forceinline__ void pk_attention_item(const PersistArgs& a, const Pe
     for (int h = 0; h <= GQ; h++) {
         if (h == GQ && !has_new) continue;
         const double tsum = s.sh[0][h] + s.sh[1][h] + s.sh[2][h] + s.sh[3][h];
-        const float rms = (float)sqrt(tsum / (double)D + (double)a.eps);
-        if (gt < half) {
-            const float* w = h < GQ ? L.n_q : L.n_k;
-            const float n0 = __fmul_rn(__fdiv_rn(x0[h], rms), __ldg(w + gt));
-            const float n1 = __fmul_rn(__fdiv_rn(x1[h], rms), __ldg(w + gt + half));
+        const FastDiv k = fast_div_by(fast_rms(tsum, 1.0 / (double)D, a.eps));
+        if (pair) {
+            const float n0 = __fmul_rn(fast_div(x0[h], k), w0[h < GQ ? 0 : 1]);
+            const float n1 = __fmul_rn(fast_div(x1[h], k), w1[h < GQ ? 0 : 1]);
             const float r0 = __fsub_rn(__fmul_rn(n0, cs.x), __fmul_rn(n1, cs.y));
             const float r1 = __fadd_rn(__fmul_rn(n0, cs.y), __fmul_rn(n1, cs.x));
             if (h < GQ) {
                 s.q[h][gt] = r0 * a.attn_scale;
                 s.q[h][gt + half] = r1 * a.attn_scale;
             } else {
+                const uint16_t b0 = f32_to_bf16_bits(r0), b1 = f32_to_bf16_bits(r1);
+                s.knew[gt] = b0; s.knew[gt + half] = b1;
                 uint16_t* dst = kbase + (int64_t)pos * KR;
-                dst[gt] = f32_to_bf16_bits(r0);
-                dst[gt + half] = f32_to_bf16_bits(r1);
+                dst[gt] = b0; dst[gt + half] = b1;
             }
         }
     }
-    if (has_new && gt < half) {
-        const float* src = a.qkv + (int64_t)(a.Hq + a.Hkv + kvh) * D;
+    if (has_new && pair) {
+        const uint16_t b0 = f32_to_bf16_bits(vn0), b1 = f32_to_bf16_bits(vn1);
+        s.vnew[gt] = b0; s.vnew[gt + half] = b1;
         uint16_t* dst = vbase + (int64_t)pos * KR;
-        dst[gt] = f32_to_bf16_bits(__ldcg(src + gt));
-        dst[gt + half] = f32_to_bf16_bits(__ldcg(src + gt + half));
+        dst[gt] = b0; dst[gt + half] = b1;
     }
-    pk_bar_group(grp);  // q in shared memory; the appended row visible to the group's loads below
-
-    // ---- every load of the chunk goes out first -------------------------------------------------
-    uint4 kreg[NIT][V8], vreg[NIT][V8];
-    bool valid[NIT];
+    pk_bar_group(grp);  // q and the new row are in shared memory
+    if (has_new) {
 #pragma unroll
-    for (int i = 0; i < NIT; i++) {
-        const int p = p0 + pg + 16 * i;
-        valid[i] = p < ctx;
-        const int64_t off = (int64_t)(valid[i] ? p : p0) * KR;
+        for (int i = 0; i < NIT; i++)
+            if (p0 + pg + 16 * i == pos) {
 #pragma unroll
-        for (int v = 0; v < V8; v++) {
-            kreg[i][v] = __ldcg((const uint4*)(kbase + off + (v * 8 + l8) * 8));
-            vreg[i][v] = __ldcg((const uint4*)(vbase + off + (v * 8 + l8) * 8));
-        }
+                for (int v = 0; v < V8; v++) {
+                    kreg[i][v] = *(const uint4*)(&s.knew[(v * 8 + l8) * 8]);
+                    vreg[i][v] = *(const uint4*)(&s.vnew[(v * 8 + l8) * 8]);
+                }
+            }
     }
     float q[GQ][E];
 #pragma unroll
@@ -490,6 +619,7 @@ __device__ __forceinline__ void pk_attention_item(const PersistArgs& a, const Pe
             q[h][v * 8 + 0] = qa.x; q[h][v * 8 + 1] = qa.y; q[h][v * 8 + 2] = qa.z; q[h][v * 8 + 3] = qa.w;
             q[h][v * 8 + 4] = qb.x; q[h][v * 8 + 5] = qb.y; q[h][v * 8 + 6] = qb.z; q[h][v * 8 + 7] = qb.w;
         }
+    // ---- scores ----------------------------------------------------------------------------------------
     float sc[NIT][GQ], mx[GQ];
 #pragma unroll
     for (int h = 0; h < GQ; h++) mx[h] = -INFINITY;
@@ -527,6 +657,7 @@ __device__ __forceinline__ void pk_attention_item(const PersistArgs& a, const Pe
     float cmax[GQ];
 #pragma unroll
     for (int h = 0; h < GQ; h++) cmax[h] = fmaxf(fmaxf(s.smax[h][0], s.smax[h][1]), fmaxf(s.smax[h][2], s.smax[h][3]));
+    // ---- weights and weighted values ---------------------------------------------------------------------
     float acc[GQ][E], lsum[GQ];
 #pragma unroll
     for (int h = 0; h < GQ; h++) {
@@ -562,7 +693,7 @@ __device__ __forceinline__ void pk_attention_item(const PersistArgs& a, const Pe
             v += __shfl_xor_sync(0xffffffffu, v, 16);
             acc[h][e] = v;
         }
-        float l = (l8 == 0) ? lsum[h] : 0.f;
+        float l = (l8 == 0) ? lsum[h] : 0.f;  // the 8 lanes of a group hold the same weight: count it once
         l = warp_sum(l);
         if (lane == 0) s.ssum[h][warp] = l;
         if (lane < 8) {
@@ -573,88 +704,109 @@ __device__ __forceinline__ void pk_attention_item(const PersistArgs& a, const Pe
         }
     }
     pk_bar_group(grp);
+    // (every thread of the group is past its reads of s.q: the query went to registers before the barriers above)
     for (int idx = gt; idx < GQ * D; idx += 128) {
         const int h = idx / D, d = idx - h * D;
         const float v = s.red[0][h][d] + s.red[1][h][d] + s.red[2][h][d] + s.red[3][h][d];
         const float l = s.ssum[h][0] + s.ssum[h][1] + s.ssum[h][2] + s.ssum[h][3];
-        const int qh = qh0 + h;
         if (used == 1) {
-            a.att[(int64_t)qh * D + d] = v / l;
+            s.q[h][d] = fast_div(v, fast_div_by(l));
         } else {
-            float* pa = a.part + ((int64_t)qh * a.nchunks_cap + chunk) * (D + 2);
+            float* pa = a.part + ((int64_t)(qh0 + h) * a.nchunks_cap + chunk) * (D + 2);
             pa[d] = v;
             if (d == 0) { pa[D] = cmax[h]; pa[D + 1] = l; }
         }
     }
-    if (used == 1) return;
+    bool emit = used == 1;
+    if (!emit) {
     // ---- the last item of this kv head to finish merges the head's chunk partials ----------------
     __threadfence();
     pk_bar_group(grp);
     if (gt == 0) {
-        const uint32_t n = atomicAdd(a.sync + 16 + kvh, 1u);
+        const uint32_t n = atomicAdd(a.sync + 64 + kvh, 1u);
         s.last = (n == (uint32_t)used - 1u) ? 1u : 0u;
-        if (s.last) { a.sync[16 + kvh] = 0u; __threadfence(); }
+        if (s.last) { a.sync[64 + kvh] = 0u; __threadfence(); }
     }
     pk_bar_group(grp);
-    if (!s.last) return;
-    constexpr int DL = D / 32, MB = 8;
-    for (int h = 0; h < GQ; h++) {
-        const int qh = qh0 + h;
-        const float* pa = a.part + (int64_t)qh * a.nchunks_cap * (D + 2);
-        float m = -INFINITY, l = 0.f, macc[DL];
+    emit = s.last != 0;
+    if (emit) {
+    // One pass over the chunks for both heads (the loads of MB chunks per warp are issued together);
+    // warp w takes chunks w, w+4, ..., lane D/32 consecutive dimensions.
+    constexpr int DL = D / 32, MB = 4;
+    float m[GQ], l[GQ], macc[GQ][DL];
 #pragma unroll
-        for (int i = 0; i < DL; i++) macc[i] = 0.f;
-        for (int c0 = warp; c0 < used; c0 += 4 * MB) {
-            float cm[MB], cl[MB];
-            float2 cv[MB][DL / 2];
+    for (int h = 0; h < GQ; h++) {
+        m[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DL; i++) macc[h][i] = 0.f;
+    }
+    for (int c0 = warp; c0 < used; c0 += 4 * MB) {
+        float cm[GQ][MB], cl[GQ][MB];
+        float2 cv[GQ][MB][DL / 2];
+#pragma unroll
+        for (int h = 0; h < GQ; h++)
 #pragma unroll
             for (int b = 0; b < MB; b++) {
                 const int c = c0 + 4 * b;
                 const bool live = c < used;
-                const float* p = pa + (int64_t)(live ? c : c0) * (D + 2);
-                cm[b] = live ? __ldcg(p + D) : -INFINITY;
-                cl[b] = live ? __ldcg(p + D + 1) : 0.f;
+                const float* p = a.part + ((int64_t)(qh0 + h) * a.nchunks_cap + (live ? c : c0)) * (D + 2);
+                cm[h][b] = live ? __ldcg(p + D) : -INFINITY;
+                cl[h][b] = live ? __ldcg(p + D + 1) : 0.f;
                 const float2* src = (const float2*)(p + lane * DL);
 #pragma unroll
-                for (int i = 0; i < DL / 2; i++) cv[b][i] = __ldcg(src + i);
+                for (int i = 0; i < DL / 2; i++) cv[h][b][i] = __ldcg(src + i);
             }
-            float bm = m;
 #pragma unroll
-            for (int b = 0; b < MB; b++) bm = fmaxf(bm, cm[b]);
+        for (int h = 0; h < GQ; h++) {
+            float bm = m[h];
+#pragma unroll
+            for (int b = 0; b < MB; b++) bm = fmaxf(bm, cm[h][b]);
             if (bm == -INFINITY) continue;
-            const float rescale = __expf(m - bm);
-            l *= rescale;
+            const float rescale = __expf(m[h] - bm);
+            l[h] *= rescale;
 #pragma unroll
-            for (int i = 0; i < DL; i++) macc[i] *= rescale;
+            for (int i = 0; i < DL; i++) macc[h][i] *= rescale;
 #pragma unroll
             for (int b = 0; b < MB; b++) {
-                const float w = __expf(cm[b] - bm);
-                l = fmaf(cl[b], w, l);
+                const float w = __expf(cm[h][b] - bm);
+                l[h] = fmaf(cl[h][b], w, l[h]);
 #pragma unroll
                 for (int i = 0; i < DL / 2; i++) {
-                    macc[2 * i] = fmaf(cv[b][i].x, w, macc[2 * i]);
-                    macc[2 * i + 1] = fmaf(cv[b][i].y, w, macc[2 * i + 1]);
+                    macc[h][2 * i] = fmaf(cv[h][b][i].x, w, macc[h][2 * i]);
+                    macc[h][2 * i + 1] = fmaf(cv[h][b][i].y, w, macc[h][2 * i + 1]);
                 }
             }
-            m = bm;
+            m[h] = bm;
         }
-        pk_bar_group(grp);  // the previous head's readers of this scratch are done
-        if (lane == 0) { s.smax[0][warp] = m; s.ssum[0][warp] = l; }
-#pragma unroll
-        for (int i = 0; i < DL; i++) s.red[warp][0][lane * DL + i] = macc[i];
-        pk_bar_group(grp);
-        const float gm = fmaxf(fmaxf(s.smax[0][0], s.smax[0][1]), fmaxf(s.smax[0][2], s.smax[0][3]));
-        float w4[4], denom = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; w++) { w4[w] = __expf(s.smax[0][w] - gm); denom = fmaf(s.ssum[0][w], w4[w], denom); }
-        for (int d = gt; d < D; d += 128)
-            a.att[(int64_t)qh * D + d] =
-                (s.red[0][0][d] * w4[0] + s.red[1][0][d] * w4[1] + s.red[2][0][d] * w4[2] + s.red[3][0][d] * w4[3]) / denom;
     }
+#pragma unroll
+    for (int h = 0; h < GQ; h++) {
+        if (lane == 0) { s.smax[h][warp] = m[h]; s.ssum[h][warp] = l[h]; }
+#pragma unroll
+        for (int i = 0; i < DL; i++) s.red[warp][h][lane * DL + i] = macc[h][i];
+    }
+    pk_bar_group(grp);
+    for (int idx = gt; idx < GQ * D; idx += 128) {
+        const int h = idx / D, d = idx - h * D;
+        const float gm = fmaxf(fmaxf(s.smax[h][0], s.smax[h][1]), fmaxf(s.smax[h][2], s.smax[h][3]));
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float e = __expf(s.smax[h][w] - gm);
+            num = fmaf(s.red[w][h][d], e, num);
+            den = fmaf(s.ssum[h][w], e, den);
+        }
+        s.q[h][d] = fast_div(num, fast_div_by(den));
+    }
+    }
+    }
+    if (!emit) return;
+    pk_bar_group(grp);
+    pk_att_emit<D, GQ>(a, s, qh0, lane, warp);
 }
 
 template <int D, int GQ>
-__global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(const PersistArgs a) {
+__global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(const __grid_constant__ PersistArgs a) {
     extern __shared__ __align__(128) unsigned char psm[];
     PkSmem sm;
     sm.full = (uint64_t*)psm;
@@ -675,8 +827,11 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(const 
     }
     __syncthreads();
 
-    if (warp == PK_CW) {
-        // ---- producer: the whole token's weight pieces of this CTA, in the consumers' order --------
+    if (warp >= PK_CW) {
+        // ---- producers: the whole token's weight pieces of this CTA, in the consumers' order. Warp 8
+        // issues the bulk copies of the 16 row pieces of a slot, warp 9 the cp.async copies of their
+        // scales and biases; both wait for the slot to be free and neither waits for the other.
+        const bool rows_warp = warp == PK_CW;
         uint32_t it = 0;
         bool ok = true;
         for (int li = 0; li < a.nlayers && ok; li++) {
@@ -687,33 +842,60 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(const 
                 const uint32_t* w0 = p == 0 ? L.qkv_w : p == 1 ? L.o_w : p == 2 ? L.gate_w : L.down_w;
                 const uint16_t* s0 = p == 0 ? L.qkv_s : p == 1 ? L.o_s : p == 2 ? L.gate_s : L.down_s;
                 const uint16_t* b0 = p == 0 ? L.qkv_b : p == 1 ? L.o_b : p == 2 ? L.gate_b : L.down_b;
+                const uint32_t* w1 = fuse ? L.up_w : w0;
+                const uint16_t* s1 = fuse ? L.up_s : s0;
+                const uint16_t* b1 = fuse ? L.up_b : b0;
                 const int64_t rowbytes = (int64_t)ph.G * 32;
-                for (int b = blockIdx.x; b < ph.nblk && ok; b += gridDim.x) {
-                    for (int sl = 0; sl < ph.nsl; sl++, it++) {
+                // the consumers' order: (wave of T row blocks, slice, team) - see pk_matvec
+                const int nrb = (int)pk_blocks(ph);
+                const int tshift = nrb >= 4 ? 2 : nrb >= 2 ? 1 : 0;
+                for (int wave = 0; (wave << tshift) < nrb && ok; wave++) {
+                    const int inwave = min(1 << tshift, nrb - (wave << tshift));
+                    for (int sl = 0; sl < ph.nsl && ok; sl++) {
+                      for (int k = 0; k < inwave; k++, it++) {
+                        const int b = blockIdx.x + ((wave << tshift) + k) * gridDim.x;
                         const int slot = it % nslots;
                         ok = __all_sync(0xffffffffu, pk_wait(&sm.empty[slot], ((it / nslots) & 1) ^ 1, sm.abort, a, PK_ST_SLOT_EMPTY));
                         if (!ok) break;
                         const int g0 = sl * ph.KS, ks = min(ph.KS, ph.G - g0), RS = pk_row_stride(ks);
                         unsigned char* sb = sm.ring + (size_t)slot * PK_SLOT_BYTES;
-                        if (lane == 0) mbar_expect_tx(&sm.full[slot], (uint32_t)(16 * ks * 32));
-                        __syncwarp();
-                        if (lane < 16) {
-                            const bool second = fuse && lane >= 8;
-                            const int64_t grow = fuse ? (int64_t)b * 8 + (lane & 7) : (int64_t)b * 16 + lane;
-                            const unsigned char* src = (const unsigned char*)(second ? L.up_w : w0) + grow * rowbytes + (int64_t)g0 * 32;
-                            bulk_g2s(sb + (size_t)lane * RS, src, (uint32_t)(ks * 32), &sm.full[slot]);
-                        }
-                        // scales and biases of the piece: ks/2 words per row and tensor, one cp.async each
-                        const int wpr = ks >> 1;
-                        for (int i = lane; i < 16 * wpr; i += 32) {
-                            const int r = i / wpr, w = i - r * wpr;
+                        if (rows_warp) {
+                            if (lane == 0) mbar_expect_tx(&sm.full[slot], (uint32_t)(16 * ks * 32));
+                            __syncwarp();
+                            if (lane < 16) {
+                                const bool second = fuse && lane >= 8;
+                                const int64_t grow = fuse ? (int64_t)b * 8 + (lane & 7) : (int64_t)b * 16 + lane;
+                                const unsigned char* src = (const unsigned char*)(second ? w1 : w0) + grow * rowbytes + (int64_t)g0 * 32;
+                                bulk_g2s(sb + (size_t)lane * RS, src, (uint32_t)(ks * 32), &sm.full[slot]);
+                            }
+                        } else {
+                            // Lane l copies for row l & 15 the units l >> 4, (l >> 4) + 2, ... of the row's scales and
+                            // biases: units of 8 bytes (4 groups) where the piece allows it, of 4 bytes otherwise.
+                            // Nothing but additions per unit - this warp sets the pace of the ring.
+                            const bool wide = ((ks | g0 | ph.G) & 3) == 0;
+                            const int ug = wide ? 4 : 2, upr = ks / ug;
+                            const int r = lane & 15;
                             const bool second = fuse && r >= 8;
                             const int64_t grow = fuse ? (int64_t)b * 8 + (r & 7) : (int64_t)b * 16 + r;
-                            const int64_t e = grow * ph.G + g0 + 2 * w;
-                            pk_cp_async4(sb + PK_SB_OFF + (size_t)(r * ks + 2 * w) * 2, (second ? L.up_s : s0) + e);
-                            pk_cp_async4(sb + PK_SB_OFF + PK_SB_HALF + (size_t)(r * ks + 2 * w) * 2, (second ? L.up_b : b0) + e);
+                            const uint16_t* ps = (second ? s1 : s0) + grow * ph.G + g0;
+                            const uint16_t* pb = (second ? b1 : b0) + grow * ph.G + g0;
+                            unsigned char* d = sb + PK_SB_OFF + (size_t)r * ks * 2;
+                            if (wide) {
+#pragma unroll 6
+                                for (int u = lane >> 4; u < upr; u += 2) {
+                                    pk_cp_async8(d + u * 8, ps + u * 4);
+                                    pk_cp_async8(d + PK_SB_HALF + u * 8, pb + u * 4);
+                                }
+                            } else {
+#pragma unroll 4
+                                for (int u = lane >> 4; u < upr; u += 2) {
+                                    pk_cp_async4(d + u * 4, ps + u * 2);
+                                    pk_cp_async4(d + PK_SB_HALF + u * 4, pb + u * 2);
+                                }
+                            }
+                            pk_cp_async_arrive(&sm.full[slot]);
                         }
-                        pk_cp_async_arrive(&sm.full[slot]);
+                      }
                     }
                 }
             }
@@ -738,48 +920,64 @@ __global__ void __launch_bounds__(PK_THREADS, 1) decode_persistent_kernel(const 
     // ---- consumers --------------------------------------------------------------------------------
     using Att = PkAttSmem<D, GQ>;
     Att* att_s = (Att*)sm.dig;  // two of them; the digits are dead during the attention phase
-    uint32_t it = 0, rbi = 0, epoch = 0;
+    uint32_t it = 0, epoch = 0;
     const float* hcur = a.h0;
     float* halt = a.h1;
     const int pos = a.row_pos[0];
     const int64_t lane_off = (int64_t)a.row_lane[0] * a.lane_stride;
     constexpr int CH = 16 * (512 / D > 0 ? 512 / D : 1);
     const int used = min(a.nchunks_cap, (pos + CH) / CH);
-    const int Gq = (a.Hq * D) >> 6, Gf = a.F >> 6;
+    const int Gh = a.H >> 6, Gq = (a.Hq * D) >> 6, Gf = a.F >> 6;
+    PkNormW nw;
+    pk_norm_prefetch(nw, nullptr, a.layers[0].n_input, Gh, lane, warp);
     for (int li = 0; li < a.nlayers; li++) {
         const PersistLayer& L = a.layers[li];
-        // q|k|v
-        if (li == 0) {
-            pk_norm_prologue(sm, a, nullptr, hcur, nullptr, nullptr, L.n_input, lane, warp);
-        } else {
-            pk_norm_prologue(sm, a, a.a, hcur, halt, a.layers[li - 1].n_post_ff, L.n_input, lane, warp);
-            const float* t = hcur; hcur = halt; halt = (float*)t;
-        }
-        pk_matvec(sm, a, a.ph[0], false, a.qkv, nslots, it, rbi, lane, warp);
-        const bool live = pk_grid_barrier(a, epoch, sm.abort, sm.okflag);
-        // attention (the barrier's verdict is the same for every thread of the CTA)
+        // q|k|v: the previous block's post-FFN norm and residual add (none for the first block), this block's input norm
+        pk_norm_prologue(sm, a, li ? a.a : nullptr, hcur, halt, nw, lane, warp);
+        if (li) { const float* t = hcur; hcur = halt; halt = (float*)t; }
+        pk_matvec(sm.full, sm.empty, sm.abort, sm.part, sm.dig, sm.ring, a, a.ph[0], false, a.qkv, nslots, it);
+        it += pk_blocks(a.ph[0]) * a.ph[0].nsl;
+        pk_grid_arrive(a, sm.abort);
+        const bool live = pk_grid_wait(a, epoch, sm.abort, sm.okflag);
+        // attention (the barrier's verdict is the same for every thread of the CTA); leaves the digit
+        // planes of its output in global memory
         if (live) {
             const int grp = warp >> 2;
             const int nitems = a.Hkv * used;
             for (int i = blockIdx.x * 2 + grp; i < nitems; i += gridDim.x * 2)
                 pk_attention_item<D, GQ>(a, L, att_s[grp], grp, i % a.Hkv, i / a.Hkv, used, pos, lane_off);
         }
-        pk_grid_barrier(a, epoch, sm.abort, sm.okflag);
+        pk_grid_arrive(a, sm.abort);
+        pk_norm_prefetch(nw, L.n_post_attn, L.n_pre_ff, Gh, lane, warp);  // for the gate|up phase, while the grid gathers
+        pk_grid_wait(a, epoch, sm.abort, sm.okflag);
         // o
-        pk_prepare_digits(sm, a.att, false, Gq, 1.f, nullptr, lane, warp);
-        pk_matvec(sm, a, a.ph[1], false, a.a, nslots, it, rbi, lane, warp);
-        pk_grid_barrier(a, epoch, sm.abort, sm.okflag);
-        // gate | up
+        pk_digits_from_global(sm, a.dig_att, Gq);
+        pk_matvec(sm.full, sm.empty, sm.abort, sm.part, sm.dig, sm.ring, a, a.ph[1], false, a.a, nslots, it);
+        it += pk_blocks(a.ph[1]) * a.ph[1].nsl;
+        pk_grid_arrive(a, sm.abort);
+        pk_grid_wait(a, epoch, sm.abort, sm.okflag);
+        // gate | up: post-attention norm + residual add, pre-FFN norm
         {
-            pk_norm_prologue(sm, a, a.a, hcur, halt, L.n_post_attn, L.n_pre_ff, lane, warp);
+            pk_norm_prologue(sm, a, a.a, hcur, halt, nw, lane, warp);
             const float* t = hcur; hcur = halt; halt = (float*)t;
         }
-        pk_matvec(sm, a, a.ph[2], true, a.act, nslots, it, rbi, lane, warp);
-        pk_grid_barrier(a, epoch, sm.abort, sm.okflag);
+        pk_matvec(sm.full, sm.empty, sm.abort, sm.part, sm.dig, sm.ring, a, a.ph[2], true, a.act, nslots, it);
+        it += pk_blocks(a.ph[2]) * a.ph[2].nsl;
+        pk_grid_arrive(a, sm.abort);
+        pk_grid_wait(a, epoch, sm.abort, sm.okflag);
+        // the GeGLU vector -> digit planes: every CTA converts its share, then all of them read the whole
+        pk_digitise_share(a.act, a.dig_act, Gf, lane, warp);
+        pk_grid_arrive(a, sm.abort);
+        if (li + 1 < a.nlayers) pk_norm_prefetch(nw, L.n_post_ff, a.layers[li + 1].n_input, Gh, lane, warp);
+        pk_grid_wait(a, epoch, sm.abort, sm.okflag);
         // down
-        pk_prepare_digits(sm, a.act, false, Gf, 1.f, nullptr, lane, warp);
-        pk_matvec(sm, a, a.ph[3], false, a.a, nslots, it, rbi, lane, warp);
-        if (li + 1 < a.nlayers) pk_grid_barrier(a, epoch, sm.abort, sm.okflag);
+        pk_digits_from_global(sm, a.dig_act, Gf);
+        pk_matvec(sm.full, sm.empty, sm.abort, sm.part, sm.dig, sm.ring, a, a.ph[3], false, a.a, nslots, it);
+        it += pk_blocks(a.ph[3]) * a.ph[3].nsl;
+        if (li + 1 < a.nlayers) {
+            pk_grid_arrive(a, sm.abort);
+            pk_grid_wait(a, epoch, sm.abort, sm.okflag);
+        }
     }
 }
 
@@ -788,7 +986,9 @@ static PersistPhase pk_phase(int64_t N, int64_t K, bool fuse) {
     PersistPhase p{};
     p.G = (int)(K >> 6);
     p.nsl = (p.G + PERSIST_SLOT_G - 1) / PERSIST_SLOT_G;
-    p.KS = ((p.G + p.nsl - 1) / p.nsl + 1) & ~1;
+    // slices of a multiple of four groups where the row allows it: their scales move as 8-byte copies
+    const int unit = (p.G & 3) == 0 ? 4 : 2;
+    p.KS = ((p.G + p.nsl - 1) / p.nsl + unit - 1) / unit * unit;
     p.nsl = (p.G + p.KS - 1) / p.KS;
     p.nblk = (int)(fuse ? N / 8 : N / 16);
     return p;
@@ -805,8 +1005,11 @@ bool persist_supported(int H, int Hq, int Hkv, int D, int F, std::string* why) {
     const int64_t Kq = (int64_t)Hq * D, Nqkv = (int64_t)(Hq + 2 * Hkv) * D;
     if (H % 128 || Kq % 128 || F % 128) return no("hidden, q width and ffn must be multiples of 128");
     if (H % 16 || Nqkv % 16 || F % 8) return no("row counts must be multiples of 16");
+    if (H > 64 * PK_CW * PK_NV) return no("hidden wider than 5632");
     return true;
 }
+
+size_t persist_digit_bytes(int Hq, int D, int F) { return (size_t)std::max(Hq * D, F) / 64 * 200; }
 
 int32_t persist_plan(int H, int Hq, int Hkv, int D, int F, PersistArgs* a, size_t* smem) {
     std::string why;
@@ -816,9 +1019,9 @@ int32_t persist_plan(int H, int Hq, int Hkv, int D, int F, PersistArgs* a, size_
     a->ph[1] = pk_phase(H, Kq, false);
     a->ph[2] = pk_phase(F, H, true);
     a->ph[3] = pk_phase(H, F, false);
-    const int Gh = H >> 6, Gmax = std::max({Gh, (int)(Kq >> 6), F >> 6});
+    const int Gmax = std::max({H >> 6, (int)(Kq >> 6), F >> 6});
     size_t dig = (size_t)Gmax * 200;
-    dig = std::max(dig, (((size_t)Gh * 200 + 15) & ~(size_t)15) + (size_t)H * 4);
+    dig = std::max(dig, (((size_t)(H >> 6) * 200 + 15) & ~(size_t)15) + (size_t)H * 4);  // a norm phase also stages the normed vector
     dig = std::max(dig, D == 64 ? pk_att_bytes<64>() : D == 128 ? pk_att_bytes<128>() : pk_att_bytes<256>());
     dig = (dig + 127) & ~(size_t)127;
     a->ring_off = (int)(PK_DIG_OFF + dig);
@@ -862,7 +1065,7 @@ static int32_t pk_launch(cudaStream_t s, const PersistArgs& a, size_t smem) {
     return LTHN_OK;
 }
 
-// a.sync must be zero when the kernel starts (PERSIST_SYNC_WORDS words): the caller clears it on the same stream
+// the sync words are cleared on the same stream before every launch
 int32_t launch_decode_persistent(cudaStream_t s, const PersistArgs& a, size_t smem) {
     LTHN_CUDA_TRY(cudaMemsetAsync(a.sync, 0, PERSIST_SYNC_WORDS * sizeof(uint32_t), s));
     if (a.D == 64) return pk_launch<64>(s, a, smem);

@@ -66,7 +66,7 @@ struct PrefillAttnArgs {
 int32_t launch_prefill_attn(cudaStream_t s, const PrefillAttnArgs& a, int D);
 // ---- all decoder blocks of one token in one cooperative kernel (batch 1, one GPU) -------------
 constexpr int PERSIST_SLOT_G = 44;       // groups of 64 input columns per ring slot at most
-constexpr int PERSIST_SYNC_WORDS = 64;   // [0] grid-barrier arrivals, [2] abort flag, [16 + kv head] attention items done
+constexpr int PERSIST_SYNC_WORDS = 128;  // [0] grid-barrier arrivals, [2] abort flag, [32] finished barrier round, [64 + kv head] attention items done
 struct PersistLayer {
     const uint32_t *qkv_w, *o_w, *gate_w, *up_w, *down_w;
     const uint16_t *qkv_s, *qkv_b, *o_s, *o_b, *gate_s, *gate_b, *up_s, *up_b, *down_s, *down_b;
@@ -79,6 +79,7 @@ struct PersistArgs {
     int nlayers;
     int H, Hq, Hkv, D, F;
     float eps, attn_scale;
+    double inv_h;                        // 1 / H
     const int32_t* row_pos;              // [1] position of the token being decoded
     const int32_t* row_lane;             // [1] its cache lane
     int64_t lane_stride;
@@ -87,7 +88,8 @@ struct PersistArgs {
     float* h0;                           // residual stream at entry (the embedding row); the two buffers alternate
     float* h1;                           //   and after 2*nlayers-1 updates the stream is in h1
     float* qkv;                          // [(Hq+2Hkv)*D]
-    float* att;                          // [Hq*D]
+    unsigned char* dig_att;              // digit planes of the attention output: persist_digit_bytes()
+    unsigned char* dig_act;              // digit planes of the GeGLU vector: persist_digit_bytes()
     float* a;                            // [H]: o / down projection output (the last down output stays here)
     float* act;                          // [F]
     float* part;                         // [Hq][nchunks_cap][D+2] split-KV partials
@@ -97,6 +99,7 @@ struct PersistArgs {
     PersistPhase ph[4];                  // q|k|v, o, gate|up, down
     int nslots, ring_off;
 };
+size_t persist_digit_bytes(int Hq, int D, int F);
 bool persist_supported(int H, int Hq, int Hkv, int D, int F, std::string* why);
 // fills ph / nslots / ring_off and the dynamic shared-memory size
 int32_t persist_plan(int H, int Hq, int Hkv, int D, int F, PersistArgs* a, size_t* smem);

@@ -28,6 +28,7 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <memory>
@@ -87,6 +88,10 @@ struct Linear {
     int64_t N = 0, K = 0;  // local (sharded) shape
 };
 enum { ROLE_Q = 0, ROLE_K, ROLE_V, ROLE_O, ROLE_GATE, ROLE_UP, ROLE_DOWN, ROLE_COUNT };
+// phases of a decode step as the tracer reports them
+enum { PH_EMBED = 0, PH_ATTN, PH_MLP, PH_EXCHANGE, PH_BLOCKS, PH_HEAD, PH_COUNT };
+static const char* const kPhaseName[PH_COUNT] = {"embedding", "attention: q|k|v, norms + rope, sdpa, o", "mlp: norms, gate|up, down",
+                                                 "tensor-parallel exchange", "decoder blocks (one kernel)", "head: final norm, lm_head, argmax"};
 enum { NORM_INPUT = 0, NORM_POST_ATTN, NORM_PRE_FF, NORM_POST_FF, NORM_Q, NORM_K, NORM_COUNT };
 
 struct Layer {
@@ -160,6 +165,17 @@ struct Model {
     bool site_fused[2] = {};    // tensor parallel: the site's norm runs inside the consuming matvec (push mode)
     bool xchg_ready = false;
     bool fuse_norm = false;  // batch 1-2: norms run inside the matvec that consumes them
+    // engine.DecodePhaseTracer: while on, one-row decode steps run kernel by kernel with an event between phases
+    struct PhaseTrace {
+        bool on = false;
+        std::vector<cudaEvent_t> ev;
+        std::vector<int> ends;      // the phase that ends at event i (-1: start of the step)
+        size_t used = 0;
+        double phase_us[PH_COUNT] = {};
+        double gpu_us = 0;
+        int tokens = 0;
+        std::chrono::steady_clock::time_point t0;
+    } trace;
     // batch 1 on one GPU: every decoder block of a token in one cooperative kernel (decode_persistent.cu)
     bool persist_ok = false;
     PersistArgs pk{};
@@ -344,6 +360,33 @@ __global__ void tp_pick_kernel(const float* gathered, int ranks, int rows, int32
 // bf16 split columns in xn_cols when `split` matches what the matvec wants): logits land in
 // m->logits rows 0.., tokens in d_next[logit_row0..]. Vocab-sharded under tensor parallelism: the
 // local best (value, global index) per row is gathered from all ranks.
+// An event on the model's stream that closes `phase` (-1 opens the step); a no-op unless a trace is on.
+static void trace_mark(Model* m, int phase) {
+    auto& t = m->trace;
+    if (!t.on) return;
+    if (t.used == t.ev.size()) {
+        cudaEvent_t e = nullptr;
+        if (cudaEventCreate(&e) != cudaSuccess) { t.on = false; return; }
+        t.ev.push_back(e);
+        t.ends.push_back(phase);
+    }
+    t.ends[t.used] = phase;
+    cudaEventRecord(t.ev[t.used++], m->stream);
+}
+// after the step's stream synchronisation: fold the event spans into the phase totals
+static void trace_collect(Model* m) {
+    auto& t = m->trace;
+    if (!t.on || t.used < 2) { t.used = 0; return; }
+    for (size_t i = 1; i < t.used; i++) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, t.ev[i - 1], t.ev[i]) != cudaSuccess) continue;
+        if (t.ends[i] >= 0) t.phase_us[t.ends[i]] += 1e3 * ms;
+        t.gpu_us += 1e3 * ms;
+    }
+    t.used = 0;
+    t.tokens++;
+}
+
 static int32_t lm_head_pick(Model* m, int rows, int logit_row0, int split) {
     const auto& c = m->c;
     cudaStream_t s = m->stream;
@@ -393,19 +436,24 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
     const bool f1 = small && (tp ? (xg && m->site_fused[1]) : m->fuse_norm);
     float* hcur = m->h;
     float* halt = m->h2;
+    trace_mark(m, -1);
     if ((rc = launch_embed(s, m->d_ids, rows, m->embed.wq, m->embed.s, m->embed.b, H, c.vocab, c.embed_scale, hcur))) return rc;
+    trace_mark(m, PH_EMBED);
     if (m->persist_ok && rows == 1 && (!want_logits || logit_row0 == 0)) {
         // one kernel for all blocks; it leaves the last down-projection output in a and the residual
         // stream in h2 (2*layers-1 updates alternate between h and h2), which is what the lm_head's
         // fused final norm reads
         if ((rc = launch_decode_persistent(s, m->pk, m->pk_smem))) return rc;
+        trace_mark(m, PH_BLOCKS);
         if (!want_logits) return LTHN_OK;
         NormFuse nf{m->a, m->h2, m->h, m->layers[c.layers - 1].norm[NORM_POST_FF], m->final_norm, c.eps};
         QmvCall hc{m->head.wq, m->head.s, m->head.b, nullptr, nullptr, nullptr, m->xn, LTHN_DTYPE_F32, m->logits, LTHN_DTYPE_F32,
                    m->head.N, m->head.K, rows};
         hc.norm = &nf;
         if ((rc = qmv_dispatch(s, hc))) return rc;
-        return launch_argmax(s, m->logits, rows, m->V_l, m->amax_v, m->amax_i, m->d_next, nullptr, 0);
+        rc = launch_argmax(s, m->logits, rows, m->V_l, m->amax_v, m->amax_i, m->d_next, nullptr, 0);
+        trace_mark(m, PH_HEAD);
+        return rc;
     }
     const int split = qmv_split_for(rows, LTHN_DTYPE_F32);
     if (!f1 && (rc = launch_rmsnorm(s, hcur, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, m->xn, rows, H, c.eps, 0, m->xn_cols, split))) return rc;
@@ -450,6 +498,7 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
         if (nchunks > 1) { oc.x_cols = m->att_cols; oc.x_split = split; }  // the merge stage wrote them
         site_out(0, f0, oc);
         if ((rc = qmv_dispatch(s, oc))) return rc;
+        trace_mark(m, PH_ATTN);
         QmvCall gc{L.gate.wq, L.gate.s, L.gate.b, L.up.wq, L.up.s, L.up.b, m->xn, LTHN_DTYPE_F32, m->act, LTHN_DTYPE_F32, L.gate.N, L.gate.K, rows};
         if (f0) {
             nf = site_norm(0, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF]);
@@ -459,6 +508,7 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
                 if ((rc = launch_rmsnorm_gather(s, m->pg[0], hcur, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, m->xn_cols, split))) return rc;
             } else {
                 if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
+                if (tp) trace_mark(m, PH_EXCHANGE);
                 if ((rc = launch_rmsnorm(s, m->a, hcur, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
             }
             gc.x_cols = m->xn_cols; gc.x_split = split;
@@ -467,6 +517,7 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
         QmvCall dc{L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, m->act, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.down.N, L.down.K, rows};
         site_out(1, f1, dc);
         if ((rc = qmv_dispatch(s, dc))) return rc;
+        trace_mark(m, PH_MLP);
         const float* next_norm = li + 1 < c.layers ? m->layers[li + 1].norm[NORM_INPUT] : m->final_norm;
         if (f1) {
             // folded into the next block's QKV matvec (or the lm_head below)
@@ -474,6 +525,7 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
             if ((rc = launch_rmsnorm_gather(s, m->pg[1], hcur, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, m->xn_cols, split))) return rc;
         } else {
             if ((rc = all_reduce(m, m->a, (size_t)rows * H))) return rc;
+            if (tp) trace_mark(m, PH_EXCHANGE);
             if ((rc = launch_rmsnorm(s, m->a, hcur, L.norm[NORM_POST_FF], next_norm, m->xn, rows, H, c.eps, 1, m->xn_cols, split))) return rc;
         }
     }
@@ -484,13 +536,20 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
                    m->head.N, m->head.K, rows};
         hc.norm = &nf;
         if ((rc = qmv_dispatch(s, hc))) return rc;
-        if (!tp) return launch_argmax(s, m->logits, rows, m->V_l, m->amax_v, m->amax_i, m->d_next, nullptr, 0);
+        if (!tp) {
+            rc = launch_argmax(s, m->logits, rows, m->V_l, m->amax_v, m->amax_i, m->d_next, nullptr, 0);
+            trace_mark(m, PH_HEAD);
+            return rc;
+        }
         if ((rc = launch_argmax(s, m->logits, rows, m->V_l, m->amax_v, m->amax_i, m->d_next, m->best_v, m->v0))) return rc;
         LTHN_CUDA_TRY(launch_k(tp_pair_gather_kernel, dim3(1), dim3(64), 0, s, m->pairg, (const float*)m->best_v, m->d_next, rows));
+        trace_mark(m, PH_HEAD);
         return LTHN_OK;
     }
     if (!want_logits) return LTHN_OK;
-    return lm_head_pick(m, rows, logit_row0, split);
+    rc = lm_head_pick(m, rows, logit_row0, split);
+    trace_mark(m, PH_HEAD);
+    return rc;
 }
 
 static int32_t forward_full(Model* m, int rows, int max_ctx, bool want_logits, int logit_row0) {
@@ -558,6 +617,7 @@ static int32_t prefill_chunk(Model* m, int lane, int rows, int pos0, bool last) 
 // max_len so the graph does not depend on the current context length. LTHN_CUDA_NO_GRAPH=1
 // keeps the eager path.
 static int32_t decode_step(Model* m, int rows) {
+    if (m->trace.on) return forward_full(m, rows, m->c.max_len, true, 0);  // events between the phases need separate launches
     if (m->step_graph[rows]) {
         LTHN_CUDA_TRY(cudaGraphLaunch(m->step_graph[rows], m->stream));
         return LTHN_OK;
@@ -754,6 +814,7 @@ static int32_t feed_lane(Model* m, Lane* ln, const int32_t* ids, int n) {
             if ((rc = device_status_read_async(m->stream, (uint32_t*)(hp + 4 * kMaxRows)))) return rc;
         }
         LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));  // the pinned staging is reused by the next chunk
+        if (n == 1) trace_collect(m); else m->trace.used = 0;  // the tracer follows decode steps, not prompts
     }
     ln->next_tok = m->h_pinned[3 * kMaxRows];
     ln->have_next = true;
@@ -1140,9 +1201,10 @@ int32_t lthn_model_finalize(void* model) {
     {
         // the one-kernel decode step serves one row on one GPU, behind the fused final norm of the lm_head
         const auto& c = m->c;
-        const char* env = getenv("LTHN_CUDA_NO_PERSIST");
+        // Off unless LTHN_CUDA_PERSIST=1: measured slower than the kernel chain on both benchmark models so far.
+        const char* env = getenv("LTHN_CUDA_PERSIST");
         std::string why;
-        if (!(env && env[0] == '1') && c.tp_size <= 1 && m->fuse_norm &&
+        if (env && env[0] == '1' && c.tp_size <= 1 && m->fuse_norm &&
             persist_supported(c.hidden, m->Hq_l, m->Hkv_l, c.head_dim, m->F_l, &why)) {
             int32_t rc;
             PersistArgs& a = m->pk;
@@ -1169,10 +1231,13 @@ int32_t lthn_model_finalize(void* model) {
             int chunk_len = 0;
             a.layers = dl; a.nlayers = c.layers;
             a.H = c.hidden; a.Hq = m->Hq_l; a.Hkv = m->Hkv_l; a.D = c.head_dim; a.F = m->F_l;
-            a.eps = c.eps; a.attn_scale = c.attn_scale;
+            a.eps = c.eps; a.attn_scale = c.attn_scale; a.inv_h = 1.0 / (double)c.hidden;
             a.row_pos = m->d_pos; a.row_lane = m->d_lane; a.lane_stride = m->lane_stride; a.max_len = c.max_len;
             a.rope = m->rope;
-            a.h0 = m->h; a.h1 = m->h2; a.qkv = m->qkv; a.att = m->att; a.a = m->a; a.act = m->act; a.part = m->sdpa_part;
+            a.h0 = m->h; a.h1 = m->h2; a.qkv = m->qkv; a.a = m->a; a.act = m->act; a.part = m->sdpa_part;
+            if ((rc = dalloc(m, &a.dig_att, persist_digit_bytes(m->Hq_l, c.head_dim, m->F_l))) ||
+                (rc = dalloc(m, &a.dig_act, persist_digit_bytes(m->Hq_l, c.head_dim, m->F_l))))
+                return rc;
             a.nchunks_cap = sdpa_chunking(c.max_len, c.head_dim, &chunk_len);
             a.sync = sync;
             a.status = device_status_word();
@@ -1199,6 +1264,15 @@ int32_t lthn_model_tp_exchange(void* model, int32_t* mode) {
     return LTHN_OK;
 }
 
+int32_t lthn_model_decode_kernel(void* model, int32_t* mode) {
+    clear_error();
+    Model* m = (Model*)model;
+    LTHN_REQUIRE(m && mode, "lthn_model_decode_kernel: NULL argument");
+    LTHN_REQUIRE(m->finalized, "lthn_model_decode_kernel: model is not finalized");
+    *mode = m->persist_ok ? 1 : 0;
+    return LTHN_OK;
+}
+
 // 0: decode steps have not been captured (yet), 1: they replay a CUDA graph, 2: capture was not
 // possible and steps are launched kernel by kernel
 int32_t lthn_model_graph_state(void* model, int32_t* state) {
@@ -1217,6 +1291,7 @@ int32_t lthn_model_destroy(void* model) {
     cudaStreamSynchronize(m->stream);
     for (auto& g : m->step_graph)
         if (g) cudaGraphExecDestroy(g);
+    for (auto e : m->trace.ev) cudaEventDestroy(e);
     for (int r = 0; r < 8; r++)
         if (m->x_peer[r] && m->x_peer[r] != m->x_base) cudaIpcCloseMemHandle(m->x_peer[r]);
     if (m->x_base) cudaFree(m->x_base);
@@ -1299,6 +1374,50 @@ int32_t lthn_session_decode_greedy(void* session, int32_t max_new, int32_t eos_i
         s->lane.pending = tok;
         s->lane.have_next = false;
         if (eos_id >= 0 && tok == eos_id) break;
+    }
+    return LTHN_OK;
+}
+
+// engine.DecodePhaseTracer.BeginDecodePhaseTrace (engine/session.go:86-98): phase timing for the one-row decode
+// steps that follow on this session's model, until lthn_session_trace_end returns the aggregate
+// (inference.DecodePhaseBudget, inference.go:218-268). A single-flight diagnostic, as in the reference:
+// while it is on, steps are launched kernel by kernel (no graph replay) with an event between phases.
+int32_t lthn_session_trace_begin(void* session) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s != nullptr, "lthn_session_trace_begin: NULL argument");
+    Model* m = s->m;
+    std::lock_guard<std::mutex> lk(m->mu);
+    auto& t = m->trace;
+    t.on = true;
+    t.used = 0;
+    t.tokens = 0;
+    t.gpu_us = 0;
+    for (double& p : t.phase_us) p = 0;
+    t.t0 = std::chrono::steady_clock::now();
+    return LTHN_OK;
+}
+
+int32_t lthn_session_trace_end(void* session, lthn_decode_phase_budget* out) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && out, "lthn_session_trace_end: NULL argument");
+    Model* m = s->m;
+    std::lock_guard<std::mutex> lk(m->mu);
+    auto& t = m->trace;
+    memset(out, 0, sizeof(*out));
+    if (!t.on || t.tokens <= 0) { t.on = false; return LTHN_OK; }  // nothing traced: a zero budget, as the reference returns
+    const double wall_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t.t0).count();
+    t.on = false;
+    out->tokens = t.tokens;
+    out->total_per_token_us = wall_us / t.tokens;
+    out->gpu_per_token_us = t.gpu_us / t.tokens;
+    for (int p = 0; p < PH_COUNT; p++) {
+        if (t.phase_us[p] <= 0) continue;
+        auto& ph = out->phases[out->n_phases++];
+        snprintf(ph.name, sizeof(ph.name), "%s", kPhaseName[p]);
+        ph.per_token_us = t.phase_us[p] / t.tokens;
+        ph.gpu = 1;
     }
     return LTHN_OK;
 }
@@ -1505,6 +1624,7 @@ int32_t lthn_laneset_step(void* set, int32_t* lane_handles, int32_t* tokens, int
             feed[r]->logits_row = r;
         }
         ls->forwards++;
+        trace_collect(m);
         if ((rc = device_status_judge((uint32_t)hp[4 * kMaxRows], m->stream))) return rc;
         // lanes with a sampler draw their token from their row of this forward's logits
         for (int r = 0; r < rows; r++) {

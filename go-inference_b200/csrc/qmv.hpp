@@ -34,6 +34,7 @@ struct NormFuse {
     int na = 1;
     int64_t a_stride = 0;
     const PeerWait* wait = nullptr;  // in device memory
+    double inv_width = 0.0;          // 1 / vector width, set by the launcher
 };
 
 // One decode matvec: y[M,N] = x[M,K] * dequant(W)^T, optionally fused with a second

@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(384) qmv_dp4a_kernel(const Dp4aArgs a) {
 #pragma unroll
             for (int e = 0; e < 64; e++) amax = fmaxf(amax, fabsf(xv[e]));
             const float sx = amax * (1.0f / 127.0f);
-            const float inv = amax > 0.f ? 127.0f / amax : 0.f;
+            const float inv = amax > 0.f ? __fdividef(127.0f, amax) : 0.f;
             const float sx1 = sx * (1.0f / 128.0f);
             int isum = 0;
 #pragma unroll

@@ -41,7 +41,7 @@ int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p) {
     a.W = p.W; a.nblocks = p.nblocks; a.RS = p.RS; a.stg = p.stg;
     a.bs_off = p.bs_off; a.stage_off = p.stage_off;
     a.fuse_norm = c.norm ? 1 : 0;
-    if (c.norm) a.nf = *c.norm;
+    if (c.norm) { a.nf = *c.norm; a.nf.inv_width = 1.0 / (double)c.K; }
     a.npush = c.npush;
     a.push = c.push;
     if (c.npush && (c.y_dtype != LTHN_DTYPE_F32 || p.ks != 1 || c.wq2)) return fail(LTHN_ERR_INVALID, "affine_qmv: pushed results are f32, whole rows, no GeGLU");

@@ -312,16 +312,19 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
             for (int m = 0; m < MT; m++) {
                 double tsum = 0.0;
                 for (int w = 0; w < W; w++) tsum += nsum[m * 16 + w];
-                rms[m] = (float)sqrt(tsum / (double)K + (double)nf.eps);
+                rms[m] = fast_rms(tsum, nf.inv_width, nf.eps);
             }
             asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
+            FastDiv kd[MT];
+#pragma unroll
+            for (int m = 0; m < MT; m++) kd[m] = fast_div_by(rms[m]);
 #pragma unroll
             for (int j = 0; j < J; j++) {
                 const int64_t e0 = (int64_t)(warp * J + j) * 64 + 2 * lane;
 #pragma unroll
                 for (int m = 0; m < MT; m++) {
-                    hv[j][m][0] = __fadd_rn(hv[j][m][0], __fmul_rn(__fdiv_rn(xr[j][m][0], rms[m]), wp[j].x));
-                    hv[j][m][1] = __fadd_rn(hv[j][m][1], __fmul_rn(__fdiv_rn(xr[j][m][1], rms[m]), wp[j].y));
+                    hv[j][m][0] = __fadd_rn(hv[j][m][0], __fmul_rn(fast_div(xr[j][m][0], kd[m]), wp[j].x));
+                    hv[j][m][1] = __fadd_rn(hv[j][m][1], __fmul_rn(fast_div(xr[j][m][1], kd[m]), wp[j].y));
                     if (blockIdx.x == 0) *(float2*)(nf.h_out + (int64_t)m * K + e0) = make_float2(hv[j][m][0], hv[j][m][1]);
                 }
             }
@@ -346,11 +349,11 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
         for (int m = 0; m < MT; m++) {
             double tsum = 0.0;
             for (int w = 0; w < W; w++) tsum += nsum[m * 16 + w];
-            const float rms2 = (float)sqrt(tsum / (double)K + (double)nf.eps);
+            const FastDiv k2 = fast_div_by(fast_rms(tsum, nf.inv_width, nf.eps));
 #pragma unroll
             for (int j = 0; j < J; j++) {
-                xr[j][m][0] = __fmul_rn(__fdiv_rn(hv[j][m][0], rms2), wn[j].x);
-                xr[j][m][1] = __fmul_rn(__fdiv_rn(hv[j][m][1], rms2), wn[j].y);
+                xr[j][m][0] = __fmul_rn(fast_div(hv[j][m][0], k2), wn[j].x);
+                xr[j][m][1] = __fmul_rn(fast_div(hv[j][m][1], k2), wn[j].y);
             }
         }
     }
@@ -367,9 +370,10 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
 #pragma unroll
             for (int m = 0; m < MT; m++) {
                 const float xv[2] = {xr[j][m][0], xr[j][m][1]};
-                const float amax = warp_max(fmaxf(fabsf(xv[0]), fabsf(xv[1])));
+                // non-negative floats order like their bit patterns: one redux instead of five shuffles
+                const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(fabsf(xv[0]), fabsf(xv[1])))));
                 const float sx = amax * (1.0f / 127.0f);
-                const float inv = amax > 0.f ? 127.0f / amax : 0.f;
+                const float inv = amax > 0.f ? __fdividef(127.0f, amax) : 0.f;
                 const float sx1 = sx * (1.0f / 128.0f);
                 int isum = 0;
 #pragma unroll
@@ -391,8 +395,7 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
                     Bw[m * 192 + 64 + off] = (unsigned char)(i1 & 0xff);
                     Bw[m * 192 + 128 + off] = (unsigned char)(i2 & 0xff);
                 }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);
+                isum = __reduce_add_sync(0xffffffffu, isum);
                 if (m == dm) { sx_d = sx; xs_d = (float)isum * (sx * (1.0f / 16384.0f)); }
             }
             __syncwarp();

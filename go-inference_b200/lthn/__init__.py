@@ -76,6 +76,19 @@ class Sampler:
             self.h = None
 
 
+class _PhaseShare(C.Structure):
+    _fields_ = [("name", C.c_char * 48), ("per_token_us", C.c_double), ("gpu", C.c_int32)]
+
+
+class DecodePhaseBudget(C.Structure):
+    """inference.DecodePhaseBudget."""
+    _fields_ = [("tokens", C.c_int32), ("total_per_token_us", C.c_double), ("gpu_per_token_us", C.c_double),
+                ("n_phases", C.c_int32), ("phases", _PhaseShare * 8)]
+
+    def shares(self):
+        return [(self.phases[i].name.decode(), float(self.phases[i].per_token_us), bool(self.phases[i].gpu)) for i in range(self.n_phases)]
+
+
 class ModelConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab",
                                          "group_size", "bits", "max_len", "max_lanes")] + \
@@ -163,6 +176,7 @@ class _Sig:
     lthn_model_weight_bytes = (i32, [vp, C.POINTER(u64)])
     lthn_model_tp_exchange = (i32, [vp, C.POINTER(i32)])
     lthn_model_graph_state = (i32, [vp, C.POINTER(i32)])
+    lthn_model_decode_kernel = (i32, [vp, C.POINTER(i32)])
     lthn_model_destroy = (i32, [vp])
     lthn_tp_unique_id = (i32, [vp])
     lthn_tp_init = (i32, [i32, i32, vp, pvp])
@@ -174,6 +188,8 @@ class _Sig:
     lthn_session_pos = (i32, [vp])
     lthn_session_decode_greedy = (i32, [vp, i32, i32, vp, C.POINTER(i32)])
     lthn_session_logits = (i32, [vp, vp, i64])
+    lthn_session_trace_begin = (i32, [vp])
+    lthn_session_trace_end = (i32, [vp, C.POINTER(DecodePhaseBudget)])
     lthn_session_decode_sampled = (i32, [vp, vp, C.POINTER(SampleParams), i32, vp, i32, vp, C.POINTER(i32)])
     lthn_sampler_create = (i32, [u64, pvp])
     lthn_sampler_destroy = (i32, [vp])
@@ -557,6 +573,13 @@ class Model:
         return int(v.value)
 
     @property
+    def decode_kernel(self):
+        """0: per-op kernel chain, 1: one cooperative kernel per token (one row, one GPU)."""
+        v = C.c_int32()
+        check(lib().lthn_model_decode_kernel(self.h, C.byref(v)))
+        return int(v.value)
+
+    @property
     def graph_state(self):
         """0 decode steps not captured yet, 1 replaying a CUDA graph, 2 capture impossible (eager)."""
         v = C.c_int32()
@@ -609,6 +632,15 @@ class Session:
         check(lib().lthn_session_decode_sampled(self.h, sampler.h, C.byref(params), max_new, st.ctypes.data if st.size else None,
                                                 st.size, out.ctypes.data, C.byref(n)))
         return out[:n.value].copy()
+
+    def trace_begin(self):
+        """engine.DecodePhaseTracer.BeginDecodePhaseTrace; trace_end() is the stop function."""
+        check(lib().lthn_session_trace_begin(self.h))
+
+    def trace_end(self) -> DecodePhaseBudget:
+        out = DecodePhaseBudget()
+        check(lib().lthn_session_trace_end(self.h, C.byref(out)))
+        return out
 
     def logits(self):
         n = self.model.cfg.vocab // max(1, self.model.cfg.tp_size)

@@ -297,6 +297,11 @@ int32_t lthn_model_tp_exchange(void* model, int32_t* mode);
 /* Whether decode steps replay a captured CUDA graph: 0 not captured yet, 1 graph, 2 capture was
  * not possible (kernel-by-kernel launches; LTHN_CUDA_NO_GRAPH=1 forces this). No counterpart in the reference. */
 int32_t lthn_model_graph_state(void* model, int32_t* state);
+/* How a finalized model runs a one-row decode step: 0 a chain of per-op kernels (the default), 1 one
+ * cooperative kernel for all decoder blocks (opt-in with LTHN_CUDA_PERSIST=1 at finalize; one GPU,
+ * two query heads per kv head, head_dim 64 / 128 / 256, hidden <= 5632). Steps of more rows,
+ * prompts and tensor-parallel models always take the chain. No counterpart in the reference. */
+int32_t lthn_model_decode_kernel(void* model, int32_t* mode);
 int32_t lthn_model_destroy(void* model);   /* TokenModel.Close (engine/model.go:30) */
 
 /* model.Load (model/load.go:19-108) for a gemma3-style MLX-affine checkpoint directory: reads
@@ -359,6 +364,25 @@ int32_t lthn_session_logits(void* session, float* logits_host, int64_t n);
 int32_t lthn_session_kv_export(void* session, int32_t layer, int32_t which, void* out_host, size_t out_bytes);
 int32_t lthn_session_kv_import(void* session, int32_t layer, int32_t which, const void* in_host, int32_t tokens);
 int32_t lthn_session_set_state(void* session, int32_t pos, int32_t pending_token);
+/* engine.DecodePhaseTracer (engine/session.go:86-98) with inference.DecodePhaseBudget
+ * (inference.go:218-268): lthn_session_trace_begin turns per-token phase timing on for the one-row
+ * decode steps that follow on this session's model; lthn_session_trace_end turns it off and returns
+ * the averages over the traced steps. While a trace is on, steps run kernel by kernel (no CUDA-graph
+ * replay) with CUDA events between the phases, so total_per_token_us is the traced wall time, not the
+ * untraced speed. Without traced steps the budget is all zeros. A single-flight diagnostic. */
+typedef struct {
+    int32_t tokens;               /* decode steps the aggregate is averaged over */
+    double total_per_token_us;    /* wall time from begin to end, per step */
+    double gpu_per_token_us;      /* device time between the first and the last event of a step */
+    int32_t n_phases;
+    struct {
+        char name[48];
+        double per_token_us;
+        int32_t gpu;              /* 1: device time */
+    } phases[8];
+} lthn_decode_phase_budget;
+int32_t lthn_session_trace_begin(void* session);
+int32_t lthn_session_trace_end(void* session, lthn_decode_phase_budget* budget);
 int32_t lthn_session_close(void* session);
 
 /* ---- sampling: model.Sampler / model.SampleParams (model/sample.go:52-400) ------------------

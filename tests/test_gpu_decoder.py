@@ -375,3 +375,107 @@ def test_gemma_2b_shape_greedy_256_tokens(oracle, monkeypatch):
     assert first_bad is None, f"diverged at step {first_bad}: reference margin {float(margin[first_bad]):.3e}, " \
                               f"min margin so far {float(margin[:first_bad + 1].min()):.3e}"
     s.close(); m.close()
+
+
+# ---- the one-kernel decode step (LTHN_CUDA_PERSIST=1) ------------------------------------------------
+WIDE_2L = dict(layers=2, hidden=2304, q_heads=8, kv_heads=4, head_dim=256, ffn=9216, vocab=4096)
+WIDE_5376 = dict(layers=2, hidden=5376, q_heads=32, kv_heads=16, head_dim=128, ffn=21504, vocab=4096)
+
+
+def _decode_both_ways(lthn, monkeypatch, build, ids, new, layers):
+    outs = {}
+    for mode in ("persist", "chain"):
+        if mode == "persist":
+            monkeypatch.setenv("LTHN_CUDA_PERSIST", "1")
+        else:
+            monkeypatch.delenv("LTHN_CUDA_PERSIST", raising=False)
+        m = build()
+        assert m.decode_kernel == (1 if mode == "persist" else 0)
+        s = m.open_session()
+        s.prefill(ids)
+        toks = s.decode_greedy(new)
+        assert lthn.device_status() == 0
+        kv = [s.kv_export(layer, which) for layer in range(layers) for which in (0, 1)]
+        outs[mode] = (toks.tolist(), kv)
+        s.close(); m.close()
+    return outs
+
+
+@pytest.mark.parametrize("cfg,prompt", [(SMALL, 37), (SMALL, 150), (MID, 70)], ids=["small", "small-2-chunks", "mid-2-chunks"])
+def test_one_kernel_decode_step_matches_kernel_chain_and_oracle(oracle, cfg, prompt, monkeypatch):
+    """Every decoder block of a token in one cooperative kernel against the chain of per-op kernels
+    and against the CPU reference decoder: the same greedy tokens, and cache rows equal up to rare
+    one-ulp flips (norm sums are added in another order, and the kernel divides by multiplying with a
+    refined reciprocal). The longer prompts put more than one key chunk into the attention phase, so
+    the chunk merge by the last item of a kv head runs too."""
+    import lthn
+    monkeypatch.setenv("LTHN_CUDA_PREFILL_F32", "1")
+    w, norms = synth_weights(oracle, lthn, cfg, seed=13, random_norms=True)
+    ids = np.random.default_rng(2).integers(0, cfg["vocab"], prompt).astype(np.int32)
+    new = 40
+    outs = _decode_both_ways(lthn, monkeypatch, lambda: build_device(lthn, cfg, w, norms, prompt + new + 8), ids, new, cfg["layers"])
+    assert outs["persist"][0] == outs["chain"][0]
+    for a, b in zip(outs["persist"][1], outs["chain"][1]):
+        assert a.shape == b.shape and float(np.mean(a != b)) < 2e-2
+        fa, fb = oracle.bf16_to_f32(a), oracle.bf16_to_f32(b)
+        # one bf16 ulp, or (where rotation pairs cancel to almost nothing) f32 noise relative to the row's scale
+        assert np.all(np.abs(fa - fb) <= 2.0 ** -6 * np.abs(fb) + 5e-3 * np.max(np.abs(fb)))
+    od = build_oracle(oracle, cfg, w, norms, prompt + new + 8)
+    want, margin = od.generate(od.forward(ids), new)
+    got = outs["persist"][0]
+    first_bad = next((i for i in range(new) if got[i] != want[i]), None)
+    assert first_bad is None, (first_bad, float(margin[first_bad]))
+
+
+@pytest.mark.parametrize("cfg", [WIDE_2L, WIDE_5376], ids=["2304x9216-d256", "5376x21504-d128"])
+def test_one_kernel_decode_step_at_benchmark_widths(cfg, monkeypatch):
+    """The projection shapes of the two benchmark decoders (two blocks each): input widths of 2304 /
+    9216 and 5376 / 4096 / 21504, i.e. ring slots of one, two, four and eight slices per row block,
+    and both head sizes. Tokens equal the kernel chain's, over a context of several key chunks."""
+    import lthn
+    ids = np.random.default_rng(9).integers(0, cfg["vocab"], 200).astype(np.int32)
+
+    def build():
+        mc = lthn.make_config(cfg["layers"], cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"],
+                              cfg["vocab"], 280, 1)
+        m = lthn.Model(mc)
+        m.synthesize(5, 0.02)
+        m.finalize()
+        return m
+    outs = _decode_both_ways(lthn, monkeypatch, build, ids, 48, cfg["layers"])
+    assert outs["persist"][0] == outs["chain"][0]
+    for a, b in zip(outs["persist"][1], outs["chain"][1]):
+        assert float(np.mean(a != b)) < 2e-2
+
+
+def test_decode_phase_trace(oracle, monkeypatch):
+    """engine.DecodePhaseTracer: begin, decode, end gives the steps traced, a wall time per step, the
+    device time per step and its split into named phases that add up to it; tracing does not change
+    the tokens; an end without traced steps is a zero budget (the reference's _Bad case)."""
+    import lthn
+    cfg = MID
+    w, norms = synth_weights(oracle, lthn, cfg, seed=21)
+    m = build_device(lthn, cfg, w, norms, 128)
+    ids = np.random.default_rng(5).integers(0, cfg["vocab"], 20).astype(np.int32)
+    s = m.open_session()
+    s.prefill(ids)
+    plain = s.decode_greedy(24).tolist()
+    zero = s.trace_end()
+    assert zero.tokens == 0 and zero.total_per_token_us == 0 and zero.n_phases == 0
+    s.prefill(ids)
+    s.trace_begin()
+    traced = s.decode_greedy(24).tolist()
+    b = s.trace_end()
+    assert traced == plain
+    assert b.tokens == 23            # the first token came with the prompt's forward; 23 one-row steps followed
+    assert 0 < b.gpu_per_token_us <= b.total_per_token_us
+    shares = b.shares()
+    print(f"{b.total_per_token_us:.1f} us/step wall, {b.gpu_per_token_us:.1f} us device:", [(n, round(u, 1)) for n, u, _ in shares])
+    names = [n for n, _, _ in shares]
+    assert any(n.startswith("attention") for n in names) and any(n.startswith("mlp") for n in names) and any(n.startswith("head") for n in names)
+    assert all(g for _, _, g in shares)
+    assert abs(sum(u for _, u, _ in shares) - b.gpu_per_token_us) <= 1e-6 * b.gpu_per_token_us + 1e-3
+    # steps after the trace replay the graph again and give the same tokens
+    s.prefill(ids)
+    assert s.decode_greedy(24).tolist() == plain
+    s.close(); m.close()
