@@ -14,6 +14,7 @@
 //  * reductions have a fixed order (no atomics in the value path).
 #include "common.cuh"
 #include "decoder_kernels.hpp"
+#include "attn_item.cuh"
 
 namespace lthn {
 
@@ -667,6 +668,53 @@ __global__ void __launch_bounds__(128) sdpa_merge_kernel(const float* __restrict
         out[((int64_t)row * Hq + qh) * D + d] = o;
         if (cols) store_split(cols, split, row, Hq * D, qh * D + d, o);
     }
+}
+
+// ---- decode attention in one kernel ---------------------------------------------------------
+// Per-head RMSNorm + RoPE of q and of the new key, the KV append, split-KV attention and the merge
+// of the chunk partials (by the last CTA of a kv head to finish, through a counter) in one launch
+// instead of three (qknorm_rope_append, sdpa_decode, sdpa_merge): grid (kv head, key chunk, row).
+// The item itself is attn_item.cuh, shared with the one-kernel decode step.
+template <int D, int GQ>
+__global__ void __launch_bounds__(128) sdpa_fused_kernel(const SdpaFusedArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ AttnItemSmem<D, GQ> s;
+    constexpr int CH = 16 * (512 / D > 0 ? 512 / D : 1);
+    const int kvh = blockIdx.x, chunk = blockIdx.y, row = blockIdx.z;
+    const int pos = a.row_pos[row];
+    const int used = min(a.nchunks, (pos + CH) / CH);
+    if (chunk >= used) return;
+    AttnItemArgs it;
+    it.qkv = a.qkv + (int64_t)row * (a.Hq + 2 * a.Hkv) * D;
+    it.n_q = a.n_q; it.n_k = a.n_k; it.rope = a.rope;
+    const int64_t lane_off = (int64_t)a.row_lane[row] * a.lane_stride;
+    it.kc = a.kcache + lane_off; it.vc = a.vcache + lane_off;
+    it.part = a.part + (int64_t)row * a.Hq * a.nchunks * (D + 2);
+    it.counter = a.counters + (int64_t)row * a.Hkv;
+    it.Hq = a.Hq; it.Hkv = a.Hkv; it.nchunks_cap = a.nchunks; it.max_len = a.max_len;
+    it.eps = a.eps; it.scale = a.scale;
+    attn_item<D, GQ>(it, s, [] { __syncthreads(); },
+                     [&](AttnItemSmem<D, GQ>& sm, int qh0) {
+                         for (int idx = threadIdx.x; idx < GQ * D; idx += 128) {
+                             const int h = idx / D, d = idx - h * D;
+                             const float v = sm.q[h][d];
+                             a.out[((int64_t)row * a.Hq + qh0 + h) * D + d] = v;
+                             if (a.cols) store_split(a.cols, a.split, row, a.Hq * D, (qh0 + h) * D + d, v);
+                         }
+                     },
+                     kvh, chunk, used, pos);
+}
+
+bool sdpa_fused_supported(int Hq, int Hkv, int D) { return Hq == 2 * Hkv && (D == 64 || D == 128 || D == 256); }
+
+int32_t launch_sdpa_fused(cudaStream_t s, const SdpaFusedArgs& a, int rows, int D) {
+    if (!sdpa_fused_supported(a.Hq, a.Hkv, D)) return fail(LTHN_ERR_INVALID, "sdpa_fused: needs two query heads per kv head and head_dim 64, 128 or 256");
+    dim3 grid(a.Hkv, a.nchunks, rows);
+    if (D == 64) LTHN_CUDA_TRY(launch_k(sdpa_fused_kernel<64, 2>, grid, dim3(128), 0, s, a));
+    else if (D == 128) LTHN_CUDA_TRY(launch_k(sdpa_fused_kernel<128, 2>, grid, dim3(128), 0, s, a));
+    else LTHN_CUDA_TRY(launch_k(sdpa_fused_kernel<256, 2>, grid, dim3(128), 0, s, a));
+    return LTHN_OK;
 }
 
 // ---- greedy argmax --------------------------------------------------------------------

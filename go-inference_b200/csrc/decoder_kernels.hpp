@@ -54,6 +54,27 @@ int32_t launch_rmsnorm_rope(cudaStream_t s, const float* x, const float* w, cons
 int sdpa_chunking(int max_ctx, int D, int* chunk_len);
 size_t sdpa_scratch_bytes(int rows, int Hq, int D, int nchunks);
 int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D);
+// Decode attention in one launch: head norms + RoPE, KV append, split-KV attention, merge.
+struct SdpaFusedArgs {
+    const float* qkv;          // [rows, (Hq + 2*Hkv) * D] f32 projection output
+    const float* n_q;          // [D]
+    const float* n_k;
+    const float2* rope;        // [max_len][D/2]
+    const int32_t* row_pos;
+    const int32_t* row_lane;
+    uint16_t* kcache;          // this block's cache
+    uint16_t* vcache;
+    int64_t lane_stride;
+    float* out;                // [rows, Hq, D]
+    float* part;               // [rows, Hq, nchunks, D+2]
+    uint32_t* counters;        // [rows, Hkv], zero between launches (the kernel leaves them zero)
+    int Hq, Hkv, nchunks, max_len;
+    float eps, scale;
+    uint16_t* cols = nullptr;  // optional bf16 split columns of the output
+    int split = 0;
+};
+bool sdpa_fused_supported(int Hq, int Hkv, int D);
+int32_t launch_sdpa_fused(cudaStream_t s, const SdpaFusedArgs& a, int rows, int D);
 // Causal attention of `rows` consecutive prompt positions pos0.. of one cache lane (prefill).
 struct PrefillAttnArgs {
     const float* q;          // [rows, Hq, D] f32, normed and rotated

@@ -177,6 +177,8 @@ struct Model {
         std::chrono::steady_clock::time_point t0;
     } trace;
     // batch 1 on one GPU: every decoder block of a token in one cooperative kernel (decode_persistent.cu)
+    bool attn_fused = false;       // one or two rows: norms + rope + append + attention + merge in one launch
+    uint32_t* att_ctr = nullptr;  // its per-(row, kv head) counters
     bool persist_ok = false;
     PersistArgs pk{};
     size_t pk_smem = 0;
@@ -489,13 +491,19 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
         if ((rc = qmv_dispatch(s, qc))) return rc;
         uint16_t* kc = m->kcache + (int64_t)li * m->layer_stride;
         uint16_t* vc = m->vcache + (int64_t)li * m->layer_stride;
-        if ((rc = launch_qknorm_rope_append(s, m->qkv, L.norm[NORM_Q], L.norm[NORM_K], m->rope, m->d_pos, m->d_lane, m->q, kc, vc,
-                                            rows, m->Hq_l, m->Hkv_l, D, c.eps, m->lane_stride, c.max_len))) return rc;
-        SdpaArgs sa{m->q, kc, vc, m->d_pos, m->d_lane, m->att, m->sdpa_part, m->lane_stride, m->Hq_l, m->Hkv_l, nchunks, chunk_len, c.attn_scale};
-        sa.cols = m->att_cols; sa.split = split;
-        if ((rc = launch_sdpa_decode(s, sa, rows, D))) return rc;
+        if (small && m->attn_fused) {
+            SdpaFusedArgs fa{m->qkv, L.norm[NORM_Q], L.norm[NORM_K], m->rope, m->d_pos, m->d_lane, kc, vc, m->lane_stride, m->att, m->sdpa_part,
+                             m->att_ctr, m->Hq_l, m->Hkv_l, nchunks, c.max_len, c.eps, c.attn_scale};
+            if ((rc = launch_sdpa_fused(s, fa, rows, D))) return rc;
+        } else {
+            if ((rc = launch_qknorm_rope_append(s, m->qkv, L.norm[NORM_Q], L.norm[NORM_K], m->rope, m->d_pos, m->d_lane, m->q, kc, vc,
+                                                rows, m->Hq_l, m->Hkv_l, D, c.eps, m->lane_stride, c.max_len))) return rc;
+            SdpaArgs sa{m->q, kc, vc, m->d_pos, m->d_lane, m->att, m->sdpa_part, m->lane_stride, m->Hq_l, m->Hkv_l, nchunks, chunk_len, c.attn_scale};
+            sa.cols = m->att_cols; sa.split = split;
+            if ((rc = launch_sdpa_decode(s, sa, rows, D))) return rc;
+        }
         QmvCall oc{L.o.wq, L.o.s, L.o.b, nullptr, nullptr, nullptr, m->att, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.o.N, L.o.K, rows};
-        if (nchunks > 1) { oc.x_cols = m->att_cols; oc.x_split = split; }  // the merge stage wrote them
+        if (nchunks > 1 && !(small && m->attn_fused)) { oc.x_cols = m->att_cols; oc.x_split = split; }  // the merge stage wrote them
         site_out(0, f0, oc);
         if ((rc = qmv_dispatch(s, oc))) return rc;
         trace_mark(m, PH_ATTN);
@@ -1197,6 +1205,17 @@ int32_t lthn_model_finalize(void* model) {
         const Layer& L0 = m->layers[0];
         m->fuse_norm = !(env && env[0] == '1') && m->c.tp_size <= 1 && qmv_can_fuse_norm(L0.qkv.N, L0.qkv.K, 2, false) &&
                        qmv_can_fuse_norm(L0.gate.N, L0.gate.K, 1, true) && qmv_can_fuse_norm(m->head.N, m->head.K, 2, false);
+    }
+    {
+        // Opt-in (LTHN_CUDA_ATTN_FUSION=1): measured slower than the three kernels it replaces - every CTA repeats the
+        // head norms in front of its loads, and the merge by the last CTA puts a fence + counter round trip on the tail.
+        const char* env = getenv("LTHN_CUDA_ATTN_FUSION");
+        m->attn_fused = env && env[0] == '1' && sdpa_fused_supported(m->Hq_l, m->Hkv_l, m->c.head_dim);
+        if (m->attn_fused) {
+            int32_t rc;
+            if ((rc = dalloc(m, &m->att_ctr, (size_t)kMaxRows * m->Hkv_l))) return rc;
+            LTHN_CUDA_TRY(cudaMemset(m->att_ctr, 0, (size_t)kMaxRows * m->Hkv_l * sizeof(uint32_t)));
+        }
     }
     {
         // the one-kernel decode step serves one row on one GPU, behind the fused final norm of the lm_head

@@ -479,3 +479,45 @@ def test_decode_phase_trace(oracle, monkeypatch):
     s.prefill(ids)
     assert s.decode_greedy(24).tolist() == plain
     s.close(); m.close()
+
+
+@pytest.mark.parametrize("cfg,prompt", [(SMALL, 30), (SMALL, 200), (MID, 100)], ids=["small", "small-2-chunks", "mid-2-chunks"])
+def test_attention_in_one_launch_equals_three_kernels(oracle, cfg, prompt, monkeypatch):
+    """Decode attention as one launch (LTHN_CUDA_ATTN_FUSION=1 at finalize: head norms + RoPE, KV append,
+    split-KV attention, merge by the last CTA of a kv head) against the three kernels of the default path:
+    the same greedy tokens and the same cache rows up to rare one-ulp flips, with one and with several
+    key chunks, for one-row steps and for a two-lane set (two rows per step)."""
+    import lthn
+    monkeypatch.setenv("LTHN_CUDA_PREFILL_F32", "1")
+    w, norms = synth_weights(oracle, lthn, cfg, seed=17, random_norms=True)
+    ids = np.random.default_rng(4).integers(0, cfg["vocab"], prompt).astype(np.int32)
+    new = 36
+    outs = []
+    for fused in (True, False):
+        if fused:
+            monkeypatch.setenv("LTHN_CUDA_ATTN_FUSION", "1")
+        else:
+            monkeypatch.delenv("LTHN_CUDA_ATTN_FUSION", raising=False)
+        m = build_device(lthn, cfg, w, norms, prompt + new + 8, max_lanes=3)
+        s = m.open_session()
+        s.prefill(ids)
+        toks = s.decode_greedy(new).tolist()
+        kv = [oracle.bf16_to_f32(s.kv_export(layer, which)) for layer in range(cfg["layers"]) for which in (0, 1)]
+        s.close()
+        ls = m.open_lane_set(2)
+        h = [ls.prepare(ids[:prompt - 3], max_new=12), ls.prepare(ids[5:], max_new=12)]
+        lanes = {x: [] for x in h}
+        while True:
+            res = ls.step()
+            if not res:
+                break
+            for hh, tok, _, _ in res:
+                lanes[hh].append(tok)
+        assert lthn.device_status() == 0
+        outs.append((toks, kv, [lanes[x] for x in h]))
+        ls.close(); m.close()
+    assert outs[0][0] == outs[1][0]
+    assert outs[0][2] == outs[1][2]
+    for a, b in zip(outs[0][1], outs[1][1]):
+        assert float(np.mean(a != b)) < 2e-2
+        assert np.all(np.abs(a - b) <= 2.0 ** -6 * np.abs(b) + 5e-3 * np.max(np.abs(b)))
