@@ -1532,6 +1532,130 @@ int32_t lthn_session_kv_import(void* session, int32_t layer, int32_t which, cons
     return LTHN_OK;
 }
 
+// kv.Snapshot support (kv/snapshot.go:98-143, engine/session.go:53-58): token ranges of a layer's cache -
+// what RangeKVBlocks streams block by block and CaptureOptions.BlockStartToken skips a prefix of.
+static int32_t kv_range_check(Session* s, int32_t layer, int32_t token0, int32_t ntokens, bool within_pos, const char* who) {
+    Model* m = s->m;
+    if (layer < 0 || layer >= m->c.layers) return fail(LTHN_ERR_INVALID, std::string(who) + ": layer out of range");
+    if (token0 < 0 || ntokens < 0 || (int64_t)token0 + ntokens > (within_pos ? s->lane.pos : m->c.max_len))
+        return fail(LTHN_ERR_INVALID, std::string(who) + (within_pos ? ": token range reaches past the session's position" : ": token range reaches past the context length"));
+    return LTHN_OK;
+}
+
+int32_t lthn_session_kv_export_range(void* session, int32_t layer, int32_t which, int32_t token0, int32_t ntokens, void* out_host,
+                                     size_t out_bytes) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && (out_host || ntokens == 0), "lthn_session_kv_export_range: NULL argument");
+    int32_t rc;
+    if ((rc = kv_range_check(s, layer, token0, ntokens, true, "lthn_session_kv_export_range"))) return rc;
+    Model* m = s->m;
+    const size_t bytes = (size_t)ntokens * m->KR_l * 2;
+    LTHN_REQUIRE(out_bytes == bytes, "lthn_session_kv_export_range: buffer must hold ntokens*kv_heads*head_dim bf16 values");
+    if (!bytes) return LTHN_OK;
+    const uint16_t* src = (which ? m->vcache : m->kcache) + (int64_t)s->lane.id * m->lane_stride + (int64_t)layer * m->layer_stride +
+                          (int64_t)token0 * m->KR_l;
+    std::lock_guard<std::mutex> lk(m->mu);
+    LTHN_CUDA_TRY(cudaMemcpyAsync(out_host, src, bytes, cudaMemcpyDeviceToHost, m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LTHN_OK;
+}
+
+int32_t lthn_session_kv_import_range(void* session, int32_t layer, int32_t which, int32_t token0, const void* in_host, int32_t ntokens) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && (in_host || ntokens == 0), "lthn_session_kv_import_range: NULL argument");
+    int32_t rc;
+    if ((rc = kv_range_check(s, layer, token0, ntokens, false, "lthn_session_kv_import_range"))) return rc;
+    if (!ntokens) return LTHN_OK;
+    Model* m = s->m;
+    uint16_t* dst = (which ? m->vcache : m->kcache) + (int64_t)s->lane.id * m->lane_stride + (int64_t)layer * m->layer_stride +
+                    (int64_t)token0 * m->KR_l;
+    std::lock_guard<std::mutex> lk(m->mu);
+    LTHN_CUDA_TRY(cudaMemcpyAsync(dst, in_host, (size_t)ntokens * m->KR_l * 2, cudaMemcpyHostToDevice, m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LTHN_OK;
+}
+
+// Under tensor parallelism a rank holds kv_heads/tp of the heads. Every rank calls this with the same
+// arguments; each gets the rows with all heads in model order ([ntokens][kv_heads*head_dim]), gathered
+// with one NCCL all-gather. On a single GPU it is lthn_session_kv_export_range.
+int32_t lthn_session_kv_gather_range(void* session, int32_t layer, int32_t which, int32_t token0, int32_t ntokens, void* out_host,
+                                     size_t out_bytes) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && (out_host || ntokens == 0), "lthn_session_kv_gather_range: NULL argument");
+    Model* m = s->m;
+    const int t = std::max(1, m->c.tp_size);
+    if (t == 1) return lthn_session_kv_export_range(session, layer, which, token0, ntokens, out_host, out_bytes);
+    int32_t rc;
+    if ((rc = kv_range_check(s, layer, token0, ntokens, true, "lthn_session_kv_gather_range"))) return rc;
+    const size_t per = (size_t)ntokens * m->KR_l * 2;  // bytes of one rank's rows
+    LTHN_REQUIRE(out_bytes == per * t, "lthn_session_kv_gather_range: buffer must hold ntokens*kv_heads*head_dim bf16 values of the whole model");
+    if (!per) return LTHN_OK;
+    if (!m->comm) return fail(LTHN_ERR_STATE, "lthn_session_kv_gather_range: the model has no communicator");
+    void* scratch = nullptr;
+    if ((rc = scratch_get(per * t, &scratch, 3))) return rc;
+    const uint16_t* src = (which ? m->vcache : m->kcache) + (int64_t)s->lane.id * m->lane_stride + (int64_t)layer * m->layer_stride +
+                          (int64_t)token0 * m->KR_l;
+    std::vector<uint16_t> all(per * t / 2);
+    {
+        std::lock_guard<std::mutex> lk(m->mu);
+        if ((rc = nccl_check(g_nccl.AllGather(src, scratch, per / 4, kNcclFloat32, m->comm, m->stream), "ncclAllGather"))) return rc;
+        LTHN_CUDA_TRY(cudaMemcpyAsync(all.data(), scratch, per * t, cudaMemcpyDeviceToHost, m->stream));
+        LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    }
+    // [rank][token][local heads] -> [token][rank][local heads]
+    uint16_t* out = (uint16_t*)out_host;
+    const size_t kr = (size_t)m->KR_l;
+    for (int r = 0; r < t; r++)
+        for (int tk = 0; tk < ntokens; tk++)
+            memcpy(out + ((size_t)tk * t + r) * kr, all.data() + ((size_t)r * ntokens + tk) * kr, kr * 2);
+    return LTHN_OK;
+}
+
+// Session.Fork (enginetest/session.go:72-90): a second session on a KV lane of its own that starts as a
+// copy of this one - the cache rows up to the position are copied on the device - and then advances
+// independently.
+int32_t lthn_session_fork(void* session, void** fork) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s && fork, "lthn_session_fork: NULL argument");
+    Model* m = s->m;
+    const int id = lane_acquire(m);
+    if (id < 0) return fail(LTHN_ERR_STATE, "lthn_session_fork: every KV lane is in use");
+    Session* f = new Session{m, s->lane};
+    f->lane.id = id;
+    f->lane.logits_serial = 0;  // the fork has no logits of its own: the model's buffer belongs to the parent's last forward
+    f->lane.samp.reset();
+    {
+        std::lock_guard<std::mutex> lk(m->mu);
+        const size_t bytes = (size_t)s->lane.pos * m->KR_l * 2;
+        for (int li = 0; li < m->c.layers && bytes; li++)
+            for (int which = 0; which < 2; which++) {
+                uint16_t* base = (which ? m->vcache : m->kcache) + (int64_t)li * m->layer_stride;
+                const cudaError_t e = cudaMemcpyAsync(base + (int64_t)id * m->lane_stride, base + (int64_t)s->lane.id * m->lane_stride, bytes,
+                                                      cudaMemcpyDeviceToDevice, m->stream);
+                if (e != cudaSuccess) { lane_release(m, id); delete f; return cuda_fail(e, "cudaMemcpyAsync"); }
+            }
+        const cudaError_t e = cudaStreamSynchronize(m->stream);
+        if (e != cudaSuccess) { lane_release(m, id); delete f; return cuda_fail(e, "cudaStreamSynchronize"); }
+    }
+    *fork = f;
+    return LTHN_OK;
+}
+
+// Session.Reset: forget the sequence; the lane stays with the session.
+int32_t lthn_session_reset(void* session) {
+    clear_error();
+    Session* s = (Session*)session;
+    LTHN_REQUIRE(s != nullptr, "lthn_session_reset: NULL argument");
+    const int id = s->lane.id;
+    s->lane = Lane{};
+    s->lane.id = id;
+    return LTHN_OK;
+}
+
 // After importing every layer: declares the restored length and the token to continue from.
 int32_t lthn_session_set_state(void* session, int32_t pos, int32_t pending_token) {
     clear_error();

@@ -200,6 +200,11 @@ class _Sig:
     lthn_laneset_prepare_sampled = (i32, [vp, vp, i32, i32, vp, i32, C.POINTER(SampleParams), u64, C.POINTER(i32)])
     lthn_session_kv_export = (i32, [vp, i32, i32, vp, sz])
     lthn_session_kv_import = (i32, [vp, i32, i32, vp, i32])
+    lthn_session_kv_export_range = (i32, [vp, i32, i32, i32, i32, vp, C.c_size_t])
+    lthn_session_kv_import_range = (i32, [vp, i32, i32, i32, vp, i32])
+    lthn_session_kv_gather_range = (i32, [vp, i32, i32, i32, i32, vp, C.c_size_t])
+    lthn_session_fork = (i32, [vp, pvp])
+    lthn_session_reset = (i32, [vp])
     lthn_session_set_state = (i32, [vp, i32, i32])
     lthn_session_close = (i32, [vp])
     lthn_laneset_open = (i32, [vp, i32, pvp])
@@ -657,6 +662,41 @@ class Session:
     def kv_import(self, layer, which, data):
         a = np.ascontiguousarray(data, dtype=np.uint16)
         check(lib().lthn_session_kv_import(self.h, layer, which, a.ctypes.data, a.shape[0]))
+
+    def _kr(self, gathered=False):
+        c = self.model.cfg
+        return (c.kv_heads if gathered else c.kv_heads // max(1, c.tp_size)) * c.head_dim
+
+    def kv_export_range(self, layer, which, token0, ntokens, gathered=False):
+        out = np.empty((ntokens, self._kr(gathered)), dtype=np.uint16)
+        fn = lib().lthn_session_kv_gather_range if gathered else lib().lthn_session_kv_export_range
+        check(fn(self.h, layer, which, token0, ntokens, out.ctypes.data, out.nbytes))
+        return out
+
+    def kv_import_range(self, layer, which, token0, data):
+        a = np.ascontiguousarray(data, dtype=np.uint16)
+        check(lib().lthn_session_kv_import_range(self.h, layer, which, token0, a.ctypes.data, a.shape[0]))
+
+    def range_kv_blocks(self, block_size, block_start_token=0):
+        """Session.RangeKVBlocks: yields (index, token_start, token_count, {(layer, which): rows}) for the
+        blocks that end after block_start_token (kv.CaptureOptions.BlockStartToken)."""
+        pos, layers = self.pos, self.model.cfg.layers
+        for index, t0 in enumerate(range(0, pos, block_size)):
+            n = min(block_size, pos - t0)
+            if t0 + n <= block_start_token:
+                continue
+            yield index, t0, n, {(li, w): self.kv_export_range(li, w, t0, n) for li in range(layers) for w in (0, 1)}
+
+    def fork(self) -> "Session":
+        f = Session.__new__(Session)
+        f.model = self.model
+        h = C.c_void_p()
+        check(lib().lthn_session_fork(self.h, C.byref(h)))
+        f.h = h
+        return f
+
+    def reset(self):
+        check(lib().lthn_session_reset(self.h))
 
     def set_state(self, pos, pending):
         check(lib().lthn_session_set_state(self.h, pos, pending))

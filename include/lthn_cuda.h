@@ -364,6 +364,21 @@ int32_t lthn_session_logits(void* session, float* logits_host, int64_t n);
 int32_t lthn_session_kv_export(void* session, int32_t layer, int32_t which, void* out_host, size_t out_bytes);
 int32_t lthn_session_kv_import(void* session, int32_t layer, int32_t which, const void* in_host, int32_t tokens);
 int32_t lthn_session_set_state(void* session, int32_t pos, int32_t pending_token);
+/* kv.Snapshot by token ranges (kv/snapshot.go:98-143; Session.RangeKVBlocks and CaptureOptions.BlockStartToken,
+ * engine/session.go:53-58): rows [token0, token0+ntokens) of a layer's K (which = 0) or V (1), ntokens x
+ * (local kv heads * head_dim) bf16 values. Export reads below the session's position, import may write
+ * anywhere below the context length (follow it with lthn_session_set_state). */
+int32_t lthn_session_kv_export_range(void* session, int32_t layer, int32_t which, int32_t token0, int32_t ntokens, void* out_host,
+                                     size_t out_bytes);
+int32_t lthn_session_kv_import_range(void* session, int32_t layer, int32_t which, int32_t token0, const void* in_host, int32_t ntokens);
+/* The same rows with the kv heads of every tensor-parallel rank, in model order (ntokens x kv_heads *
+ * head_dim): every rank calls it with the same arguments (one NCCL all-gather) and gets the full rows. */
+int32_t lthn_session_kv_gather_range(void* session, int32_t layer, int32_t which, int32_t token0, int32_t ntokens, void* out_host,
+                                     size_t out_bytes);
+/* Session.Fork / Session.Reset (engine/enginetest/session.go:72-105): a copy of the session on a KV lane of
+ * its own (the model needs a free lane); forget the sequence. */
+int32_t lthn_session_fork(void* session, void** fork);
+int32_t lthn_session_reset(void* session);
 /* engine.DecodePhaseTracer (engine/session.go:86-98) with inference.DecodePhaseBudget
  * (inference.go:218-268): lthn_session_trace_begin turns per-token phase timing on for the one-row
  * decode steps that follow on this session's model; lthn_session_trace_end turns it off and returns

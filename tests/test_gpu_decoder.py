@@ -521,3 +521,59 @@ def test_attention_in_one_launch_equals_three_kernels(oracle, cfg, prompt, monke
     for a, b in zip(outs[0][1], outs[1][1]):
         assert float(np.mean(a != b)) < 2e-2
         assert np.all(np.abs(a - b) <= 2.0 ** -6 * np.abs(b) + 5e-3 * np.max(np.abs(b)))
+
+
+def test_kv_ranges_blocks_fork_and_reset(oracle):
+    """kv.Snapshot by token ranges: block-wise export equals slices of the whole-layer export;
+    BlockStartToken skips the trusted prefix; a session restored block by block continues with the
+    tokens of the original; a fork starts as a copy on its own lane and neither side disturbs the
+    other; after a reset the session prefills afresh (engine/enginetest/session.go:54-155)."""
+    import lthn
+    cfg = SMALL
+    w, norms = synth_weights(oracle, lthn, cfg, seed=31)
+    m = build_device(lthn, cfg, w, norms, 160, max_lanes=3)
+    ids = np.random.default_rng(8).integers(0, cfg["vocab"], 45).astype(np.int32)
+    s = m.open_session()
+    s.prefill(ids)
+    whole = {(li, wh): s.kv_export(li, wh) for li in range(cfg["layers"]) for wh in (0, 1)}
+    blocks = list(s.range_kv_blocks(16))
+    assert [(i, t0, n) for i, t0, n, _ in blocks] == [(0, 0, 16), (1, 16, 16), (2, 32, 13)]
+    for _, t0, n, rows in blocks:
+        for key, r in rows.items():
+            assert (r == whole[key][t0:t0 + n]).all()
+    assert [i for i, _, _, _ in s.range_kv_blocks(16, block_start_token=32)] == [2]
+    assert s.kv_export_range(0, 0, 45, 0).shape[0] == 0
+    with pytest.raises(lthn.LthnError):
+        s.kv_export_range(0, 0, 40, 6)          # past the position
+    with pytest.raises(lthn.LthnError):
+        s.kv_export_range(cfg["layers"], 0, 0, 1)
+    # fork: same continuation as the parent, on another lane, in either order
+    f = s.fork()
+    ftoks = f.decode_greedy(12).tolist()
+    stoks = s.decode_greedy(12).tolist()
+    assert ftoks == stoks
+    assert f.pos == s.pos == 45 + 11
+    more_f = f.decode_greedy(5).tolist()
+    # the parent's cache rows are untouched by the fork's extra steps
+    assert (s.kv_export(0, 0)[:45] == whole[(0, 0)]).all()
+    # restore block by block into a fresh session
+    r = m.open_session()
+    for _, t0, n, rows in blocks:
+        for (li, wh), data in rows.items():
+            r.kv_import_range(li, wh, t0, data)
+    r.set_state(45, int(stoks[0]))              # the token the prompt determined is the next one to feed
+    assert r.decode_greedy(11).tolist() == stoks[1:]
+    with pytest.raises(lthn.LthnError):
+        r.kv_import_range(0, 0, 159, np.zeros((2, 2 * 64), dtype=np.uint16))   # past the context length
+    # a third fork finds no free lane (three lanes: s, f, r)
+    with pytest.raises(lthn.LthnError):
+        s.fork()
+    # reset
+    r.reset()
+    assert r.pos == 0
+    r.prefill(ids)
+    assert r.decode_greedy(12).tolist() == stoks
+    assert more_f == s.decode_greedy(5).tolist()
+    for x in (s, f, r):
+        x.close()
+    m.close()

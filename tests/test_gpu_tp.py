@@ -32,7 +32,7 @@ def _free_port():
     return p
 
 
-def _run_model(lthn, cfg, seed, rank, world, comm, ids, new, want_mode=None):
+def _run_model(lthn, cfg, seed, rank, world, comm, ids, new, want_mode=None, kv_out=None):
     mc = lthn.make_config(cfg["layers"], cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"],
                           cfg["vocab"], len(ids) + new, 1, tp_rank=rank, tp_size=world)
     m = lthn.Model(mc)
@@ -44,6 +44,10 @@ def _run_model(lthn, cfg, seed, rank, world, comm, ids, new, want_mode=None):
         assert m.tp_exchange == want_mode, (m.tp_exchange, want_mode)
     s = m.open_session()
     s.prefill(ids)
+    if kv_out is not None:
+        # rows 3..19 of the first layer's keys and values with the kv heads of every rank (one all-gather)
+        kv_out["k"] = s.kv_export_range(0, 0, 3, 17, gathered=True)
+        kv_out["v"] = s.kv_export_range(0, 1, 3, 17, gathered=True)
     toks = s.decode_greedy(new)
     s.close()
     m.close()
@@ -70,13 +74,17 @@ def _worker(rank, world, port, wide, out):
                 res["peer"] = _run_model(lthn, CFG_WIDE, WIDE_SEED, rank, world, comm, ids, WIDE_NEW, want_mode=2).tolist()
             else:
                 ids = np.random.default_rng(4).integers(0, CFG["vocab"], 31).astype(np.int32)
-                res["peer"] = _run_model(lthn, CFG, 21, rank, world, comm, ids, 24, want_mode=2).tolist()
+                kv = {}
+                res["peer"] = _run_model(lthn, CFG, 21, rank, world, comm, ids, 24, want_mode=2, kv_out=kv).tolist()
+                res["kv"] = kv
                 os.environ["LTHN_CUDA_TP_NCCL"] = "1"
                 res["nccl"] = _run_model(lthn, CFG, 21, rank, world, comm, ids, 24, want_mode=1).tolist()
                 del os.environ["LTHN_CUDA_TP_NCCL"]
             if rank == 0:
                 cfg, seed, new = (CFG_WIDE, WIDE_SEED, WIDE_NEW) if wide else (CFG, 21, 24)
-                res["solo"] = _run_model(lthn, cfg, seed, 0, 1, None, ids, new, want_mode=0).tolist()
+                skv = {} if not wide else None
+                res["solo"] = _run_model(lthn, cfg, seed, 0, 1, None, ids, new, want_mode=0, kv_out=skv).tolist()
+                res["solo_kv"] = skv
             lthn.check(lthn.lib().lthn_tp_destroy(comm))
             out.put((rank, res, None))
         finally:
@@ -129,6 +137,13 @@ def test_tp_tokens_equal_single_gpu(world):
     for r in range(world):
         assert res[r]["peer"] == solo, r   # the peer-memory exchange reproduces the single-GPU tokens on every rank
         assert res[r]["nccl"] == solo, r   # and so does the NCCL all-reduce path
+        # the gathered cache rows hold every rank's kv heads in model order: the single-GPU rows, up to rare one-ulp flips
+        for which in ("k", "v"):
+            got, want = res[r]["kv"][which], res[0]["solo_kv"][which]
+            assert got.shape == want.shape == (17, CFG["kv_heads"] * CFG["head_dim"]), (got.shape, want.shape)
+            f = lambda a: (a.astype(np.uint32) << 16).view(np.float32)
+            assert float(np.mean(got != want)) < 2e-2, (r, which, float(np.mean(got != want)))
+            assert np.all(np.abs(f(got) - f(want)) <= 2.0 ** -6 * np.abs(f(want)) + 5e-3 * np.max(np.abs(f(want))))
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
