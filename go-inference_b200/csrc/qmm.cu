@@ -63,6 +63,9 @@ struct QmmArgs {
     uint32_t* status;
     int M, N, K;   // N = output columns
     int y_f32;
+    // split-K (gridDim.z > 1): CTA z works on k-blocks [z*kb_per, (z+1)*kb_per) and stores its f32 partial
+    // sums at y + z*M*N; a second kernel adds the partials
+    int kb_per;
 };
 
 // ---- tcgen05 / TMA wrappers -----------------------------------------------------------
@@ -172,6 +175,8 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * NO, m0 = blockIdx.y * QMM_MT;
     const int KB = a.K / QMM_BK;
+    const int kb_lo = gridDim.z > 1 ? (int)blockIdx.z * a.kb_per : 0;
+    const int kb_hi = gridDim.z > 1 ? min(KB, kb_lo + a.kb_per) : KB;
     bool ok = true;
 
     if (threadIdx.x == 0) {
@@ -195,8 +200,8 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
     if (warp == 0) {
         // ---- TMA producer ------------------------------------------------------------
         if (lane == 0) {
-            for (int kb = 0; kb < KB && ok; kb++) {
-                const int s = kb % STAGES, ph = (kb / STAGES) & 1;
+            for (int kb = kb_lo; kb < kb_hi && ok; kb++) {
+                const int s = (kb - kb_lo) % STAGES, ph = ((kb - kb_lo) / STAGES) & 1;
                 ok = mbar_wait(&empty[s], ph ^ 1);
                 if (!ok) break;
                 mbar_expect_tx(&full_x[s], S::X_BYTES);
@@ -208,8 +213,8 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
         // ---- MMA issuer ----------------------------------------------------------------
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
-            for (int kb = 0; kb < KB && ok; kb++) {
-                const int s = kb % STAGES, ph = (kb / STAGES) & 1;
+            for (int kb = kb_lo; kb < kb_hi && ok; kb++) {
+                const int s = (kb - kb_lo) % STAGES, ph = ((kb - kb_lo) / STAGES) & 1;
                 ok = mbar_wait(&full_x[s], ph) && mbar_wait(&full_w[s], ph);
                 if (!ok) break;
                 tc_fence_after();
@@ -220,7 +225,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
 #pragma unroll
                     for (int j = 0; j < 4; j++)
                         umma_bf16(tmem_base + h * NT, umma_desc(xs + h * 128 * 128 + j * 32), umma_desc(ws + j * 32), idesc,
-                                  (kb > 0 || j > 0) ? 1u : 0u);
+                                  (kb > kb_lo || j > 0) ? 1u : 0u);
                 umma_commit(&empty[s]);
             }
             if (ok) umma_commit(accum_full);
@@ -249,10 +254,10 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
             }
             sb = (uint32_t)__ldg(sp + kb) | ((uint32_t)__ldg(bp + kb) << 16);
         };
-        load_kb(0, wcur, sbcur);
-        for (int kb = 0; kb < KB && ok; kb++) {
-            const int s = kb % STAGES, ph = (kb / STAGES) & 1;
-            if (kb + 1 < KB) load_kb(kb + 1, wnxt, sbnxt);
+        load_kb(kb_lo, wcur, sbcur);
+        for (int kb = kb_lo; kb < kb_hi && ok; kb++) {
+            const int s = (kb - kb_lo) % STAGES, ph = ((kb - kb_lo) / STAGES) & 1;
+            if (kb + 1 < kb_hi) load_kb(kb + 1, wnxt, sbnxt);
             ok = mbar_wait(&empty[s], ph ^ 1);
             if (!ok) break;
             const uint32_t s2 = (sbcur & 0xffffu) | (sbcur << 16);
@@ -293,7 +298,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
                 }
                 if (m < a.M) {
                     if (a.y_f32) {
-                        float* yrow = (float*)a.y + (int64_t)m * a.N + n0 + c0;
+                        float* yrow = (float*)a.y + (gridDim.z > 1 ? (int64_t)blockIdx.z * a.M * a.N : 0) + (int64_t)m * a.N + n0 + c0;
                         if (n0 + c0 + 32 <= a.N && (((uintptr_t)yrow) & 15) == 0) {
 #pragma unroll
                             for (int v = 0; v < 8; v++)
@@ -347,8 +352,27 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// adds the split-K partial sums [splits][n] (f32) in split order; out: f32 or bf16
+__global__ void qmm_splitk_sum_kernel(const float* __restrict__ part, int splits, int64_t n, void* __restrict__ out, int out_f32) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    float4 acc = *(const float4*)(part + i);
+    for (int z = 1; z < splits; z++) {
+        const float4 v = *(const float4*)(part + (int64_t)z * n + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (out_f32) {
+        *(float4*)((float*)out + i) = acc;
+    } else {
+        uint2 o;
+        o.x = (uint32_t)f32_to_bf16_bits(acc.x) | ((uint32_t)f32_to_bf16_bits(acc.y) << 16);
+        o.y = (uint32_t)f32_to_bf16_bits(acc.z) | ((uint32_t)f32_to_bf16_bits(acc.w) << 16);
+        *(uint2*)((uint16_t*)out + i) = o;
+    }
+}
+
 template <int NT, int GEGLU>
-static int32_t launch_qmm(cudaStream_t s, const CUtensorMap& map, const QmmArgs& a) {
+static int32_t launch_qmm(cudaStream_t s, const CUtensorMap& map, const QmmArgs& a, int splits = 1) {
     static int attr_dev = -1;
     static std::mutex mu;
     int dev = 0;
@@ -361,7 +385,7 @@ static int32_t launch_qmm(cudaStream_t s, const CUtensorMap& map, const QmmArgs&
         }
     }
     constexpr int NO = GEGLU ? NT / 2 : NT;
-    dim3 grid((a.N + NO - 1) / NO, (a.M + QMM_MT - 1) / QMM_MT);
+    dim3 grid((a.N + NO - 1) / NO, (a.M + QMM_MT - 1) / QMM_MT, splits);
     qmm_tcgen05_kernel<NT, GEGLU><<<grid, QMM_THREADS, QmmSmem<NT>::TOTAL, s>>>(map, a);
     LTHN_CUDA_TRY(cudaGetLastError());
     return LTHN_OK;
@@ -382,7 +406,7 @@ int32_t qmm_launch(cudaStream_t s, const QmmCall& c) {
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(LTHN_ERR_CUDA, "affine_qmm: cuTensorMapEncodeTiled failed (" + std::to_string((int)cr) + ")");
-    QmmArgs a{c.wq, c.scales, c.biases, c.wq2, c.scales2, c.biases2, c.y, device_status_word(), c.M, (int)c.N, (int)c.K, c.y_f32};
+    QmmArgs a{c.wq, c.scales, c.biases, c.wq2, c.scales2, c.biases2, c.y, device_status_word(), c.M, (int)c.N, (int)c.K, c.y_f32, 0};
     if (!a.status) return fail(LTHN_ERR_CUDA, "affine_qmm: no device status word");
     const int64_t mt = (c.M + QMM_MT - 1) / QMM_MT;
     // Tile width by wave efficiency: one CTA per SM, so a grid of T tiles takes ceil(T/SMs) waves
@@ -400,6 +424,27 @@ int32_t qmm_launch(cudaStream_t s, const QmmCall& c) {
     int nt = e256 >= e128 ? 256 : 128;
     if (g_force_nt == 128 || g_force_nt == 256) nt = g_force_nt;
     if (c.wq2) return nt == 256 ? launch_qmm<256, 1>(s, map, a) : launch_qmm<128, 1>(s, map, a);
+    // Split-K when the output has too few tiles to fill the GPU (the long-K, narrow projections of a
+    // short prompt: 2304 x 9216 with 512 tokens is 36 tiles): z CTAs per tile each take a slice of at
+    // least 16 k-blocks and leave f32 partial sums that a second kernel adds in slice order.
+    const int64_t tiles = ((c.N + (nt == 256 ? 256 : 128) - 1) / (nt == 256 ? 256 : 128)) * mt;
+    const int KB = (int)(c.K / QMM_BK);
+    int splits = (int)std::min<int64_t>({4, sms / std::max<int64_t>(tiles, 1), KB / 16});
+    if (splits >= 2 && ((int64_t)c.M * c.N) % 4 == 0) {
+        a.kb_per = (KB + splits - 1) / splits;
+        splits = (KB + a.kb_per - 1) / a.kb_per;
+        void* part = nullptr;
+        int32_t rc;
+        if ((rc = scratch_get((size_t)splits * c.M * c.N * sizeof(float), &part, 0))) return rc;
+        QmmArgs pa = a;
+        pa.y = part;
+        pa.y_f32 = 1;
+        if ((rc = nt == 256 ? launch_qmm<256, 0>(s, map, pa, splits) : launch_qmm<128, 0>(s, map, pa, splits))) return rc;
+        const int64_t n = (int64_t)c.M * c.N;
+        qmm_splitk_sum_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>((const float*)part, splits, n, c.y, c.y_f32);
+        LTHN_CUDA_TRY(cudaGetLastError());
+        return LTHN_OK;
+    }
     return nt == 256 ? launch_qmm<256, 0>(s, map, a) : launch_qmm<128, 0>(s, map, a);
 }
 
