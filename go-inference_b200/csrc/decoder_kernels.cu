@@ -461,8 +461,9 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int l8 = lane & 7, pg = warp * 4 + (lane >> 3);  // position group 0..15
     const int ctx = a.row_pos[row] + 1;                    // keys 0..pos inclusive
+    const int lo = a.window > 0 ? max(0, ctx - a.window) : 0;  // sliding block: keys lo..pos
     const int p0 = chunk * (16 * NIT);
-    if (p0 >= ctx) return;
+    if (p0 >= ctx || p0 + 16 * NIT <= lo) return;
     const int KR = a.Hkv * D;
     const uint16_t* kbase = a.kcache + (int64_t)a.row_lane[row] * a.lane_stride + (int64_t)kvh * D;
     const uint16_t* vbase = a.vcache + (int64_t)a.row_lane[row] * a.lane_stride + (int64_t)kvh * D;
@@ -473,8 +474,8 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
 #pragma unroll
     for (int i = 0; i < NIT; i++) {
         const int p = p0 + pg + 16 * i;
-        valid[i] = p < ctx;
-        const int64_t off = (int64_t)(valid[i] ? p : p0) * KR;
+        valid[i] = p < ctx && p >= lo;
+        const int64_t off = (int64_t)(valid[i] ? p : min(max(p0, lo), ctx - 1)) * KR;
 #pragma unroll
         for (int v = 0; v < V8; v++) {
             kreg[i][v] = __ldg((const uint4*)(kbase + off + (v * 8 + l8) * 8));
@@ -608,7 +609,7 @@ template <int D>
 __global__ void __launch_bounds__(128) sdpa_merge_kernel(const float* __restrict__ part,
                                                          const int32_t* __restrict__ row_pos, int Hq, int nchunks,
                                                          int chunk_len, float* __restrict__ out,
-                                                         uint16_t* __restrict__ cols, int split) {
+                                                         uint16_t* __restrict__ cols, int split, int window) {
     pdl_trigger();
     pdl_wait();
     constexpr int DL = D / 32;  // dimensions per lane (2, 4, 8 or 16)
@@ -617,11 +618,12 @@ __global__ void __launch_bounds__(128) sdpa_merge_kernel(const float* __restrict
     const int row = blockIdx.y, qh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int ctx = row_pos[row] + 1;
     const int used = min(nchunks, (ctx + chunk_len - 1) / chunk_len);
+    const int first = window > 0 ? max(0, ctx - window) / chunk_len : 0;  // chunks below the window wrote nothing
     const float* pa = part + ((int64_t)row * Hq + qh) * nchunks * (D + 2);
     float m = -INFINITY, l = 0.f, acc[DL];
 #pragma unroll
     for (int i = 0; i < DL; i++) acc[i] = 0.f;
-    for (int c0 = warp; c0 < used; c0 += 4 * MERGE_BATCH) {
+    for (int c0 = first + warp; c0 < used; c0 += 4 * MERGE_BATCH) {
         float cm[MERGE_BATCH], cl[MERGE_BATCH];
         float2 cv[MERGE_BATCH][DL / 2];
 #pragma unroll
@@ -858,10 +860,10 @@ int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D) {
     if (a.nchunks > 1) {
         dim3 grid(a.Hq, rows);
         const float* cpart = a.part;
-        if (D == 64) LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<64>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split));
-        else if (D == 128) LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<128>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split));
-        else if (D == 256) LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<256>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split));
-        else LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<512>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split));
+        if (D == 64) LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<64>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split, a.window));
+        else if (D == 128) LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<128>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split, a.window));
+        else if (D == 256) LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<256>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split, a.window));
+        else LTHN_CUDA_TRY(launch_k(sdpa_merge_kernel<512>, grid, dim3(128), 0, s, cpart, a.row_pos, a.Hq, a.nchunks, a.chunk_len, a.out, a.cols, a.split, a.window));
     }
     return LTHN_OK;
 }

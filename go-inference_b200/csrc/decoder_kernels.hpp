@@ -24,6 +24,7 @@ struct SdpaArgs {
     float scale;
     uint16_t* cols = nullptr;  // optional bf16 split columns of the output (written by the merge stage)
     int split = 0;
+    int window = 0;            // > 0: a row attends only its last `window` keys (sliding-attention block)
 };
 
 int32_t launch_embed(cudaStream_t s, const int32_t* ids, int rows, const uint32_t* packed, const uint16_t* scales,
@@ -83,6 +84,7 @@ struct PrefillAttnArgs {
     uint16_t* out;           // [rows, Hq, D] bf16
     int rows, pos0, Hq, Hkv;
     float scale_log2e;       // softmax scale times log2(e)
+    int window = 0;          // > 0: a row attends only its last `window` keys
 };
 int32_t launch_prefill_attn(cudaStream_t s, const PrefillAttnArgs& a, int D);
 // ---- all decoder blocks of one token in one cooperative kernel (batch 1, one GPU) -------------

@@ -127,6 +127,7 @@ struct Model {
     bool have_embed = false;
     float* final_norm = nullptr;
     float2* rope = nullptr;
+    float2* rope_local = nullptr;  // sliding-attention blocks rotate with rope_local_base
     uint16_t *kcache = nullptr, *vcache = nullptr;
     int64_t lane_stride = 0, layer_stride = 0;
     std::vector<char> lane_used;
@@ -362,6 +363,12 @@ __global__ void tp_pick_kernel(const float* gathered, int ranks, int rows, int32
 // bf16 split columns in xn_cols when `split` matches what the matvec wants): logits land in
 // m->logits rows 0.., tokens in d_next[logit_row0..]. Vocab-sharded under tensor parallelism: the
 // local best (value, global index) per row is gathered from all ranks.
+// gemma3 layer types (model/arch/google/gemma3/gemma3.go:111-122): block i is global when (i+1) % pattern == 0
+static inline int layer_window(const Model* m, int li) {
+    return (m->c.sliding_window > 0 && (li + 1) % m->c.sliding_pattern != 0) ? m->c.sliding_window : 0;
+}
+static inline const float2* layer_rope(const Model* m, int li) { return layer_window(m, li) ? m->rope_local : m->rope; }
+
 // An event on the model's stream that closes `phase` (-1 opens the step); a no-op unless a trace is on.
 static void trace_mark(Model* m, int phase) {
     auto& t = m->trace;
@@ -492,14 +499,14 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
         uint16_t* kc = m->kcache + (int64_t)li * m->layer_stride;
         uint16_t* vc = m->vcache + (int64_t)li * m->layer_stride;
         if (small && m->attn_fused) {
-            SdpaFusedArgs fa{m->qkv, L.norm[NORM_Q], L.norm[NORM_K], m->rope, m->d_pos, m->d_lane, kc, vc, m->lane_stride, m->att, m->sdpa_part,
+            SdpaFusedArgs fa{m->qkv, L.norm[NORM_Q], L.norm[NORM_K], layer_rope(m, li), m->d_pos, m->d_lane, kc, vc, m->lane_stride, m->att, m->sdpa_part,
                              m->att_ctr, m->Hq_l, m->Hkv_l, nchunks, c.max_len, c.eps, c.attn_scale};
             if ((rc = launch_sdpa_fused(s, fa, rows, D))) return rc;
         } else {
-            if ((rc = launch_qknorm_rope_append(s, m->qkv, L.norm[NORM_Q], L.norm[NORM_K], m->rope, m->d_pos, m->d_lane, m->q, kc, vc,
+            if ((rc = launch_qknorm_rope_append(s, m->qkv, L.norm[NORM_Q], L.norm[NORM_K], layer_rope(m, li), m->d_pos, m->d_lane, m->q, kc, vc,
                                                 rows, m->Hq_l, m->Hkv_l, D, c.eps, m->lane_stride, c.max_len))) return rc;
             SdpaArgs sa{m->q, kc, vc, m->d_pos, m->d_lane, m->att, m->sdpa_part, m->lane_stride, m->Hq_l, m->Hkv_l, nchunks, chunk_len, c.attn_scale};
-            sa.cols = m->att_cols; sa.split = split;
+            sa.cols = m->att_cols; sa.split = split; sa.window = layer_window(m, li);
             if ((rc = launch_sdpa_decode(s, sa, rows, D))) return rc;
         }
         QmvCall oc{L.o.wq, L.o.s, L.o.b, nullptr, nullptr, nullptr, m->att, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.o.N, L.o.K, rows};
@@ -594,10 +601,11 @@ static int32_t prefill_chunk(Model* m, int lane, int rows, int pos0, bool last) 
         if ((rc = qmm_launch(s, qc))) return rc;
         uint16_t* kc = m->kcache + (int64_t)li * m->layer_stride;
         uint16_t* vc = m->vcache + (int64_t)li * m->layer_stride;
-        if ((rc = launch_qknorm_rope_append(s, m->p_qkv, L.norm[NORM_Q], L.norm[NORM_K], m->rope, m->p_pos, m->p_lane, m->p_q, kc, vc,
+        if ((rc = launch_qknorm_rope_append(s, m->p_qkv, L.norm[NORM_Q], L.norm[NORM_K], layer_rope(m, li), m->p_pos, m->p_lane, m->p_q, kc, vc,
                                             rows, m->Hq_l, m->Hkv_l, D, c.eps, m->lane_stride, c.max_len))) return rc;
         PrefillAttnArgs pa{m->p_q, kc + (int64_t)lane * m->lane_stride, vc + (int64_t)lane * m->lane_stride, m->p_att, rows, pos0,
                            m->Hq_l, m->Hkv_l, scale_log2e};
+        pa.window = layer_window(m, li);
         if ((rc = launch_prefill_attn(s, pa, D))) return rc;
         QmmCall oc{m->p_att, rows, L.o.wq, L.o.s, L.o.b, nullptr, nullptr, nullptr, L.o.N, L.o.K, m->p_a, 1};
         if ((rc = qmm_launch(s, oc))) return rc;
@@ -878,6 +886,9 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
     if (c.tp_size <= 0) c.tp_size = 1;
     if (c.eps <= 0) c.eps = 1e-6f;
     if (c.rope_base <= 0) c.rope_base = 10000.0f;
+    if (c.sliding_window < 0) c.sliding_window = 0;
+    if (c.sliding_pattern <= 0) c.sliding_pattern = 6;   // gemma3: every sixth block is global
+    if (c.rope_local_base <= 0) c.rope_local_base = 10000.0f;
     if (c.attn_scale <= 0) c.attn_scale = (float)(1.0 / std::sqrt((double)c.head_dim));  // gemma3.go:150
     if (c.embed_scale <= 0)  // bf16(sqrt(hidden)), hip_gemma4_q4_layer.go:2757-2763
         c.embed_scale = bf16_bits_to_f32(f32_to_bf16_bits((float)std::sqrt((double)c.hidden)));
@@ -919,18 +930,21 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
     m->head.s = m->embed.s + (int64_t)m->v0 * (H / 64);
     m->head.b = m->embed.b + (int64_t)m->v0 * (H / 64);
     if ((rc = dalloc(m, &m->final_norm, (size_t)H))) return bail(rc);
-    // RoPE table, f64 on the host exactly as hipReferenceRoPENeoXWithFrequencyDimScale
-    {
+    // RoPE tables, f64 on the host exactly as hipReferenceRoPENeoXWithFrequencyDimScale: one for the global
+    // blocks and, with a sliding window, one with the local base for the sliding blocks
+    for (int local = 0; local < (c.sliding_window > 0 ? 2 : 1); local++) {
         const int half = c.head_dim / 2;
+        const double base = local ? (double)c.rope_local_base : (double)c.rope_base;
         std::vector<float2> tab((size_t)c.max_len * half);
         for (int p = 0; p < c.max_len; p++)
             for (int i = 0; i < half; i++) {
-                const double freq = 1.0 / std::pow((double)c.rope_base, (double)(2 * i) / (double)c.head_dim);
+                const double freq = 1.0 / std::pow(base, (double)(2 * i) / (double)c.head_dim);
                 const double angle = (double)p * freq * 1.0;
                 tab[(size_t)p * half + i] = make_float2((float)std::cos(angle), (float)std::sin(angle));
             }
-        if ((rc = dalloc(m, &m->rope, tab.size()))) return bail(rc);
-        e = cudaMemcpy(m->rope, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice);
+        float2** dst = local ? &m->rope_local : &m->rope;
+        if ((rc = dalloc(m, dst, tab.size()))) return bail(rc);
+        e = cudaMemcpy(*dst, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice);
         if (e != cudaSuccess) { cuda_fail(e, "rope table upload"); return bail(LTHN_ERR_CUDA); }
     }
     m->layer_stride = (int64_t)c.max_len * m->KR_l;
@@ -1210,7 +1224,7 @@ int32_t lthn_model_finalize(void* model) {
         // Opt-in (LTHN_CUDA_ATTN_FUSION=1): measured slower than the three kernels it replaces - every CTA repeats the
         // head norms in front of its loads, and the merge by the last CTA puts a fence + counter round trip on the tail.
         const char* env = getenv("LTHN_CUDA_ATTN_FUSION");
-        m->attn_fused = env && env[0] == '1' && sdpa_fused_supported(m->Hq_l, m->Hkv_l, m->c.head_dim);
+        m->attn_fused = env && env[0] == '1' && m->c.sliding_window == 0 && sdpa_fused_supported(m->Hq_l, m->Hkv_l, m->c.head_dim);
         if (m->attn_fused) {
             int32_t rc;
             if ((rc = dalloc(m, &m->att_ctr, (size_t)kMaxRows * m->Hkv_l))) return rc;
@@ -1223,7 +1237,7 @@ int32_t lthn_model_finalize(void* model) {
         // Off unless LTHN_CUDA_PERSIST=1: measured slower than the kernel chain on both benchmark models so far.
         const char* env = getenv("LTHN_CUDA_PERSIST");
         std::string why;
-        if (env && env[0] == '1' && c.tp_size <= 1 && m->fuse_norm &&
+        if (env && env[0] == '1' && c.tp_size <= 1 && m->fuse_norm && c.sliding_window == 0 &&
             persist_supported(c.hidden, m->Hq_l, m->Hkv_l, c.head_dim, m->F_l, &why)) {
             int32_t rc;
             PersistArgs& a = m->pk;

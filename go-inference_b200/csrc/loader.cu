@@ -263,6 +263,7 @@ struct Checkpoint {
     // resolved
     int layers = 0, hidden = 0, q_heads = 0, kv_heads = 0, head_dim = 0, ffn = 0, vocab = 0, gs = 0, bits = 0;
     int sliding_window = 0, sliding_pattern = 0, max_pos = 0;
+    float rope_local = 10000.0f;  // gemma3 default (model/arch/google/gemma3/gemma3.go:24)
     float eps = 1e-6f, rope_theta = 1000000.0f;
     std::string model_type;
     std::map<std::string, std::pair<int, int>> overrides;  // module path -> (group_size, bits)
@@ -304,6 +305,7 @@ bool open_checkpoint(const std::string& dir, Checkpoint* ck, std::string* err) {
     double d;
     if (tc->number("rms_norm_eps", &d)) ck->eps = (float)d;
     if (tc->number("rope_theta", &d)) ck->rope_theta = (float)d;
+    if (tc->number("rope_local_base_freq", &d) && d > 0) ck->rope_local = (float)d;
     // quantization block: top level or nested (gemma3.go:50-59)
     const JValue* q = top.get("quantization");
     if (!q || q->type != JValue::Obj) q = tc->get("quantization");
@@ -449,10 +451,6 @@ int32_t lthn_model_load_dir(const char* dir, const lthn_load_options* opts, void
     Checkpoint ck;
     std::string err;
     if (!open_checkpoint(dir, &ck, &err)) return fail(LTHN_ERR_INVALID, "lthn_model_load_dir: " + err);
-    if (ck.sliding_window > 0 && ck.sliding_pattern != 1 && !o.uniform_attention)
-        return fail(LTHN_ERR_INVALID, "lthn_model_load_dir: the checkpoint declares sliding-window layers (sliding_window " +
-                                          std::to_string(ck.sliding_window) + "), which this engine does not serve; set uniform_attention "
-                                          "to run every layer with full attention and one rope base");
     lthn_model_config c{};
     c.layers = ck.layers; c.hidden = ck.hidden; c.q_heads = ck.q_heads; c.kv_heads = ck.kv_heads; c.head_dim = ck.head_dim;
     c.ffn = ck.ffn; c.vocab = ck.vocab; c.group_size = ck.gs; c.bits = ck.bits;
@@ -460,6 +458,12 @@ int32_t lthn_model_load_dir(const char* dir, const lthn_load_options* opts, void
     c.max_lanes = o.max_lanes > 0 ? o.max_lanes : 1;
     c.eps = ck.eps; c.rope_base = ck.rope_theta;
     c.tp_rank = o.tp_rank; c.tp_size = o.tp_size;
+    if (ck.sliding_window > 0 && !o.uniform_attention) {
+        // gemma3 layer types: sliding blocks with the local rope base, every pattern-th block global
+        c.sliding_window = ck.sliding_window;
+        c.sliding_pattern = ck.sliding_pattern > 0 ? ck.sliding_pattern : 6;
+        c.rope_local_base = ck.rope_local;
+    }
     void* m = nullptr;
     int32_t rc = lthn_model_create(&c, &m);
     if (rc) return rc;

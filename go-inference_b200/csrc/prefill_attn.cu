@@ -89,7 +89,9 @@ __global__ void __launch_bounds__(PA_THREADS) prefill_attn_kernel(const PrefillA
         }
         cp_async_commit();
     };
-    load_kv(0, 0);
+    // sliding block: the first query row of this CTA sees keys from pos - window + 1 on; key tiles below that are skipped
+    const int j0 = a.window > 0 ? max(0, a.pos0 + m0 - a.window + 1) / BN : 0;
+    load_kv(j0, 0);
 
     // queries: f32 -> bf16 into shared memory (rows past the chunk are zero)
     for (int i = tid; i < PA_BM * (D / 4); i += PA_THREADS) {
@@ -105,8 +107,8 @@ __global__ void __launch_bounds__(PA_THREADS) prefill_attn_kernel(const PrefillA
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
     const int qpos0 = a.pos0 + m0 + warp * 16 + g;  // position of this thread's first row; the second is +8
 
-    for (int j = 0; j < ntiles; j++) {
-        const int buf = j & 1;
+    for (int j = j0; j < ntiles; j++) {
+        const int buf = (j - j0) & 1;
         cp_async_wait<0>();
         __syncthreads();  // tile j (and, first time, the queries) visible; everyone is done with tile j-1
         if (j + 1 < ntiles) load_kv(j + 1, buf ^ 1);
@@ -138,7 +140,7 @@ __global__ void __launch_bounds__(PA_THREADS) prefill_attn_kernel(const PrefillA
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const int k = key + (e & 1), qp = qpos0 + (e >> 1) * 8;
-                const float v = k <= qp ? s[n][e] * a.scale_log2e : -INFINITY;
+                const float v = (k <= qp && (a.window <= 0 || k > qp - a.window)) ? s[n][e] * a.scale_log2e : -INFINITY;
                 s[n][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }

@@ -93,7 +93,8 @@ class ModelConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab",
                                          "group_size", "bits", "max_len", "max_lanes")] + \
                [(n, C.c_float) for n in ("eps", "rope_base", "attn_scale", "embed_scale")] + \
-               [("tp_rank", C.c_int32), ("tp_size", C.c_int32)]
+               [("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("sliding_window", C.c_int32), ("sliding_pattern", C.c_int32),
+                ("rope_local_base", C.c_float)]
 
 
 _lib = None
@@ -505,10 +506,11 @@ NORM = dict(input=0, post_attn=1, pre_ff=2, post_ff=3, q_norm=4, k_norm=5)
 
 
 def make_config(layers, hidden, q_heads, kv_heads, head_dim, ffn, vocab, max_len, max_lanes=1, eps=1e-6,
-                rope_base=10000.0, tp_rank=0, tp_size=1) -> ModelConfig:
+                rope_base=10000.0, tp_rank=0, tp_size=1, sliding_window=0, sliding_pattern=0, rope_local_base=0.0) -> ModelConfig:
     return ModelConfig(layers=layers, hidden=hidden, q_heads=q_heads, kv_heads=kv_heads, head_dim=head_dim, ffn=ffn,
                        vocab=vocab, group_size=64, bits=4, max_len=max_len, max_lanes=max_lanes, eps=eps,
-                       rope_base=rope_base, attn_scale=0.0, embed_scale=0.0, tp_rank=tp_rank, tp_size=tp_size)
+                       rope_base=rope_base, attn_scale=0.0, embed_scale=0.0, tp_rank=tp_rank, tp_size=tp_size,
+                       sliding_window=sliding_window, sliding_pattern=sliding_pattern, rope_local_base=rope_local_base)
 
 
 def checkpoint_inspect(path: str) -> dict:

@@ -267,6 +267,13 @@ typedef struct {
     float attn_scale;           /* 0 -> 1/sqrt(head_dim) (model.Arch.AttnScale) */
     float embed_scale;          /* 0 -> bf16(sqrt(hidden)) (model.Arch.EmbedScale) */
     int32_t tp_rank, tp_size;   /* tensor-parallel rank / degree (tp_size 0 or 1: single GPU) */
+    /* gemma3 sliding/global attention (model/arch/google/gemma3/gemma3.go:111-158): with sliding_window > 0,
+     * block i attends only the last sliding_window keys (the current one included) unless
+     * (i+1) % sliding_pattern == 0 (pattern 0 -> 6), and rotates q/k with rope_local_base (0 -> 10000)
+     * instead of rope_base. The cache keeps every row (no ring): what the reference's ring of
+     * sliding_window rows computes (engine/metal/decode_step.go:298-316), without its memory saving. */
+    int32_t sliding_window, sliding_pattern;
+    float rope_local_base;
 } lthn_model_config;
 
 enum { LTHN_ROLE_Q = 0, LTHN_ROLE_K, LTHN_ROLE_V, LTHN_ROLE_O, LTHN_ROLE_GATE, LTHN_ROLE_UP, LTHN_ROLE_DOWN };
@@ -313,9 +320,10 @@ int32_t lthn_model_destroy(void* model);   /* TokenModel.Close (engine/model.go:
  * F16 scales/biases/norms to bf16 (model/safetensors/widen.go), applies the gemma (1+w) norm fold
  * in the tensor's dtype (model/norm_bias.go:22-49), uploads this rank's shard of every tensor and
  * finalizes. The files are mapped read-only for the duration of the call. Linears other than
- * 4-bit / group 64 (e.g. an 8-bit per-module override) and checkpoints that declare
- * sliding-window layers are rejected with the tensor or field named; uniform_attention = 1 loads
- * the latter anyway, every layer with full attention and the checkpoint's rope_theta. */
+ * 4-bit / group 64 (e.g. an 8-bit per-module override) are rejected with the tensor named. A
+ * checkpoint with sliding_window runs gemma3's layer pattern (sliding blocks with
+ * rope_local_base_freq, every sliding_window_pattern-th block global); uniform_attention = 1 runs
+ * every block with full attention and the checkpoint's rope_theta instead. */
 typedef struct {
     int32_t max_len;            /* KV positions per lane; 0 -> min(max_position_embeddings, 4096) */
     int32_t max_lanes;          /* 0 -> 1 */

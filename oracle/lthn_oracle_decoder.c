@@ -52,6 +52,12 @@ typedef struct {
      * dequantised weights are rounded to bf16, products accumulate in f64, outputs stay f32;
      * the attention query is rounded to bf16 too. Shorter forwards (decode) stay f32. */
     int32_t prefill_bf16;
+    /* gemma3 sliding/global pattern (model/arch/google/gemma3/gemma3.go:111-158): with sliding_window > 0,
+     * block i is a sliding block unless (i+1) % sliding_pattern == 0; a sliding block attends the last
+     * sliding_window keys (what the ring of engine/metal/decode_step.go:298-316 holds) and rotates with
+     * rope_local_base. */
+    int32_t sliding_window, sliding_pattern;
+    float rope_local_base;
 } lthn_o_decoder_config;
 
 enum { L_Q = 0, L_K, L_V, L_O, L_GATE, L_UP, L_DOWN, L_COUNT };
@@ -164,6 +170,9 @@ int lthn_o_decoder_forward(void *h, const int32_t *ids, long n, float *logits, f
         const lin_t *lin = d->lin + L * L_COUNT;
         const float **nw = d->norm + L * N_COUNT;
         float *kc = d->kc + (size_t)L * c->max_len * KR, *vc = d->vc + (size_t)L * c->max_len * KR;
+        const int pattern = c->sliding_pattern > 0 ? c->sliding_pattern : 6;
+        const int sliding = c->sliding_window > 0 && (L + 1) % pattern != 0;
+        const double rope_base = sliding ? (double)(c->rope_local_base > 0 ? c->rope_local_base : 10000.0f) : (double)c->rope_base;
         norm_rows(hid, nw[N_INPUT], n, H, c->eps, xn);
         tapcpy(d, L, 0, xn, n * H);
         proj(&lin[L_Q], xn, n, c->gs, c->bits, q);
@@ -175,12 +184,12 @@ int lthn_o_decoder_forward(void *h, const int32_t *ids, long n, float *logits, f
             for (long hh = 0; hh < c->q_heads; hh++) {
                 float *qh = q + t * QR + hh * D;
                 lthn_o_rmsnorm(qh, nw[N_QNORM], D, c->eps, tmp);
-                lthn_o_rope_neox(tmp, D, p, (double)c->rope_base, D, D, 1.0, qh);
+                lthn_o_rope_neox(tmp, D, p, rope_base, D, D, 1.0, qh);
             }
             for (long hh = 0; hh < c->kv_heads; hh++) {
                 float *kh = k + t * KR + hh * D;
                 lthn_o_rmsnorm(kh, nw[N_KNORM], D, c->eps, tmp);
-                lthn_o_rope_neox(tmp, D, p, (double)c->rope_base, D, D, 1.0, kh);
+                lthn_o_rope_neox(tmp, D, p, rope_base, D, D, 1.0, kh);
             }
             memcpy(kc + p * KR, k + t * KR, sizeof(float) * KR);
             memcpy(vc + p * KR, v + t * KR, sizeof(float) * KR);
@@ -196,7 +205,9 @@ int lthn_o_decoder_forward(void *h, const int32_t *ids, long n, float *logits, f
             for (long t = 0; t < n; t++)
                 for (long hh = 0; hh < c->q_heads; hh++) {
                     long kvh = lthn_o_kv_head_for_query(hh, c->q_heads, c->kv_heads);
-                    lthn_o_attention_single_head(q + t * QR + hh * D, kc + kvh * D, vc + kvh * D, d->pos + t + 1, D, KR,
+                    const long count = d->pos + t + 1;
+                    const long first = sliding && count > c->sliding_window ? count - c->sliding_window : 0;
+                    lthn_o_attention_single_head(q + t * QR + hh * D, kc + first * KR + kvh * D, vc + first * KR + kvh * D, count - first, D, KR,
                                                  c->attn_scale, att + t * QR + hh * D, lsc);
                 }
             free(lsc);

@@ -52,7 +52,8 @@ class DecoderConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
                 ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab", "gs", "bits", "max_len")] + \
                [(n, C.c_float) for n in ("eps", "rope_base", "attn_scale", "embed_scale")] + \
-               [("kv_bf16", C.c_int32), ("prefill_bf16", C.c_int32)]
+               [("kv_bf16", C.c_int32), ("prefill_bf16", C.c_int32), ("sliding_window", C.c_int32), ("sliding_pattern", C.c_int32),
+                ("rope_local_base", C.c_float)]
 
 
 def _declare(l):

@@ -59,13 +59,15 @@ def synth_weights_from_device(lthn, cfg, seed, sigma=0.02):
     return w, norms
 
 
-def build_oracle(oracle, cfg, w, norms, max_len, prefill_bf16=0):
+def build_oracle(oracle, cfg, w, norms, max_len, prefill_bf16=0, sliding=None):
     embed_scale = float(oracle.bf16_to_f32(oracle.f32_to_bf16(np.array([np.sqrt(cfg["hidden"])], dtype=np.float32)))[0])
     oc = oracle.DecoderConfig(layers=cfg["layers"], hidden=cfg["hidden"], q_heads=cfg["q_heads"],
                               kv_heads=cfg["kv_heads"], head_dim=cfg["head_dim"], ffn=cfg["ffn"], vocab=cfg["vocab"],
                               gs=64, bits=4, max_len=max_len, eps=1e-6, rope_base=10000.0,
                               attn_scale=float(np.float32(1.0 / np.sqrt(cfg["head_dim"]))), embed_scale=embed_scale,
                               kv_bf16=1, prefill_bf16=prefill_bf16)
+    if sliding:   # (window, pattern, local rope base)
+        oc.sliding_window, oc.sliding_pattern, oc.rope_local_base = sliding
     d = oracle.Decoder(oc)
     for li in range(cfg["layers"]):
         for role in ROLES:
@@ -77,9 +79,11 @@ def build_oracle(oracle, cfg, w, norms, max_len, prefill_bf16=0):
     return d
 
 
-def build_device(lthn, cfg, w, norms, max_len, max_lanes=1, tp_rank=0, tp_size=1, comm=None):
+def build_device(lthn, cfg, w, norms, max_len, max_lanes=1, tp_rank=0, tp_size=1, comm=None, sliding=None):
     mc = lthn.make_config(cfg["layers"], cfg["hidden"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"],
                           cfg["vocab"], max_len, max_lanes, tp_rank=tp_rank, tp_size=tp_size)
+    if sliding:
+        mc.sliding_window, mc.sliding_pattern, mc.rope_local_base = sliding
     m = lthn.Model(mc)
     for li in range(cfg["layers"]):
         for role in ROLES:

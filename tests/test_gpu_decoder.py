@@ -577,3 +577,50 @@ def test_kv_ranges_blocks_fork_and_reset(oracle):
     for x in (s, f, r):
         x.close()
     m.close()
+
+
+@pytest.mark.parametrize("cfg,window,prompt", [(SMALL, 24, 70), (MID, 40, 150), (MID, 200, 90)], ids=["small-w24", "mid-w40", "mid-window-wider-than-context"])
+def test_sliding_window_blocks_match_oracle(oracle, cfg, window, prompt, monkeypatch):
+    """gemma3's sliding/global layer pattern (pattern 2: block 0 sliding, block 1 global, ...): a sliding
+    block attends its last `window` keys and rotates with the local rope base (here 3000 against 10000, so
+    that a mix-up shows). f32 path: prompt logits, KV rows and 40 greedy tokens against the CPU decoder
+    with the same pattern - the prompt (decode kernels, 32 rows per forward) and the decode steps both
+    cross the window, and the split-KV merge starts at the first chunk inside it. Then the tensor-core
+    prefill of the same prompt against the bf16-contract oracle, at the bounds of the other prefill tests."""
+    import lthn
+    monkeypatch.setenv("LTHN_CUDA_PREFILL_F32", "1")
+    sliding = (window, 2, 3000.0)
+    w, norms = synth_weights(oracle, lthn, cfg, seed=23, random_norms=True)
+    max_len = prompt + 48
+    od = build_oracle(oracle, cfg, w, norms, max_len, sliding=sliding)
+    m = build_device(lthn, cfg, w, norms, max_len, sliding=sliding)
+    ids = np.random.default_rng(6).integers(0, cfg["vocab"], prompt).astype(np.int32)
+    want_logits = od.forward(ids)
+    s = m.open_session()
+    s.prefill(ids)
+    assert logits_close(s.logits(), want_logits)
+    for layer in range(cfg["layers"]):
+        for which in (0, 1):
+            dev_kv, ref_kv = oracle.bf16_to_f32(s.kv_export(layer, which)), od.read_kv(layer, which)
+            assert float(np.mean(dev_kv != ref_kv)) < (1e-2 if layer == 0 else 0.25)
+    want_tokens, margin = od.generate(want_logits, 40)
+    got = s.decode_greedy(40)
+    first_bad = next((i for i in range(40) if got[i] != want_tokens[i]), None)
+    assert first_bad is None, (first_bad, float(margin[first_bad]))
+    # and it is not what full attention gives (unless the window covers the whole context)
+    full = build_oracle(oracle, cfg, w, norms, max_len, sliding=(10 ** 6, 2, 3000.0))
+    differs = float(np.max(np.abs(full.forward(ids) - want_logits))) > 1e-3
+    assert differs == (window < prompt)
+    s.close(); m.close()
+    # tensor-core prefill (bf16 contract)
+    monkeypatch.delenv("LTHN_CUDA_PREFILL_F32")
+    oc = build_oracle(oracle, cfg, w, norms, max_len, prefill_bf16=1, sliding=sliding)
+    want_c = oc.forward(ids)
+    m2 = build_device(lthn, cfg, w, norms, max_len, sliding=sliding)
+    s2 = m2.open_session()
+    s2.prefill(ids)
+    got_c = s2.logits()
+    rms = float(np.sqrt(np.mean(want_c.astype(np.float64) ** 2)))
+    assert float(np.max(np.abs(got_c - want_c))) <= 5e-2 * rms
+    assert float(np.sqrt(np.mean((got_c - want_c).astype(np.float64) ** 2))) <= 1e-2 * rms
+    s2.close(); m2.close()

@@ -60,16 +60,19 @@ def test_load_rejects_what_the_engine_does_not_serve(oracle, tmp_path):
     with pytest.raises(lthn.LthnError) as e:
         lthn.Model.load_dir(d, max_len=32)
     assert "k_norm" in str(e.value)
-    # sliding-window layers: refused unless every layer may run with full attention
-    write_checkpoint(d, cfg, w, norms, extra_config={"sliding_window": 512, "sliding_window_pattern": 6})
-    with pytest.raises(lthn.LthnError) as e:
-        lthn.Model.load_dir(d, max_len=32)
-    assert "sliding" in str(e.value)
-    m = lthn.Model.load_dir(d, max_len=32, uniform_attention=True)
-    s = m.open_session()
-    s.prefill(np.arange(5, dtype=np.int32))
-    assert len(s.decode_greedy(3)) == 3
-    s.close(); m.close()
+    # sliding-window layers follow gemma3's pattern; uniform_attention runs every block with full attention.
+    # With a window of 8 the two differ once the prompt is longer than the window.
+    write_checkpoint(d, cfg, w, norms, extra_config={"sliding_window": 8, "sliding_window_pattern": 2, "rope_local_base_freq": 10000.0})
+    ids = (np.arange(24, dtype=np.int32) * 37) % cfg["vocab"]
+    outs = []
+    for uniform in (False, True):
+        m = lthn.Model.load_dir(d, max_len=48, uniform_attention=uniform)
+        s = m.open_session()
+        s.prefill(ids)
+        outs.append(s.logits().copy())
+        assert len(s.decode_greedy(3)) == 3
+        s.close(); m.close()
+    assert float(np.max(np.abs(outs[0] - outs[1]))) > 1e-3
     # geometry that contradicts the quantization block
     cfgj = json.load(open(os.path.join(d, "config.json")))
     cfgj["quantization"]["language_model.model.layers.0.mlp.gate_proj"] = {"group_size": 32, "bits": 4}

@@ -308,3 +308,49 @@ def test_synth_normal_is_roughly_gaussian(oracle):
     assert abs(float(v.mean())) < 2e-4 and abs(float(v.std()) - 0.02) < 2e-4
     assert v[5] == oracle.lib().lthn_o_synth_normal(7, 5, 0.02)
     assert np.array_equal(oracle.synth_normal(7, 100, 16, 0.02), v[100:116])
+
+
+def test_decoder_sliding_window_reduces_to_known_cases(oracle):
+    """The sliding/global pattern of the restated decoder against cases with a known answer: a window
+    wider than the context with the local rope base equal to the global one is the plain decoder;
+    pattern 1 makes every block global whatever the window; a window of 1 makes a sliding block's
+    attention output the value row itself, which a tap on the attention stage shows."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(__file__))
+    from decoder_util import NORMS, ROLES, linear_shapes
+    cfg = dict(layers=2, hidden=128, q_heads=2, kv_heads=1, head_dim=64, ffn=256, vocab=64)
+    rng = np.random.default_rng(3)
+    w = {(li, role): oracle.quantize((rng.standard_normal(shape) * 0.05).astype(np.float32))
+         for li in range(cfg["layers"]) for role, shape in linear_shapes(cfg).items()}
+    w["embed"] = oracle.quantize((rng.standard_normal((cfg["vocab"], cfg["hidden"])) * 0.05).astype(np.float32))
+    ids = rng.integers(0, cfg["vocab"], 12).astype(np.int32)
+
+    def run(sliding, tap=None):
+        oc = oracle.DecoderConfig(layers=cfg["layers"], hidden=cfg["hidden"], q_heads=cfg["q_heads"], kv_heads=cfg["kv_heads"],
+                                  head_dim=cfg["head_dim"], ffn=cfg["ffn"], vocab=cfg["vocab"], gs=64, bits=4, max_len=32, eps=1e-6,
+                                  rope_base=10000.0, attn_scale=0.125, embed_scale=1.0, kv_bf16=0, prefill_bf16=0)
+        if sliding:
+            oc.sliding_window, oc.sliding_pattern, oc.rope_local_base = sliding
+        d = oracle.Decoder(oc)
+        ones = {"h": np.ones(cfg["hidden"], dtype=np.float32), "d": np.ones(cfg["head_dim"], dtype=np.float32)}
+        for li in range(cfg["layers"]):
+            for role in ROLES:
+                d.set_linear(li, role, *w[(li, role)])
+            for role in NORMS:
+                d.set_norm(li, role, ones["d"] if role in ("q_norm", "k_norm") else ones["h"])
+        d.set_linear(-1, 0, *w["embed"])
+        d.set_norm(-1, 0, ones["h"])
+        buf = d.tap(tap, 1, len(ids), cfg["q_heads"] * cfg["head_dim"]) if tap is not None else None   # stage 1: attention output
+        logits = d.forward(ids)
+        return logits, buf, d
+
+    plain, _, _ = run(None)
+    wide, _, _ = run((1000, 2, 10000.0))
+    assert (plain == wide).all()
+    all_global, _, _ = run((3, 1, 3000.0))
+    assert (plain == all_global).all()
+    narrow, att, d = run((1, 2, 10000.0), tap=0)   # block 0 sliding with a window of one key
+    assert not (narrow == plain).all()
+    v = d.read_kv(0, 1)[:len(ids)]                  # [tokens, kv_heads*head_dim]
+    for h in range(cfg["q_heads"]):
+        assert np.allclose(att[:, h * 64:(h + 1) * 64], v[:, :64], rtol=0, atol=1e-6)
