@@ -14,6 +14,8 @@
 //  * reductions have a fixed order (no atomics in the value path).
 #include "common.cuh"
 #include "decoder_kernels.hpp"
+#include <algorithm>
+#include <cstdlib>
 #include "attn_item.cuh"
 
 namespace lthn {
@@ -451,7 +453,8 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
     pdl_wait();
     constexpr int E = D / 8;          // elements per lane
     constexpr int V8 = E / 8;         // 16-byte loads per lane per row
-    constexpr int NIT = 512 / D > 0 ? 512 / D : 1;  // positions per lane group: 16*NIT per CTA
+    constexpr int NIT = 512 / D > 0 ? 512 / D : 1;  // positions per lane group and tile: a tile is 16*NIT positions
+    constexpr int TILE = 16 * NIT;
     __shared__ float red[4][GQ][D + 2];
     __shared__ float smax[GQ][4], ssum[GQ][4];
 
@@ -462,26 +465,13 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
     const int l8 = lane & 7, pg = warp * 4 + (lane >> 3);  // position group 0..15
     const int ctx = a.row_pos[row] + 1;                    // keys 0..pos inclusive
     const int lo = a.window > 0 ? max(0, ctx - a.window) : 0;  // sliding block: keys lo..pos
-    const int p0 = chunk * (16 * NIT);
-    if (p0 >= ctx || p0 + 16 * NIT <= lo) return;
+    const int c0 = chunk * a.chunk_len;                    // a chunk is one or more tiles, walked with a running softmax
+    if (c0 >= ctx || c0 + a.chunk_len <= lo) return;
+    const int c1 = min(c0 + a.chunk_len, ctx);
     const int KR = a.Hkv * D;
     const uint16_t* kbase = a.kcache + (int64_t)a.row_lane[row] * a.lane_stride + (int64_t)kvh * D;
     const uint16_t* vbase = a.vcache + (int64_t)a.row_lane[row] * a.lane_stride + (int64_t)kvh * D;
 
-    // ---- every load of the chunk goes out first ---------------------------------------------
-    uint4 kreg[NIT][V8], vreg[NIT][V8];
-    bool valid[NIT];
-#pragma unroll
-    for (int i = 0; i < NIT; i++) {
-        const int p = p0 + pg + 16 * i;
-        valid[i] = p < ctx && p >= lo;
-        const int64_t off = (int64_t)(valid[i] ? p : min(max(p0, lo), ctx - 1)) * KR;
-#pragma unroll
-        for (int v = 0; v < V8; v++) {
-            kreg[i][v] = __ldg((const uint4*)(kbase + off + (v * 8 + l8) * 8));
-            vreg[i][v] = __ldg((const uint4*)(vbase + off + (v * 8 + l8) * 8));
-        }
-    }
     // query slices of this lane for the GQ heads, pre-multiplied by the softmax scale
     float q[GQ][E];
 #pragma unroll
@@ -497,72 +487,92 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
             q[h][v * 8 + 6] = qb.z * a.scale; q[h][v * 8 + 7] = qb.w * a.scale;
         }
     }
-    // ---- scores ---------------------------------------------------------------------------------
-    float sc[NIT][GQ], mx[GQ];
-#pragma unroll
-    for (int h = 0; h < GQ; h++) mx[h] = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < NIT; i++) {
-        float dot[GQ];
-#pragma unroll
-        for (int h = 0; h < GQ; h++) dot[h] = 0.f;
-#pragma unroll
-        for (int v = 0; v < V8; v++) {
-            const uint32_t kw[4] = {kreg[i][v].x, kreg[i][v].y, kreg[i][v].z, kreg[i][v].w};
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float k0 = __uint_as_float(kw[e] << 16), k1 = __uint_as_float(kw[e] & 0xffff0000u);
-#pragma unroll
-                for (int h = 0; h < GQ; h++) dot[h] = fmaf(q[h][v * 8 + 2 * e + 1], k1, fmaf(q[h][v * 8 + 2 * e], k0, dot[h]));
-            }
-        }
-#pragma unroll
-        for (int h = 0; h < GQ; h++) {
-            float d = dot[h];
-            d += __shfl_xor_sync(0xffffffffu, d, 1);
-            d += __shfl_xor_sync(0xffffffffu, d, 2);
-            d += __shfl_xor_sync(0xffffffffu, d, 4);
-            sc[i][h] = valid[i] ? d : -INFINITY;
-            mx[h] = fmaxf(mx[h], sc[i][h]);
-        }
-    }
+    // running state of this warp over its positions: maximum, sum of weights, weighted values
+    float mrun[GQ], lsum[GQ], acc[GQ][E];
 #pragma unroll
     for (int h = 0; h < GQ; h++) {
-        const float m = warp_max(mx[h]);
-        if (lane == 0) smax[h][warp] = m;
-    }
-    __syncthreads();
-    float cmax[GQ];
-#pragma unroll
-    for (int h = 0; h < GQ; h++) cmax[h] = fmaxf(fmaxf(smax[h][0], smax[h][1]), fmaxf(smax[h][2], smax[h][3]));
-    // ---- weights and weighted values ---------------------------------------------------------------
-    float acc[GQ][E], lsum[GQ];
-#pragma unroll
-    for (int h = 0; h < GQ; h++) {
-        lsum[h] = 0.f;
+        mrun[h] = -INFINITY; lsum[h] = 0.f;
 #pragma unroll
         for (int e = 0; e < E; e++) acc[h][e] = 0.f;
     }
+    const int t0 = c0 + (lo > c0 ? (lo - c0) / TILE * TILE : 0);  // tiles wholly below the window are skipped
+    for (int p0 = t0; p0 < c1; p0 += TILE) {
+        // ---- every load of the tile goes out first --------------------------------------------
+        uint4 kreg[NIT][V8], vreg[NIT][V8];
+        bool valid[NIT];
 #pragma unroll
-    for (int i = 0; i < NIT; i++) {
-        float w[GQ];
+        for (int i = 0; i < NIT; i++) {
+            const int p = p0 + pg + 16 * i;
+            valid[i] = p < ctx && p >= lo;
+            const int64_t off = (int64_t)(valid[i] ? p : min(max(p0, lo), ctx - 1)) * KR;
 #pragma unroll
-        for (int h = 0; h < GQ; h++) { w[h] = valid[i] ? __expf(sc[i][h] - cmax[h]) : 0.f; lsum[h] += w[h]; }
+            for (int v = 0; v < V8; v++) {
+                kreg[i][v] = __ldg((const uint4*)(kbase + off + (v * 8 + l8) * 8));
+                vreg[i][v] = __ldg((const uint4*)(vbase + off + (v * 8 + l8) * 8));
+            }
+        }
+        // ---- scores ---------------------------------------------------------------------------
+        float sc[NIT][GQ], mx[GQ];
 #pragma unroll
-        for (int v = 0; v < V8; v++) {
-            const uint32_t vw[4] = {vreg[i][v].x, vreg[i][v].y, vreg[i][v].z, vreg[i][v].w};
+        for (int h = 0; h < GQ; h++) mx[h] = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float v0 = __uint_as_float(vw[e] << 16), v1 = __uint_as_float(vw[e] & 0xffff0000u);
+        for (int i = 0; i < NIT; i++) {
+            float dot[GQ];
 #pragma unroll
-                for (int h = 0; h < GQ; h++) {
-                    acc[h][v * 8 + 2 * e] = fmaf(w[h], v0, acc[h][v * 8 + 2 * e]);
-                    acc[h][v * 8 + 2 * e + 1] = fmaf(w[h], v1, acc[h][v * 8 + 2 * e + 1]);
+            for (int h = 0; h < GQ; h++) dot[h] = 0.f;
+#pragma unroll
+            for (int v = 0; v < V8; v++) {
+                const uint32_t kw[4] = {kreg[i][v].x, kreg[i][v].y, kreg[i][v].z, kreg[i][v].w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float k0 = __uint_as_float(kw[e] << 16), k1 = __uint_as_float(kw[e] & 0xffff0000u);
+#pragma unroll
+                    for (int h = 0; h < GQ; h++) dot[h] = fmaf(q[h][v * 8 + 2 * e + 1], k1, fmaf(q[h][v * 8 + 2 * e], k0, dot[h]));
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < GQ; h++) {
+                float d = dot[h];
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                sc[i][h] = valid[i] ? d : -INFINITY;
+                mx[h] = fmaxf(mx[h], sc[i][h]);
+            }
+        }
+        // ---- running softmax of the warp: rescale what it has, add the tile -----------------------
+        float mref[GQ];
+#pragma unroll
+        for (int h = 0; h < GQ; h++) {
+            const float mnew = fmaxf(mrun[h], warp_max(mx[h]));
+            mref[h] = mnew == -INFINITY ? 0.f : mnew;      // no visible key yet: keep exp() finite
+            const float rescale = __expf(mrun[h] - mref[h]);  // -inf -> 0
+            mrun[h] = mnew;
+            lsum[h] *= rescale;
+#pragma unroll
+            for (int e = 0; e < E; e++) acc[h][e] *= rescale;
+        }
+#pragma unroll
+        for (int i = 0; i < NIT; i++) {
+            float w[GQ];
+#pragma unroll
+            for (int h = 0; h < GQ; h++) { w[h] = valid[i] ? __expf(sc[i][h] - mref[h]) : 0.f; lsum[h] += w[h]; }
+#pragma unroll
+            for (int v = 0; v < V8; v++) {
+                const uint32_t vw[4] = {vreg[i][v].x, vreg[i][v].y, vreg[i][v].z, vreg[i][v].w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float v0 = __uint_as_float(vw[e] << 16), v1 = __uint_as_float(vw[e] & 0xffff0000u);
+#pragma unroll
+                    for (int h = 0; h < GQ; h++) {
+                        acc[h][v * 8 + 2 * e] = fmaf(w[h], v0, acc[h][v * 8 + 2 * e]);
+                        acc[h][v * 8 + 2 * e + 1] = fmaf(w[h], v1, acc[h][v * 8 + 2 * e + 1]);
+                    }
                 }
             }
         }
     }
-    // combine the 4 position groups of a warp, then the 4 warps
+    // combine the 4 position groups of a warp, then the 4 warps (each with its own maximum)
 #pragma unroll
     for (int h = 0; h < GQ; h++) {
 #pragma unroll
@@ -574,7 +584,7 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
         }
         float l = (l8 == 0) ? lsum[h] : 0.f;  // the 8 lanes of a group hold the same weight: count it once
         l = warp_sum(l);
-        if (lane == 0) ssum[h][warp] = l;
+        if (lane == 0) { ssum[h][warp] = l; smax[h][warp] = mrun[h]; }
         if (lane < 8) {
 #pragma unroll
             for (int v = 0; v < V8; v++)
@@ -585,15 +595,21 @@ __global__ void __launch_bounds__(128) sdpa_decode_kernel(const SdpaArgs a) {
     __syncthreads();
     for (int idx = tid; idx < GQ * D; idx += 128) {
         const int h = idx / D, d = idx - h * D;
-        const float v = red[0][h][d] + red[1][h][d] + red[2][h][d] + red[3][h][d];
-        const float l = ssum[h][0] + ssum[h][1] + ssum[h][2] + ssum[h][3];
+        const float m = fmaxf(fmaxf(smax[h][0], smax[h][1]), fmaxf(smax[h][2], smax[h][3]));  // finite: the chunk holds a visible key
+        float v = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float e = __expf(smax[h][w] - m);  // a warp without a visible key: exp(-inf) = 0
+            v = fmaf(red[w][h][d], e, v);
+            l = fmaf(ssum[h][w], e, l);
+        }
         const int qh = qh0 + h;
         if (a.nchunks == 1) {
             a.out[((int64_t)row * a.Hq + qh) * D + d] = v / l;
         } else {
             float* pa = a.part + (((int64_t)row * a.Hq + qh) * a.nchunks + chunk) * (D + 2);
             pa[d] = v;
-            if (d == 0) { pa[D] = cmax[h]; pa[D + 1] = l; }
+            if (d == 0) { pa[D] = m; pa[D + 1] = l; }
         }
     }
 }
@@ -817,11 +833,29 @@ int32_t launch_rmsnorm_rope(cudaStream_t s, const float* x, const float* w, cons
     return LTHN_OK;
 }
 
-int sdpa_chunking(int max_ctx, int D, int* chunk_len) {
-    // a CTA covers as many keys as fit in registers with all loads in flight: 8192/D
-    const int nit = 512 / D > 0 ? 512 / D : 1;
-    *chunk_len = 16 * nit;
+int sdpa_chunking(int max_ctx, int D, int* chunk_len, int rows, int bundles) {
+    // A tile is what a CTA holds in registers with all its loads in flight (8192/D keys); a chunk is one or
+    // more tiles walked with a running softmax. One tile per chunk while that keeps the grid under ~2.5 CTAs
+    // per SM (few heads: the 26-layer model decodes 6 % slower with two tiles per chunk) and whenever more
+    // than two rows share the launch (16 lanes: 5 % slower with long chunks - the grid is full anyway and a
+    // CTA's tiles are a serial chain); beyond that, longer chunks mean fewer partials for the merge and fewer
+    // CTA prologues (62-layer model, one row, 4096 keys: 3 tiles per chunk, 2-3.5 % faster per token).
+    // LTHN_CUDA_SDPA_TILES=n forces n tiles per chunk.
+    const int nit = 512 / D > 0 ? 512 / D : 1, tile = 16 * nit;
+    const int tiles = (max_ctx + tile - 1) / tile;
+    static const int forced = [] { const char* e = getenv("LTHN_CUDA_SDPA_TILES"); return e ? atoi(e) : 0; }();
+    int tl = rows <= 2 ? (int)((int64_t)tiles * std::max(1, rows * bundles) / 370) : 1;
+    tl = std::min(4, tl);
+    if (forced > 0) tl = forced;
+    tl = std::min(8, std::max(1, tl));
+    *chunk_len = tile * tl;
     return (max_ctx + *chunk_len - 1) / *chunk_len;
+}
+
+// chunks of one tile each: what the one-launch attention and the one-kernel decode step use
+int sdpa_item_chunks(int max_ctx, int D) {
+    const int nit = 512 / D > 0 ? 512 / D : 1, tile = 16 * nit;
+    return (max_ctx + tile - 1) / tile;
 }
 
 size_t sdpa_scratch_bytes(int rows, int Hq, int D, int nchunks) {

@@ -52,7 +52,8 @@ int32_t launch_qknorm_rope_append(cudaStream_t s, const float* qkv, const float*
                                   float eps, int64_t lane_stride, int max_len);
 int32_t launch_rmsnorm_rope(cudaStream_t s, const float* x, const float* w, const int32_t* positions, float* out,
                             int rows, int heads, int D, int rotary, float eps, float rope_base, int bf16_seams);
-int sdpa_chunking(int max_ctx, int D, int* chunk_len);
+int sdpa_chunking(int max_ctx, int D, int* chunk_len, int rows, int bundles);
+int sdpa_item_chunks(int max_ctx, int D);
 size_t sdpa_scratch_bytes(int rows, int Hq, int D, int nchunks);
 int32_t launch_sdpa_decode(cudaStream_t s, SdpaArgs a, int rows, int D);
 // Decode attention in one launch: head norms + RoPE, KV append, split-KV attention, merge.

@@ -467,7 +467,7 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
     const int split = qmv_split_for(rows, LTHN_DTYPE_F32);
     if (!f1 && (rc = launch_rmsnorm(s, hcur, nullptr, m->layers[0].norm[NORM_INPUT], nullptr, m->xn, rows, H, c.eps, 0, m->xn_cols, split))) return rc;
     int chunk_len = 0;
-    const int nchunks = sdpa_chunking(max_ctx, D, &chunk_len);
+    const int nchunks = sdpa_chunking(max_ctx, D, &chunk_len, rows, std::max(1, m->Hkv_l));
     const size_t need = sdpa_scratch_bytes(rows, m->Hq_l, D, nchunks);
     if (nchunks > 1 && need > m->sdpa_part_bytes) return fail(LTHN_ERR_STATE, "forward: attention scratch too small");
     NormFuse nf{};
@@ -500,7 +500,7 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
         uint16_t* vc = m->vcache + (int64_t)li * m->layer_stride;
         if (small && m->attn_fused) {
             SdpaFusedArgs fa{m->qkv, L.norm[NORM_Q], L.norm[NORM_K], layer_rope(m, li), m->d_pos, m->d_lane, kc, vc, m->lane_stride, m->att, m->sdpa_part,
-                             m->att_ctr, m->Hq_l, m->Hkv_l, nchunks, c.max_len, c.eps, c.attn_scale};
+                             m->att_ctr, m->Hq_l, m->Hkv_l, sdpa_item_chunks(max_ctx, D), c.max_len, c.eps, c.attn_scale};
             if ((rc = launch_sdpa_fused(s, fa, rows, D))) return rc;
         } else {
             if ((rc = launch_qknorm_rope_append(s, m->qkv, L.norm[NORM_Q], L.norm[NORM_K], layer_rope(m, li), m->d_pos, m->d_lane, m->q, kc, vc,
@@ -967,8 +967,7 @@ int32_t lthn_model_create(const lthn_model_config* cfg, void** model) {
     m->d_pos = m->d_ids + R;
     m->d_lane = m->d_ids + 2 * R;
     {
-        int chunk_len = 0;
-        const int nch = sdpa_chunking(c.max_len, c.head_dim, &chunk_len);
+        const int nch = sdpa_item_chunks(c.max_len, c.head_dim);  // the finest chunking any attention path uses
         m->sdpa_part_bytes = sdpa_scratch_bytes(kMaxRows, m->Hq_l, c.head_dim, nch);
         if ((rc = dalloc(m, &m->sdpa_part, m->sdpa_part_bytes / sizeof(float) + 64))) return bail(rc);
     }
@@ -1271,7 +1270,7 @@ int32_t lthn_model_finalize(void* model) {
             if ((rc = dalloc(m, &a.dig_att, persist_digit_bytes(m->Hq_l, c.head_dim, m->F_l))) ||
                 (rc = dalloc(m, &a.dig_act, persist_digit_bytes(m->Hq_l, c.head_dim, m->F_l))))
                 return rc;
-            a.nchunks_cap = sdpa_chunking(c.max_len, c.head_dim, &chunk_len);
+            a.nchunks_cap = sdpa_item_chunks(c.max_len, c.head_dim);
             a.sync = sync;
             a.status = device_status_word();
             m->persist_ok = true;
@@ -1875,7 +1874,7 @@ int32_t lthn_sdpa_decode(void* stream, const float* q, const uint16_t* kcache, c
     LTHN_REQUIRE(rows > 0 && q_heads > 0 && kv_heads > 0 && max_ctx > 0, "lthn_sdpa_decode: dimensions must be positive");
     if (scale <= 0) scale = (float)(1.0 / std::sqrt((double)head_dim));
     int chunk_len = 0;
-    const int nchunks = sdpa_chunking(max_ctx, head_dim, &chunk_len);
+    const int nchunks = sdpa_chunking(max_ctx, head_dim, &chunk_len, rows, std::max(1, kv_heads));
     void* part = nullptr;
     if (nchunks > 1) {
         int32_t rc = scratch_get(sdpa_scratch_bytes(rows, q_heads, head_dim, nchunks), &part, 2);
