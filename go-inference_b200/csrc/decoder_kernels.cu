@@ -362,7 +362,7 @@ __global__ void qknorm_rope_append_kernel(const float* __restrict__ qkv, const f
                                           const int32_t* __restrict__ row_pos, const int32_t* __restrict__ row_lane,
                                           float* __restrict__ q_out, uint16_t* __restrict__ kcache,
                                           uint16_t* __restrict__ vcache, int Hq, int Hkv, int D, float eps,
-                                          int64_t lane_stride, int max_len) {
+                                          int64_t lane_stride, int max_len, double inv_d) {
     pdl_trigger();
     pdl_wait();
     __shared__ double sh[32];
@@ -379,13 +379,16 @@ __global__ void qknorm_rope_append_kernel(const float* __restrict__ qkv, const f
         return;
     }
     const float x0 = src[i], x1 = src[i + half];
+    // the weights and the rotation are loaded before the reduction is waited for; rms and the two divisions take
+    // the short forms of the matvec prologues (fast_rms, fast_div: no f64 square root, no branch)
+    const float* w = head < Hq ? q_norm : k_norm;
+    const float w0 = w[i], w1 = w[i + half];
+    const float2 cs = rope_table[(int64_t)min(pos, max_len - 1) * half + i];
     double ss = (double)__fmul_rn(x0, x0) + (double)__fmul_rn(x1, x1);
     ss = block_sum_f64(ss, sh);
-    const float rms = (float)sqrt(ss / (double)D + (double)eps);
-    const float* w = head < Hq ? q_norm : k_norm;
-    const float n0 = __fmul_rn(__fdiv_rn(x0, rms), w[i]);
-    const float n1 = __fmul_rn(__fdiv_rn(x1, rms), w[i + half]);
-    const float2 cs = rope_table[(int64_t)min(pos, max_len - 1) * half + i];
+    const FastDiv k = fast_div_by(fast_rms(ss, inv_d, eps));
+    const float n0 = __fmul_rn(fast_div(x0, k), w0);
+    const float n1 = __fmul_rn(fast_div(x1, k), w1);
     const float r0 = __fsub_rn(__fmul_rn(n0, cs.x), __fmul_rn(n1, cs.y));
     const float r1 = __fadd_rn(__fmul_rn(n0, cs.y), __fmul_rn(n1, cs.x));
     if (head < Hq) {
@@ -821,7 +824,7 @@ int32_t launch_qknorm_rope_append(cudaStream_t s, const float* qkv, const float*
                                   float eps, int64_t lane_stride, int max_len) {
     dim3 grid(rows, Hq + 2 * Hkv);
     LTHN_CUDA_TRY(launch_k(qknorm_rope_append_kernel, grid, dim3(D / 2), 0, s, qkv, q_norm, k_norm, rope_table, row_pos, row_lane,
-                           q_out, kcache, vcache, Hq, Hkv, D, eps, lane_stride, max_len));
+                           q_out, kcache, vcache, Hq, Hkv, D, eps, lane_stride, max_len, 1.0 / (double)D));
     return LTHN_OK;
 }
 
