@@ -238,7 +238,7 @@ def run_decode(lthn, cfg, name, prompt_len, new_tokens, batch, peak, comm=None, 
            "weight_bytes_per_token_per_gpu": decode_weight_bytes(cfg, world)}
     s = m.open_session()
     ids = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
-    s.prefill(ids[:64])          # warm-up (first use allocates scratch)
+    s.prefill(ids)               # warm-up at the timed size (first use of a shape allocates scratch)
     s.decode_greedy(4)
     short_toks = None
     if check_tp1:
