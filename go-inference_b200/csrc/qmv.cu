@@ -646,6 +646,15 @@ int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M,
     int32_t rc = qmv_validate(x, x_dtype, M, packed, scales, biases, N, K, gs, bits, y, y_dtype, s, &done);
     if (rc || done) return rc;
     const bool fast = bits == 4 && gs == 64 && ((uintptr_t)packed & 7) == 0 && ((uintptr_t)x & 15) == 0;
+    if (bits == 8 && gs == 64 && M <= 2 && g_force_kernel == 0 && ((uintptr_t)packed & 15) == 0 && ((uintptr_t)x & 15) == 0) {
+        // 8-bit codes (the MLP projections of QAT packs): the integer tensor-core kernel takes the bytes as they are
+        I8Plan pl;
+        if (i8_plan_b8(N, K, M, &pl)) {
+            QmvCall c8{packed, scales, biases, nullptr, nullptr, nullptr, x, x_dtype, y, y_dtype, N, K, M};
+            c8.bits = 8;
+            return i8_launch(s, c8, pl);
+        }
+    }
     if (!fast) {
         const int wpb = 8;
         const unsigned grid = (unsigned)((N + wpb - 1) / wpb);

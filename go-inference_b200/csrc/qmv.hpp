@@ -60,6 +60,7 @@ struct QmvCall {
     // of y - a tensor-parallel rank pushing its partial sums into every peer's memory
     float* const* push = nullptr;  // array of npush pointers, in device memory
     int npush = 0;
+    int bits = 4;  // 8: the integer tensor-core kernel's 8-bit form (plain matvec, M <= 2)
 };
 
 // true when a call of this shape can carry a fused norm prologue
@@ -80,6 +81,7 @@ extern __attribute__((visibility("hidden"))) int g_i8_stg;
 // max_slices: 1 = whole rows only; > 1 lets the plan cut K into up to that many slices (partial sums)
 bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I8Plan* p, int max_slices = 1,
              bool has_norm = false);
+bool i8_plan_b8(int64_t N, int64_t K, int M, I8Plan* p);
 int32_t i8_launch(cudaStream_t st, const QmvCall& c, const I8Plan& p);
 
 // y[i] = sum over s < ks of part[s*n + i]

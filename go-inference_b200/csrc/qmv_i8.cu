@@ -10,6 +10,8 @@ namespace lthn {
 struct I8Args;
 template <int J>
 int32_t launch_i8_w(cudaStream_t st, const I8Args& a, const I8Plan& p, int M, int fuse);
+template <int J>
+int32_t launch_i8_b8(cudaStream_t st, const I8Args& a, const I8Plan& p, int M);
 int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p);
 
 // ---- host side --------------------------------------------------------------------
@@ -19,7 +21,7 @@ LTHN_HIDDEN int g_i8_stg = 0;  // ring-stage override: zero in the product libra
 static const size_t kI8MaxSmem = 224 * 1024;
 static const int kI8J[] = {1, 2, 3, 4, 6, 7, 8, 9, 12, 16, 18, 21};
 
-static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_w, bool has_norm, I8Plan* p) {
+static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_w, bool has_norm, I8Plan* p, int bits = 4) {
     // (J, W): W consumer warps of J groups each. Measured on B200: a long stream (many row blocks
     // per SM) runs fastest with few warps per block and many blocks per SM (less hand-off per row
     // block, more independent pipelines: 5.9 TB/s with 4 warps against 4.4 with 12 on the 340 MB
@@ -35,6 +37,7 @@ static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_
         if (Gs % cand) continue;
         const int w = Gs / cand;
         if (w < 1 || w > 16) continue;
+        if (bits == 8 && ((cand != 2 && cand != 3 && cand != 4 && cand != 6 && cand != 9 && cand != 12) || (cand > 9 && w > 8))) continue;
         if (cand > 9 && w > 8) continue;  // many groups per warp only in small blocks (registers)
         // the five-blocks-per-SM build of the 4-warp class holds 72 registers: the digit fragments of
         // more than 9 groups (4 registers each) do not fit and spill (K = 5376 as 4 x 21 groups
@@ -46,7 +49,7 @@ static bool i8_plan_slice(int64_t N, int Gs, int ks, int M, int fuse, int force_
     }
     if (best < 0) return false;
     const int sets = fuse == 1 ? 2 : 1;
-    const int rsw = Gs * 8;
+    const int rsw = Gs * 2 * bits;  // words of codes per row (slice)
     const int padw = ((8 - rsw % 32) + 32) % 32;
     const int RS = (rsw + padw) * 4;
     const int RB = 16;
@@ -94,6 +97,21 @@ bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I
         if (d < best_d) { best_d = d; best_ks = ks; *p = q; }
     }
     return best_ks != 0;
+}
+
+// 8-bit codes (plain matvec, one or two rows): whole rows while a 16-row block fits the ring (K <= ~5376), else the
+// fewest K slices that do
+bool i8_plan_b8(int64_t N, int64_t K, int M, I8Plan* p) {
+    if (M < 1 || M > 2 || K % 64 != 0 || N < 16 || N % 16 != 0) return false;
+    const int G = (int)(K / 64);
+    if (i8_plan_slice(N, G, 1, M, 0, 0, false, p, 8)) return true;
+    for (int ks : {2, 3, 4, 6, 8}) {
+        if (G % ks) continue;
+        const int Gs = G / ks;
+        if ((Gs & 1) || (G & 1) || Gs < 8) continue;
+        if (i8_plan_slice(N, Gs, ks, M, 0, 0, false, p, 8)) return true;
+    }
+    return false;
 }
 
 bool qmv_can_fuse_norm(int64_t N, int64_t K, int M, bool geglu) {

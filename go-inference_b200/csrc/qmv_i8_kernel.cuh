@@ -48,6 +48,7 @@ struct I8Args {
     int bs_off, stage_off;  // byte offsets into dynamic shared memory
     int fuse_norm;          // 1: activations come from the fused residual RMSNorm prologue (nf)
     int ks, Gs;             // K slices (CTA c works on slice c % ks) and groups per slice
+    int bits;               // 4 or 8 (8: plain matvec only, one byte per code, no unpack step)
     float* ypart;           // ks > 1: partial sums [ks][M][N] f32 instead of y
     NormFuse nf;
     float* const* push;     // npush > 0: f32 results go to these buffers (array in device memory) instead of y
@@ -83,8 +84,14 @@ __device__ __forceinline__ float bf16f(uint16_t h) { return __uint_as_float((uin
 // FUSE != 0: two weight sets, output gelu_tanh(W1 x) * (W2 x). FUSE=1 stages 16 rows of each set
 // per row block (short rows: fewer, fatter blocks); FUSE=2 stages 8 rows of each set as MMA rows
 // 0-7 and 8-15, so a stage is as large as an unfused one (long rows: more blocks fit an SM).
-template <int J, int RT, int MT, int FUSE>
+// BITS = 8 (plain matvec only): a group of a row is 64 code bytes that go into the MMA as they are. The MMA's k
+// index may be permuted freely as long as both operands agree, so thread t of a fragment takes the eight
+// consecutive bytes 8t..8t+7 of a 32-code half group (one 8-byte load per row) and the activation digits sit in
+// natural order.
+template <int J, int RT, int MT, int FUSE, int BITS = 4>
 __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
+    static_assert(BITS == 4 || (BITS == 8 && FUSE == 0), "8-bit codes: plain matvec only");
+    constexpr int GB = BITS * 8;  // code bytes per group and row
     constexpr int SETS = FUSE == 1 ? 2 : 1;
     constexpr int OR = FUSE == 2 ? 8 : 16;  // output rows per row block
     constexpr int RB = 16 * RT;
@@ -98,7 +105,7 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
     // partial sums (small matrices then fill the GPU, long rows fit the shared-memory ring)
     const int G = (int)(K >> 6), Gs = a.Gs, ks = a.ks;
     const int slice = blockIdx.x % ks, cta = blockIdx.x / ks;
-    const int rowbytes = Gs * 32, sbrow = Gs * 2, RS = a.RS;
+    const int rowbytes = Gs * GB, sbrow = Gs * 2, RS = a.RS;
     const int sb_bytes = (RB * sbrow + 15) & ~15;
     const int set_bytes = RB * RS + 2 * sb_bytes;
     const int stage_bytes = SETS * set_bytes;
@@ -148,7 +155,7 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
                 unsigned char* d = sbase + (size_t)s * set_bytes;
                 const unsigned char* wsrc = (const unsigned char*)a.wq[s] + (size_t)slice * rowbytes;
                 for (int r = lane; r < rows; r += 32)
-                    bulk_g2s(d + (size_t)r * RS, wsrc + (row0 + r) * (K >> 1), (uint32_t)rowbytes, &full[st]);
+                    bulk_g2s(d + (size_t)r * RS, wsrc + (row0 + r) * (K * BITS / 8), (uint32_t)rowbytes, &full[st]);
                 if (ks == 1) {
                     if (lane == 0)
                         bulk_g2s(d + (size_t)RB * RS, (const unsigned char*)a.scales[s] + row0 * sbrow, (uint32_t)(rows * sbrow), &full[st]);
@@ -390,7 +397,7 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
                     // fragment owns words 2t (first MMA) and 2t+1 (second); even nibbles feed the
                     // low k half, odd nibbles the high k half.
                     const int e = 2 * lane + q;
-                    const int off = ((((e >> 3) & 1) * 4 + (e >> 4)) * 2 + (e & 1)) * 4 + ((e & 7) >> 1);
+                    const int off = BITS == 8 ? e : ((((e >> 3) & 1) * 4 + (e >> 4)) * 2 + (e & 1)) * 4 + ((e & 7) >> 1);
                     Bw[m * 192 + off] = (unsigned char)(i0 & 0xff);
                     Bw[m * 192 + 64 + off] = (unsigned char)(i1 & 0xff);
                     Bw[m * 192 + 128 + off] = (unsigned char)(i2 & 0xff);
@@ -436,16 +443,23 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
             for (int rt = 0; rt < RT; rt++) {
                 acc[s][rt][0] = 0.f; acc[s][rt][1] = 0.f; accb[s][rt] = 0.f;
                 const unsigned char* setp = sbase + (size_t)s * set_bytes;
-                const unsigned char* rowp = setp + (size_t)(rt * 16 + gq) * RS + t * 8 + warp * J * 32;
+                const unsigned char* rowp = setp + (size_t)(rt * 16 + gq) * RS + t * 8 + warp * J * GB;
                 const uint16_t* sp = (const uint16_t*)(setp + (size_t)RB * RS) + (rt * 16 + gq) * Gs + warp * J;
                 const uint16_t* bp = (const uint16_t*)(setp + (size_t)RB * RS + sb_bytes) + (rt * 16 + gq + 8 * (t & 1)) * Gs + warp * J;
 #pragma unroll
                 for (int j = 0; j < J; j++) {
-                    const uint2 wa = *(const uint2*)(rowp + j * 32);
-                    const uint2 wb = *(const uint2*)(rowp + (size_t)8 * RS + j * 32);
                     int c[4];
-                    mma_u8s8_z(c, wa.x & NIB, wb.x & NIB, (wa.x >> 4) & NIB, (wb.x >> 4) & NIB, bfrag[j][0][0], bfrag[j][0][1]);
-                    mma_u8s8(c, wa.y & NIB, wb.y & NIB, (wa.y >> 4) & NIB, (wb.y >> 4) & NIB, bfrag[j][1][0], bfrag[j][1][1]);
+                    if constexpr (BITS == 8) {
+                        const uint2 wa0 = *(const uint2*)(rowp + j * 64), wb0 = *(const uint2*)(rowp + (size_t)8 * RS + j * 64);
+                        const uint2 wa1 = *(const uint2*)(rowp + j * 64 + 32), wb1 = *(const uint2*)(rowp + (size_t)8 * RS + j * 64 + 32);
+                        mma_u8s8_z(c, wa0.x, wb0.x, wa0.y, wb0.y, bfrag[j][0][0], bfrag[j][0][1]);
+                        mma_u8s8(c, wa1.x, wb1.x, wa1.y, wb1.y, bfrag[j][1][0], bfrag[j][1][1]);
+                    } else {
+                        const uint2 wa = *(const uint2*)(rowp + j * 32);
+                        const uint2 wb = *(const uint2*)(rowp + (size_t)8 * RS + j * 32);
+                        mma_u8s8_z(c, wa.x & NIB, wb.x & NIB, (wa.x >> 4) & NIB, (wb.x >> 4) & NIB, bfrag[j][0][0], bfrag[j][0][1]);
+                        mma_u8s8(c, wa.y & NIB, wb.y & NIB, (wa.y >> 4) & NIB, (wb.y >> 4) & NIB, bfrag[j][1][0], bfrag[j][1][1]);
+                    }
                     const float s0 = bf16f(sp[j]), s1 = bf16f(sp[8 * Gs + j]);
                     const float2 gc = GC_SMEM ? gconst[j * 4] : make_float2(cg[j], xsb[j]);
                     const float f0 = (float)(c[0] * 128 + c[1]) * gc.x;
@@ -514,13 +528,19 @@ __global__ void __launch_bounds__(LB) qmv_i8_kernel(const I8Args a) { qmv_i8_bod
 template <int J, int RT, int MT, int FUSE>
 __global__ void __launch_bounds__(160, 5) qmv_i8_kernel_small(const I8Args a) { qmv_i8_body<J, RT, MT, FUSE>(a); }
 
-template <int J, int RT, int MT, int FUSE, int LB>
+// 8-bit codes: one block per SM class only (the stages are twice as large, so two to four blocks fit an SM anyway)
+template <int J, int MT, int LB>
+__global__ void __launch_bounds__(LB) qmv_i8_b8_kernel(const I8Args a) { qmv_i8_body<J, 1, MT, 0, 8>(a); }
+
+template <int J, int RT, int MT, int FUSE, int LB, int BITS = 4>
 inline int32_t launch_i8_t(cudaStream_t st, const I8Args& a, const I8Plan& p) {
     static int attr_dev = -1;
     static std::mutex mu;  // guards attr_dev and occ_cache: entry points may be called from several host threads
     int dev = 0;
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
-    void (*kern)(const I8Args) = LB == 160 ? qmv_i8_kernel_small<J, RT, MT, FUSE> : qmv_i8_kernel<J, RT, MT, FUSE, LB>;
+    void (*kern)(const I8Args);
+    if constexpr (BITS == 8) kern = qmv_i8_b8_kernel<J, MT, LB>;
+    else kern = LB == 160 ? qmv_i8_kernel_small<J, RT, MT, FUSE> : qmv_i8_kernel<J, RT, MT, FUSE, LB>;
     std::unique_lock<std::mutex> lk(mu);
     if (attr_dev != dev) {
         LTHN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
@@ -553,6 +573,14 @@ inline int32_t launch_i8_j(cudaStream_t st, const I8Args& a, const I8Plan& p, in
     if (fuse == 2) return M == 1 ? launch_i8_t<J, 1, 1, 2, LB>(st, a, p) : launch_i8_t<J, 1, 2, 2, LB>(st, a, p);
     if (M == 1) return launch_i8_t<J, 1, 1, 0, LB>(st, a, p);
     return launch_i8_t<J, 1, 2, 0, LB>(st, a, p);
+}
+
+// 8-bit codes, plain matvec: J in {2, 3, 4, 6, 9, 12}, block classes of up to 8 and up to 16 consumer warps
+template <int J>
+int32_t launch_i8_b8(cudaStream_t st, const I8Args& a, const I8Plan& p, int M) {
+    if (p.W <= 8) return M == 1 ? launch_i8_t<J, 1, 1, 0, 288, 8>(st, a, p) : launch_i8_t<J, 1, 2, 0, 288, 8>(st, a, p);
+    if constexpr (J <= 9) return M == 1 ? launch_i8_t<J, 1, 1, 0, 544, 8>(st, a, p) : launch_i8_t<J, 1, 2, 0, 544, 8>(st, a, p);
+    return fail(LTHN_ERR_INVALID, "affine_qmv: no 8-bit integer tensor-core instantiation for this plan");
 }
 
 // block-size classes: up to 4, 8 and 16 consumer warps (plus the producer warp)

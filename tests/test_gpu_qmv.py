@@ -372,3 +372,31 @@ def test_zero_sized_and_rejected_arguments(oracle):
     with pytest.raises(lthn.LthnError):
         lthn.check(lthn.lib().lthn_affine_qmv(None, x.ptr, lthn.BF16, 1, q.packed.ptr, q.scales.ptr, q.biases.ptr,
                                               16, 64, 64, 3, y.ptr, lthn.F32))
+
+
+@pytest.mark.parametrize("M", [1, 2])
+@pytest.mark.parametrize("N,K", [(4096, 2304), (9216, 2304), (2304, 9216), (5376, 21504), (1008, 128), (16, 64)])
+def test_eight_bit_codes_on_the_integer_kernel(oracle, N, K, M):
+    """8-bit group-64 weights (the per-module override QAT packs give their MLP projections) through
+    affine_qmv with one or two rows: the integer tensor-core kernel takes the code bytes as MMA operands
+    without an unpack step - whole rows for K = 2304, K slices with partial sums for K = 9216 and 21504.
+    f32-grade against the f64 reference (the activations go through the same three digit planes), and
+    the same numbers as the general kernel that serves the other row counts."""
+    import lthn
+    p, s, b = make_weight(oracle, N, K, seed=N + K, bits=8)
+    q = lthn.QuantWeight.from_host(p, s, b, 8, 64)
+    xf, xb = make_x(oracle, M, K, seed=3 + M)
+    want = oracle.matnt_quant_host(xf, p, s, b, 64, 8, threads=8)
+    for x_arr, dt in ((xb, lthn.BF16), (xf, lthn.F32)):
+        got = run_qmv(lthn, x_arr, dt, M, q, lthn.F32)
+        assert rel_err(got, want) <= REF_TOL
+        assert rms_err(got, want) <= F32_TOL_RMS
+    got_b = oracle.bf16_to_f32(run_qmv(lthn, xb, lthn.BF16, M, q, lthn.BF16))
+    assert rel_err(got_b, want) <= 1e-2
+    # three rows take the general kernel: rows 0 and 1 of that result are the same matvecs
+    if M == 2:
+        x3 = np.concatenate([xf, xf[:1]], axis=0)
+        got3 = run_qmv(lthn, x3, lthn.F32, 3, q, lthn.F32)
+        assert rms_err(got3[:2], want) <= F32_TOL_RMS
+    assert lthn.device_status() == 0
+    q.free()
