@@ -949,7 +949,26 @@ __global__ void advance_kernel(int32_t* row_pos, int32_t* ids, const int32_t* ne
     if (r < rows) { row_pos[r] += 1; ids[r] = next[r]; }
 }
 
+// act = gelu_tanh(gate) * up for a block whose gate and up projections ran as separate matvecs
+// (8-bit codes); gelu_tanh as hipGemma4Q4HostGELU (engine/hip/hip_gemma4_q4_layer.go:3582-3597)
+__global__ void geglu_kernel(const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ out, int64_t n) {
+    pdl_trigger();
+    pdl_wait();
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float x = g[i];
+        const float inner = k0 * (x + k1 * x * x * x);
+        out[i] = 0.5f * x * (1.0f + tanhf(inner)) * u[i];
+    }
+}
+
 // ---- launch wrappers ----------------------------------------------------------------------
+int32_t launch_geglu(cudaStream_t s, const float* g, const float* u, float* out, int64_t n) {
+    const unsigned grid = (unsigned)std::min<int64_t>((n + 255) / 256, 148 * 8);
+    LTHN_CUDA_TRY(launch_k(geglu_kernel, dim3(grid), dim3(256), 0, s, g, u, out, n));
+    return LTHN_OK;
+}
+
 int32_t launch_embed(cudaStream_t s, const int32_t* ids, int rows, const uint32_t* packed, const uint16_t* scales,
                      const uint16_t* biases, int hidden, int vocab, float embed_scale, float* out) {
     LTHN_CUDA_TRY(launch_k(embed_kernel, dim3(rows), dim3(256), 0, s, ids, packed, scales, biases, hidden, vocab, embed_scale, out));

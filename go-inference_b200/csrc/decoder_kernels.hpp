@@ -27,6 +27,7 @@ struct SdpaArgs {
     int window = 0;            // > 0: a row attends only its last `window` keys (sliding-attention block)
 };
 
+int32_t launch_geglu(cudaStream_t s, const float* g, const float* u, float* out, int64_t n);
 int32_t launch_embed(cudaStream_t s, const int32_t* ids, int rows, const uint32_t* packed, const uint16_t* scales,
                      const uint16_t* biases, int hidden, int vocab, float embed_scale, float* out);
 int32_t launch_rmsnorm(cudaStream_t s, const float* a, float* h, const float* w_post, const float* w_next, float* out,

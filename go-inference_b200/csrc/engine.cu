@@ -86,6 +86,7 @@ enum { kNcclFloat32 = 7, kNcclSum = 0 };
 struct Linear {
     uint32_t* wq = nullptr; uint16_t* s = nullptr; uint16_t* b = nullptr;
     int64_t N = 0, K = 0;  // local (sharded) shape
+    int bits = 4;          // 8 for an MLP projection of a mixed-precision pack
 };
 enum { ROLE_Q = 0, ROLE_K, ROLE_V, ROLE_O, ROLE_GATE, ROLE_UP, ROLE_DOWN, ROLE_COUNT };
 // phases of a decode step as the tracer reports them
@@ -166,6 +167,10 @@ struct Model {
     bool site_fused[2] = {};    // tensor parallel: the site's norm runs inside the consuming matvec (push mode)
     bool xchg_ready = false;
     bool fuse_norm = false;  // batch 1-2: norms run inside the matvec that consumes them
+    // mixed precision: some MLP projections hold 8-bit codes; their gate and up run as separate matvecs into g8 / u8
+    bool mixed = false;
+    bool pair8_ok = false;  // an 8-bit gate/up pair of this shape runs as one fused matvec for one and two rows
+    float *g8 = nullptr, *u8 = nullptr;
     // engine.DecodePhaseTracer: while on, one-row decode steps run kernel by kernel with an event between phases
     struct PhaseTrace {
         bool on = false;
@@ -287,6 +292,13 @@ static int32_t shard_plan(Model* m, int layer, int role, ShardPlan* p) {
     }
     (void)t;
     return LTHN_OK;
+}
+
+// y[rows, N] = x[rows, K] W^T for one linear at its own code width (f32 in, f32 out, no fused norm or GeGLU)
+static int32_t project_plain(cudaStream_t s, const Linear& l, const float* x, float* y, int rows) {
+    if (l.bits == 8) return lthn_affine_qmv(s, x, LTHN_DTYPE_F32, rows, l.wq, l.s, l.b, l.N, l.K, 64, 8, y, LTHN_DTYPE_F32);
+    QmvCall q{l.wq, l.s, l.b, nullptr, nullptr, nullptr, x, LTHN_DTYPE_F32, y, LTHN_DTYPE_F32, l.N, l.K, rows};
+    return qmv_dispatch(s, q);
 }
 
 static int32_t all_reduce(Model* m, float* buf, size_t n) {
@@ -528,10 +540,22 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
             }
             gc.x_cols = m->xn_cols; gc.x_split = split;
         }
-        if ((rc = qmv_dispatch(s, gc))) return rc;
+        if (L.gate.bits == 8 && L.up.bits == 8 && rows <= 2 && m->pair8_ok) {
+            // both at 8 bits, one or two rows: the same fused pair (and norm prologue, when f0) on the code bytes
+            gc.bits = 8;
+            gc.x_cols = nullptr; gc.x_split = 0;
+            if ((rc = qmv_dispatch(s, gc))) return rc;
+        } else if (L.gate.bits == 8 || L.up.bits == 8) {
+            // other row counts, or only one of the two at 8 bits: separate matvecs, GeGLU in a kernel of its own
+            if ((rc = project_plain(s, L.gate, m->xn, m->g8, rows)) || (rc = project_plain(s, L.up, m->xn, m->u8, rows)) ||
+                (rc = launch_geglu(s, m->g8, m->u8, m->act, (int64_t)rows * L.gate.N)))
+                return rc;
+        } else if ((rc = qmv_dispatch(s, gc))) return rc;
         QmvCall dc{L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, m->act, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.down.N, L.down.K, rows};
         site_out(1, f1, dc);
-        if ((rc = qmv_dispatch(s, dc))) return rc;
+        if (L.down.bits == 8) {
+            if ((rc = project_plain(s, L.down, m->act, m->a, rows))) return rc;
+        } else if ((rc = qmv_dispatch(s, dc))) return rc;
         trace_mark(m, PH_MLP);
         const float* next_norm = li + 1 < c.layers ? m->layers[li + 1].norm[NORM_INPUT] : m->final_norm;
         if (f1) {
@@ -1023,9 +1047,57 @@ int32_t lthn_model_upload_linear(void* model, int32_t layer, int32_t role, const
     int32_t rc = shard_plan(m, layer, role, &p);
     if (rc) return rc;
     LTHN_REQUIRE(N == p.Nfull && K == p.Kfull, "lthn_model_upload_linear: tensor shape does not match the model configuration");
+    LTHN_REQUIRE(p.dst->bits == 4, "lthn_model_upload_linear: this linear was uploaded with 8-bit codes");
     rc = upload_shard(m, p.dst, p.dst_row0, (const uint8_t*)packed, (const uint8_t*)scales, (const uint8_t*)biases, K, p.r0, p.n, p.c0, p.k);
     if (rc == LTHN_OK) m->layers[layer].have[role] = true;
     return rc;
+}
+
+// A linear at its own code width. 4 bits: lthn_model_upload_linear. 8 bits (group 64): the MLP projections of a
+// mixed-precision pack on one GPU; the linear's buffers are replaced by ones of the wider pitch.
+int32_t lthn_model_upload_linear_bits(void* model, int32_t layer, int32_t role, const void* packed, const void* scales,
+                                      const void* biases, int64_t N, int64_t K, int32_t bits) {
+    if (bits == 4) return lthn_model_upload_linear(model, layer, role, packed, scales, biases, N, K);
+    clear_error();
+    Model* m = (Model*)model;
+    LTHN_REQUIRE(m && packed && scales && biases, "lthn_model_upload_linear_bits: NULL argument");
+    LTHN_REQUIRE(bits == 8, "lthn_model_upload_linear_bits: a linear holds 4-bit or 8-bit codes");
+    LTHN_REQUIRE(!m->finalized, "lthn_model_upload_linear_bits: the model is finalized");
+    LTHN_REQUIRE(m->c.tp_size <= 1, "lthn_model_upload_linear_bits: 8-bit linears are served on one GPU only");
+    LTHN_REQUIRE(layer >= 0 && layer < m->c.layers, "lthn_model_upload_linear_bits: layer out of range");
+    LTHN_REQUIRE(role == ROLE_GATE || role == ROLE_UP || role == ROLE_DOWN,
+                 "lthn_model_upload_linear_bits: only the MLP projections (gate, up, down) take 8-bit codes");
+    ShardPlan p;
+    int32_t rc = shard_plan(m, layer, role, &p);
+    if (rc) return rc;
+    LTHN_REQUIRE(N == p.Nfull && K == p.Kfull, "lthn_model_upload_linear_bits: tensor shape does not match the model configuration");
+    Linear* l = p.dst;
+    if (l->bits != 8) {
+        // swap the 4-bit buffers for 8-bit ones
+        for (void* old : {(void*)l->wq, (void*)l->s, (void*)l->b}) {
+            auto it = std::find(m->allocs.begin(), m->allocs.end(), old);
+            if (it != m->allocs.end()) m->allocs.erase(it);
+            LTHN_CUDA_TRY(cudaFree(old));
+        }
+        l->wq = nullptr; l->s = nullptr; l->b = nullptr;
+        m->weight_bytes -= (uint64_t)N * K * 9 / 16;
+        if ((rc = dalloc(m, &l->wq, (size_t)N * K / 4)) || (rc = dalloc(m, &l->s, (size_t)N * K / 64)) ||
+            (rc = dalloc(m, &l->b, (size_t)N * K / 64)))
+            return rc;
+        m->weight_bytes += (uint64_t)N * K * 17 / 16;
+        l->bits = 8;
+    }
+    if (!m->g8) {
+        if ((rc = dalloc(m, &m->g8, (size_t)kMaxRows * m->F_l)) || (rc = dalloc(m, &m->u8, (size_t)kMaxRows * m->F_l))) return rc;
+    }
+    m->mixed = true;
+    const size_t sg = (size_t)N * K / 64 * 2;
+    LTHN_CUDA_TRY(cudaMemcpyAsync(l->wq, packed, (size_t)N * K, cudaMemcpyHostToDevice, m->stream));
+    LTHN_CUDA_TRY(cudaMemcpyAsync(l->s, scales, sg, cudaMemcpyHostToDevice, m->stream));
+    LTHN_CUDA_TRY(cudaMemcpyAsync(l->b, biases, sg, cudaMemcpyHostToDevice, m->stream));
+    LTHN_CUDA_TRY(cudaStreamSynchronize(m->stream));  // the caller's buffers may be unmapped after return
+    m->layers[layer].have[role] = true;
+    return LTHN_OK;
 }
 
 int32_t lthn_model_upload_norm(void* model, int32_t layer, int32_t role, const float* w, int64_t n) {
@@ -1219,6 +1291,22 @@ int32_t lthn_model_finalize(void* model) {
         m->fuse_norm = !(env && env[0] == '1') && m->c.tp_size <= 1 && qmv_can_fuse_norm(L0.qkv.N, L0.qkv.K, 2, false) &&
                        qmv_can_fuse_norm(L0.gate.N, L0.gate.K, 1, true) && qmv_can_fuse_norm(m->head.N, m->head.K, 2, false);
     }
+    if (m->mixed) {
+        // 8-bit MLP projections. The prefill GEMM reads 4-bit codes, so prompts go through the batched matvec path.
+        // The norms stay inside the matvecs when every block's gate/up pair has one width and, where that is 8 bits,
+        // the 8-bit kernel plans the fused pair with the norm prologue.
+        m->prefill_tc = false;
+        const Layer& L0 = m->layers[0];
+        I8Plan pl;
+        m->pair8_ok = i8_plan_b8(L0.gate.N, L0.gate.K, 2, &pl, 0, 0, 1, false);
+        bool ok = true, any_pair8 = false;
+        for (const Layer& L : m->layers) {
+            ok = ok && L.gate.bits == L.up.bits;
+            any_pair8 = any_pair8 || L.gate.bits == 8;
+        }
+        if (any_pair8) ok = ok && m->pair8_ok && qmv_can_fuse_norm(L0.gate.N, L0.gate.K, 2, true, 8);
+        m->fuse_norm = m->fuse_norm && ok;
+    }
     {
         // Opt-in (LTHN_CUDA_ATTN_FUSION=1): measured slower than the three kernels it replaces - every CTA repeats the
         // head norms in front of its loads, and the merge by the last CTA puts a fence + counter round trip on the tail.
@@ -1236,7 +1324,7 @@ int32_t lthn_model_finalize(void* model) {
         // Off unless LTHN_CUDA_PERSIST=1: measured slower than the kernel chain on both benchmark models so far.
         const char* env = getenv("LTHN_CUDA_PERSIST");
         std::string why;
-        if (env && env[0] == '1' && c.tp_size <= 1 && m->fuse_norm && c.sliding_window == 0 &&
+        if (env && env[0] == '1' && c.tp_size <= 1 && m->fuse_norm && !m->mixed && c.sliding_window == 0 &&
             persist_supported(c.hidden, m->Hq_l, m->Hkv_l, c.head_dim, m->F_l, &why)) {
             int32_t rc;
             PersistArgs& a = m->pk;

@@ -493,14 +493,18 @@ int32_t lthn_model_load_dir(const char* dir, const lthn_load_options* opts, void
         if (got_gs != gs || got_bits != bits || tw.shape[1] * 32 != K * got_bits)
             return bail(LTHN_ERR_INVALID, base + ": tensor geometry says group " + std::to_string(got_gs) + " / " + std::to_string(got_bits) +
                                               " bit, the quantization block says group " + std::to_string(gs) + " / " + std::to_string(bits) + " bit");
-        if (gs != 64 || bits != 4)
+        // 4-bit group-64 everywhere; an 8-bit group-64 override on an MLP projection of a one-GPU model
+        const bool mlp = layer >= 0 && (role == LTHN_ROLE_GATE || role == LTHN_ROLE_UP || role == LTHN_ROLE_DOWN);
+        const bool wide = bits == 8 && gs == 64 && mlp && o.tp_size <= 1;
+        if (gs != 64 || (bits != 4 && !wide))
             return bail(LTHN_ERR_INVALID, base + ": " + std::to_string(bits) + "-bit group-" + std::to_string(gs) +
-                                              " weights: the decoder engine serves 4-bit group-64 linears only");
+                                              " weights: the decoder engine serves 4-bit group-64 linears (8-bit group-64 for the MLP"
+                                              " projections on one GPU) only");
         std::vector<uint16_t> ts16, tb16;
         const uint16_t *ps, *pb;
         std::string e2;
         if (!as_bf16(ts, &ts16, &ps, &e2, base + ".scales") || !as_bf16(tb, &tb16, &pb, &e2, base + ".biases")) return bail(LTHN_ERR_INVALID, e2);
-        const int32_t r = lthn_model_upload_linear(m, layer, role, tw.data, ps, pb, N, K);
+        const int32_t r = lthn_model_upload_linear_bits(m, layer, role, tw.data, ps, pb, N, K, bits);
         return r ? bail_keep(r) : LTHN_OK;
     };
     auto upload_norm = [&](const std::string& name, int layer, int role, int64_t n) -> int32_t {

@@ -533,6 +533,22 @@ LTHN_HIDDEN int g_force_rt = 0, g_force_warps = 0, g_force_kernel = 0;
 // tensor-core kernel (f32 activations are first split into bf16 columns).
 int32_t qmv_dispatch(cudaStream_t s, const QmvCall& c) {
     const int fuse = c.wq2 ? 1 : 0;
+    if (c.bits == 8) {
+        // 8-bit codes, one or two rows: the integer tensor-core kernel (plain, GeGLU pair, fused norm prologue)
+        I8Plan plan;
+        bool aligned = (((uintptr_t)c.wq | (uintptr_t)c.scales | (uintptr_t)c.biases) & 15) == 0;
+        if (c.norm) {
+            const NormFuse& n = *c.norm;
+            aligned = aligned && (((uintptr_t)n.a | (uintptr_t)n.h_in | (uintptr_t)n.h_out | (uintptr_t)n.w_post | (uintptr_t)n.w_next) & 7) == 0;
+        } else {
+            aligned = aligned && ((uintptr_t)c.x & 15) == 0;
+        }
+        if (c.wq2) aligned = aligned && (((uintptr_t)c.wq2 | (uintptr_t)c.scales2 | (uintptr_t)c.biases2) & 15) == 0;
+        const bool forced = g_force_kernel == 3;
+        if (c.M <= 2 && aligned && i8_plan_b8(c.N, c.K, c.M, &plan, forced ? g_force_rt : 0, forced ? g_force_warps : 0, fuse, c.norm != nullptr))
+            return i8_launch(s, c, plan);
+        return fail(LTHN_ERR_INVALID, "affine_qmv: no integer tensor-core plan for this 8-bit call");
+    }
     // Measured on B200: the dp4a kernel wins once a matrix is large enough to amortise its
     // activation conversion (it streams at ~4.5 TB/s where the tensor-core kernel is capped near
     // 3 TB/s by the mma.sync issue rate); small matrices are launch/latency sized and the
@@ -646,10 +662,10 @@ int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M,
     int32_t rc = qmv_validate(x, x_dtype, M, packed, scales, biases, N, K, gs, bits, y, y_dtype, s, &done);
     if (rc || done) return rc;
     const bool fast = bits == 4 && gs == 64 && ((uintptr_t)packed & 7) == 0 && ((uintptr_t)x & 15) == 0;
-    if (bits == 8 && gs == 64 && M <= 2 && g_force_kernel == 0 && ((uintptr_t)packed & 15) == 0 && ((uintptr_t)x & 15) == 0) {
+    if (bits == 8 && gs == 64 && M <= 2 && (g_force_kernel == 0 || g_force_kernel == 3) && ((uintptr_t)packed & 15) == 0 && ((uintptr_t)x & 15) == 0) {
         // 8-bit codes (the MLP projections of QAT packs): the integer tensor-core kernel takes the bytes as they are
         I8Plan pl;
-        if (i8_plan_b8(N, K, M, &pl)) {
+        if (i8_plan_b8(N, K, M, &pl, g_force_kernel == 3 ? g_force_rt : 0, g_force_kernel == 3 ? g_force_warps : 0)) {
             QmvCall c8{packed, scales, biases, nullptr, nullptr, nullptr, x, x_dtype, y, y_dtype, N, K, M};
             c8.bits = 8;
             return i8_launch(s, c8, pl);
@@ -673,16 +689,27 @@ int32_t lthn_affine_qmv_geglu(void* stream, const void* x, int32_t x_dtype, int3
                               const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
                               const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, void* y,
                               int32_t y_dtype) {
+    return lthn_affine_qmv_geglu_bits(stream, x, x_dtype, M, gate_packed, gate_scales, gate_biases, up_packed, up_scales, up_biases,
+                                      N, K, 4, y, y_dtype);
+}
+
+int32_t lthn_affine_qmv_geglu_bits(void* stream, const void* x, int32_t x_dtype, int32_t M, const uint32_t* gate_packed,
+                                   const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
+                                   const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, int32_t bits,
+                                   void* y, int32_t y_dtype) {
     clear_error();
     cudaStream_t s = (cudaStream_t)stream;
     bool done = false;
-    int32_t rc = qmv_validate(x, x_dtype, M, gate_packed, gate_scales, gate_biases, N, K, 64, 4, y, y_dtype, s, &done);
+    LTHN_REQUIRE(bits == 4 || bits == 8, "affine_qmv_geglu: 4-bit or 8-bit codes");
+    LTHN_REQUIRE(bits == 4 || M <= 2, "affine_qmv_geglu: 8-bit codes serve one or two rows");
+    int32_t rc = qmv_validate(x, x_dtype, M, gate_packed, gate_scales, gate_biases, N, K, 64, bits, y, y_dtype, s, &done);
     if (rc || done) return rc;
     LTHN_REQUIRE(up_packed && up_scales && up_biases, "affine_qmv_geglu: NULL pointer");
     LTHN_REQUIRE(K > 0 && K % 64 == 0, "affine_qmv_geglu: K must be a positive multiple of 64");
     LTHN_REQUIRE((((uintptr_t)gate_packed | (uintptr_t)up_packed) & 7) == 0 && ((uintptr_t)x & 15) == 0,
                  "affine_qmv_geglu: packed weights must be 8-byte and x 16-byte aligned");
     QmvCall c{gate_packed, gate_scales, gate_biases, up_packed, up_scales, up_biases, x, x_dtype, y, y_dtype, N, K, M};
+    c.bits = bits;
     return qmv_dispatch(s, c);
 }
 
@@ -690,7 +717,16 @@ int32_t lthn_affine_qmv_normed(void* stream, const float* a, const float* h_in, 
                                const float* w_next, float eps, int32_t M, const uint32_t* packed, const uint16_t* scales,
                                const uint16_t* biases, const uint32_t* up_packed, const uint16_t* up_scales,
                                const uint16_t* up_biases, int64_t N, int64_t K, void* y, int32_t y_dtype) {
+    return lthn_affine_qmv_normed_bits(stream, a, h_in, h_out, w_post, w_next, eps, M, packed, scales, biases, up_packed, up_scales,
+                                       up_biases, N, K, 4, y, y_dtype);
+}
+
+int32_t lthn_affine_qmv_normed_bits(void* stream, const float* a, const float* h_in, float* h_out, const float* w_post,
+                                    const float* w_next, float eps, int32_t M, const uint32_t* packed, const uint16_t* scales,
+                                    const uint16_t* biases, const uint32_t* up_packed, const uint16_t* up_scales,
+                                    const uint16_t* up_biases, int64_t N, int64_t K, int32_t bits, void* y, int32_t y_dtype) {
     clear_error();
+    LTHN_REQUIRE(bits == 4 || bits == 8, "affine_qmv_normed: 4-bit or 8-bit codes");
     cudaStream_t s = (cudaStream_t)stream;
     LTHN_REQUIRE(M >= 0 && N >= 0 && K >= 0, "affine_qmv_normed: negative dimension");
     if (M == 0 || N == 0) return LTHN_OK;
@@ -704,6 +740,7 @@ int32_t lthn_affine_qmv_normed(void* stream, const float* a, const float* h_in, 
     NormFuse nf{a, h_in, h_out, w_post, w_next, eps};
     QmvCall c{packed, scales, biases, up_packed, up_scales, up_biases, nullptr, LTHN_DTYPE_F32, y, y_dtype, N, K, M};
     c.norm = &nf;
+    c.bits = bits;
     return qmv_dispatch(s, c);
 }
 

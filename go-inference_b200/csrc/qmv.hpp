@@ -64,7 +64,7 @@ struct QmvCall {
 };
 
 // true when a call of this shape can carry a fused norm prologue
-bool qmv_can_fuse_norm(int64_t N, int64_t K, int M, bool geglu);
+bool qmv_can_fuse_norm(int64_t N, int64_t K, int M, bool geglu, int bits = 4);
 
 // bf16 columns a tensor-core matvec over f32 activations wants per activation row
 int32_t qmv_split_for(int M, int x_dtype);
@@ -81,7 +81,7 @@ extern __attribute__((visibility("hidden"))) int g_i8_stg;
 // max_slices: 1 = whole rows only; > 1 lets the plan cut K into up to that many slices (partial sums)
 bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I8Plan* p, int max_slices = 1,
              bool has_norm = false);
-bool i8_plan_b8(int64_t N, int64_t K, int M, I8Plan* p);
+bool i8_plan_b8(int64_t N, int64_t K, int M, I8Plan* p, int force_ks = 0, int force_w = 0, int fuse = 0, bool has_norm = false);
 int32_t i8_launch(cudaStream_t st, const QmvCall& c, const I8Plan& p);
 
 // y[i] = sum over s < ks of part[s*n + i]

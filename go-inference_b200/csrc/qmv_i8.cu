@@ -11,7 +11,7 @@ struct I8Args;
 template <int J>
 int32_t launch_i8_w(cudaStream_t st, const I8Args& a, const I8Plan& p, int M, int fuse);
 template <int J>
-int32_t launch_i8_b8(cudaStream_t st, const I8Args& a, const I8Plan& p, int M);
+int32_t launch_i8_b8(cudaStream_t st, const I8Args& a, const I8Plan& p, int M, int fuse);
 int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p);
 
 // ---- host side --------------------------------------------------------------------
@@ -99,23 +99,34 @@ bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I
     return best_ks != 0;
 }
 
-// 8-bit codes (plain matvec, one or two rows): whole rows while a 16-row block fits the ring (K <= ~5376), else the
-// fewest K slices that do
-bool i8_plan_b8(int64_t N, int64_t K, int M, I8Plan* p) {
+// 8-bit codes, one or two rows: whole rows while a 16-row block fits the ring (K <= ~5376), else K slices with
+// partial sums. Measured on B200 (one row): 2304 x 9216 takes 15.0 / 15.4 / 14.0 / 10.4 / 10.9 us with 2 / 3 / 4 /
+// 6 / 8 slices, 5376 x 21504 59 / 61 / 46 us with 4 / 6 / 8 - many short slices (several blocks per SM, all of
+// the matrix in flight at once) beat few long ones, so the slice count whose slices are nearest 24 groups wins.
+// A GeGLU pair (fuse) or a fused norm prologue needs whole rows; rows of 2048 codes and more take the
+// interleaved 8 + 8 row block, as 4-bit rows of the same byte length do.
+bool i8_plan_b8(int64_t N, int64_t K, int M, I8Plan* p, int force_ks, int force_w, int fuse, bool has_norm) {
     if (M < 1 || M > 2 || K % 64 != 0 || N < 16 || N % 16 != 0) return false;
     const int G = (int)(K / 64);
-    if (i8_plan_slice(N, G, 1, M, 0, 0, false, p, 8)) return true;
+    if (fuse) fuse = K >= 2048 ? 2 : 1;
+    if (force_ks <= 1 && i8_plan_slice(N, G, 1, M, fuse, force_w, has_norm, p, 8)) return true;
+    if (fuse || has_norm) return false;
+    int best_ks = 0, best_d = 1 << 30;
     for (int ks : {2, 3, 4, 6, 8}) {
-        if (G % ks) continue;
+        if (G % ks || (force_ks > 1 && ks != force_ks)) continue;
         const int Gs = G / ks;
         if ((Gs & 1) || (G & 1) || Gs < 8) continue;
-        if (i8_plan_slice(N, Gs, ks, M, 0, 0, false, p, 8)) return true;
+        I8Plan q;
+        if (!i8_plan_slice(N, Gs, ks, M, 0, force_w, false, &q, 8)) continue;
+        const int d = std::abs(Gs - 24);
+        if (d < best_d) { best_d = d; best_ks = ks; *p = q; }
     }
-    return false;
+    return best_ks != 0;
 }
 
-bool qmv_can_fuse_norm(int64_t N, int64_t K, int M, bool geglu) {
+bool qmv_can_fuse_norm(int64_t N, int64_t K, int M, bool geglu, int bits) {
     I8Plan p;
+    if (bits == 8) return i8_plan_b8(N, K, M, &p, 0, 0, geglu ? 1 : 0, true);
     return i8_plan(N, K, M, geglu ? 1 : 0, 0, 0, &p, 1, true);
 }
 

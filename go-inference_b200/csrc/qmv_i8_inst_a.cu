@@ -15,12 +15,12 @@ extern template int32_t launch_i8_w<12>(cudaStream_t, const I8Args&, const I8Pla
 extern template int32_t launch_i8_w<16>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
 extern template int32_t launch_i8_w<18>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
 extern template int32_t launch_i8_w<21>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
-extern template int32_t launch_i8_b8<2>(cudaStream_t, const I8Args&, const I8Plan&, int);
-extern template int32_t launch_i8_b8<3>(cudaStream_t, const I8Args&, const I8Plan&, int);
-extern template int32_t launch_i8_b8<4>(cudaStream_t, const I8Args&, const I8Plan&, int);
-extern template int32_t launch_i8_b8<6>(cudaStream_t, const I8Args&, const I8Plan&, int);
-extern template int32_t launch_i8_b8<9>(cudaStream_t, const I8Args&, const I8Plan&, int);
-extern template int32_t launch_i8_b8<12>(cudaStream_t, const I8Args&, const I8Plan&, int);
+extern template int32_t launch_i8_b8<2>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
+extern template int32_t launch_i8_b8<3>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
+extern template int32_t launch_i8_b8<4>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
+extern template int32_t launch_i8_b8<6>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
+extern template int32_t launch_i8_b8<9>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
+extern template int32_t launch_i8_b8<12>(cudaStream_t, const I8Args&, const I8Plan&, int, int);
 
 // y[i] = sum over the K slices of part[s][i], slices added in order
 __global__ void sum_parts_kernel(const float* __restrict__ part, int ks, int64_t n, void* __restrict__ y, int y_dtype) {
@@ -53,7 +53,7 @@ int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p) {
     if (c.npush && (c.y_dtype != LTHN_DTYPE_F32 || p.ks != 1 || c.wq2)) return fail(LTHN_ERR_INVALID, "affine_qmv: pushed results are f32, whole rows, no GeGLU");
     a.ks = p.ks; a.Gs = p.Gs;
     a.bits = c.bits;
-    if (c.bits == 8 && (c.wq2 || c.norm || c.npush)) return fail(LTHN_ERR_INVALID, "affine_qmv: 8-bit codes take the plain matvec only");
+    if (c.bits == 8 && c.npush) return fail(LTHN_ERR_INVALID, "affine_qmv: 8-bit codes do not push their results to peers");
     if (c.norm && p.ks != 1) return fail(LTHN_ERR_INVALID, "affine_qmv: a fused norm prologue needs whole rows");
     if (p.ks > 1) {
         if (c.parts) {
@@ -75,12 +75,12 @@ int32_t i8_launch_args(cudaStream_t st, const QmvCall& c, const I8Plan& p) {
     int32_t rc = LTHN_ERR_INVALID;
     if (c.bits == 8) {
         switch (p.J) {
-            case 2: rc = launch_i8_b8<2>(st, a, p, c.M); break;
-            case 3: rc = launch_i8_b8<3>(st, a, p, c.M); break;
-            case 4: rc = launch_i8_b8<4>(st, a, p, c.M); break;
-            case 6: rc = launch_i8_b8<6>(st, a, p, c.M); break;
-            case 9: rc = launch_i8_b8<9>(st, a, p, c.M); break;
-            case 12: rc = launch_i8_b8<12>(st, a, p, c.M); break;
+            case 2: rc = launch_i8_b8<2>(st, a, p, c.M, fuse); break;
+            case 3: rc = launch_i8_b8<3>(st, a, p, c.M, fuse); break;
+            case 4: rc = launch_i8_b8<4>(st, a, p, c.M, fuse); break;
+            case 6: rc = launch_i8_b8<6>(st, a, p, c.M, fuse); break;
+            case 9: rc = launch_i8_b8<9>(st, a, p, c.M, fuse); break;
+            case 12: rc = launch_i8_b8<12>(st, a, p, c.M, fuse); break;
             default: return fail(LTHN_ERR_INVALID, "affine_qmv: no 8-bit integer tensor-core instantiation for this plan");
         }
     } else

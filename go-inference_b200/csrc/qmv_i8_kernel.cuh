@@ -84,13 +84,13 @@ __device__ __forceinline__ float bf16f(uint16_t h) { return __uint_as_float((uin
 // FUSE != 0: two weight sets, output gelu_tanh(W1 x) * (W2 x). FUSE=1 stages 16 rows of each set
 // per row block (short rows: fewer, fatter blocks); FUSE=2 stages 8 rows of each set as MMA rows
 // 0-7 and 8-15, so a stage is as large as an unfused one (long rows: more blocks fit an SM).
-// BITS = 8 (plain matvec only): a group of a row is 64 code bytes that go into the MMA as they are. The MMA's k
+// BITS = 8: a group of a row is 64 code bytes that go into the MMA as they are. The MMA's k
 // index may be permuted freely as long as both operands agree, so thread t of a fragment takes the eight
 // consecutive bytes 8t..8t+7 of a 32-code half group (one 8-byte load per row) and the activation digits sit in
 // natural order.
 template <int J, int RT, int MT, int FUSE, int BITS = 4>
 __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
-    static_assert(BITS == 4 || (BITS == 8 && FUSE == 0), "8-bit codes: plain matvec only");
+    static_assert(BITS == 4 || BITS == 8, "4-bit or 8-bit codes");
     constexpr int GB = BITS * 8;  // code bytes per group and row
     constexpr int SETS = FUSE == 1 ? 2 : 1;
     constexpr int OR = FUSE == 2 ? 8 : 16;  // output rows per row block
@@ -142,7 +142,7 @@ __device__ __forceinline__ void qmv_i8_body(const I8Args& a) {
                 unsigned char* d = sbase;
                 if (lane < 16) {
                     const int set = lane >> 3, r = lane & 7;
-                    bulk_g2s(d + (size_t)lane * RS, (const unsigned char*)a.wq[set] + (row0 + r) * (K >> 1), (uint32_t)rowbytes, &full[st]);
+                    bulk_g2s(d + (size_t)lane * RS, (const unsigned char*)a.wq[set] + (row0 + r) * (K * BITS / 8), (uint32_t)rowbytes, &full[st]);
                 } else if (lane < 20) {
                     const int set = lane & 1, which = (lane >> 1) & 1;  // which: 0 scales, 1 biases
                     const uint16_t* src = which ? a.biases[set] : a.scales[set];
@@ -529,8 +529,8 @@ template <int J, int RT, int MT, int FUSE>
 __global__ void __launch_bounds__(160, 5) qmv_i8_kernel_small(const I8Args a) { qmv_i8_body<J, RT, MT, FUSE>(a); }
 
 // 8-bit codes: one block per SM class only (the stages are twice as large, so two to four blocks fit an SM anyway)
-template <int J, int MT, int LB>
-__global__ void __launch_bounds__(LB) qmv_i8_b8_kernel(const I8Args a) { qmv_i8_body<J, 1, MT, 0, 8>(a); }
+template <int J, int MT, int FUSE, int LB>
+__global__ void __launch_bounds__(LB) qmv_i8_b8_kernel(const I8Args a) { qmv_i8_body<J, 1, MT, FUSE, 8>(a); }
 
 template <int J, int RT, int MT, int FUSE, int LB, int BITS = 4>
 inline int32_t launch_i8_t(cudaStream_t st, const I8Args& a, const I8Plan& p) {
@@ -539,7 +539,7 @@ inline int32_t launch_i8_t(cudaStream_t st, const I8Args& a, const I8Plan& p) {
     int dev = 0;
     LTHN_CUDA_TRY(cudaGetDevice(&dev));
     void (*kern)(const I8Args);
-    if constexpr (BITS == 8) kern = qmv_i8_b8_kernel<J, MT, LB>;
+    if constexpr (BITS == 8) kern = qmv_i8_b8_kernel<J, MT, FUSE, LB>;
     else kern = LB == 160 ? qmv_i8_kernel_small<J, RT, MT, FUSE> : qmv_i8_kernel<J, RT, MT, FUSE, LB>;
     std::unique_lock<std::mutex> lk(mu);
     if (attr_dev != dev) {
@@ -575,11 +575,17 @@ inline int32_t launch_i8_j(cudaStream_t st, const I8Args& a, const I8Plan& p, in
     return launch_i8_t<J, 1, 2, 0, LB>(st, a, p);
 }
 
-// 8-bit codes, plain matvec: J in {2, 3, 4, 6, 9, 12}, block classes of up to 8 and up to 16 consumer warps
+// 8-bit codes: J in {2, 3, 4, 6, 9, 12}, block classes of up to 8 and up to 16 consumer warps
+template <int J, int LB>
+inline int32_t launch_i8_b8_j(cudaStream_t st, const I8Args& a, const I8Plan& p, int M, int fuse) {
+    if (fuse == 1) return M == 1 ? launch_i8_t<J, 1, 1, 1, LB, 8>(st, a, p) : launch_i8_t<J, 1, 2, 1, LB, 8>(st, a, p);
+    if (fuse == 2) return M == 1 ? launch_i8_t<J, 1, 1, 2, LB, 8>(st, a, p) : launch_i8_t<J, 1, 2, 2, LB, 8>(st, a, p);
+    return M == 1 ? launch_i8_t<J, 1, 1, 0, LB, 8>(st, a, p) : launch_i8_t<J, 1, 2, 0, LB, 8>(st, a, p);
+}
 template <int J>
-int32_t launch_i8_b8(cudaStream_t st, const I8Args& a, const I8Plan& p, int M) {
-    if (p.W <= 8) return M == 1 ? launch_i8_t<J, 1, 1, 0, 288, 8>(st, a, p) : launch_i8_t<J, 1, 2, 0, 288, 8>(st, a, p);
-    if constexpr (J <= 9) return M == 1 ? launch_i8_t<J, 1, 1, 0, 544, 8>(st, a, p) : launch_i8_t<J, 1, 2, 0, 544, 8>(st, a, p);
+int32_t launch_i8_b8(cudaStream_t st, const I8Args& a, const I8Plan& p, int M, int fuse) {
+    if (p.W <= 8) return launch_i8_b8_j<J, 288>(st, a, p, M, fuse);
+    if constexpr (J <= 9) return launch_i8_b8_j<J, 544>(st, a, p, M, fuse);
     return fail(LTHN_ERR_INVALID, "affine_qmv: no 8-bit integer tensor-core instantiation for this plan");
 }
 

@@ -161,6 +161,8 @@ class _Sig:
     lthn_affine_qmv_noalloc = (i32, [vp, vp, i32, vp, vp, vp, i64, i64, vp])
     lthn_affine_qmv_geglu = (i32, [vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, i64, i64, vp, i32])
     lthn_affine_qmv_normed = (i32, [vp, vp, vp, vp, vp, vp, f32, i32, vp, vp, vp, vp, vp, vp, i64, i64, vp, i32])
+    lthn_affine_qmv_geglu_bits = (i32, [vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, i64, i64, i32, vp, i32])
+    lthn_affine_qmv_normed_bits = (i32, [vp, vp, vp, vp, vp, vp, f32, i32, vp, vp, vp, vp, vp, vp, i64, i64, i32, vp, i32])
     lthn_rmsnorm = (i32, [vp, vp, vp, vp, i32, i32, f32])
     lthn_rmsnorm_residual = (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32])
     lthn_debug_rmsnorm_gather_local = (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, i32, C.c_uint32])
@@ -171,6 +173,7 @@ class _Sig:
     lthn_model_load_dir = (i32, [C.c_char_p, C.POINTER(LoadOptions), pvp])
     lthn_checkpoint_inspect = (i32, [C.c_char_p, C.c_char_p, sz])
     lthn_model_upload_linear = (i32, [vp, i32, i32, vp, vp, vp, i64, i64])
+    lthn_model_upload_linear_bits = (i32, [vp, i32, i32, vp, vp, vp, i64, i64, i32])
     lthn_model_upload_norm = (i32, [vp, i32, i32, vp, i64])
     lthn_model_synthesize = (i32, [vp, u64, f32])
     lthn_model_finalize = (i32, [vp])
@@ -482,6 +485,10 @@ def topk_candidates(logits_f32: Buf, rows, vocab, k, scratch_bf16: Buf, out_ids:
 
 
 def qmv_geglu(x: Buf, x_dtype, M, gate: QuantWeight, up: QuantWeight, y: Buf, y_dtype, stream=None):
+    if gate.bits != 4:
+        check(lib().lthn_affine_qmv_geglu_bits(_s(stream), x.ptr, x_dtype, M, gate.packed.ptr, gate.scales.ptr, gate.biases.ptr,
+                                               up.packed.ptr, up.scales.ptr, up.biases.ptr, gate.N, gate.K, gate.bits, y.ptr, y_dtype))
+        return
     check(lib().lthn_affine_qmv_geglu(_s(stream), x.ptr, x_dtype, M, gate.packed.ptr, gate.scales.ptr, gate.biases.ptr,
                                       up.packed.ptr, up.scales.ptr, up.biases.ptr, gate.N, gate.K, y.ptr, y_dtype))
 
@@ -544,13 +551,18 @@ class Model:
                             info["vocab"], max_len, max_lanes, tp_rank=tp_rank, tp_size=tp_size)
         return m
 
-    def upload_linear(self, layer, role, packed, scales, biases):
+    def upload_linear(self, layer, role, packed, scales, biases, bits=4):
+        """bits=8: an MLP projection of a mixed-precision pack (one code per byte, group 64)."""
         pk = np.ascontiguousarray(packed, dtype=np.uint32)
         sc = np.ascontiguousarray(scales, dtype=np.uint16)
         bi = np.ascontiguousarray(biases, dtype=np.uint16)
         r = ROLE[role] if isinstance(role, str) else role
-        check(lib().lthn_model_upload_linear(self.h, layer, r, pk.ctypes.data, sc.ctypes.data, bi.ctypes.data,
-                                             pk.shape[0], pk.shape[1] * 8))
+        if bits == 4:
+            check(lib().lthn_model_upload_linear(self.h, layer, r, pk.ctypes.data, sc.ctypes.data, bi.ctypes.data,
+                                                 pk.shape[0], pk.shape[1] * 8))
+        else:
+            check(lib().lthn_model_upload_linear_bits(self.h, layer, r, pk.ctypes.data, sc.ctypes.data, bi.ctypes.data,
+                                                      pk.shape[0], pk.shape[1] * 32 // bits, bits))
 
     def upload_norm(self, layer, role, w):
         a = np.ascontiguousarray(w, dtype=np.float32)

@@ -164,6 +164,14 @@ int32_t lthn_affine_qmv_normed(void* stream, const float* a, const float* h_in, 
                                const uint16_t* biases, const uint32_t* up_packed, const uint16_t* up_scales,
                                const uint16_t* up_biases, int64_t N, int64_t K, void* y, int32_t y_dtype);
 
+/* The same with the weights' code width given: bits = 4 is lthn_affine_qmv_normed; bits = 8 (group 64,
+ * one code per byte - the MLP projections of a mixed-precision pack) runs the same prologue in front of
+ * the 8-bit form of the kernel. No counterpart in the reference. */
+int32_t lthn_affine_qmv_normed_bits(void* stream, const float* a, const float* h_in, float* h_out, const float* w_post,
+                                    const float* w_next, float eps, int32_t M, const uint32_t* packed, const uint16_t* scales,
+                                    const uint16_t* biases, const uint32_t* up_packed, const uint16_t* up_scales,
+                                    const uint16_t* up_biases, int64_t N, int64_t K, int32_t bits, void* y, int32_t y_dtype);
+
 /* Fused GeGLU pair: y[M,N] = gelu_tanh(x * dequant(Wgate)^T) * (x * dequant(Wup)^T),
  * both weights [N,K], 4 bit, group 64; gate and up rows are streamed together so
  * the activation is read once and the intermediate never reaches memory.
@@ -174,6 +182,12 @@ int32_t lthn_affine_qmv_geglu(void* stream, const void* x, int32_t x_dtype, int3
                               const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
                               const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, void* y,
                               int32_t y_dtype);
+/* The same with the code width given: bits = 4 as above; bits = 8 (group 64, one or two rows) for the
+ * gate and up projections of a mixed-precision pack (per-module overrides, model/quant_config.go:39-88). */
+int32_t lthn_affine_qmv_geglu_bits(void* stream, const void* x, int32_t x_dtype, int32_t M, const uint32_t* gate_packed,
+                                   const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
+                                   const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, int32_t bits,
+                                   void* y, int32_t y_dtype);
 
 /* ---- affine_qmm: prefill-time quantized matmul on the tensor cores --------------
  * y[M,N] (bf16) = x[M,K] (bf16) * dequant(W[N,K])^T, fp32 accumulation in TMEM.
@@ -289,6 +303,14 @@ enum { LTHN_NORM_INPUT = 0, LTHN_NORM_POST_ATTN, LTHN_NORM_PRE_FF, LTHN_NORM_POS
 int32_t lthn_model_create(const lthn_model_config* cfg, void** model);
 int32_t lthn_model_upload_linear(void* model, int32_t layer, int32_t role, const void* packed, const void* scales,
                                  const void* biases, int64_t N, int64_t K);
+/* The same for a linear whose quantization override names its own code width (the mixed-precision
+ * QAT packs of model/quant_config.go:39-88 keep the MLP projections at 8 bits). bits = 4 is
+ * lthn_model_upload_linear; bits = 8 (group 64) is accepted for LTHN_ROLE_GATE / UP / DOWN on one
+ * GPU: packed holds N*K bytes, one code per byte. A model with such a linear runs its gate and up
+ * projections as separate matvecs followed by a GeGLU kernel, its norms as kernels of their own,
+ * and prompts through the batched matvec path (the prefill GEMM reads 4-bit codes only). */
+int32_t lthn_model_upload_linear_bits(void* model, int32_t layer, int32_t role, const void* packed, const void* scales,
+                                      const void* biases, int64_t N, int64_t K, int32_t bits);
 int32_t lthn_model_upload_norm(void* model, int32_t layer, int32_t role, const float* w, int64_t n);
 /* Synthetic weights (benchmarks, tests): tensor (layer, role) is the seeded synthetic
  * [N,K] tensor of stream seed*1000003 + (layer+1)*16 + role quantised with the
@@ -319,8 +341,9 @@ int32_t lthn_model_destroy(void* model);   /* TokenModel.Close (engine/model.go:
  * geometry against the quantization block as affineGeometry does (model/linear.go:91-102), widens
  * F16 scales/biases/norms to bf16 (model/safetensors/widen.go), applies the gemma (1+w) norm fold
  * in the tensor's dtype (model/norm_bias.go:22-49), uploads this rank's shard of every tensor and
- * finalizes. The files are mapped read-only for the duration of the call. Linears other than
- * 4-bit / group 64 (e.g. an 8-bit per-module override) are rejected with the tensor named. A
+ * finalizes. The files are mapped read-only for the duration of the call. Linears are 4-bit /
+ * group 64; an 8-bit / group-64 per-module override is taken on the MLP projections of a one-GPU
+ * model (lthn_model_upload_linear_bits); anything else is rejected with the tensor named. A
  * checkpoint with sliding_window runs gemma3's layer pattern (sliding blocks with
  * rope_local_base_freq, every sliding_window_pattern-th block global); uniform_attention = 1 runs
  * every block with full attention and the checkpoint's rope_theta instead. */

@@ -63,7 +63,7 @@ typedef struct {
 enum { L_Q = 0, L_K, L_V, L_O, L_GATE, L_UP, L_DOWN, L_COUNT };
 enum { N_INPUT = 0, N_POST_ATTN, N_PRE_FF, N_POST_FF, N_QNORM, N_KNORM, N_COUNT };
 
-typedef struct { const uint32_t *w; const uint16_t *s, *b; long rows, cols; } lin_t;
+typedef struct { const uint32_t *w; const uint16_t *s, *b; long rows, cols; int bits; /* 0: the model's width */ } lin_t;
 
 typedef struct {
     lthn_o_decoder_config c;
@@ -98,10 +98,18 @@ void lthn_o_decoder_destroy(void *h) {
 int lthn_o_decoder_set_linear(void *h, int layer, int role, const uint32_t *w, const uint16_t *s,
                               const uint16_t *b, long rows, long cols) {
     dec_t *d = (dec_t *)h;
-    lin_t l = {w, s, b, rows, cols};
+    lin_t l = {w, s, b, rows, cols, 0};
     if (layer < 0) { d->embed = l; return 0; }
     if (layer >= d->c.layers || role < 0 || role >= L_COUNT) return 1;
     d->lin[layer * L_COUNT + role] = l;
+    return 0;
+}
+/* A linear whose quantization override names its own code width (model/quant_config.go:39-88);
+ * call after lthn_o_decoder_set_linear. */
+int lthn_o_decoder_set_linear_bits(void *h, int layer, int role, int bits) {
+    dec_t *d = (dec_t *)h;
+    if (layer < 0 || layer >= d->c.layers || role < 0 || role >= L_COUNT) return 1;
+    d->lin[layer * L_COUNT + role].bits = bits;
     return 0;
 }
 int lthn_o_decoder_set_norm(void *h, int layer, int role, const float *w) {
@@ -127,6 +135,7 @@ int lthn_o_proj_bf16_contract(const float *x, long tokens, const uint32_t *weigh
                               const uint16_t *biases, long rows, long cols, int gs, int bits, float *out);
 static int g_bf16_contract = 0; /* set per forward call (the oracle is driven from one thread) */
 static void proj(const lin_t *l, const float *x, long tokens, int gs, int bits, float *out) {
+    if (l->bits) bits = l->bits;
     if (g_bf16_contract) lthn_o_proj_bf16_contract(x, tokens, l->w, l->s, l->b, l->rows, l->cols, gs, bits, out);
     else lthn_o_hip_affine_projection_rows(x, tokens, l->w, l->s, l->b, l->rows, l->cols, gs, bits, out);
 }

@@ -98,6 +98,7 @@ def _declare(l):
     l.lthn_o_decoder_create.argtypes = [C.POINTER(DecoderConfig)]
     l.lthn_o_decoder_destroy.argtypes = [vp]
     l.lthn_o_decoder_set_linear.argtypes = [vp, i32, i32, vp, vp, vp, i64, i64]
+    l.lthn_o_decoder_set_linear_bits.argtypes = [vp, i32, i32, i32]
     l.lthn_o_decoder_set_norm.argtypes = [vp, i32, i32, vp]
     l.lthn_o_decoder_pos.restype = i64
     l.lthn_o_decoder_pos.argtypes = [vp]
@@ -381,14 +382,17 @@ class Decoder:
         self._keep = []
         self.h = lib().lthn_o_decoder_create(C.byref(cfg))
 
-    def set_linear(self, layer, role, packed, scales, biases):
+    def set_linear(self, layer, role, packed, scales, biases, bits=None):
+        """bits: the linear's own code width where a quantization override gives one (default: the model's)."""
         pk = np.ascontiguousarray(packed, dtype=np.uint32)
         s = np.ascontiguousarray(scales, dtype=np.uint16)
         b = np.ascontiguousarray(biases, dtype=np.uint16)
         self._keep += [pk, s, b]
-        rows, cols = pk.shape[0], pk.shape[1] * 32 // self.cfg.bits
+        rows, cols = pk.shape[0], pk.shape[1] * 32 // (bits or self.cfg.bits)
         r = ROLE[role] if isinstance(role, str) else role
         _check(lib().lthn_o_decoder_set_linear(self.h, layer, r, _p(pk), _p(s), _p(b), rows, cols), "set_linear")
+        if bits and bits != self.cfg.bits:
+            _check(lib().lthn_o_decoder_set_linear_bits(self.h, layer, r, bits), "set_linear_bits")
 
     def set_norm(self, layer, role, w):
         a = np.ascontiguousarray(w, dtype=np.float32)

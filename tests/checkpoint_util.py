@@ -51,7 +51,7 @@ def checkpoint_tensors(cfg, w, norms, norm_dtype="BF16", prefix=""):
     for li in range(cfg["layers"]):
         base = f"model.layers.{li}."
         for role in ROLES:
-            p, s, b = w[(li, role)]
+            p, s, b = w[(li, role)][:3]
             n = prefix + base + LINEAR_NAMES[role]
             t[n + ".weight"], t[n + ".scales"], t[n + ".biases"] = ("U32", p), ("BF16", s), ("BF16", b)
         for role in NORMS:
@@ -89,6 +89,9 @@ def write_checkpoint(path, cfg, w, norms, norm_dtype="BF16", shards=1, prefix=""
     if extra_config:
         text.update(extra_config)
     quant = {"group_size": 64, "bits": 4, "mode": "affine"}
+    for key, val in w.items():   # linears that carry their own code width get a per-module override
+        if key != "embed" and len(val) == 4:
+            quant[f"model.layers.{key[0]}.{LINEAR_NAMES[key[1]]}"] = {"group_size": 64, "bits": int(val[3])}
     if quant_extra:
         quant.update(quant_extra)
     config = {"model_type": "gemma3", "text_config": text, "quantization": quant} if nest_text_config else dict(text, quantization=quant)

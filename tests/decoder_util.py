@@ -38,6 +38,19 @@ def synth_weights(oracle, lthn, cfg, seed, sigma=0.02, random_norms=False):
     return w, norms
 
 
+def widen_linears(oracle, lthn, cfg, w, seed, roles=("gate", "up", "down"), layers=None, sigma=0.02):
+    """A mixed-precision pack: the named projections re-quantised at 8 bits (group 64) from the same dense
+    source, as the per-module overrides of a QAT checkpoint keep them. Entries become (packed, scales, biases, 8)."""
+    shapes = linear_shapes(cfg)
+    out = dict(w)
+    for li in (range(cfg["layers"]) if layers is None else layers):
+        for role in roles:
+            n, k = shapes[role]
+            dense = oracle.synth_normal(lthn.tensor_seed(seed, li, ROLES.index(role)), 0, n * k, sigma).reshape(n, k)
+            out[(li, role)] = (*oracle.quantize(dense, bits=8), 8)
+    return out
+
+
 def synth_weights_from_device(lthn, cfg, seed, sigma=0.02):
     """The same tensors for models too large to generate on the CPU in seconds: drawn and quantised
     by the device generator (tests/test_gpu_codec.py holds it bit-identical to the oracle's) and

@@ -3,7 +3,7 @@ against the CPU reference decoder on identical weights and token ids."""
 import numpy as np
 import pytest
 
-from decoder_util import GEMMA_2B, MID, SMALL, build_device, build_oracle, synth_weights
+from decoder_util import GEMMA_2B, MID, SMALL, build_device, build_oracle, linear_shapes, synth_weights, widen_linears
 
 pytestmark = pytest.mark.gpu
 
@@ -624,3 +624,55 @@ def test_sliding_window_blocks_match_oracle(oracle, cfg, window, prompt, monkeyp
     assert float(np.max(np.abs(got_c - want_c))) <= 5e-2 * rms
     assert float(np.sqrt(np.mean((got_c - want_c).astype(np.float64) ** 2))) <= 1e-2 * rms
     s2.close(); m2.close()
+
+
+@pytest.mark.parametrize("cfg,roles", [(SMALL, ("gate", "up", "down")), (MID, ("gate", "up", "down")), (MID, ("down",)), (SMALL, ("gate",))],
+                         ids=["small-mlp8", "mid-mlp8", "mid-down8", "small-gate8"])
+def test_mixed_precision_mlp_matches_oracle(oracle, cfg, roles):
+    """Mixed-precision packs keep MLP projections at 8 bits (per-module overrides, model/quant_config.go:39-88).
+    Such a model runs gate and up as separate matvecs with a GeGLU kernel, its norms unfused, and prompts through
+    the batched matvec path (32 rows: the general kernel; the tail and the decode steps: the integer tensor-core
+    kernel on the code bytes). Prompt logits, KV rows and 40 greedy tokens against the CPU decoder holding the
+    same tensors, at the bounds of the 4-bit f32 path; two lanes stepping together give the same tokens."""
+    import lthn
+    w, norms = synth_weights(oracle, lthn, cfg, seed=29, random_norms=True)
+    w = widen_linears(oracle, lthn, cfg, w, seed=29, roles=roles)
+    prompt, max_len = 70, 120
+    od = build_oracle(oracle, cfg, w, norms, max_len)
+    m = build_device(lthn, cfg, w, norms, max_len, max_lanes=2)
+    m4 = build_device(lthn, cfg, synth_weights(oracle, lthn, cfg, seed=29, random_norms=True)[0], norms, max_len)
+    shapes = linear_shapes(cfg)
+    extra = sum(shapes[r][0] * shapes[r][1] // 2 for r in roles) * cfg["layers"]
+    assert m.weight_bytes == m4.weight_bytes + extra
+    m4.close()
+    ids = np.random.default_rng(8).integers(0, cfg["vocab"], prompt).astype(np.int32)
+    want_logits = od.forward(ids)
+    s = m.open_session()
+    s.prefill(ids)
+    assert logits_close(s.logits(), want_logits)
+    for layer in range(cfg["layers"]):
+        for which in (0, 1):
+            dev_kv, ref_kv = oracle.bf16_to_f32(s.kv_export(layer, which)), od.read_kv(layer, which)
+            assert float(np.mean(dev_kv != ref_kv)) < (1e-2 if layer == 0 else 0.25)
+    want_tokens, margin = od.generate(want_logits, 40)
+    got = s.decode_greedy(40)
+    first_bad = next((i for i in range(40) if got[i] != want_tokens[i]), None)
+    assert first_bad is None, (first_bad, float(margin[first_bad]))
+    s.close()
+    # two and five lanes stepping together (rows 2: the integer kernel with two rows; rows 5: the general kernel)
+    for lanes in (2, 5):
+        mm = build_device(lthn, cfg, w, norms, max_len, max_lanes=lanes)
+        ls = mm.open_lane_set(lanes)
+        handles = [ls.prepare(ids, max_new=12) for _ in range(lanes)]
+        got_l = {h: [] for h in handles}
+        while True:
+            res = ls.step()
+            if not res:
+                break
+            for h, tok, has, term in res:
+                got_l[h].append(tok)
+        for h in handles:
+            n_same = _margin_aware_tokens(got_l[h], want_tokens[:12], margin[:12], 2e-2 * float(np.sqrt(np.mean(want_logits.astype(np.float64) ** 2))))
+            assert n_same >= 1
+        ls.close(); mm.close()
+    m.close()

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from checkpoint_util import effective_norms, write_checkpoint
-from decoder_util import MID, SMALL, build_device, build_oracle, synth_weights
+from decoder_util import MID, SMALL, build_device, build_oracle, synth_weights, widen_linears
 
 pytestmark = pytest.mark.gpu
 
@@ -41,16 +41,50 @@ def test_loaded_checkpoint_equals_uploaded_tensors(oracle, tmp_path, norm_dtype,
     a.close(); b.close(); loaded.close(); up.close()
 
 
+def test_mixed_precision_checkpoint_loads(oracle, tmp_path):
+    """A QAT pack whose quantization block overrides the MLP projections to 8 bits (model/quant_config.go:39-88):
+    the loaded model equals the one built from the same tensors by upload, and follows the CPU decoder."""
+    import lthn
+    cfg = SMALL
+    w, norms = synth_weights(oracle, lthn, cfg, seed=31, random_norms=True)
+    w = widen_linears(oracle, lthn, cfg, w, seed=31)
+    d = str(tmp_path / "ck")
+    write_checkpoint(d, cfg, w, norms, shards=2)
+    loaded = lthn.Model.load_dir(d, max_len=96)
+    eff = effective_norms(oracle, norms, "BF16")
+    up = build_device(lthn, cfg, w, eff, 96)
+    assert loaded.weight_bytes == up.weight_bytes
+    ids = np.random.default_rng(2).integers(0, cfg["vocab"], 20).astype(np.int32)
+    a, b = loaded.open_session(), up.open_session()
+    a.prefill(ids)
+    la = a.logits()
+    ta = a.decode_greedy(16)
+    b.prefill(ids)
+    assert np.array_equal(la, b.logits())
+    assert np.array_equal(ta, b.decode_greedy(16))
+    od = build_oracle(oracle, cfg, w, eff, 96)
+    want_logits = od.forward(ids)
+    rms = float(np.sqrt(np.mean(want_logits.astype(np.float64) ** 2)))
+    assert float(np.max(np.abs(la - want_logits))) <= 1e-2 * rms
+    a.close(); b.close(); loaded.close(); up.close()
+
+
 def test_load_rejects_what_the_engine_does_not_serve(oracle, tmp_path):
     import lthn
     cfg = SMALL
     w, norms = synth_weights(oracle, lthn, cfg, seed=31)
     d = str(tmp_path / "ck")
-    # an 8-bit per-module override (QAT packs keep MLP projections at 8 bit): named and refused
+    # an 8-bit per-module override outside the MLP projections: named and refused
+    w8 = widen_linears(oracle, lthn, cfg, w, seed=31, roles=("q",), layers=[1])
+    write_checkpoint(d, cfg, w8, norms)
+    with pytest.raises(lthn.LthnError) as e:
+        lthn.Model.load_dir(d, max_len=32)
+    assert "model.layers.1.self_attn.q_proj" in str(e.value) and "8-bit" in str(e.value)
+    # an override the tensor does not follow
     write_checkpoint(d, cfg, w, norms, quant_extra={"model.layers.1.mlp.down_proj": {"group_size": 64, "bits": 8}})
     with pytest.raises(lthn.LthnError) as e:
         lthn.Model.load_dir(d, max_len=32)
-    assert "model.layers.1.mlp.down_proj" in str(e.value)
+    assert "model.layers.1.mlp.down_proj" in str(e.value) and "geometry" in str(e.value)
     # a missing tensor
     write_checkpoint(d, cfg, w, norms)
     import checkpoint_util as cu

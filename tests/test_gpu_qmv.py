@@ -400,3 +400,53 @@ def test_eight_bit_codes_on_the_integer_kernel(oracle, N, K, M):
         assert rms_err(got3[:2], want) <= F32_TOL_RMS
     assert lthn.device_status() == 0
     q.free()
+
+
+@pytest.mark.parametrize("M", [1, 2])
+@pytest.mark.parametrize("N,K,geglu", [(9216, 2304, True), (2688, 5376, True), (512, 1024, True), (4096, 2304, False), (64, 128, True)])
+def test_eight_bit_codes_with_geglu_and_fused_norm(oracle, M, N, K, geglu):
+    """8-bit group-64 gate/up pairs (the MLP projections of a mixed-precision pack) with the GeGLU epilogue
+    (two full row sets per block for K < 2048, the interleaved 8 + 8 row block from there), alone and behind
+    the fused residual-norm prologue, against the same steps from the oracle at the bounds of the 4-bit forms."""
+    import lthn
+    L = lthn.lib()
+    rng = np.random.default_rng(N + K + M)
+    p, s, b = make_weight(oracle, N, K, seed=N, bits=8)
+    q = lthn.QuantWeight.from_host(p, s, b, 8, 64)
+    up = q2 = None
+    if geglu:
+        up = make_weight(oracle, N, K, seed=N + 1, bits=8)
+        q2 = lthn.QuantWeight.from_host(*up, 8, 64)
+    y = lthn.Buf(M * N * 4)
+    if geglu:
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        want = oracle.gelu_tanh(oracle.matnt_quant_host(x, p, s, b, 64, 8, threads=8)) * oracle.matnt_quant_host(x, *up, 64, 8, threads=8)
+        xb = lthn.Buf.from_array(x)
+        lthn.qmv_geglu(xb, lthn.F32, M, q, q2, y, lthn.F32)
+        lthn.sync()
+        assert rms_err(y.download(np.float32, (M, N)), want) <= 1e-4
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    h = (rng.standard_normal((M, K)) * 5).astype(np.float32)
+    w1 = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    w2 = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    ab, hb, h2b, w1b, w2b = (lthn.Buf.from_array(v) for v in (a, h, np.zeros_like(h), w1, w2))
+    for with_a in (True, False):
+        h_want = np.stack([h[r] + oracle.rmsnorm(a[r], w1, 1e-6) for r in range(M)]).astype(np.float32) if with_a else h
+        x_want = np.stack([oracle.rmsnorm(h_want[r], w2, 1e-6) for r in range(M)])
+        want = oracle.matnt_quant_host(x_want, p, s, b, 64, 8, threads=8)
+        if geglu:
+            want = oracle.gelu_tanh(want) * oracle.matnt_quant_host(x_want, *up, 64, 8, threads=8)
+        lthn.check(L.lthn_affine_qmv_normed_bits(None, ab.ptr if with_a else None, hb.ptr, h2b.ptr if with_a else None,
+                                                 w1b.ptr if with_a else None, w2b.ptr, 1e-6, M, q.packed.ptr, q.scales.ptr, q.biases.ptr,
+                                                 q2.packed.ptr if geglu else None, q2.scales.ptr if geglu else None,
+                                                 q2.biases.ptr if geglu else None, N, K, 8, y.ptr, lthn.F32))
+        lthn.sync()
+        got = y.download(np.float32, (M, N))
+        assert rms_err(got, want) <= (1e-4 if geglu else F32_TOL_RMS), with_a
+        if with_a:
+            h_got = h2b.download(np.float32, (M, K))
+            assert np.mean(h_got.view(np.uint32) == h_want.view(np.uint32)) >= 0.999
+    assert lthn.device_status() == 0
+    q.free()
+    if q2:
+        q2.free()
