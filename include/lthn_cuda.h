@@ -125,9 +125,11 @@ int32_t lthn_synth_affine_weight(void* stream, uint64_t seed, float sigma, int64
  * lthn_qmv_rows.metal:44-140) and HIP rocm_mlx_q4_projection(_batch)
  * (engine/hip/kernels/quant/affine_projection.hipinc:3-266). All pointers are
  * device pointers. x_dtype/y_dtype: LTHN_DTYPE_*. M in [1,32].
- * bits=4, gs=64 runs the tensor-core streaming kernel; bits in {2,4,8} with
- * gs in {32,64,128} is served by a general kernel. M==0, N==0 or K==0 is a
- * successful no-op (quant_reference_test.go:66-74). */
+ * bits=4, gs=64 runs the tensor-core streaming kernels; bits=8, gs=64 with one or two
+ * rows (N a multiple of 16, 16-byte aligned x and packed) runs the 8-bit form of the
+ * integer tensor-core kernel, the code bytes going into the MMA as they are; every other
+ * bits in {2,4,8} with gs in {32,64,128} is served by a general kernel. M==0, N==0 or
+ * K==0 is a successful no-op (quant_reference_test.go:66-74). */
 int32_t lthn_affine_qmv(void* stream, const void* x, int32_t x_dtype, int32_t M, const uint32_t* packed,
                         const uint16_t* scales, const uint16_t* biases, int64_t N, int64_t K, int32_t gs,
                         int32_t bits, void* y, int32_t y_dtype);
