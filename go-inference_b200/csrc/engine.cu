@@ -636,8 +636,10 @@ static int32_t prefill_chunk(Model* m, int lane, int rows, int pos0, bool last) 
         if (tp && (rc = all_reduce(m, m->p_a, (size_t)rows * H))) return rc;
         if ((rc = launch_rmsnorm(s, m->p_a, m->p_h, L.norm[NORM_POST_ATTN], L.norm[NORM_PRE_FF], nullptr, rows, H, c.eps, 1, m->p_xn, 1))) return rc;
         QmmCall gc{m->p_xn, rows, L.gate.wq, L.gate.s, L.gate.b, L.up.wq, L.up.s, L.up.b, L.gate.N, L.gate.K, m->p_act, 0};
+        gc.bits = L.gate.bits;  // the pair shares one width (finalize keeps other models off this path)
         if ((rc = qmm_launch(s, gc))) return rc;
         QmmCall dc{m->p_act, rows, L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, L.down.N, L.down.K, m->p_a, 1};
+        dc.bits = L.down.bits;
         if ((rc = qmm_launch(s, dc))) return rc;
         if (tp && (rc = all_reduce(m, m->p_a, (size_t)rows * H))) return rc;
         const bool final_layer = li + 1 == c.layers;
@@ -1292,10 +1294,9 @@ int32_t lthn_model_finalize(void* model) {
                        qmv_can_fuse_norm(L0.gate.N, L0.gate.K, 1, true) && qmv_can_fuse_norm(m->head.N, m->head.K, 2, false);
     }
     if (m->mixed) {
-        // 8-bit MLP projections. The prefill GEMM reads 4-bit codes, so prompts go through the batched matvec path.
-        // The norms stay inside the matvecs when every block's gate/up pair has one width and, where that is 8 bits,
-        // the 8-bit kernel plans the fused pair with the norm prologue.
-        m->prefill_tc = false;
+        // 8-bit MLP projections. The norms stay inside the matvecs, and prompts on the prefill GEMM (whose GeGLU
+        // tile holds rows of both matrices), when every block's gate/up pair has one width and, where that is 8 bits,
+        // the 8-bit matvec plans the fused pair with the norm prologue.
         const Layer& L0 = m->layers[0];
         I8Plan pl;
         m->pair8_ok = i8_plan_b8(L0.gate.N, L0.gate.K, 2, &pl, 0, 0, 1, false);
@@ -1306,6 +1307,7 @@ int32_t lthn_model_finalize(void* model) {
         }
         if (any_pair8) ok = ok && m->pair8_ok && qmv_can_fuse_norm(L0.gate.N, L0.gate.K, 2, true, 8);
         m->fuse_norm = m->fuse_norm && ok;
+        for (const Layer& L : m->layers) m->prefill_tc = m->prefill_tc && L.gate.bits == L.up.bits;
     }
     {
         // Opt-in (LTHN_CUDA_ATTN_FUSION=1): measured slower than the three kernels it replaces - every CTA repeats the

@@ -148,21 +148,41 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t w, uint32_t s2, uint32_t 
     return o;
 }
 
+// 8-bit codes: 8 codes of two packed words -> 8 bf16 weights in memory order. A byte is hi*16 + lo with both
+// nibbles exact in bf16 and so is their sum (8 significant bits), so scale*q + bias is rounded once, as for 4 bits.
+__device__ __forceinline__ void dequant_half8(uint32_t w, uint32_t s2, uint32_t b2, uint32_t& o01, uint32_t& o23) {
+    const uint32_t k128 = 0x43004300u, k16 = 0x41804180u;
+    const uint32_t lo02 = bf16x2_sub((w & 0x000F000Fu) | k128, k128), hi02 = bf16x2_sub(((w >> 4) & 0x000F000Fu) | k128, k128);
+    const uint32_t lo13 = bf16x2_sub(((w >> 8) & 0x000F000Fu) | k128, k128), hi13 = bf16x2_sub(((w >> 12) & 0x000F000Fu) | k128, k128);
+    const uint32_t p02 = bf16x2_fma(bf16x2_fma(hi02, k16, lo02), s2, b2);  // (c0, c2)
+    const uint32_t p13 = bf16x2_fma(bf16x2_fma(hi13, k16, lo13), s2, b2);  // (c1, c3)
+    o01 = __byte_perm(p02, p13, 0x5410);
+    o23 = __byte_perm(p02, p13, 0x7632);
+}
+__device__ __forceinline__ uint4 dequant_words8(uint32_t w0, uint32_t w1, uint32_t s2, uint32_t b2) {
+    uint4 o;
+    dequant_half8(w0, s2, b2, o.x, o.y);
+    dequant_half8(w1, s2, b2, o.z, o.w);
+    return o;
+}
+
 __device__ __forceinline__ float qmm_gelu_tanh(float x) {
     // gelu_tanh as hipGemma4Q4HostGELU (engine/hip/hip_gemma4_q4_layer.go:3582-3597)
     const float k0 = 0.7978845608028654f, k1 = 0.044715f;
     return 0.5f * x * (1.0f + tanhf(k0 * (x + k1 * x * x * x)));
 }
 
-// GEGLU: 0 plain, 1 gate/up pair (see QmmArgs)
-template <int NT, int GEGLU>
+// GEGLU: 0 plain, 1 gate/up pair (see QmmArgs). BITS: 4, or 8 (one code per byte).
+template <int NT, int GEGLU, int BITS>
 __global__ void __launch_bounds__(QMM_THREADS, 1)
 qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
     using S = QmmSmem<NT>;
     constexpr int NO = GEGLU ? NT / 2 : NT;   // output columns per CTA
     constexpr int STAGES = S::STAGES;
     constexpr int TPR = QMM_DQ_THREADS / NT;  // dequant threads per weight row: 1 (NT=256) or 2 (NT=128)
-    constexpr int WORDS = 8 / TPR;            // packed words (of the 8 in a group) per thread
+    constexpr int WPG = BITS * 2;             // packed words per group and row: 8 or 16
+    constexpr int WORDS = WPG / TPR;          // of them per thread
+    constexpr int CHUNKS = 8 / TPR;           // 16-byte chunks (8 bf16 weights) a thread writes per k-block
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + STAGES * S::STAGE_BYTES);
@@ -237,20 +257,16 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
         const int row = t / TPR, part = t - row * TPR;
         const bool second = GEGLU && row >= NO;       // tile rows NO.. come from the up matrix
         const int64_t grow = min(n0 + (second ? row - NO : row), a.N - 1);  // tail tiles re-read the last row; never stored
-        const uint32_t* wp = (second ? a.wq2 : a.wq) + grow * (a.K >> 3) + part * WORDS;
+        const uint32_t* wp = (second ? a.wq2 : a.wq) + grow * ((int64_t)a.K * BITS / 32) + part * WORDS;
         const uint16_t* sp = (second ? a.scales2 : a.scales) + grow * KB;
         const uint16_t* bp = (second ? a.biases2 : a.biases) + grow * KB;
         uint32_t wcur[WORDS], wnxt[WORDS];
         uint32_t sbcur, sbnxt = 0;
         auto load_kb = [&](int kb, uint32_t (&w)[WORDS], uint32_t& sb) {
-            if (WORDS == 8) {
-                const uint4 v0 = __ldg((const uint4*)(wp + kb * 8));
-                const uint4 v1 = __ldg((const uint4*)(wp + kb * 8) + 1);
-                w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w;
-                w[4 % WORDS] = v1.x; w[5 % WORDS] = v1.y; w[6 % WORDS] = v1.z; w[7 % WORDS] = v1.w;
-            } else {
-                const uint4 v0 = __ldg((const uint4*)(wp + kb * 8));
-                w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w;
+#pragma unroll
+            for (int v = 0; v < WORDS / 4; v++) {
+                const uint4 q = __ldg((const uint4*)(wp + (int64_t)kb * WPG) + v);
+                w[4 * v] = q.x; w[4 * v + 1] = q.y; w[4 * v + 2] = q.z; w[4 * v + 3] = q.w;
             }
             sb = (uint32_t)__ldg(sp + kb) | ((uint32_t)__ldg(bp + kb) << 16);
         };
@@ -264,9 +280,12 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs a) {
             const uint32_t b2 = (sbcur >> 16) | (sbcur & 0xffff0000u);
             unsigned char* wrow = smem + s * S::STAGE_BYTES + S::X_BYTES + row * 128;
 #pragma unroll
-            for (int i = 0; i < WORDS; i++) {
-                const int c = part * WORDS + i;  // 16-byte chunk index within the 128-byte row
-                *(uint4*)(wrow + ((c ^ (row & 7)) << 4)) = dequant_word(wcur[i], s2, b2);
+            for (int i = 0; i < CHUNKS; i++) {
+                const int c = part * CHUNKS + i;  // 16-byte chunk index within the 128-byte row
+                uint4 o;
+                if constexpr (BITS == 8) o = dequant_words8(wcur[(2 * i) % WORDS], wcur[(2 * i + 1) % WORDS], s2, b2);
+                else o = dequant_word(wcur[i % WORDS], s2, b2);
+                *(uint4*)(wrow + ((c ^ (row & 7)) << 4)) = o;
             }
             fence_async_smem();
             mbar_arrive(&full_w[s]);
@@ -371,8 +390,8 @@ __global__ void qmm_splitk_sum_kernel(const float* __restrict__ part, int splits
     }
 }
 
-template <int NT, int GEGLU>
-static int32_t launch_qmm(cudaStream_t s, const CUtensorMap& map, const QmmArgs& a, int splits = 1) {
+template <int NT, int GEGLU, int BITS>
+static int32_t launch_qmm_b(cudaStream_t s, const CUtensorMap& map, const QmmArgs& a, int splits) {
     static int attr_dev = -1;
     static std::mutex mu;
     int dev = 0;
@@ -380,21 +399,25 @@ static int32_t launch_qmm(cudaStream_t s, const CUtensorMap& map, const QmmArgs&
     {
         std::lock_guard<std::mutex> lk(mu);
         if (attr_dev != dev) {
-            LTHN_CUDA_TRY(cudaFuncSetAttribute(qmm_tcgen05_kernel<NT, GEGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, QmmSmem<NT>::TOTAL));
+            LTHN_CUDA_TRY(cudaFuncSetAttribute(qmm_tcgen05_kernel<NT, GEGLU, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, QmmSmem<NT>::TOTAL));
             attr_dev = dev;
         }
     }
     constexpr int NO = GEGLU ? NT / 2 : NT;
     dim3 grid((a.N + NO - 1) / NO, (a.M + QMM_MT - 1) / QMM_MT, splits);
-    qmm_tcgen05_kernel<NT, GEGLU><<<grid, QMM_THREADS, QmmSmem<NT>::TOTAL, s>>>(map, a);
+    qmm_tcgen05_kernel<NT, GEGLU, BITS><<<grid, QMM_THREADS, QmmSmem<NT>::TOTAL, s>>>(map, a);
     LTHN_CUDA_TRY(cudaGetLastError());
     return LTHN_OK;
+}
+template <int NT, int GEGLU>
+static int32_t launch_qmm(cudaStream_t s, const CUtensorMap& map, const QmmArgs& a, int bits, int splits = 1) {
+    return bits == 8 ? launch_qmm_b<NT, GEGLU, 8>(s, map, a, splits) : launch_qmm_b<NT, GEGLU, 4>(s, map, a, splits);
 }
 
 LTHN_HIDDEN int g_force_nt = 0;  // tile override: zero in the product library (setter: test_hooks.cu)
 
 // The tensor-core path for any M >= 1 (rows past M are zero-filled by the TMA load and never
-// stored): 4-bit codes, group 64, x and packed 16-byte aligned.
+// stored): 4-bit or 8-bit codes, group 64, x and packed 16-byte aligned.
 int32_t qmm_launch(cudaStream_t s, const QmmCall& c) {
     if (!encode_fn()) return fail(LTHN_ERR_UNAVAILABLE, "affine_qmm: cuTensorMapEncodeTiled is not available from this driver");
     CUtensorMap map;
@@ -423,7 +446,8 @@ int32_t qmm_launch(cudaStream_t s, const QmmCall& c) {
     const double e256 = eff(((c.N + no256 - 1) / no256) * mt), e128 = 0.9 * eff(((c.N + no128 - 1) / no128) * mt);
     int nt = e256 >= e128 ? 256 : 128;
     if (g_force_nt == 128 || g_force_nt == 256) nt = g_force_nt;
-    if (c.wq2) return nt == 256 ? launch_qmm<256, 1>(s, map, a) : launch_qmm<128, 1>(s, map, a);
+    if (c.bits != 4 && c.bits != 8) return fail(LTHN_ERR_INVALID, "affine_qmm: the tensor-core kernel reads 4-bit or 8-bit codes");
+    if (c.wq2) return nt == 256 ? launch_qmm<256, 1>(s, map, a, c.bits) : launch_qmm<128, 1>(s, map, a, c.bits);
     // Split-K when the output has too few tiles to fill the GPU (the long-K, narrow projections of a
     // short prompt: 2304 x 9216 with 512 tokens is 36 tiles): z CTAs per tile each take a slice of at
     // least 16 k-blocks and leave f32 partial sums that a second kernel adds in slice order.
@@ -439,13 +463,13 @@ int32_t qmm_launch(cudaStream_t s, const QmmCall& c) {
         QmmArgs pa = a;
         pa.y = part;
         pa.y_f32 = 1;
-        if ((rc = nt == 256 ? launch_qmm<256, 0>(s, map, pa, splits) : launch_qmm<128, 0>(s, map, pa, splits))) return rc;
+        if ((rc = nt == 256 ? launch_qmm<256, 0>(s, map, pa, c.bits, splits) : launch_qmm<128, 0>(s, map, pa, c.bits, splits))) return rc;
         const int64_t n = (int64_t)c.M * c.N;
         qmm_splitk_sum_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>((const float*)part, splits, n, c.y, c.y_f32);
         LTHN_CUDA_TRY(cudaGetLastError());
         return LTHN_OK;
     }
-    return nt == 256 ? launch_qmm<256, 0>(s, map, a) : launch_qmm<128, 0>(s, map, a);
+    return nt == 256 ? launch_qmm<256, 0>(s, map, a, c.bits) : launch_qmm<128, 0>(s, map, a, c.bits);
 }
 
 }  // namespace lthn
@@ -470,7 +494,7 @@ int32_t lthn_affine_qmm(void* stream, const uint16_t* x, int32_t M, const uint32
     LTHN_REQUIRE(gs == 32 || gs == 64 || gs == 128, "affine_qmm: group size must be 32, 64 or 128");
     LTHN_REQUIRE(K % gs == 0, "affine_qmm: group size must divide K");
     LTHN_REQUIRE(N < (int64_t)1 << 31 && K < (int64_t)1 << 31, "affine_qmm: dimension too large");
-    const bool tensor_path = bits == 4 && gs == 64 && M > 32 && (((uintptr_t)x | (uintptr_t)packed) & 15) == 0 && encode_fn();
+    const bool tensor_path = (bits == 4 || bits == 8) && gs == 64 && M > 32 && (((uintptr_t)x | (uintptr_t)packed) & 15) == 0 && encode_fn();
     if (!tensor_path) {
         // small M and the other widths of the format: the decode kernels, 32 rows at a time
         for (int m0 = 0; m0 < M; m0 += 32) {
@@ -482,22 +506,32 @@ int32_t lthn_affine_qmm(void* stream, const uint16_t* x, int32_t M, const uint32
         return LTHN_OK;
     }
     QmmCall c{x, M, packed, scales, biases, nullptr, nullptr, nullptr, N, K, y, 0};
+    c.bits = bits;
     return qmm_launch(s, c);
 }
 
 int32_t lthn_affine_qmm_geglu(void* stream, const uint16_t* x, int32_t M, const uint32_t* gate_packed,
                               const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
                               const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, uint16_t* y) {
+    return lthn_affine_qmm_geglu_bits(stream, x, M, gate_packed, gate_scales, gate_biases, up_packed, up_scales, up_biases, N, K, 4, y);
+}
+
+int32_t lthn_affine_qmm_geglu_bits(void* stream, const uint16_t* x, int32_t M, const uint32_t* gate_packed,
+                                   const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
+                                   const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, int32_t bits,
+                                   uint16_t* y) {
     clear_error();
+    LTHN_REQUIRE(bits == 4 || bits == 8, "affine_qmm_geglu: 4-bit or 8-bit codes");
     LTHN_REQUIRE(M >= 0 && N >= 0 && K >= 0, "affine_qmm_geglu: negative dimension");
     if (M == 0 || N == 0) return LTHN_OK;
     LTHN_REQUIRE(x && gate_packed && gate_scales && gate_biases && up_packed && up_scales && up_biases && y,
                  "affine_qmm_geglu: NULL pointer");
-    LTHN_REQUIRE(K > 0 && K % 64 == 0, "affine_qmm_geglu: K must be a positive multiple of 64 (4-bit, group 64 only)");
+    LTHN_REQUIRE(K > 0 && K % 64 == 0, "affine_qmm_geglu: K must be a positive multiple of 64 (group 64 only)");
     LTHN_REQUIRE(N < (int64_t)1 << 31 && K < (int64_t)1 << 31, "affine_qmm_geglu: dimension too large");
     LTHN_REQUIRE((((uintptr_t)x | (uintptr_t)gate_packed | (uintptr_t)up_packed) & 15) == 0,
                  "affine_qmm_geglu: x and the packed weights must be 16-byte aligned");
     QmmCall c{x, M, gate_packed, gate_scales, gate_biases, up_packed, up_scales, up_biases, N, K, y, 0};
+    c.bits = bits;
     return qmm_launch((cudaStream_t)stream, c);
 }
 

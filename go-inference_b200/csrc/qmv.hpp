@@ -95,6 +95,7 @@ struct QmmCall {
     const uint32_t* wq2; const uint16_t* scales2; const uint16_t* biases2;
     int64_t N, K;
     void* y; int y_f32;
+    int bits = 4;  // 8: one code per byte (both sets of a GeGLU pair)
 };
 int32_t qmm_launch(cudaStream_t st, const QmmCall& c);
 

@@ -220,6 +220,7 @@ class _Sig:
     lthn_laneset_close = (i32, [vp])
     lthn_affine_qmm = (i32, [vp, vp, i32, vp, vp, vp, i64, i64, i32, i32, vp])
     lthn_affine_qmm_geglu = (i32, [vp, vp, i32, vp, vp, vp, vp, vp, vp, i64, i64, vp])
+    lthn_affine_qmm_geglu_bits = (i32, [vp, vp, i32, vp, vp, vp, vp, vp, vp, i64, i64, i32, vp])
     lthn_prefill_attention = (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32])
     lthn_debug_qmm_force_tile = (None, [i32])
     lthn_debug_qmv_force_config = (None, [i32, i32])
@@ -469,6 +470,10 @@ def qmm(x: Buf, M, q: QuantWeight, y: Buf, stream=None):
 
 
 def qmm_geglu(x: Buf, M, gate: QuantWeight, up: QuantWeight, y: Buf, stream=None):
+    if gate.bits != 4:
+        check(lib().lthn_affine_qmm_geglu_bits(_s(stream), x.ptr, M, gate.packed.ptr, gate.scales.ptr, gate.biases.ptr,
+                                               up.packed.ptr, up.scales.ptr, up.biases.ptr, gate.N, gate.K, gate.bits, y.ptr))
+        return
     check(lib().lthn_affine_qmm_geglu(_s(stream), x.ptr, M, gate.packed.ptr, gate.scales.ptr, gate.biases.ptr,
                                       up.packed.ptr, up.scales.ptr, up.biases.ptr, gate.N, gate.K, y.ptr))
 

@@ -198,8 +198,9 @@ int32_t lthn_affine_qmv_geglu_bits(void* stream, const void* x, int32_t x_dtype,
  * rocm_mlx_q4_projection_batch* (engine/hip/kernels/quant/
  * affine_projection_tuned.hipinc:166-559). Weights are dequantised to bf16
  * (one rounding of scale*q+bias) tile by tile in shared memory and multiplied with
- * tcgen05.mma. bits=4, gs=64, M>32 take the tensor-core kernel; other widths and
- * small M are served by the decode kernels. x, y device pointers, 16-byte aligned. */
+ * tcgen05.mma. bits=4 or 8, gs=64, M>32 take the tensor-core kernel (8-bit codes, one per
+ * byte, are the MLP projections of mixed-precision packs); other widths and small M are
+ * served by the decode kernels. x, y device pointers, 16-byte aligned. */
 int32_t lthn_affine_qmm(void* stream, const uint16_t* x, int32_t M, const uint32_t* packed, const uint16_t* scales,
                         const uint16_t* biases, int64_t N, int64_t K, int32_t gs, int32_t bits, uint16_t* y);
 
@@ -211,6 +212,11 @@ int32_t lthn_affine_qmm(void* stream, const uint16_t* x, int32_t M, const uint32
 int32_t lthn_affine_qmm_geglu(void* stream, const uint16_t* x, int32_t M, const uint32_t* gate_packed,
                               const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
                               const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, uint16_t* y);
+/* The same with the code width given: bits = 4 as above, bits = 8 for a pair kept at 8 bits (group 64). */
+int32_t lthn_affine_qmm_geglu_bits(void* stream, const uint16_t* x, int32_t M, const uint32_t* gate_packed,
+                                   const uint16_t* gate_scales, const uint16_t* gate_biases, const uint32_t* up_packed,
+                                   const uint16_t* up_scales, const uint16_t* up_biases, int64_t N, int64_t K, int32_t bits,
+                                   uint16_t* y);
 
 /* model.QuantMatVec.MatVec (model/quant.go:35-38): bf16 LE bytes in HOST memory
  * in, bf16 LE bytes out; lengths are validated like the reference
@@ -308,9 +314,10 @@ int32_t lthn_model_upload_linear(void* model, int32_t layer, int32_t role, const
 /* The same for a linear whose quantization override names its own code width (the mixed-precision
  * QAT packs of model/quant_config.go:39-88 keep the MLP projections at 8 bits). bits = 4 is
  * lthn_model_upload_linear; bits = 8 (group 64) is accepted for LTHN_ROLE_GATE / UP / DOWN on one
- * GPU: packed holds N*K bytes, one code per byte. A model with such a linear runs its gate and up
- * projections as separate matvecs followed by a GeGLU kernel, its norms as kernels of their own,
- * and prompts through the batched matvec path (the prefill GEMM reads 4-bit codes only). */
+ * GPU: packed holds N*K bytes, one code per byte. Decode steps of one and two rows and prompts run the
+ * 8-bit forms of the same kernels (integer tensor-core matvec, prefill GEMM); a block whose gate and
+ * up projections differ in width runs them as separate matvecs followed by a GeGLU kernel, and a model
+ * with such a block keeps its norms unfused and its prompts on the batched matvec path. */
 int32_t lthn_model_upload_linear_bits(void* model, int32_t layer, int32_t role, const void* packed, const void* scales,
                                       const void* biases, int64_t N, int64_t K, int32_t bits);
 int32_t lthn_model_upload_norm(void* model, int32_t layer, int32_t role, const float* w, int64_t n);

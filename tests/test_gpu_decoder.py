@@ -628,13 +628,16 @@ def test_sliding_window_blocks_match_oracle(oracle, cfg, window, prompt, monkeyp
 
 @pytest.mark.parametrize("cfg,roles", [(SMALL, ("gate", "up", "down")), (MID, ("gate", "up", "down")), (MID, ("down",)), (SMALL, ("gate",))],
                          ids=["small-mlp8", "mid-mlp8", "mid-down8", "small-gate8"])
-def test_mixed_precision_mlp_matches_oracle(oracle, cfg, roles):
+def test_mixed_precision_mlp_matches_oracle(oracle, cfg, roles, monkeypatch):
     """Mixed-precision packs keep MLP projections at 8 bits (per-module overrides, model/quant_config.go:39-88).
     Such a model runs gate and up as separate matvecs with a GeGLU kernel, its norms unfused, and prompts through
     the batched matvec path (32 rows: the general kernel; the tail and the decode steps: the integer tensor-core
     kernel on the code bytes). Prompt logits, KV rows and 40 greedy tokens against the CPU decoder holding the
-    same tensors, at the bounds of the 4-bit f32 path; two lanes stepping together give the same tokens."""
+    same tensors, at the bounds of the 4-bit f32 path; two lanes stepping together give the same tokens. Then the
+    prompt on the tensor-core prefill (8-bit form of the GEMM where a pair shares its width) against the
+    bf16-contract oracle, at the bounds of the other prefill tests."""
     import lthn
+    monkeypatch.setenv("LTHN_CUDA_PREFILL_F32", "1")
     w, norms = synth_weights(oracle, lthn, cfg, seed=29, random_norms=True)
     w = widen_linears(oracle, lthn, cfg, w, seed=29, roles=roles)
     prompt, max_len = 70, 120
@@ -676,3 +679,16 @@ def test_mixed_precision_mlp_matches_oracle(oracle, cfg, roles):
             assert n_same >= 1
         ls.close(); mm.close()
     m.close()
+    # tensor-core prefill (bf16 contract)
+    monkeypatch.delenv("LTHN_CUDA_PREFILL_F32")
+    oc = build_oracle(oracle, cfg, w, norms, max_len, prefill_bf16=1)
+    want_c = oc.forward(ids)
+    m2 = build_device(lthn, cfg, w, norms, max_len)
+    s2 = m2.open_session()
+    s2.prefill(ids)
+    got_c = s2.logits()
+    rms = float(np.sqrt(np.mean(want_c.astype(np.float64) ** 2)))
+    assert float(np.max(np.abs(got_c - want_c))) <= 5e-2 * rms
+    assert float(np.sqrt(np.mean((got_c - want_c).astype(np.float64) ** 2))) <= 1e-2 * rms
+    assert len(s2.decode_greedy(8)) == 8
+    s2.close(); m2.close()

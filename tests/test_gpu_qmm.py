@@ -116,7 +116,7 @@ def test_qmm_geglu_pair(oracle, tile, M, N, K):
 
 def test_qmm_small_m_and_other_widths_route_to_decode_kernels(oracle):
     import lthn
-    for (M, N, K, bits, gs) in [(5, 128, 256, 4, 64), (40, 64, 256, 8, 64), (3, 24, 256, 2, 128)]:
+    for (M, N, K, bits, gs) in [(5, 128, 256, 4, 64), (40, 64, 256, 8, 32), (3, 24, 256, 2, 128)]:
         p, s, b = make_weight(oracle, N, K, seed=7, bits=bits, gs=gs)
         xf, xb = make_x(oracle, M, K, seed=1)
         want = oracle.matnt_quant_host(xf, p, s, b, gs=gs, bits=bits)
@@ -127,3 +127,48 @@ def test_qmm_small_m_and_other_widths_route_to_decode_kernels(oracle):
     lthn.qmm(x, 0, q, y)  # M == 0 is a no-op
     with pytest.raises(lthn.LthnError):
         lthn.check(lthn.lib().lthn_affine_qmm(None, x.ptr, 1, q.packed.ptr, q.scales.ptr, q.biases.ptr, 64, 128, 48, 4, y.ptr))
+
+
+@pytest.mark.parametrize("tile", [128, 256])
+@pytest.mark.parametrize("M,N,K", [(64, 256, 128), (100, 300, 192), (512, 1024, 2304), (33, 40, 512), (700, 2304, 1024), (512, 2304, 9216)])
+def test_qmm_eight_bit_codes_match_oracle(oracle, tile, M, N, K):
+    """8-bit group-64 weights (the MLP projections of a mixed-precision pack) on the tensor-core kernel: the
+    dequantisers read twice the words per group and form scale*q + bias with one bf16 rounding from the exact
+    byte value, so the bf16-contract oracle and the f64 reference bound hold as for 4 bits. The last shape runs
+    split over K."""
+    import lthn
+    p, s, b = make_weight(oracle, N, K, seed=N + K, bits=8)
+    xf, xb = make_x(oracle, M, K, seed=M)
+    want16 = oracle.qmm_bf16(xb, p, s, b, 64, 8)
+    q = lthn.QuantWeight.from_host(p, s, b, 8, 64)
+    lthn.lib().lthn_debug_qmm_force_tile(tile)
+    try:
+        got16 = run_qmm(lthn, xb, M, q)
+    finally:
+        lthn.lib().lthn_debug_qmm_force_tile(0)
+    assert bf16_close(oracle, got16, oracle.bf16_to_f32(want16))
+    ref = oracle.matnt_quant_host(xf, p, s, b, 64, 8, threads=8)
+    # K = 9216: the contract's own bf16 rounding of 9216 weights per output reaches 1.4e-2 at the worst of the
+    # 1.2 M outputs checked here (the oracle above, which rounds the same way, is matched to one bf16 ulp)
+    assert rel_err(oracle.bf16_to_f32(got16), ref) <= (2e-2 if K > 4096 else 1e-2)
+    assert lthn.device_status() == 0
+    q.free()
+
+
+@pytest.mark.parametrize("M,N,K", [(40, 200, 256), (300, 1152, 2304), (512, 2688, 5376)])
+def test_qmm_eight_bit_geglu_pair(oracle, M, N, K):
+    """The GeGLU pair with both matrices at 8 bits, against the product formed from the bf16-contract operands."""
+    import lthn
+    gp = make_weight(oracle, N, K, seed=N + 1, bits=8)
+    up = make_weight(oracle, N, K, seed=N + 2, bits=8)
+    xf, xb = make_x(oracle, M, K, seed=M)
+    wg = oracle.bf16_to_f32(oracle.f32_to_bf16(oracle.dequantize(*gp, bits=8))).astype(np.float64)
+    wu = oracle.bf16_to_f32(oracle.f32_to_bf16(oracle.dequantize(*up, bits=8))).astype(np.float64)
+    want = oracle.gelu_tanh((xf.astype(np.float64) @ wg.T).astype(np.float32)) * (xf.astype(np.float64) @ wu.T).astype(np.float32)
+    gq, uq = lthn.QuantWeight.from_host(*gp, 8, 64), lthn.QuantWeight.from_host(*up, 8, 64)
+    x, y = lthn.Buf.from_array(xb), lthn.Buf(M * N * 2)
+    lthn.qmm_geglu(x, M, gq, uq, y)
+    lthn.sync()
+    assert bf16_close(oracle, y.download(np.uint16, (M, N)), want)
+    assert lthn.device_status() == 0
+    gq.free(); uq.free()
