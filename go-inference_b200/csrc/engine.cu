@@ -171,6 +171,7 @@ struct Model {
     bool mixed = false;
     bool pair8_ok = false;  // an 8-bit gate/up pair of this shape runs as one fused matvec for one and two rows
     float *g8 = nullptr, *u8 = nullptr;
+    uint16_t* x8 = nullptr;  // bf16 activations of a 3..32-row step entering an 8-bit linear
     // engine.DecodePhaseTracer: while on, one-row decode steps run kernel by kernel with an event between phases
     struct PhaseTrace {
         bool on = false;
@@ -294,8 +295,20 @@ static int32_t shard_plan(Model* m, int layer, int role, ShardPlan* p) {
     return LTHN_OK;
 }
 
+// 3..32 rows on 8-bit linears: the 8-bit form of the prefill GEMM on the bf16 rounding of the activations (the
+// contract the 4-bit linears' tensor-core matvec has at these row counts); LTHN_CUDA_BATCH_F32=1 keeps the f32-grade
+// general kernel
+static bool batch8_on_tensor_cores(int rows) { return rows > 2 && !qmv_batch_f32(); }
+
 // y[rows, N] = x[rows, K] W^T for one linear at its own code width (f32 in, f32 out, no fused norm or GeGLU)
-static int32_t project_plain(cudaStream_t s, const Linear& l, const float* x, float* y, int rows) {
+static int32_t project_plain(Model* m, cudaStream_t s, const Linear& l, const float* x, float* y, int rows) {
+    if (l.bits == 8 && batch8_on_tensor_cores(rows)) {
+        int32_t rc = split_f32_launch(s, x, rows, l.K, 1, m->x8);
+        if (rc) return rc;
+        QmmCall q{m->x8, rows, l.wq, l.s, l.b, nullptr, nullptr, nullptr, l.N, l.K, y, 1};
+        q.bits = 8;
+        return qmm_launch(s, q);
+    }
     if (l.bits == 8) return lthn_affine_qmv(s, x, LTHN_DTYPE_F32, rows, l.wq, l.s, l.b, l.N, l.K, 64, 8, y, LTHN_DTYPE_F32);
     QmvCall q{l.wq, l.s, l.b, nullptr, nullptr, nullptr, x, LTHN_DTYPE_F32, y, LTHN_DTYPE_F32, l.N, l.K, rows};
     return qmv_dispatch(s, q);
@@ -545,16 +558,22 @@ static int32_t forward(Model* m, int rows, int max_ctx, bool want_logits, int lo
             gc.bits = 8;
             gc.x_cols = nullptr; gc.x_split = 0;
             if ((rc = qmv_dispatch(s, gc))) return rc;
+        } else if (L.gate.bits == 8 && L.up.bits == 8 && batch8_on_tensor_cores(rows)) {
+            // 3..32 rows: the pair in one pass of the 8-bit prefill GEMM
+            if ((rc = split_f32_launch(s, m->xn, rows, H, 1, m->x8))) return rc;
+            QmmCall g8{m->x8, rows, L.gate.wq, L.gate.s, L.gate.b, L.up.wq, L.up.s, L.up.b, L.gate.N, L.gate.K, m->act, 1};
+            g8.bits = 8;
+            if ((rc = qmm_launch(s, g8))) return rc;
         } else if (L.gate.bits == 8 || L.up.bits == 8) {
-            // other row counts, or only one of the two at 8 bits: separate matvecs, GeGLU in a kernel of its own
-            if ((rc = project_plain(s, L.gate, m->xn, m->g8, rows)) || (rc = project_plain(s, L.up, m->xn, m->u8, rows)) ||
+            // only one of the two at 8 bits (or the f32-grade batch path): separate matvecs, GeGLU in a kernel of its own
+            if ((rc = project_plain(m, s, L.gate, m->xn, m->g8, rows)) || (rc = project_plain(m, s, L.up, m->xn, m->u8, rows)) ||
                 (rc = launch_geglu(s, m->g8, m->u8, m->act, (int64_t)rows * L.gate.N)))
                 return rc;
         } else if ((rc = qmv_dispatch(s, gc))) return rc;
         QmvCall dc{L.down.wq, L.down.s, L.down.b, nullptr, nullptr, nullptr, m->act, LTHN_DTYPE_F32, m->a, LTHN_DTYPE_F32, L.down.N, L.down.K, rows};
         site_out(1, f1, dc);
         if (L.down.bits == 8) {
-            if ((rc = project_plain(s, L.down, m->act, m->a, rows))) return rc;
+            if ((rc = project_plain(m, s, L.down, m->act, m->a, rows))) return rc;
         } else if ((rc = qmv_dispatch(s, dc))) return rc;
         trace_mark(m, PH_MLP);
         const float* next_norm = li + 1 < c.layers ? m->layers[li + 1].norm[NORM_INPUT] : m->final_norm;
@@ -1090,7 +1109,9 @@ int32_t lthn_model_upload_linear_bits(void* model, int32_t layer, int32_t role, 
         l->bits = 8;
     }
     if (!m->g8) {
-        if ((rc = dalloc(m, &m->g8, (size_t)kMaxRows * m->F_l)) || (rc = dalloc(m, &m->u8, (size_t)kMaxRows * m->F_l))) return rc;
+        if ((rc = dalloc(m, &m->g8, (size_t)kMaxRows * m->F_l)) || (rc = dalloc(m, &m->u8, (size_t)kMaxRows * m->F_l)) ||
+            (rc = dalloc(m, &m->x8, (size_t)kMaxRows * std::max<int64_t>(m->c.hidden, m->F_l))))
+            return rc;
     }
     m->mixed = true;
     const size_t sg = (size_t)N * K / 64 * 2;

@@ -106,6 +106,8 @@ bool qmv_tc_available(const QmvCall& c);
 int32_t qmv_tc_launch(cudaStream_t st, const QmvCall& c, const uint16_t* x_bf16, int64_t x_ld);
 // LTHN_CUDA_BATCH_F32=1 keeps every row count on the f32-grade kernels (read at every call)
 bool qmv_batch_f32();
+// f32 rows -> `split` bf16 columns per row ([M*split, K]; the first is the bf16 rounding of the value)
+int32_t split_f32_launch(cudaStream_t s, const float* x, int64_t M, int64_t K, int split, uint16_t* out);
 
 // Dispatcher used by the C entry points and by the decoder engine.
 int32_t qmv_dispatch(cudaStream_t st, const QmvCall& c);

@@ -314,8 +314,9 @@ int32_t lthn_model_upload_linear(void* model, int32_t layer, int32_t role, const
 /* The same for a linear whose quantization override names its own code width (the mixed-precision
  * QAT packs of model/quant_config.go:39-88 keep the MLP projections at 8 bits). bits = 4 is
  * lthn_model_upload_linear; bits = 8 (group 64) is accepted for LTHN_ROLE_GATE / UP / DOWN on one
- * GPU: packed holds N*K bytes, one code per byte. Decode steps of one and two rows and prompts run the
- * 8-bit forms of the same kernels (integer tensor-core matvec, prefill GEMM); a block whose gate and
+ * GPU: packed holds N*K bytes, one code per byte. Decode steps of one and two rows run the 8-bit form
+ * of the integer tensor-core matvec, prompts and steps of 3..32 rows the 8-bit form of the prefill GEMM
+ * (bf16-rounded activations; LTHN_CUDA_BATCH_F32=1 keeps such steps on an f32-grade kernel); a block whose gate and
  * up projections differ in width runs them as separate matvecs followed by a GeGLU kernel, and a model
  * with such a block keeps its norms unfused and its prompts on the batched matvec path. */
 int32_t lthn_model_upload_linear_bits(void* model, int32_t layer, int32_t role, const void* packed, const void* scales,

@@ -631,13 +631,13 @@ def test_sliding_window_blocks_match_oracle(oracle, cfg, window, prompt, monkeyp
 def test_mixed_precision_mlp_matches_oracle(oracle, cfg, roles, monkeypatch):
     """Mixed-precision packs keep MLP projections at 8 bits (per-module overrides, model/quant_config.go:39-88).
     Such a model runs gate and up as separate matvecs with a GeGLU kernel, its norms unfused, and prompts through
-    the batched matvec path (32 rows: the general kernel; the tail and the decode steps: the integer tensor-core
-    kernel on the code bytes). Prompt logits, KV rows and 40 greedy tokens against the CPU decoder holding the
+    the batched matvec path (the decode steps: the integer tensor-core kernel on the code bytes). Prompt logits, KV rows and 40 greedy tokens against the CPU decoder holding the
     same tensors, at the bounds of the 4-bit f32 path; two lanes stepping together give the same tokens. Then the
     prompt on the tensor-core prefill (8-bit form of the GEMM where a pair shares its width) against the
     bf16-contract oracle, at the bounds of the other prefill tests."""
     import lthn
     monkeypatch.setenv("LTHN_CUDA_PREFILL_F32", "1")
+    monkeypatch.setenv("LTHN_CUDA_BATCH_F32", "1")   # 32-row forwards on the f32-grade general kernel
     w, norms = synth_weights(oracle, lthn, cfg, seed=29, random_norms=True)
     w = widen_linears(oracle, lthn, cfg, w, seed=29, roles=roles)
     prompt, max_len = 70, 120
@@ -662,7 +662,9 @@ def test_mixed_precision_mlp_matches_oracle(oracle, cfg, roles, monkeypatch):
     first_bad = next((i for i in range(40) if got[i] != want_tokens[i]), None)
     assert first_bad is None, (first_bad, float(margin[first_bad]))
     s.close()
-    # two and five lanes stepping together (rows 2: the integer kernel with two rows; rows 5: the general kernel)
+    # two and five lanes stepping together (rows 2: the integer kernel with two rows; rows 5, and the 32-row
+    # forwards of their prompts: the 8-bit prefill GEMM on bf16-rounded activations, hence the margin-aware check)
+    monkeypatch.delenv("LTHN_CUDA_BATCH_F32")
     for lanes in (2, 5):
         mm = build_device(lthn, cfg, w, norms, max_len, max_lanes=lanes)
         ls = mm.open_lane_set(lanes)

@@ -41,10 +41,12 @@ def test_loaded_checkpoint_equals_uploaded_tensors(oracle, tmp_path, norm_dtype,
     a.close(); b.close(); loaded.close(); up.close()
 
 
-def test_mixed_precision_checkpoint_loads(oracle, tmp_path):
+def test_mixed_precision_checkpoint_loads(oracle, tmp_path, monkeypatch):
     """A QAT pack whose quantization block overrides the MLP projections to 8 bits (model/quant_config.go:39-88):
-    the loaded model equals the one built from the same tensors by upload, and follows the CPU decoder."""
+    the loaded model equals the one built from the same tensors by upload, and follows the CPU decoder (the 20-row
+    prompt on the f32-grade kernels: LTHN_CUDA_BATCH_F32=1 keeps the 8-bit projections off the bf16-contract GEMM)."""
     import lthn
+    monkeypatch.setenv("LTHN_CUDA_BATCH_F32", "1")
     cfg = SMALL
     w, norms = synth_weights(oracle, lthn, cfg, seed=31, random_norms=True)
     w = widen_linears(oracle, lthn, cfg, w, seed=31)
