@@ -354,3 +354,57 @@ def test_decoder_sliding_window_reduces_to_known_cases(oracle):
     v = d.read_kv(0, 1)[:len(ids)]                  # [tokens, kv_heads*head_dim]
     for h in range(cfg["q_heads"]):
         assert np.allclose(att[:, h * 64:(h + 1) * 64], v[:, :64], rtol=0, atol=1e-6)
+
+
+def test_decoder_per_linear_code_width(oracle):
+    """A linear may carry its own code width (per-module overrides of a mixed-precision pack,
+    model/quant_config.go:39-88). Known answer: the same 4-bit codes stored one per byte with the same scales
+    and biases dequantise to the same weights, so the decoder whose MLP projections are declared 8-bit must give
+    bit-identical logits and cache rows, with and without the bf16 prefill contract; real 8-bit codes of the same
+    dense tensors move the logits by less than the 4-bit quantisation step does."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(__file__))
+    from decoder_util import NORMS, ROLES, linear_shapes
+    cfg = dict(layers=2, hidden=128, q_heads=2, kv_heads=1, head_dim=64, ffn=256, vocab=64)
+    rng = np.random.default_rng(5)
+    dense = {(li, role): (rng.standard_normal(shape) * 0.05).astype(np.float32)
+             for li in range(cfg["layers"]) for role, shape in linear_shapes(cfg).items()}
+    w = {k: oracle.quantize(v) for k, v in dense.items()}
+    embed = oracle.quantize((rng.standard_normal((cfg["vocab"], cfg["hidden"])) * 0.05).astype(np.float32))
+    ids = rng.integers(0, cfg["vocab"], 12).astype(np.int32)
+
+    def bytes_of_nibbles(packed):
+        shifts = (np.arange(8, dtype=np.uint32) * 4).astype(np.uint32)
+        codes = ((packed[..., None] >> shifts) & np.uint32(15)).reshape(packed.shape[0], -1).astype(np.uint8)
+        return np.ascontiguousarray(codes).view(np.uint32)
+
+    def run(weights, prefill_bf16):
+        oc = oracle.DecoderConfig(layers=cfg["layers"], hidden=cfg["hidden"], q_heads=cfg["q_heads"], kv_heads=cfg["kv_heads"],
+                                  head_dim=cfg["head_dim"], ffn=cfg["ffn"], vocab=cfg["vocab"], gs=64, bits=4, max_len=32, eps=1e-6,
+                                  rope_base=10000.0, attn_scale=0.125, embed_scale=1.0, kv_bf16=1, prefill_bf16=prefill_bf16)
+        d = oracle.Decoder(oc)
+        for li in range(cfg["layers"]):
+            for role in ROLES:
+                d.set_linear(li, role, *weights[(li, role)])
+            for role in NORMS:
+                d.set_norm(li, role, np.ones(cfg["head_dim"] if role in ("q_norm", "k_norm") else cfg["hidden"], dtype=np.float32))
+        d.set_linear(-1, 0, *embed)
+        d.set_norm(-1, 0, np.ones(cfg["hidden"], dtype=np.float32))
+        logits = d.forward(ids)
+        return logits, [d.read_kv(li, which)[:len(ids)].copy() for li in range(cfg["layers"]) for which in (0, 1)]
+
+    same_codes = dict(w)
+    real8 = dict(w)
+    for li in range(cfg["layers"]):
+        for role in ("gate", "up", "down"):
+            p, s, b = w[(li, role)]
+            same_codes[(li, role)] = (bytes_of_nibbles(p), s, b, 8)
+            real8[(li, role)] = (*oracle.quantize(dense[(li, role)], bits=8), 8)
+    for contract in (0, 1):
+        base, kv0 = run(w, contract)
+        got, kv1 = run(same_codes, contract)
+        assert np.array_equal(base, got)
+        assert all(np.array_equal(a, b) for a, b in zip(kv0, kv1))
+        finer, _ = run(real8, contract)
+        assert not np.array_equal(base, finer)
+        assert float(np.max(np.abs(finer - base))) < 0.25 * float(np.max(np.abs(base)))
