@@ -1148,6 +1148,7 @@ int32_t lthn_model_synthesize(void* model, uint64_t seed, float sigma) {
     clear_error();
     Model* m = (Model*)model;
     LTHN_REQUIRE(m != nullptr, "lthn_model_synthesize: model is NULL");
+    LTHN_REQUIRE(!m->mixed, "lthn_model_synthesize: the synthetic tensors are 4-bit; call it before uploading 8-bit linears");
     int32_t rc;
     const auto& c = m->c;
     for (int li = 0; li < c.layers; li++) {
