@@ -84,7 +84,7 @@ bool i8_plan(int64_t N, int64_t K, int M, int fuse, int force_ks, int force_w, I
     // slower than whole rows on small matrices, so the dispatcher only uses them when asked to
     // (max_slices > 1). A GeGLU epilogue needs whole rows.
     if (force_ks <= 1 && i8_plan_slice(N, G, 1, M, fuse, force_w, has_norm, p)) return true;
-    if (fuse || max_slices <= 1) return false;
+    if (fuse || has_norm || max_slices <= 1) return false;  // a GeGLU epilogue and a norm prologue need whole rows
     int best_ks = 0, best_d = 1 << 30;
     for (int ks : {2, 3, 4, 6, 8}) {
         if (ks > max_slices || G % ks) continue;

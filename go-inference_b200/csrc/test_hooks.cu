@@ -30,6 +30,20 @@ void lthn_debug_qmv_force_kernel(int32_t kernel) {
 }
 void lthn_debug_qmm_force_tile(int32_t nt) { g_force_nt = nt; }
 
+// The plan the integer tensor-core matvec would run for a call (host logic only, no CUDA call): returns 1 and
+// out = {J, W, stg, RS, nblocks, threads, bs_off, stage_off, ks, Gs, fuse, smem bytes}, or 0 when the kernel
+// does not serve the shape. bits 4 or 8; fuse: a GeGLU pair; norm: a fused norm prologue; slices: the most K
+// slices the 4-bit plan may use (the 8-bit plan slices by itself).
+int32_t lthn_debug_i8_plan(int64_t N, int64_t K, int32_t M, int32_t bits, int32_t fuse, int32_t norm, int32_t slices, int64_t* out) {
+    I8Plan p{};
+    const bool ok = bits == 8 ? i8_plan_b8(N, K, M, &p, 0, 0, fuse, norm != 0)
+                              : i8_plan(N, K, M, fuse, 0, 0, &p, slices > 1 ? slices : 1, norm != 0);
+    if (!ok) return 0;
+    const int64_t v[12] = {p.J, p.W, p.stg, p.RS, p.nblocks, p.threads, p.bs_off, p.stage_off, p.ks, p.Gs, p.fuse, (int64_t)p.smem};
+    for (int i = 0; i < 12; i++) out[i] = v[i];
+    return 1;
+}
+
 // The tensor-parallel residual norm on one GPU: the t "ranks" are t local buffers ([t][rows*width]
 // in parts). flags_preset != 0: every "peer" has already signalled, nothing waits, and the call
 // checks the rank-order sum and the fused norms. flags_preset == 0: no peer ever signals, so the

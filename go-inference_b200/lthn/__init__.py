@@ -223,6 +223,7 @@ class _Sig:
     lthn_affine_qmm_geglu_bits = (i32, [vp, vp, i32, vp, vp, vp, vp, vp, vp, i64, i64, i32, vp])
     lthn_prefill_attention = (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32])
     lthn_debug_qmm_force_tile = (None, [i32])
+    lthn_debug_i8_plan = (i32, [i64, i64, i32, i32, i32, i32, i32, vp])
     lthn_debug_qmv_force_config = (None, [i32, i32])
     lthn_debug_qmv_force_kernel = (None, [i32])
 
