@@ -32,7 +32,7 @@ def test_product_library_has_no_test_hooks():
     missing = [n for n in declared_symbols() if not hasattr(prod, n)]
     assert not missing, missing
     for hook in ("lthn_debug_qmv_force_config", "lthn_debug_qmv_force_kernel", "lthn_debug_qmm_force_tile",
-                 "lthn_debug_rmsnorm_gather_local"):
+                 "lthn_debug_rmsnorm_gather_local", "lthn_debug_i8_plan"):
         assert not hasattr(prod, hook), hook
     hooks = ctypes.CDLL(os.path.join(ROOT, "go-inference_b200", "liblthn_cuda_hooks.so"))
     assert hasattr(hooks, "lthn_debug_qmv_force_kernel")
